@@ -1,0 +1,112 @@
+"""Tensor-parallel ``Embedding``.
+
+Counterpart of the reference's ``axonn/intra_layer/embedding.py:57-222``: the
+table is kept as ``[V, H]`` with ``H`` split over the outer group (inner group
+when ``transpose``), flattened and depth-sharded; the other group must have
+size one.  Forward gathers the table over depth, looks rows up and, in easy
+mode, gathers the hidden dimension back.
+"""
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from .. import axonn as ax
+from ..utils import divide
+from .communication import Drop, ForwardGather_BackwardReduceScatter, Gather
+
+
+@torch.no_grad()
+def extract_local_params_from_full_params(params, hidden_group, depth_group):
+    """``[V, H]`` -> my hidden chunk -> flat -> my depth slice."""
+    n, me = dist.get_world_size(hidden_group), dist.get_rank(hidden_group)
+    h_l = params.shape[1] // n
+    block = params[:, me * h_l:(me + 1) * h_l].contiguous().view(-1)
+    nd, dz = dist.get_world_size(depth_group), dist.get_rank(depth_group)
+    k = divide(block.numel(), nd)
+    return block[dz * k:(dz + 1) * k].clone()
+
+
+@torch.no_grad()
+def default_init_method(weight, padding_idx=None):
+    return torch.nn.init.normal_(weight)
+
+
+class Embedding(torch.nn.Module):
+    def __init__(self, num_embeddings, embedding_dim, padding_idx=None, max_norm=None, norm_type=2.0,
+                 scale_grad_by_freq=False, sparse=False, _weight=None, _freeze=False, *args,
+                 transpose=False, init_method=None, expert_mode=False, dtype=None, **kwargs):
+        assert _weight is None, "_weight argument is not supported."
+        super().__init__()
+        assert ax.is_initialized
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        if padding_idx is not None:
+            if not -num_embeddings <= padding_idx < num_embeddings:
+                raise ValueError("padding_idx must be within num_embeddings")
+            if padding_idx < 0:
+                padding_idx += num_embeddings
+        self.padding_idx, self.max_norm, self.norm_type = padding_idx, max_norm, norm_type
+        self.scale_grad_by_freq, self.sparse = scale_grad_by_freq, sparse
+        ch = ax.comm_handle
+        self.inner_group = ch.inner_intra_layer_parallel_group
+        self.outer_group = ch.outer_intra_layer_parallel_group
+        self.depth_group = ch.depth_intra_layer_parallel_group
+        self.inner_group_size = dist.get_world_size(self.inner_group)
+        self.outer_group_size = dist.get_world_size(self.outer_group)
+        self.depth_group_size = dist.get_world_size(self.depth_group)
+        self.transpose, self.expert_mode = transpose, expert_mode
+        if not transpose:
+            if self.inner_group_size != 1:
+                raise ValueError("Embedding needs G_intra_c == 1 (or transpose=True with G_intra_r == 1)")
+            self.hidden_group = self.outer_group
+        else:
+            if self.outer_group_size != 1:
+                raise ValueError("Embedding(transpose=True) needs G_intra_r == 1")
+            self.hidden_group = self.inner_group
+        self.local_in_features = num_embeddings
+        self.local_out_features = divide(embedding_dim, dist.get_world_size(self.hidden_group))
+        self.in_features, self.out_features = num_embeddings, embedding_dim
+        if init_method is None:
+            init_method = default_init_method
+        dtype = dtype or torch.get_default_dtype()
+        full = torch.empty((num_embeddings, embedding_dim), device=ax.config.device, dtype=dtype)
+        init_method(full)
+        if padding_idx is not None:
+            full[padding_idx].fill_(0)
+        self.weight = torch.nn.Parameter(
+            extract_local_params_from_full_params(full, self.hidden_group, self.depth_group),
+            requires_grad=not _freeze)
+        del full
+        self.weight.is_tensor_parallel = True
+        self.weight.needs_depth_parallel_gradient_sync = False
+        self.weight.process_group_for_norm_reduction = ch.intra_layer_group
+
+    def get_output_feature_size(self):
+        return self.local_out_features
+
+    def forward(self, x):
+        weight = ForwardGather_BackwardReduceScatter.apply(self.weight, self.depth_group).reshape(
+            self.local_in_features, self.local_out_features)
+        x = F.embedding(x, weight, self.padding_idx, self.max_norm, self.norm_type,
+                        self.scale_grad_by_freq, self.sparse)
+        if not self.expert_mode:
+            x = Gather.apply(x, self.hidden_group)
+        return x
+
+    def _is_full_weight_matrix(self, w):
+        return w.ndim == 2 and tuple(w.shape) == (self.num_embeddings, self.embedding_dim)
+
+    def _is_sharded_weight_matrix(self, w):
+        return w.ndim == 1 and w.size(0) == divide(
+            self.local_in_features * self.local_out_features, self.depth_group_size)
+
+    @torch.no_grad()
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        w = state_dict.get(prefix + "weight")
+        if w is not None:
+            if self._is_full_weight_matrix(w):
+                state_dict[prefix + "weight"] = extract_local_params_from_full_params(
+                    w, self.hidden_group, self.depth_group)
+            elif not self._is_sharded_weight_matrix(w):
+                raise ValueError("embedding weight is neither the full table nor this rank's shard")
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)

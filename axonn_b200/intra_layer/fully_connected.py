@@ -1,0 +1,273 @@
+"""3-D tensor-parallel ``Linear`` (row x column x depth).
+
+Behavioural twin of the reference's ``axonn/intra_layer/fully_connected.py``
+(``Linear`` ``:190-400``, ``AsyncLinear`` ``:96-187``):
+
+* the ``[out, in]`` weight is block-sharded — ``in`` over the *inner* group,
+  ``out`` over the *outer* group — the local block is flattened and its 1-D
+  view is sharded over the *depth* group, so the ``nn.Parameter`` is a flat
+  1-D tensor (this is also the checkpoint format);
+* forward: depth all-gather -> ``X @ W^T`` -> all-reduce over inner;
+* backward: ``dX = dY @ W`` -> all-reduce over outer, ``dW = dY^T @ X`` ->
+  reduce-scatter over depth;
+* ``transpose=True`` swaps inner and outer so that consecutive layers chain
+  without re-layout; ``expert_mode=False`` adds the data-parallel <-> tensor-
+  parallel layout switches around the layer.
+
+On CUDA the three GEMMs run on this package's tcgen05 kernels and, when the
+group's ranks share an NVLink peer-memory heap, on the variants that fuse the
+collective with the GEMM (``axonn_b200.parallel.fused``); on CPU the same
+autograd function runs on ``torch.matmul`` + ``torch.distributed``.
+"""
+
+import math
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+from torch.autograd import Function
+
+from .. import axonn as ax
+from .. import ops
+from ..utils import divide
+from . import overlap_communication as oc
+from .asym_communication import (
+    Dropv,
+    GatherBatchScatterChannels,
+    GatherChannelsScatterBatch,
+    Gatherv,
+    gather_batch_sizes,
+)
+from .communication import Drop, GatherSumBackward, _gather, _reduce_scatter
+
+
+@torch.no_grad()
+def extract_local_params_from_full_params(params, out_features_group, in_features_group, depth_group):
+    """``W[out, in]`` -> this rank's flat shard:
+    rows of my outer chunk, columns of my inner chunk, flattened, my depth slice
+    (the layout stated at reference ``fully_connected.py:62-70``)."""
+    no, ni = dist.get_world_size(out_features_group), dist.get_world_size(in_features_group)
+    ro, ci = dist.get_rank(out_features_group), dist.get_rank(in_features_group)
+    out_l, in_l = params.shape[0] // no, params.shape[1] // ni
+    block = params[ro * out_l:(ro + 1) * out_l, ci * in_l:(ci + 1) * in_l].contiguous().view(-1)
+    nd, dz = dist.get_world_size(depth_group), dist.get_rank(depth_group)
+    n = divide(block.numel(), nd)
+    return block[dz * n:(dz + 1) * n].clone()
+
+
+@torch.no_grad()
+def default_init_method(weight):
+    return torch.nn.init.kaiming_uniform_(weight, a=math.sqrt(5))
+
+
+@torch.no_grad()
+def initialize_params(out_features, in_features, out_features_group, in_features_group, depth_group,
+                      init_method, init_device=None, dtype=torch.float32):
+    """Materialise the full matrix with the caller's RNG stream (identical on
+    every rank when seeded identically), keep this rank's shard."""
+    if init_device is None:
+        init_device = ax.config.device
+    params = torch.empty((out_features, in_features), device=init_device, dtype=dtype)
+    init_method(params)
+    return extract_local_params_from_full_params(params, out_features_group, in_features_group, depth_group)
+
+
+def _gathered_weight(weight, depth_group, local_shape, cache):
+    """Depth all-gather of the flat shard, shaped ``[out_l, in_l]``."""
+    full = _gather(weight, dim=0, process_group=depth_group, cache=cache)
+    return full.reshape(local_shape)
+
+
+class AsyncLinear(Function):
+    """``y = x @ W^T`` with the three collectives of 3-D tensor parallelism."""
+
+    @staticmethod
+    def forward(ctx, input_, weight, forward_all_reduce_group, backward_all_reduce_group,
+                depth_parallel_group, local_weight_shape, cache_weights):
+        cache = bool(cache_weights) or oc.CACHE_WEIGHTS
+        w_shard = weight
+        compute_dtype = input_.dtype
+        if torch.is_autocast_enabled(input_.device.type):
+            compute_dtype = torch.get_autocast_dtype(input_.device.type)
+            input_ = input_.to(compute_dtype)
+        w = _gathered_weight(w_shard, depth_parallel_group, local_weight_shape, cache)
+        if w.dtype != compute_dtype:
+            w = w.to(compute_dtype)
+        ctx.save_for_backward(input_, w_shard)
+        ctx.backward_all_reduce_group = backward_all_reduce_group
+        ctx.depth_parallel_group = depth_parallel_group
+        ctx.shape = local_weight_shape
+        ctx.cache = cache
+        ctx.compute_dtype = compute_dtype
+        x2 = input_.reshape(-1, input_.shape[-1])
+        out = ops.matmul_nt(x2, w)
+        if dist.get_world_size(forward_all_reduce_group) > 1:
+            dist.all_reduce(out, group=forward_all_reduce_group)
+        return out.reshape(*input_.shape[:-1], local_weight_shape[0])
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input_, w_shard = ctx.saved_tensors
+        grad_output = grad_output.to(ctx.compute_dtype)
+        go2 = grad_output.reshape(-1, grad_output.shape[-1])
+        x2 = input_.reshape(-1, input_.shape[-1])
+        overlap_rs = oc.OVERLAP_REDUCE_SCATTER
+        overlap_ar = oc.OVERLAP_ALL_REDUCE
+        outer_n = dist.get_world_size(ctx.backward_all_reduce_group)
+        depth_n = dist.get_world_size(ctx.depth_parallel_group)
+        grad_input = grad_weight = None
+        handle = None
+
+        def wgrad():
+            gw = ops.matmul_tn(go2, x2, out_dtype=w_shard.dtype).reshape(-1)
+            if depth_n > 1:
+                gw = _reduce_scatter(gw, 0, ctx.depth_parallel_group, overlap_comm=overlap_rs)
+                if overlap_rs:
+                    oc.accumulate_later(w_shard, gw)
+                    return None
+            return gw
+
+        def dgrad():
+            # the cached copy (if any) is consumed here; otherwise gather again
+            w = _gathered_weight(w_shard, ctx.depth_parallel_group, ctx.shape, cache=False)
+            if w.dtype != ctx.compute_dtype:
+                w = w.to(ctx.compute_dtype)
+            return ops.matmul_nn(go2, w)
+
+        if outer_n > 1 or not overlap_rs:
+            # dgrad first so that its all-reduce hides under the wgrad GEMM
+            if ctx.needs_input_grad[0]:
+                grad_input = dgrad()
+                if outer_n > 1:
+                    handle = dist.all_reduce(grad_input, group=ctx.backward_all_reduce_group, async_op=overlap_ar)
+            if ctx.needs_input_grad[1]:
+                grad_weight = wgrad()
+            if handle is not None and overlap_ar:
+                handle.wait()
+        else:
+            # no activation all-reduce: start the reduce-scatter first, hide it under dgrad
+            if ctx.needs_input_grad[1]:
+                grad_weight = wgrad()
+            if ctx.needs_input_grad[0]:
+                grad_input = dgrad()
+        if grad_input is not None:
+            grad_input = grad_input.reshape(input_.shape)
+        return grad_input, grad_weight, None, None, None, None, None
+
+
+class Linear(torch.nn.Module):
+    """Drop-in ``nn.Linear`` whose weight is sharded over the 3-D grid.
+
+    Arguments follow reference ``fully_connected.py:191-203``."""
+
+    def __init__(self, in_features, out_features, *args, transpose=False, bias=True, skip_bias_add=False,
+                 init_method=None, expert_mode=False, tensor_parallel_dims: Optional[Sequence[int]] = None,
+                 **kwargs):
+        super().__init__()
+        assert ax.is_initialized, "call axonn_b200.axonn.init(...) first"
+        for k in ("use_easy_api", "easy_api"):
+            # spelled this way by the reference's HF patches; honoured here
+            if k in kwargs:
+                expert_mode = not kwargs.pop(k)
+        ch = ax.comm_handle
+        self.inner_group, self.outer_group, self.depth_group = ch.get_intra_layer_groups(tensor_parallel_dims)
+        if transpose:
+            self.inner_group, self.outer_group = self.outer_group, self.inner_group
+        self.inner_group_size = dist.get_world_size(self.inner_group)
+        self.outer_group_size = dist.get_world_size(self.outer_group)
+        self.depth_group_size = dist.get_world_size(self.depth_group)
+        self.in_features, self.out_features = in_features, out_features
+        self.expert_mode = expert_mode
+        self.transpose = transpose
+        self.local_in_features = divide(in_features, self.inner_group_size)
+        self.local_out_features = divide(out_features, self.outer_group_size)
+        if init_method is None:
+            init_method = default_init_method
+        dtype = kwargs.get("dtype") or torch.get_default_dtype()
+        initial = initialize_params(out_features, in_features, self.outer_group, self.inner_group,
+                                    self.depth_group, init_method, dtype=dtype)
+        self.weight = torch.nn.Parameter(initial, requires_grad=True)
+        self.weight.is_tensor_parallel = True
+        self.weight.needs_depth_parallel_gradient_sync = False
+        self.weight.process_group_for_norm_reduction = ch.intra_layer_group
+        if bias:
+            self.bias = torch.nn.Parameter(torch.zeros(self.local_out_features, dtype=dtype,
+                                                       device=initial.device))
+            self.bias.is_tensor_parallel = True
+            self.bias.needs_depth_parallel_gradient_sync = True
+            # a bias shard is replicated over inner and depth, distinct over outer
+            self.bias.process_group_for_norm_reduction = self.outer_group
+        else:
+            self.bias = None
+        self.skip_bias_add = skip_bias_add
+
+    @property
+    def local_weight_shape(self):
+        return (self.local_out_features, self.local_in_features)
+
+    def extra_repr(self):
+        return (f"in={self.in_features}, out={self.out_features}, local={self.local_weight_shape}, "
+                f"grid(inner,outer,depth)=({self.inner_group_size},{self.outer_group_size},"
+                f"{self.depth_group_size}), transpose={self.transpose}, expert_mode={self.expert_mode}")
+
+    def forward(self, x, cache_weights_in_all_gather=False):
+        lead_shape = x.shape[:-1]
+        x = x.reshape(-1, x.shape[-1])
+        switch_layout = (not self.expert_mode) and self.inner_group_size * self.outer_group_size > 1
+        if switch_layout:
+            inner_sizes = gather_batch_sizes(x.shape[0], self.inner_group, device=x.device)
+            x = GatherBatchScatterChannels.apply(x, inner_sizes, self.inner_group)
+            outer_sizes = gather_batch_sizes(x.shape[0], self.outer_group, device=x.device)
+            x = Gatherv.apply(x, outer_sizes, self.outer_group)
+        x = AsyncLinear.apply(x, self.weight, self.inner_group, self.outer_group, self.depth_group,
+                              self.local_weight_shape, cache_weights_in_all_gather)
+        if switch_layout:
+            x = GatherChannelsScatterBatch.apply(x, outer_sizes, self.outer_group)
+            x = Dropv.apply(x, inner_sizes, self.inner_group)
+        x = x.reshape(*lead_shape, x.shape[-1])
+        if self.bias is None:
+            return x
+        bias = self.bias
+        if not self.expert_mode:
+            bias = GatherSumBackward.apply(bias, self.outer_group, self.inner_group)
+        if self.skip_bias_add:
+            return x, bias
+        return x + bias.to(x.dtype)
+
+    # ---------------------------------------------------------------- state dict
+    def _is_full_weight_matrix(self, w):
+        return w.ndim == 2 and w.size(0) == self.out_features and w.size(1) == self.in_features
+
+    def _is_sharded_weight_matrix(self, w):
+        return w.ndim == 1 and w.size(0) == divide(
+            self.local_out_features * self.local_in_features, self.depth_group_size)
+
+    @torch.no_grad()
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        """Accept either a full ``[out, in]`` matrix (e.g. from ``nn.Linear`` or a
+        run on another grid) or this rank's flat shard; same for the bias."""
+        w = state_dict.get(prefix + "weight")
+        if w is not None:
+            if self._is_full_weight_matrix(w):
+                state_dict[prefix + "weight"] = extract_local_params_from_full_params(
+                    w, self.outer_group, self.inner_group, self.depth_group)
+            elif not self._is_sharded_weight_matrix(w):
+                raise ValueError(f"{prefix}weight of shape {tuple(w.shape)} is neither the full "
+                                 f"[{self.out_features},{self.in_features}] matrix nor this rank's shard")
+        if self.bias is not None:
+            b = state_dict.get(prefix + "bias")
+            if b is not None:
+                if b.size(0) == self.out_features and self.outer_group_size > 1:
+                    state_dict[prefix + "bias"] = Drop.apply(b, self.outer_group).clone()
+                elif b.size(0) != self.local_out_features:
+                    raise ValueError(f"{prefix}bias of length {b.size(0)} matches neither the full nor the "
+                                     f"local output width")
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
+    @torch.no_grad()
+    def full_weight(self):
+        """Reassemble the full ``[out, in]`` matrix on every rank (tests, export)."""
+        w = _gather(self.weight.detach(), 0, self.depth_group).reshape(self.local_weight_shape)
+        w = _gather(w, 1, self.inner_group)
+        w = _gather(w, 0, self.outer_group)
+        return w

@@ -1,0 +1,21 @@
+"""Operators: hand-written sm_100a kernels on GPU, PyTorch on CPU.
+
+Every function here has two implementations with identical semantics: a CUDA
+kernel from ``axonn_b200/csrc`` reached through ``ops._lib`` and a plain
+PyTorch composition used on CPU (and as the numerical oracle in the tests).
+"""
+
+from .gemm import (  # noqa: F401
+    EPI_BIAS,
+    EPI_BIAS_GELU,
+    EPI_GELU,
+    EPI_NONE,
+    matmul_nn,
+    matmul_nt,
+    matmul_tn,
+)
+from .multi_tensor import (  # noqa: F401
+    all_reduce_bucketed_,
+    multi_tensor_l2norm_sq,
+    multi_tensor_scale_,
+)
