@@ -1,0 +1,413 @@
+// bf16/fp16 GEMM on 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+// One persistent CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer: streams 128xBK (A) and BNxBK (B) tiles into a
+//               multi-stage shared-memory ring (128-byte swizzle, mbarrier
+//               transaction counts);
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN,
+//               K=16) from shared-memory descriptors into one of two TMEM
+//               accumulators (2 x BN fp32 columns), and commits to mbarriers
+//               to recycle smem stages and to publish finished accumulators;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM
+//               lanes), apply bias / GELU / accumulate, convert and store; runs
+//               concurrently with the next tile's main loop thanks to the
+//               double-buffered accumulator.
+//
+// Operand layouts: each of A and B is either K-major (row = M/N index, K
+// contiguous) or MN-major (row = K index, M/N contiguous); both are expressed
+// to the tensor core through the majorness bits of the instruction descriptor
+// and the matching canonical shared-memory layout, so forward (A Bt), input
+// gradient (A B) and weight gradient (At B) need no transposed copies.
+//
+// Every wait is bounded; on expiry the CTA raises an abort flag, records the
+// reason in the device status word, drains its TMA copies, frees TMEM and
+// returns.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace axb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  void* C;
+  const void* bias;
+  void* aux;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int out_dtype;  // 0 bf16, 1 fp16, 2 fp32
+  int in_dtype;   // 0 bf16, 1 fp16
+  int epilogue;
+  int accumulate;
+  unsigned int* status;
+  unsigned long long timeout_ns;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024 /* alignment slack */;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group, int& tm, int& tn) {
+  const int per_group = group * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group;
+  const int gsize = min(group, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % gsize;
+  tn = r / gsize;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int dtype) {
+  if (dtype == 0) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void unpack2(uint32_t u, int dtype, float& a, float& b) {
+  if (dtype == 0) {
+    __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
+    a = __bfloat162float(v.x); b = __bfloat162float(v.y);
+  } else {
+    __half2 v = *reinterpret_cast<__half2*>(&u);
+    a = __half2float(v.x); b = __half2float(v.y);
+  }
+}
+
+// Store 32 consecutive columns of one output row (fp32 values in v).
+__device__ __forceinline__ void store_row32(void* base, int out_dtype, size_t row, int ld, int col, int N,
+                                            const float (&v)[32], bool accumulate) {
+  if (out_dtype == 2) {
+    float* p = reinterpret_cast<float*>(base) + row * ld + col;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (col + g * 4 + 4 <= N) {
+        float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+        if (accumulate) {
+          float4 old = *reinterpret_cast<float4*>(p + g * 4);
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        *reinterpret_cast<float4*>(p + g * 4) = o;
+      }
+    }
+  } else {
+    uint16_t* p = reinterpret_cast<uint16_t*>(base) + row * ld + col;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (col + g * 8 + 8 <= N) {
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = v[g * 8 + i];
+        if (accumulate) {
+          uint4 old = *reinterpret_cast<uint4*>(p + g * 8);
+          float a, b;
+          unpack2(old.x, out_dtype, a, b); f[0] += a; f[1] += b;
+          unpack2(old.y, out_dtype, a, b); f[2] += a; f[3] += b;
+          unpack2(old.z, out_dtype, a, b); f[4] += a; f[5] += b;
+          unpack2(old.w, out_dtype, a, b); f[6] += a; f[7] += b;
+        }
+        uint4 o;
+        o.x = pack2(f[0], f[1], out_dtype); o.y = pack2(f[2], f[3], out_dtype);
+        o.z = pack2(f[4], f[5], out_dtype); o.w = pack2(f[6], f[7], out_dtype);
+        *reinterpret_cast<uint4*>(p + g * 8) = o;
+      }
+    }
+  }
+}
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + S::STAGES;
+  uint64_t* tmem_full = empty_bar + S::STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int group = (BN == 256) ? 16 : 8;
+  const uint64_t timeout = p.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 1) { tmem_alloc(tmem_ptr_smem, 2 * BN); tmem_relinquish(); }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      uint32_t armed_mask = 0, armed_parity = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, timeout)) { ok = false; break; }
+          uint8_t* sA = smem + stage * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          armed_mask |= 1u << stage;
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d(sA, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * j, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(sB, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0);
+          }
+          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // drain: wait (bounded) until every copy this thread started has landed
+        for (int s = 0; s < S::STAGES; ++s) {
+          if (armed_mask & (1u << s)) {
+            uint32_t par = (armed_parity >> s) & 1u;
+            uint64_t t0 = globaltimer_ns();
+            while (!mbar_try_wait(&full_bar[s], par) && globaltimer_ns() - t0 < 2000000ull) {}
+          }
+        }
+        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x101u;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc(p.in_dtype == 0 ? 1 : 0, A_MN, B_MN, BM, BN);
+      // K-major: 8-row groups 1024 B apart, K step = 32 B inside the swizzle row.
+      // MN-major: 64-wide MN chunks BK*128 B apart (leading), 8-K-row groups
+      // 1024 B apart (stride), K step = 16 rows * 128 B.
+      const uint32_t a_lbo = A_MN ? BK * 128 : 16, a_sbo = 1024, a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t b_lbo = B_MN ? BK * 128 : 16, b_sbo = 1024, b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      int t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        const uint32_t acc_phase = (t >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, timeout)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, timeout)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = umma_smem_desc(a_addr + k * a_kstep, a_lbo, a_sbo);
+            const uint64_t bdesc = umma_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
+      }
+      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x102u;
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    bool ok = true;
+    int t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+      int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+      const int buf = t & 1;
+      const uint32_t acc_phase = (t >> 1) & 1;
+      if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, timeout)) { ok = false; break; }
+      tcgen05_fence_after();
+      const size_t row = static_cast<size_t>(tm) * BM + q * 32 + lane;
+      const bool row_ok = row < static_cast<size_t>(p.M);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col = tn * BN + c * 32;
+        if (col >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        if (p.epilogue == 1 || p.epilogue == 2) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col + i < p.N) {
+              float b = (p.in_dtype == 0)
+                            ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + i])
+                            : __half2float(reinterpret_cast<const __half*>(p.bias)[col + i]);
+              v[i] += b;
+            }
+          }
+        }
+        if (p.epilogue >= 2) {
+          if (p.aux != nullptr && row_ok) store_row32(p.aux, p.out_dtype, row, p.N, col, p.N, v, false);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        }
+        if (row_ok) store_row32(p.C, p.out_dtype, row, p.N, col, p.N, v, p.accumulate != 0);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+    if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x104u;
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of 16-bit elements; box = box_rows x 64 columns (128 B), 128 B swizzle.
+int make_tmap_2d_16bit(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                       int dtype) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { set_error("cuTensorMapEncodeTiled entry point not available"); return -1; }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) { set_error("TMA base address must be 16-byte aligned"); return -1; }
+  if ((cols * 2) % 16 != 0) { set_error("TMA row pitch must be a multiple of 16 bytes (cols=%llu)", (unsigned long long)cols); return -1; }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                   const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r); return -1; }
+  return 0;
+}
+
+int sm_count(int device) {
+  static int cached[64] = {0};
+  if (device < 0 || device >= 64) return 148;
+  if (!cached[device]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+    cached[device] = n;
+  }
+  return cached[device];
+}
+
+template <int BN, int A_MN, int B_MN>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int device, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  static bool configured[64] = {false};
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN>;
+  if (!configured[device & 63]) {
+    AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured[device & 63] = true;
+  }
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace axb
+
+extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,
+                        int K, int in_dtype, int out_dtype, int epilogue, int accumulate, int device, void* stream) {
+  using namespace axb;
+  if (M <= 0 || N <= 0 || K <= 0) { set_error("axb_gemm: empty problem"); return -1; }
+  if (layout < 0 || layout > 2) { set_error("axb_gemm: bad layout %d", layout); return -1; }
+  if (in_dtype != 0 && in_dtype != 1) { set_error("axb_gemm: operands must be bf16 or fp16"); return -1; }
+  if ((N % 8) || (K % 8) || (layout == 2 && (M % 8))) { set_error("axb_gemm: dims must be multiples of 8"); return -1; }
+  if ((epilogue == 1 || epilogue == 2) && !bias) { set_error("axb_gemm: epilogue needs bias"); return -1; }
+  unsigned int* status_dev = nullptr;
+  if (!device_status_word(device, &status_dev)) { set_error("axb_gemm: no status word"); return -1; }
+
+  const int tiles_m = (M + BM - 1) / BM;
+  const bool wide = static_cast<long long>(tiles_m) * ((N + 255) / 256) >= sm_count(device);
+  const int BN = wide ? 256 : 128;
+  const int a_mn = (layout == 2) ? 1 : 0;
+  const int b_mn = (layout == 0) ? 0 : 1;
+
+  CUtensorMap tmA, tmB;
+  // K-major operand [R, K]: box 64(K) x tile rows.  MN-major operand [K, R]: box 64(R) x 64(K).
+  if (a_mn == 0) { if (make_tmap_2d_16bit(&tmA, A, M, K, BM, in_dtype)) return -1; }
+  else           { if (make_tmap_2d_16bit(&tmA, A, K, M, BK, in_dtype)) return -1; }
+  if (b_mn == 0) { if (make_tmap_2d_16bit(&tmB, B, N, K, BN, in_dtype)) return -1; }
+  else           { if (make_tmap_2d_16bit(&tmB, B, K, N, BK, in_dtype)) return -1; }
+
+  GemmParams p;
+  p.C = C; p.bias = bias; p.aux = aux; p.M = M; p.N = N; p.K = K;
+  p.out_dtype = out_dtype; p.in_dtype = in_dtype; p.epilogue = epilogue; p.accumulate = accumulate;
+  p.status = status_dev; p.timeout_ns = 2000000000ull;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define AXB_DISPATCH(BN_, A_, B_) return launch<BN_, A_, B_>(tmA, tmB, p, device, s)
+  if (BN == 256) {
+    if (layout == 0) AXB_DISPATCH(256, 0, 0);
+    if (layout == 1) AXB_DISPATCH(256, 0, 1);
+    AXB_DISPATCH(256, 1, 1);
+  } else {
+    if (layout == 0) AXB_DISPATCH(128, 0, 0);
+    if (layout == 1) AXB_DISPATCH(128, 0, 1);
+    AXB_DISPATCH(128, 1, 1);
+  }
+#undef AXB_DISPATCH
+}

@@ -1,0 +1,89 @@
+"""tcgen05 GEMM against a plain PyTorch fp32 reference of the same product."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(layout, a, b):
+    a, b = a.float(), b.float()
+    if layout == "nt":
+        return a @ b.t()
+    if layout == "nn":
+        return a @ b
+    return a.t() @ b
+
+
+def _operands(layout, M, N, K, dtype, dev):
+    g = torch.Generator(device=dev).manual_seed(M * 7 + N * 3 + K)
+    sa = (M, K) if layout != "tn" else (K, M)
+    sb = (N, K) if layout == "nt" else (K, N)
+    a = (torch.randn(sa, device=dev, generator=g) * 0.5).to(dtype)
+    b = (torch.randn(sb, device=dev, generator=g) * 0.5).to(dtype)
+    return a, b
+
+
+SHAPES = [
+    (128, 128, 64), (128, 256, 128), (256, 512, 256), (384, 640, 192),
+    (200, 136, 72),            # ragged M, N, K (multiples of 8 only)
+    (1024, 1024, 1024), (4096, 2048, 512), (520, 2056, 1032),
+]
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_matches_fp32_reference(layout, shape):
+    from axonn_b200 import ops
+    from axonn_b200.ops import _lib
+
+    M, N, K = shape
+    dev = torch.device("cuda", 0)
+    a, b = _operands(layout, M, N, K, torch.bfloat16, dev)
+    fn = {"nt": ops.matmul_nt, "nn": ops.matmul_nn, "tn": ops.matmul_tn}[layout]
+    out = fn(a, b)
+    torch.cuda.synchronize()
+    assert _lib.lib().axb_device_status(0, 1) == 0
+    ref = _ref(layout, a, b)
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, f"{layout} {shape}: max err {err} (scale {scale})"
+    # fp32 output: only accumulation-order differences remain
+    out32 = fn(a, b, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    err32 = (out32 - ref).abs().max().item()
+    assert err32 <= 2e-4 * scale + 1e-4, f"{layout} {shape}: fp32-out max err {err32}"
+
+
+def test_gemm_fp16_and_accumulate():
+    from axonn_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    a, b = _operands("nt", 512, 384, 256, torch.float16, dev)
+    out = ops.matmul_nt(a, b, out_dtype=torch.float32)
+    ref = _ref("nt", a, b)
+    assert (out - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    acc = torch.ones_like(out)
+    ops.matmul_nt(a, b, out=acc, accumulate=True)
+    assert (acc - (ref + 1)).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    a, b = _operands("tn", 256, 512, 1024, torch.bfloat16, dev)
+    acc = torch.full((256, 512), 2.0, device=dev)
+    ops.matmul_tn(a, b, out=acc, accumulate=True)
+    ref = _ref("tn", a, b) + 2
+    assert (acc - ref).abs().max().item() <= 2e-4 * ref.abs().max().item() + 1e-4
+
+
+def test_gemm_bias_gelu_epilogue():
+    from axonn_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    a, b = _operands("nt", 384, 512, 256, torch.bfloat16, dev)
+    bias = (torch.randn(512, device=dev) * 0.5).bfloat16()
+    z_ref = _ref("nt", a, b) + bias.float()
+    out = ops.matmul_nt(a, b, bias=bias, epilogue=ops.EPI_BIAS)
+    assert (out.float() - z_ref).abs().max().item() <= 1e-2 * z_ref.abs().max().item() + 1e-2
+    aux = torch.empty(384, 512, device=dev, dtype=torch.bfloat16)
+    out = ops.matmul_nt(a, b, bias=bias, epilogue=ops.EPI_BIAS_GELU, aux=aux)
+    g_ref = torch.nn.functional.gelu(z_ref, approximate="tanh")
+    assert (aux.float() - z_ref).abs().max().item() <= 1e-2 * z_ref.abs().max().item() + 1e-2
+    assert (out.float() - g_ref).abs().max().item() <= 1e-2 * g_ref.abs().max().item() + 1e-2
