@@ -1,0 +1,284 @@
+// LayerNorm / RMSNorm forward and backward for sm_100a.
+//
+// Rows are processed by persistent blocks (grid = a small multiple of the SM
+// count); every thread owns fixed 8-element column chunks, so the backward
+// kernel can accumulate its dgamma/dbeta partial sums in registers across all
+// the rows the block visits and write one partial row per block; a second tiny
+// kernel folds the partials.  All loads/stores are 16-byte vectors.
+//
+// Three modes serve tensor-parallel hidden dimensions (the row statistics are
+// then sums over shards that the caller all-reduces between the two calls):
+//   mode 0  statistics computed locally and applied in one kernel
+//   mode 1  only emit per-row partial sums
+//   mode 2  apply with externally supplied (already reduced) statistics
+#include "common.cuh"
+
+namespace axb {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_CHUNKS = 8;  // hidden <= 256 * 8 * 8 = 16384
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Vec8<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&f)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&f)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+// Sum two values over the block; result broadcast to all threads.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red /* [2*32] */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) { red[w] = a; red[32 + w] = b; }
+  __syncthreads();
+  a = l < nw ? red[l] : 0.f; b = l < nw ? red[32 + l] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+}
+
+// stats layout: [rows, 2]: LayerNorm -> (sum x, sum x^2) in mode 1, (mean, rstd) otherwise;
+// RMSNorm -> (unused, sum x^2) in mode 1, (0, rstd) otherwise.
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                T* __restrict__ y, float* __restrict__ stats, int rows, int H, int H_total, float eps, int mode) {
+  __shared__ float red[64];
+  const int nchunk = H / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + static_cast<size_t>(row) * H;
+    float mean = 0.f, rstd = 0.f;
+    if (mode != 2) {
+      float s1 = 0.f, s2 = 0.f;
+      for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
+        float f[8]; Vec8<T>::load(xr + c * 8, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s1 += f[i]; s2 += f[i] * f[i]; }
+      }
+      block_sum2(s1, s2, red);
+      if (mode == 1) {
+        if (threadIdx.x == 0) { stats[2 * row] = s1; stats[2 * row + 1] = s2; }
+        continue;
+      }
+      if (RMS) { mean = 0.f; rstd = rsqrtf(s2 / H_total + eps); }
+      else { mean = s1 / H_total; rstd = rsqrtf(fmaxf(s2 / H_total - mean * mean, 0.f) + eps); }
+      if (threadIdx.x == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
+    } else {
+      mean = stats[2 * row]; rstd = stats[2 * row + 1];
+    }
+    T* yr = y + static_cast<size_t>(row) * H;
+    for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
+      float f[8], g[8], b[8];
+      Vec8<T>::load(xr + c * 8, f);
+      Vec8<T>::load(gamma + c * 8, g);
+      if (!RMS && beta) Vec8<T>::load(beta + c * 8, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v = (f[i] - mean) * rstd * g[i];
+        if (!RMS && beta) v += b[i];
+        f[i] = v;
+      }
+      Vec8<T>::store(yr + c * 8, f);
+    }
+  }
+}
+
+// Backward.  sums layout [rows, 2] = (sum g*dy, sum g*dy*xhat) over the full hidden dimension.
+template <typename T, bool RMS, int CH>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                const float* __restrict__ stats, T* __restrict__ dx, float* __restrict__ sums,
+                float* __restrict__ dgamma_part, float* __restrict__ dbeta_part, int rows, int H, int H_total,
+                int mode) {
+  __shared__ float red[64];
+  const int nchunk = H / 8;
+  float ag[CH][8], ab[CH][8];
+#pragma unroll
+  for (int k = 0; k < CH; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { ag[k][i] = 0.f; ab[k][i] = 0.f; }
+
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + static_cast<size_t>(row) * H;
+    const T* dyr = dy + static_cast<size_t>(row) * H;
+    const float mean = stats[2 * row], rstd = stats[2 * row + 1];
+    float s1 = 0.f, s2 = 0.f;
+    if (mode != 2) {
+      for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
+        float f[8], d[8], g[8];
+        Vec8<T>::load(xr + c * 8, f); Vec8<T>::load(dyr + c * 8, d); Vec8<T>::load(gamma + c * 8, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float xh = (f[i] - mean) * rstd, gd = g[i] * d[i];
+          s1 += gd; s2 += gd * xh;
+        }
+      }
+      block_sum2(s1, s2, red);
+      if (mode == 1) {
+        if (threadIdx.x == 0) { sums[2 * row] = s1; sums[2 * row + 1] = s2; }
+        continue;
+      }
+    } else {
+      s1 = sums[2 * row]; s2 = sums[2 * row + 1];
+    }
+    const float m1 = RMS ? 0.f : s1 / H_total, m2 = s2 / H_total;
+    T* dxr = dx + static_cast<size_t>(row) * H;
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      const int c = threadIdx.x + k * NORM_THREADS;
+      if (c < nchunk) {
+        float f[8], d[8], g[8], o[8];
+        Vec8<T>::load(xr + c * 8, f); Vec8<T>::load(dyr + c * 8, d); Vec8<T>::load(gamma + c * 8, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float xh = (f[i] - mean) * rstd;
+          o[i] = rstd * (g[i] * d[i] - m1 - xh * m2);
+          ag[k][i] += d[i] * xh; ab[k][i] += d[i];
+        }
+        Vec8<T>::store(dxr + c * 8, o);
+      }
+    }
+  }
+  if (mode != 1 && dgamma_part) {
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      const int c = threadIdx.x + k * NORM_THREADS;
+      if (c >= nchunk) continue;
+      float* pg = dgamma_part + static_cast<size_t>(blockIdx.x) * H + c * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pg[i] = ag[k][i];
+      if (!RMS && dbeta_part) {
+        float* pb = dbeta_part + static_cast<size_t>(blockIdx.x) * H + c * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pb[i] = ab[k][i];
+      }
+    }
+  }
+}
+
+// out[c] = sum_b part[b, c]   (optionally two tables at once)
+__global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb, float* __restrict__ oa,
+                                     float* __restrict__ ob, int nblocks, int H) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float a = 0.f, b = 0.f;
+  for (int r = 0; r < nblocks; ++r) {
+    a += pa[static_cast<size_t>(r) * H + c];
+    if (pb) b += pb[static_cast<size_t>(r) * H + c];
+  }
+  oa[c] = a;
+  if (pb) ob[c] = b;
+}
+
+int sm_count(int device);
+
+template <typename T>
+static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
+                      int H_total, float eps, int rms, int mode, int grid, cudaStream_t s) {
+  if (rms)
+    norm_fwd_kernel<T, true><<<grid, NORM_THREADS, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
+                                                          stats, rows, H, H_total, eps, mode);
+  else
+    norm_fwd_kernel<T, false><<<grid, NORM_THREADS, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
+                                                           stats, rows, H, H_total, eps, mode);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <typename T>
+static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const float* stats, void* dx, float* sums,
+                      float* dgp, float* dbp, int rows, int H, int H_total, int rms, int mode, int grid,
+                      cudaStream_t s) {
+  const int nchunk = H / 8;
+  const int ch = (nchunk + NORM_THREADS - 1) / NORM_THREADS;
+#define AXB_NORM_BWD(RMS_, CH_)                                                                              \
+  norm_bwd_kernel<T, RMS_, CH_><<<grid, NORM_THREADS, 0, s>>>((const T*)dy, (const T*)x, (const T*)gamma, stats, \
+                                                              (T*)dx, sums, dgp, dbp, rows, H, H_total, mode)
+  if (rms) {
+    if (ch <= 1) AXB_NORM_BWD(true, 1); else if (ch <= 2) AXB_NORM_BWD(true, 2);
+    else if (ch <= 4) AXB_NORM_BWD(true, 4); else AXB_NORM_BWD(true, 8);
+  } else {
+    if (ch <= 1) AXB_NORM_BWD(false, 1); else if (ch <= 2) AXB_NORM_BWD(false, 2);
+    else if (ch <= 4) AXB_NORM_BWD(false, 4); else AXB_NORM_BWD(false, 8);
+  }
+#undef AXB_NORM_BWD
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace axb
+
+extern "C" int axb_norm_grid(int device, int rows) {
+  int g = 4 * axb::sm_count(device);
+  return rows < g ? rows : g;
+}
+
+extern "C" int axb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
+                            int H_total, float eps, int rms, int mode, int dtype, int device, void* stream) {
+  using namespace axb;
+  if (H % 8 || H > NORM_THREADS * 8 * NORM_MAX_CHUNKS) { set_error("norm: hidden %d unsupported", H); return -1; }
+  if (rows <= 0) return 0;
+  const int grid = axb_norm_grid(device, rows);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0) return norm_fwd_t<__nv_bfloat16>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s);
+  if (dtype == 1) return norm_fwd_t<__half>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s);
+  return norm_fwd_t<float>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s);
+}
+
+// dgamma_part / dbeta_part: [grid, H] fp32 scratch (grid from axb_norm_grid); dgamma/dbeta: [H] fp32 outputs.
+extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* stats, void* dx,
+                            float* sums, float* dgamma_part, float* dbeta_part, float* dgamma, float* dbeta, int rows,
+                            int H, int H_total, int rms, int mode, int dtype, int device, void* stream) {
+  using namespace axb;
+  if (H % 8 || H > NORM_THREADS * 8 * NORM_MAX_CHUNKS) { set_error("norm: hidden %d unsupported", H); return -1; }
+  if (rows <= 0) return 0;
+  const int grid = axb_norm_grid(device, rows);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (dtype == 0) rc = norm_bwd_t<__nv_bfloat16>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s);
+  else if (dtype == 1) rc = norm_bwd_t<__half>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s);
+  else rc = norm_bwd_t<float>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s);
+  if (rc) return rc;
+  if (mode != 1 && dgamma_part && dgamma) {
+    fold_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(dgamma_part, rms ? nullptr : dbeta_part, dgamma,
+                                                        rms ? nullptr : dbeta, grid, H);
+    AXB_CUDA(cudaGetLastError());
+  }
+  return 0;
+}

@@ -1,0 +1,166 @@
+// Multi-tensor kernels: fused AdamW step, squared L2 norm, in-place scale.
+//
+// A launch covers a whole list of tensors through a device table; work is cut
+// into fixed-size chunks and a grid-stride loop maps chunk -> (tensor, offset)
+// by binary search in the table's chunk prefix sums, so one launch replaces
+// hundreds of per-parameter launches.
+#include "common.cuh"
+
+namespace axb {
+
+constexpr int MT_CHUNK = 1 << 16;
+constexpr int MT_THREADS = 512;
+
+// table row for norm/scale: {ptr, numel, dtype (0 fp32, 1 bf16, 2 fp16), chunk_prefix}
+// table row for adamw:      {master fp32, model bf16 or 0, grad, exp_avg, exp_avg_sq, numel, grad dtype, chunk_prefix}
+__device__ __forceinline__ int find_tensor(const long long* table, int width, int prefix_col, int n, long long chunk) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (table[(size_t)mid * width + prefix_col] <= chunk) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float load_as_f32(const void* p, long long i, int dtype) {
+  if (dtype == 0) return reinterpret_cast<const float*>(p)[i];
+  if (dtype == 1) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ void store_from_f32(void* p, long long i, int dtype, float v) {
+  if (dtype == 0) reinterpret_cast<float*>(p)[i] = v;
+  else if (dtype == 1) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+
+__global__ void __launch_bounds__(MT_THREADS)
+multi_l2norm_sq_kernel(const long long* __restrict__ table, int n, long long total_chunks, float* __restrict__ out) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    const int t = find_tensor(table, 4, 3, n, chunk);
+    const long long* row = table + (size_t)t * 4;
+    const void* p = reinterpret_cast<const void*>(row[0]);
+    const long long numel = row[1];
+    const int dtype = (int)row[2];
+    const long long begin = (chunk - row[3]) * MT_CHUNK;
+    const long long end = begin + MT_CHUNK < numel ? begin + MT_CHUNK : numel;
+    const bool vec = (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+    if (vec && dtype == 1) {
+      const long long nv = (end - begin) / 8;
+      const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + begin);
+      for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+        uint4 u = q[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); acc += f.x * f.x + f.y * f.y; }
+      }
+      for (long long i = begin + nv * 8 + threadIdx.x; i < end; i += blockDim.x) {
+        float v = load_as_f32(p, i, dtype); acc += v * v;
+      }
+    } else if (vec && dtype == 0) {
+      const long long nv = (end - begin) / 4;
+      const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + begin);
+      for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+        float4 f = q[i]; acc += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+      }
+      for (long long i = begin + nv * 4 + threadIdx.x; i < end; i += blockDim.x) {
+        float v = load_as_f32(p, i, dtype); acc += v * v;
+      }
+    } else {
+      for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        float v = load_as_f32(p, i, dtype); acc += v * v;
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    acc = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (threadIdx.x == 0) atomicAdd(out, acc);
+  }
+}
+
+__global__ void __launch_bounds__(MT_THREADS)
+multi_scale_kernel(const long long* __restrict__ table, int n, long long total_chunks, const float* __restrict__ scale_ptr) {
+  const float s = *scale_ptr;
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    const int t = find_tensor(table, 4, 3, n, chunk);
+    const long long* row = table + (size_t)t * 4;
+    void* p = reinterpret_cast<void*>(row[0]);
+    const long long numel = row[1];
+    const int dtype = (int)row[2];
+    const long long begin = (chunk - row[3]) * MT_CHUNK;
+    const long long end = begin + MT_CHUNK < numel ? begin + MT_CHUNK : numel;
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x)
+      store_from_f32(p, i, dtype, load_as_f32(p, i, dtype) * s);
+  }
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2;
+  const float* grad_scale;       // device scalar multiplied into every gradient (may be null)
+  const float* found_inf;        // device scalar; non-zero => skip the whole step (may be null)
+};
+
+__global__ void __launch_bounds__(MT_THREADS)
+multi_adamw_kernel(const long long* __restrict__ table, int n, long long total_chunks, AdamArgs a) {
+  if (a.found_inf && *a.found_inf != 0.f) return;
+  const float gs = a.grad_scale ? *a.grad_scale : 1.f;
+  const float decay = 1.f - a.lr * a.weight_decay;
+  const float step = a.lr / a.bias_c1;
+  const float inv_sqrt_c2 = rsqrtf(a.bias_c2);
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    const int t = find_tensor(table, 8, 7, n, chunk);
+    const long long* row = table + (size_t)t * 8;
+    float* master = reinterpret_cast<float*>(row[0]);
+    __nv_bfloat16* model = reinterpret_cast<__nv_bfloat16*>(row[1]);
+    const void* grad = reinterpret_cast<const void*>(row[2]);
+    float* m = reinterpret_cast<float*>(row[3]);
+    float* v = reinterpret_cast<float*>(row[4]);
+    const long long numel = row[5];
+    const int gdtype = (int)row[6];
+    const long long begin = (chunk - row[7]) * MT_CHUNK;
+    const long long end = begin + MT_CHUNK < numel ? begin + MT_CHUNK : numel;
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      const float g = load_as_f32(grad, i, gdtype) * gs;
+      const float mi = a.beta1 * m[i] + (1.f - a.beta1) * g;
+      const float vi = a.beta2 * v[i] + (1.f - a.beta2) * g * g;
+      m[i] = mi; v[i] = vi;
+      const float denom = sqrtf(vi) * inv_sqrt_c2 + a.eps;
+      const float p = master[i] * decay - step * mi / denom;
+      master[i] = p;
+      if (model) model[i] = __float2bfloat16_rn(p);
+    }
+  }
+}
+
+int sm_count(int device);
+static inline int mt_grid(long long chunks) { return (int)(chunks < 148 * 4 ? (chunks < 1 ? 1 : chunks) : 148 * 4); }
+
+}  // namespace axb
+
+using namespace axb;
+
+extern "C" int axb_multi_l2norm_sq(const long long* table, int n, long long total_chunks, float* out, void* stream) {
+  multi_l2norm_sq_kernel<<<mt_grid(total_chunks), MT_THREADS, 0, (cudaStream_t)stream>>>(table, n, total_chunks, out);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+extern "C" int axb_multi_scale(const long long* table, int n, long long total_chunks, const float* scale, void* stream) {
+  multi_scale_kernel<<<mt_grid(total_chunks), MT_THREADS, 0, (cudaStream_t)stream>>>(table, n, total_chunks, scale);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+extern "C" int axb_multi_adamw(const long long* table, int n, long long total_chunks, float lr, float beta1, float beta2,
+                               float eps, float weight_decay, float bias_c1, float bias_c2, const float* grad_scale,
+                               const float* found_inf, void* stream) {
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale, found_inf};
+  multi_adamw_kernel<<<mt_grid(total_chunks), MT_THREADS, 0, (cudaStream_t)stream>>>(table, n, total_chunks, a);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -55,14 +55,17 @@ class Embedding(torch.nn.Module):
         self.outer_group_size = dist.get_world_size(self.outer_group)
         self.depth_group_size = dist.get_world_size(self.depth_group)
         self.transpose, self.expert_mode = transpose, expert_mode
+        # The hidden dimension is split over one group.  In expert mode the table may
+        # additionally be replicated over the other group (its ranks see the same
+        # tokens and the same output gradient, so the replicas stay identical); in
+        # easy mode the other group must have size one, as in the reference
+        # (``embedding.py:110,123``).
         if not transpose:
-            if self.inner_group_size != 1:
-                raise ValueError("Embedding needs G_intra_c == 1 (or transpose=True with G_intra_r == 1)")
-            self.hidden_group = self.outer_group
+            self.hidden_group, other = self.outer_group, self.inner_group_size
         else:
-            if self.outer_group_size != 1:
-                raise ValueError("Embedding(transpose=True) needs G_intra_r == 1")
-            self.hidden_group = self.inner_group
+            self.hidden_group, other = self.inner_group, self.outer_group_size
+        if other != 1 and not expert_mode:
+            raise ValueError("easy-mode Embedding needs the non-hidden tensor-parallel group to have size 1")
         self.local_in_features = num_embeddings
         self.local_out_features = divide(embedding_dim, dist.get_world_size(self.hidden_group))
         self.in_features, self.out_features = num_embeddings, embedding_dim
@@ -80,6 +83,7 @@ class Embedding(torch.nn.Module):
         self.weight.is_tensor_parallel = True
         self.weight.needs_depth_parallel_gradient_sync = False
         self.weight.process_group_for_norm_reduction = ch.intra_layer_group
+        self.weight.norm_reduction_replicas = other
 
     def get_output_feature_size(self):
         return self.local_out_features

@@ -79,10 +79,13 @@ def _gathered_weight(weight, depth_group, local_shape, cache):
 
 
 class AsyncLinear(Function):
-    """``y = x @ W^T`` with the three collectives of 3-D tensor parallelism."""
+    """``y = act(x @ W^T + b)`` with the three collectives of 3-D tensor parallelism.
+
+    ``bias`` and ``activation`` are optional; when the forward all-reduce group has
+    one rank they are applied in the GEMM epilogue, otherwise after the all-reduce."""
 
     @staticmethod
-    def forward(ctx, input_, weight, forward_all_reduce_group, backward_all_reduce_group,
+    def forward(ctx, input_, weight, bias, activation, forward_all_reduce_group, backward_all_reduce_group,
                 depth_parallel_group, local_weight_shape, cache_weights):
         cache = bool(cache_weights) or oc.CACHE_WEIGHTS
         w_shard = weight
@@ -93,29 +96,50 @@ class AsyncLinear(Function):
         w = _gathered_weight(w_shard, depth_parallel_group, local_weight_shape, cache)
         if w.dtype != compute_dtype:
             w = w.to(compute_dtype)
-        ctx.save_for_backward(input_, w_shard)
+        x2 = input_.reshape(-1, input_.shape[-1])
+        inner_n = dist.get_world_size(forward_all_reduce_group)
+        b = None if bias is None else bias.to(compute_dtype)
+        pre_act = None
+        if inner_n == 1 and x2.is_cuda and (b is not None or activation):
+            if activation == "gelu":
+                pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype, device=x2.device)
+                epi = ops.EPI_BIAS_GELU if b is not None else ops.EPI_GELU
+                out = ops.matmul_nt(x2, w, bias=b, epilogue=epi, aux=pre_act)
+            else:
+                out = ops.matmul_nt(x2, w, bias=b, epilogue=ops.EPI_BIAS)
+        else:
+            out = ops.matmul_nt(x2, w)
+            if inner_n > 1:
+                dist.all_reduce(out, group=forward_all_reduce_group)
+            if b is not None:
+                out = out.add_(b)
+            if activation == "gelu":
+                pre_act = out
+                out = ops.gelu(out.detach())
+        if activation not in (None, "gelu"):
+            raise ValueError(f"unsupported fused activation {activation!r}")
+        ctx.save_for_backward(input_, w_shard, pre_act)
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = None if bias is None else bias.dtype
         ctx.backward_all_reduce_group = backward_all_reduce_group
         ctx.depth_parallel_group = depth_parallel_group
         ctx.shape = local_weight_shape
-        ctx.cache = cache
         ctx.compute_dtype = compute_dtype
-        x2 = input_.reshape(-1, input_.shape[-1])
-        out = ops.matmul_nt(x2, w)
-        if dist.get_world_size(forward_all_reduce_group) > 1:
-            dist.all_reduce(out, group=forward_all_reduce_group)
         return out.reshape(*input_.shape[:-1], local_weight_shape[0])
 
     @staticmethod
     def backward(ctx, grad_output):
-        input_, w_shard = ctx.saved_tensors
+        input_, w_shard, pre_act = ctx.saved_tensors
         grad_output = grad_output.to(ctx.compute_dtype)
         go2 = grad_output.reshape(-1, grad_output.shape[-1])
+        if pre_act is not None:
+            go2 = ops.gelu_backward(go2, pre_act)
         x2 = input_.reshape(-1, input_.shape[-1])
         overlap_rs = oc.OVERLAP_REDUCE_SCATTER
         overlap_ar = oc.OVERLAP_ALL_REDUCE
         outer_n = dist.get_world_size(ctx.backward_all_reduce_group)
         depth_n = dist.get_world_size(ctx.depth_parallel_group)
-        grad_input = grad_weight = None
+        grad_input = grad_weight = grad_bias = None
         handle = None
 
         def wgrad():
@@ -142,6 +166,8 @@ class AsyncLinear(Function):
                     handle = dist.all_reduce(grad_input, group=ctx.backward_all_reduce_group, async_op=overlap_ar)
             if ctx.needs_input_grad[1]:
                 grad_weight = wgrad()
+            if ctx.has_bias and ctx.needs_input_grad[2]:
+                grad_bias = go2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
             if handle is not None and overlap_ar:
                 handle.wait()
         else:
@@ -150,9 +176,11 @@ class AsyncLinear(Function):
                 grad_weight = wgrad()
             if ctx.needs_input_grad[0]:
                 grad_input = dgrad()
+            if ctx.has_bias and ctx.needs_input_grad[2]:
+                grad_bias = go2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
         if grad_input is not None:
             grad_input = grad_input.reshape(input_.shape)
-        return grad_input, grad_weight, None, None, None, None, None
+        return grad_input, grad_weight, grad_bias, None, None, None, None, None, None
 
 
 class Linear(torch.nn.Module):
@@ -210,7 +238,10 @@ class Linear(torch.nn.Module):
                 f"grid(inner,outer,depth)=({self.inner_group_size},{self.outer_group_size},"
                 f"{self.depth_group_size}), transpose={self.transpose}, expert_mode={self.expert_mode}")
 
-    def forward(self, x, cache_weights_in_all_gather=False):
+    def forward(self, x, cache_weights_in_all_gather=False, activation=None):
+        """``activation="gelu"`` fuses bias + GELU (tanh form) into the layer; only
+        meaningful when the bias is added inside the layer (expert mode, no
+        ``skip_bias_add``)."""
         lead_shape = x.shape[:-1]
         x = x.reshape(-1, x.shape[-1])
         switch_layout = (not self.expert_mode) and self.inner_group_size * self.outer_group_size > 1
@@ -219,13 +250,17 @@ class Linear(torch.nn.Module):
             x = GatherBatchScatterChannels.apply(x, inner_sizes, self.inner_group)
             outer_sizes = gather_batch_sizes(x.shape[0], self.outer_group, device=x.device)
             x = Gatherv.apply(x, outer_sizes, self.outer_group)
-        x = AsyncLinear.apply(x, self.weight, self.inner_group, self.outer_group, self.depth_group,
-                              self.local_weight_shape, cache_weights_in_all_gather)
+        fuse_bias = self.expert_mode and not self.skip_bias_add
+        if activation is not None and not fuse_bias and self.bias is not None:
+            raise ValueError("activation= needs the bias to be added inside the layer")
+        x = AsyncLinear.apply(x, self.weight, self.bias if fuse_bias else None, activation, self.inner_group,
+                              self.outer_group, self.depth_group, self.local_weight_shape,
+                              cache_weights_in_all_gather)
         if switch_layout:
             x = GatherChannelsScatterBatch.apply(x, outer_sizes, self.outer_group)
             x = Dropv.apply(x, inner_sizes, self.inner_group)
         x = x.reshape(*lead_shape, x.shape[-1])
-        if self.bias is None:
+        if self.bias is None or fuse_bias:
             return x
         bias = self.bias
         if not self.expert_mode:

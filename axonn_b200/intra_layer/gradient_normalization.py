@@ -42,12 +42,17 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2.0, error_if_nonfinite=Fals
         if getattr(p, "is_tensor_parallel", False):
             assert hasattr(p, "process_group_for_norm_reduction"), (
                 "tensor-parallel parameters need process_group_for_norm_reduction")
-            by_group[p.process_group_for_norm_reduction].append(p.grad)
+            # a shard that is held by several ranks of its reduction group (e.g. an
+            # embedding replicated over the row group) must count once
+            replicas = int(getattr(p, "norm_reduction_replicas", 1))
+            by_group[(p.process_group_for_norm_reduction, replicas)].append(p.grad)
         else:
             plain.append(p.grad)
     pieces = []
-    for group, grads in by_group.items():
+    for (group, replicas), grads in by_group.items():
         v = _local_norm_pow(grads, norm_type)
+        if replicas > 1 and norm_type != inf:
+            v = v / replicas
         if dist.get_world_size(group) > 1:
             dist.all_reduce(v, op=dist.ReduceOp.MAX if norm_type == inf else dist.ReduceOp.SUM, group=group)
         pieces.append(v)

@@ -1,0 +1,169 @@
+"""Tensor-parallel transformer building blocks (expert-mode layout).
+
+Activation layout between blocks: ``[batch_local, seq, hidden / G_c]`` — the
+hidden dimension is split over the column ("inner") group, the batch over the
+depth and data groups, and everything is replicated over the row group.  A
+non-transposed ``Linear`` consumes that layout and produces features split
+over the row group; a transposed ``Linear`` maps back.  Attention heads are
+therefore split over the row group, and normalisation layers reduce their row
+statistics over the column group.
+
+These modules replace the HF monkey patches of the reference
+(``axonn/models/transformers/modify_*.py``) and Megatron's ``ParallelTransformer``
+used by ``external/models/nvidia_transformer.py``.
+"""
+
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import axonn as ax
+from .. import ops
+from ..intra_layer import Embedding, Linear
+from ..utils import divide
+
+
+def _groups():
+    ch = ax.comm_handle
+    return ch.inner_intra_layer_parallel_group, ch.outer_intra_layer_parallel_group
+
+
+def _tag_sharded(param, shard_group):
+    """Bookkeeping for a parameter sharded over ``shard_group`` and replicated over depth."""
+    param.is_tensor_parallel = True
+    param.needs_depth_parallel_gradient_sync = True
+    param.process_group_for_norm_reduction = shard_group
+    return param
+
+
+class TPNorm(nn.Module):
+    """LayerNorm / RMSNorm whose hidden dimension is split over the column group."""
+
+    def __init__(self, hidden, eps=1e-5, rms=False, dtype=None):
+        super().__init__()
+        inner, _ = _groups()
+        self.group = inner if dist.get_world_size(inner) > 1 else None
+        self.local = divide(hidden, dist.get_world_size(inner))
+        dev = ax.config.device
+        self.weight = nn.Parameter(torch.ones(self.local, dtype=dtype, device=dev))
+        self.bias = None if rms else nn.Parameter(torch.zeros(self.local, dtype=dtype, device=dev))
+        self.eps, self.rms = eps, rms
+        for p in self.parameters():
+            _tag_sharded(p, inner)
+
+    def forward(self, x):
+        if self.rms:
+            return ops.rms_norm(x, self.weight, self.eps, self.group)
+        return ops.layer_norm(x, self.weight, self.bias, self.eps, self.group)
+
+
+class ParallelAttention(nn.Module):
+    """Causal self-attention; KV groups (a KV head with its query heads) are split
+    over the row group.
+
+    The fused projection's output features are ordered group by group:
+    ``[q heads of group 0 | k_0 | v_0 | q heads of group 1 | k_1 | v_1 | ...]``, so a
+    contiguous slice of the rows of the weight holds whole groups and the model
+    is the same function for every tensor-parallel degree."""
+
+    def __init__(self, hidden, n_heads, n_kv_heads=None, bias=True, rope_theta=None, max_seq=4096, dtype=None,
+                 init_std=0.02, out_init_std=None):
+        super().__init__()
+        _, outer = _groups()
+        r = dist.get_world_size(outer)
+        n_kv_heads = n_kv_heads or n_heads
+        self.head_dim = divide(hidden, n_heads)
+        self.q_per_kv = divide(n_heads, n_kv_heads)
+        self.groups_l = divide(n_kv_heads, r)
+        self.rope_theta, self.max_seq = rope_theta, max_seq
+        qkv_out = (n_heads + 2 * n_kv_heads) * self.head_dim
+        self.qkv = Linear(hidden, qkv_out, bias=bias, expert_mode=True, dtype=dtype,
+                          init_method=lambda w: nn.init.normal_(w, std=init_std))
+        self.proj = Linear(n_heads * self.head_dim, hidden, bias=bias, expert_mode=True, transpose=True,
+                           init_method=lambda w: nn.init.normal_(w, std=out_init_std or init_std), dtype=dtype)
+
+    def forward(self, x):
+        B, S, _ = x.shape
+        D, G, qpk = self.head_dim, self.groups_l, self.q_per_kv
+        qkv = self.qkv(x).view(B, S, G, qpk + 2, D)
+        if self.rope_theta is not None:
+            table = ops.rope_table(max(S, self.max_seq), D, self.rope_theta, x.device)
+            if x.is_cuda:
+                ops.apply_rope(qkv[:, :, :, :qpk + 1], table)  # q heads and the k head, in place
+            else:
+                qkv = torch.cat([ops.apply_rope(qkv[:, :, :, :qpk + 1], table), qkv[:, :, :, qpk + 1:]], 3)
+        o = ops.flash_attention_packed(qkv, causal=True)  # [B, S, G * qpk, D]
+        return self.proj(o.reshape(B, S, G * qpk * D))
+
+
+class ParallelMLP(nn.Module):
+    """``fc2(act(fc1(x)))`` with GELU, or SwiGLU with a fused gate|up projection."""
+
+    def __init__(self, hidden, ffn, activation="gelu", bias=True, dtype=None, init_std=0.02, out_init_std=None):
+        super().__init__()
+        self.activation = activation
+        mult = 2 if activation == "swiglu" else 1
+        _, outer = _groups()
+        self.ffn_l = divide(ffn, dist.get_world_size(outer))
+        # SwiGLU: gate and up rows are interleaved in blocks of 8 (see ops.swiglu), so any
+        # contiguous row slice of the fused weight is self-contained
+        self.fc1 = Linear(hidden, mult * ffn, bias=bias, expert_mode=True, dtype=dtype,
+                          init_method=lambda w: nn.init.normal_(w, std=init_std))
+        self.fc2 = Linear(ffn, hidden, bias=bias, expert_mode=True, transpose=True, dtype=dtype,
+                          init_method=lambda w: nn.init.normal_(w, std=out_init_std or init_std))
+
+    def forward(self, x):
+        if self.activation == "swiglu":
+            return self.fc2(ops.swiglu(self.fc1(x)))
+        return self.fc2(self.fc1(x, activation="gelu"))
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, hidden, n_heads, ffn, n_kv_heads=None, activation="gelu", rms=False, bias=True,
+                 rope_theta=None, max_seq=4096, eps=1e-5, dtype=None, n_layers=1):
+        super().__init__()
+        out_std = 0.02 / math.sqrt(2 * n_layers)
+        self.norm1 = TPNorm(hidden, eps, rms, dtype)
+        self.attn = ParallelAttention(hidden, n_heads, n_kv_heads, bias, rope_theta, max_seq, dtype,
+                                      out_init_std=out_std)
+        self.norm2 = TPNorm(hidden, eps, rms, dtype)
+        self.mlp = self._make_mlp(hidden, ffn, activation, bias, dtype, out_std)
+
+    def _make_mlp(self, hidden, ffn, activation, bias, dtype, out_std):
+        return ParallelMLP(hidden, ffn, activation, bias, dtype, out_init_std=out_std)
+
+    def forward(self, x):
+        x = x + self.attn(self.norm1(x))
+        return x + self.mlp(self.norm2(x))
+
+
+class ParallelLMHead(nn.Module):
+    """Final projection to a vocabulary split over the row group + parallel cross-entropy."""
+
+    def __init__(self, hidden, vocab, dtype=None):
+        super().__init__()
+        _, outer = _groups()
+        self.group = outer if dist.get_world_size(outer) > 1 else None
+        self.proj = Linear(hidden, vocab, bias=False, expert_mode=True, dtype=dtype,
+                           init_method=lambda w: nn.init.normal_(w, std=0.02))
+
+    def forward(self, x, targets=None):
+        logits = self.proj(x)
+        if targets is None:
+            return logits
+        return ops.cross_entropy(logits, targets, group=self.group)
+
+
+def count_parameters(module, local=False):
+    """Global (or local) parameter count of a tensor-parallel module."""
+    total = 0
+    for p in module.parameters():
+        n = p.numel()
+        if not local and getattr(p, "is_tensor_parallel", False):
+            g = getattr(p, "process_group_for_norm_reduction", None)
+            if g is not None:
+                n *= dist.get_world_size(g)
+        total += n
+    return total

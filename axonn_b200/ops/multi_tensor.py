@@ -16,23 +16,24 @@ from . import _lib
 _CHUNK = 1 << 16
 
 
+_DT_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
 class _PtrTable:
-    """Device table {pointer, numel, dtype} for a list of tensors."""
+    """Device table {pointer, numel, dtype, chunk prefix} for a list of tensors."""
 
     def __init__(self, tensors):
         dev = tensors[0].device
-        n = len(tensors)
-        host = torch.empty((n, 3), dtype=torch.int64, pin_memory=True)
-        code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
-        for i, t in enumerate(tensors):
+        rows, prefix = [], 0
+        for t in tensors:
             assert t.is_contiguous(), "multi-tensor ops need contiguous tensors"
-            host[i, 0] = t.data_ptr()
-            host[i, 1] = t.numel()
-            host[i, 2] = code[t.dtype]
-        self.n = n
-        self.dev = host.to(dev, non_blocking=True)
-        self.host = host
-        self.blocks = sum((t.numel() + _CHUNK - 1) // _CHUNK for t in tensors)
+            rows.append((t.data_ptr(), t.numel(), _DT_CODE[t.dtype], prefix))
+            prefix += (t.numel() + _CHUNK - 1) // _CHUNK
+        self.n = len(rows)
+        self.total_chunks = prefix
+        self.host = torch.tensor(rows, dtype=torch.int64).pin_memory()
+        self.dev = self.host.to(dev, non_blocking=True)
+        self.keep = tensors
 
 
 def multi_tensor_l2norm_sq(tensors):
@@ -43,8 +44,8 @@ def multi_tensor_l2norm_sq(tensors):
     if tensors[0].is_cuda:
         tab = _PtrTable(tensors)
         out = torch.zeros((), dtype=torch.float32, device=tensors[0].device)
-        st = _lib.lib().axb_multi_l2norm_sq(_lib.ptr(tab.dev), ctypes.c_int(tab.n), _lib.ptr(out),
-                                            _lib.stream_ptr())
+        st = _lib.lib().axb_multi_l2norm_sq(_lib.ptr(tab.dev), ctypes.c_int(tab.n),
+                                            ctypes.c_longlong(tab.total_chunks), _lib.ptr(out), _lib.stream_ptr())
         _lib.check(st, "axb_multi_l2norm_sq")
         return out
     return torch.stack([t.detach().float().pow(2).sum() for t in tensors]).sum()
@@ -62,8 +63,8 @@ def multi_tensor_scale_(tensors, scale):
             scale = torch.tensor(float(scale), dtype=torch.float32, device=tensors[0].device)
         else:
             scale = scale.to(device=tensors[0].device, dtype=torch.float32)
-        st = _lib.lib().axb_multi_scale(_lib.ptr(tab.dev), ctypes.c_int(tab.n), _lib.ptr(scale),
-                                        _lib.stream_ptr())
+        st = _lib.lib().axb_multi_scale(_lib.ptr(tab.dev), ctypes.c_int(tab.n),
+                                        ctypes.c_longlong(tab.total_chunks), _lib.ptr(scale), _lib.stream_ptr())
         _lib.check(st, "axb_multi_scale")
         return
     for t in tensors:

@@ -1,0 +1,116 @@
+"""Training-step driver for models without pipelining (``G_inter == 1``).
+
+``Trainer.train_step(tokens, targets)`` is the call a user makes once per
+optimizer step.  It takes this rank's batch (host tensors, ideally pinned),
+copies it to the GPU, runs forward/backward over microbatches inside
+``optimize_communication`` with gradient synchronisation deferred to the last
+microbatch, optionally prunes gradients (top-k by magnitude), synchronises and
+clips them, steps the optimizer and returns the mean loss as a Python float.
+
+It packages the loop the reference leaves to user scripts and to its Lightning
+strategy (``axonn/lightning/axonn_strategy.py:148-164,241-256``).
+"""
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import axonn as ax
+from . import ops
+from .intra_layer import (clip_grad_norm_, no_grad_sync, optimize_communication,
+                          overlap_all_gathers_for_checkpointed_forward, sync_gradients)
+
+
+class Trainer:
+    def __init__(self, model, optimizer, micro_batch_size: Optional[int] = None, clip_grad: float = 0.0,
+                 prune_keep_fraction: Optional[float] = None, overlap: bool = True,
+                 loss_fn: Optional[Callable] = None, expert_mode: bool = True):
+        assert ax.is_initialized
+        if ax.config.G_inter != 1:
+            raise ValueError("Trainer drives non-pipelined models; use AxoNN_Inter_Layer_Engine for G_inter > 1")
+        self.model, self.optimizer = model, optimizer
+        self.micro_batch_size = micro_batch_size
+        self.clip_grad = clip_grad
+        self.prune_keep_fraction = prune_keep_fraction
+        self.overlap = overlap
+        self.loss_fn = loss_fn
+        self.expert_mode = expert_mode
+        self.device = ax.comm_handle.device
+        self._params = [p for p in model.parameters() if p.requires_grad]
+        self._reversed_modules = list(model.modules())[::-1]
+
+    # ------------------------------------------------------------------ pieces
+    def _to_device(self, t):
+        if t.device == self.device:
+            return t
+        return t.to(self.device, non_blocking=True)
+
+    def _forward_loss(self, inputs, targets):
+        if self.loss_fn is None:
+            return self.model(inputs, targets)
+        return self.loss_fn(self.model(inputs), targets)
+
+    def forward_backward(self, inputs, targets):
+        """Microbatched forward/backward on device tensors; returns the mean loss
+        as a 0-d device tensor.  Gradients are left unsynchronised."""
+        B = inputs.shape[0]
+        mbs = self.micro_batch_size or B
+        n_micro = max(1, B // mbs)
+        total = None
+        for i in range(n_micro):
+            x, y = inputs[i * mbs:(i + 1) * mbs], targets[i * mbs:(i + 1) * mbs]
+            with optimize_communication(overlap_all_reduce=self.overlap, overlap_reduce_scatter=self.overlap,
+                                        cache_weights=False, overlap_all_gather=self.overlap,
+                                        model_object_for_overlapping_allgathers=self.model):
+                loss = self._forward_loss(x, y)
+                # backward consumes the layers in reverse: prefetch depth all-gathers in that order
+                with overlap_all_gathers_for_checkpointed_forward(self._reversed_modules):
+                    (loss / n_micro).backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        return total / n_micro
+
+    def finish_step(self):
+        """Prune (optional), synchronise, clip (optional) and apply gradients."""
+        if self.prune_keep_fraction is not None:
+            for p in self._params:
+                if p.grad is not None and p.grad.numel() >= 1024:
+                    ops.prune_topk_(p.grad, self.prune_keep_fraction)
+        sync_gradients(self.model, mean=True, expert_mode=self.expert_mode)
+        if self.clip_grad and self.clip_grad > 0:
+            clip_grad_norm_(self._params, self.clip_grad)
+        self.optimizer.step()
+        self.optimizer.zero_grad(set_to_none=True)
+
+    # ------------------------------------------------------------------ public step
+    def train_step_device(self, inputs, targets):
+        """One optimizer step on tensors that already live on the device; returns a
+        0-d device tensor (no host synchronisation)."""
+        self.model.train()
+        with no_grad_sync():
+            loss = self.forward_backward(inputs, targets)
+        self.finish_step()
+        return loss
+
+    def train_step(self, inputs, targets) -> float:
+        """One optimizer step from host tensors; returns the loss as a float."""
+        loss = self.train_step_device(self._to_device(inputs), self._to_device(targets))
+        return float(loss.item())
+
+
+def replica_index() -> int:
+    """Index of this rank's data shard: ranks that differ only in row/column
+    coordinates consume the same samples."""
+    c = ax.config
+    return c.data_parallel_rank * c.G_intra_d + c.intra_layer_depth_parallel_rank
+
+
+def num_replicas() -> int:
+    return ax.config.G_data * ax.config.G_intra_d
+
+
+def all_reduce_max(value: float, device) -> float:
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
