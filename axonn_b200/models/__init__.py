@@ -3,3 +3,5 @@
 from .gpt import GPT, GPTConfig  # noqa: F401
 from .llama import Llama, LlamaConfig  # noqa: F401
 from .mlp import MLP  # noqa: F401
+from .vgg import DistributedVGG16  # noqa: F401
+from .vit import DistributedViT  # noqa: F401

@@ -1,0 +1,96 @@
+"""Pipeline engine on CPU ranks: a ViT trained with G_inter=2 must follow the
+same loss curve as with G_inter=1, data parallelism must compose with it, and
+eval mode must not change the weights (pattern of the reference's
+``axonn/tests/test_vit.py``, without the MNIST download)."""
+
+import pytest
+import torch
+
+from _dist import run_distributed
+
+
+def _vit_run(rank, world, G_inter, G_data, steps, dtype_name):
+    import torch.distributed as dist
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200.inter_layer import AxoNN_Inter_Layer_Engine
+    from axonn_b200.models import DistributedViT
+
+    ax.init(G_inter=G_inter, G_data=G_data)
+    dtype = getattr(torch, dtype_name)
+    # build every stage with the same RNG stream so that all layouts share weights
+    stages = []
+    for s in range(G_inter):
+        torch.manual_seed(100)
+        full = [DistributedViT(image_size=16, patch_size=4, num_classes=10, dim=32, depth=4, heads=4,
+                               mlp_dim=64, channels=1, G_inter=1, stage=0)]
+        stages.append(full[0])
+    full = stages[0]
+    mine = DistributedViT(image_size=16, patch_size=4, num_classes=10, dim=32, depth=4, heads=4, mlp_dim=64,
+                          channels=1)
+    # copy the matching slice of the single-stage model
+    sd = full.state_dict()
+    per = 4 // G_inter
+    stage = ax.config.inter_layer_parallel_rank
+    new = {}
+    for k, v in sd.items():
+        if k.startswith("layers."):
+            idx = int(k.split(".")[1])
+            if stage * per <= idx < (stage + 1) * per:
+                new["layers.%d.%s" % (idx - stage * per, k.split(".", 2)[2])] = v
+        elif k in mine.state_dict():
+            new[k] = v
+    mine.load_state_dict(new)
+    opt = torch.optim.SGD(mine.parameters(), lr=0.05)
+    engine = AxoNN_Inter_Layer_Engine(mine, torch.nn.functional.cross_entropy, computation_dtype=dtype)
+    ax.config.micro_batch_size = 4
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(16, 1, 16, 16, generator=g)
+    Y = torch.randint(0, 10, (16,), generator=g)
+    per_dp = 16 // G_data
+    dp = ax.config.data_parallel_rank
+    xb, yb = X[dp * per_dp:(dp + 1) * per_dp], Y[dp * per_dp:(dp + 1) * per_dp]
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        losses.append(engine.forward_backward_optimizer(xb, yb, opt))
+    ev = engine.forward_backward_optimizer(xb, yb, opt, eval_mode=True)
+    # the loss lives on the last stage; average it over data-parallel replicas
+    t = torch.tensor(losses + [ev], dtype=torch.float64)
+    if ax.config.inter_layer_parallel_rank != G_inter - 1:
+        t.zero_()
+    dist.all_reduce(t)
+    return (t / G_data).tolist()
+
+
+def test_pipeline_matches_single_stage_fp32():
+    ref = run_distributed(_vit_run, 1, 1, 1, 4, "float32")[0]
+    two = run_distributed(_vit_run, 2, 2, 1, 4, "float32")[0]
+    assert two == pytest.approx(ref, rel=1e-5)
+    assert ref[3] < ref[0]
+    four = run_distributed(_vit_run, 4, 2, 2, 4, "float32")[0]
+    assert four == pytest.approx(ref, rel=1e-4)
+
+
+def test_pipeline_four_stages_bf16_trains():
+    out = run_distributed(_vit_run, 4, 4, 1, 6, "bfloat16")[0]
+    assert out[5] < out[0]
+
+
+def test_vgg_partition_and_shapes():
+    from axonn_b200.models.vgg import DistributedVGG16, _units, partition
+
+    units = _units(224, 1000)
+    assert len(units) == 16 and sum(1 for _ in units) == 13 + 3
+    b = partition([u[2] for u in units], 4)
+    assert b[0] == 0 and b[-1] == 16 and sorted(b) == b and len(b) == 5
+    prev_out = None
+    x = torch.randn(2, 3, 32, 32)
+    for s in range(4):
+        m = DistributedVGG16(image_size=32, num_classes=10, G_inter=4, stage=s)
+        if prev_out is not None:
+            assert m.get_input_shape()[1:] == prev_out
+        x = m(x)
+        assert list(x.shape[1:]) == m.get_output_shape()[1:]
+        prev_out = m.get_output_shape()[1:]
+    assert x.shape == (2, 10)

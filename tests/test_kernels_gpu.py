@@ -1,0 +1,168 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same operation."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _close(a, b, rel, abs_=1e-3):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    assert err <= rel * b.abs().max().item() + abs_, f"max err {err} vs scale {b.abs().max().item()}"
+
+
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("shape", [(512, 2048), (333, 1024), (64, 4096), (1000, 256)])
+def test_norm_fwd_bwd(rms, shape):
+    from axonn_b200 import ops
+
+    torch.manual_seed(0)
+    rows, H = shape
+    x = torch.randn(rows, H, device=DEV).bfloat16().requires_grad_(True)
+    g = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True)
+    b = (0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True)
+    dy = torch.randn(rows, H, device=DEV).bfloat16()
+    y = ops.rms_norm(x, g, 1e-5) if rms else ops.layer_norm(x, g, b, 1e-5)
+    y.backward(dy)
+    xr, gr, br = (t.detach().float().requires_grad_(True) for t in (x, g, b))
+    if rms:
+        yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * gr
+    else:
+        yr = F.layer_norm(xr, (H,), gr, br, 1e-5)
+    yr.backward(dy.float())
+    _close(y, yr, 1e-2)
+    _close(x.grad, xr.grad, 2e-2)
+    _close(g.grad, gr.grad, 2e-2, 5e-2)
+    if not rms:
+        _close(b.grad, br.grad, 2e-2, 5e-2)
+
+
+def test_gelu_swiglu():
+    from axonn_b200 import ops
+    from axonn_b200.ops.activation import _split_gu
+
+    torch.manual_seed(1)
+    x = torch.randn(257, 1024, device=DEV).bfloat16().requires_grad_(True)
+    dy = torch.randn_like(x)
+    y = ops.gelu(x)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    yr = F.gelu(xr, approximate="tanh")
+    yr.backward(dy.float())
+    _close(y, yr, 1e-2)
+    _close(x.grad, xr.grad, 1e-2)
+
+    gu = torch.randn(130, 2 * 512, device=DEV).bfloat16().requires_grad_(True)
+    do = torch.randn(130, 512, device=DEV).bfloat16()
+    o = ops.swiglu(gu)
+    o.backward(do)
+    gur = gu.detach().float().requires_grad_(True)
+    gg, uu = _split_gu(gur)
+    orf = F.silu(gg) * uu
+    orf.backward(do.float())
+    _close(o, orf, 1e-2)
+    _close(gu.grad, gur.grad, 1e-2)
+
+
+def test_rope_matches_reference_and_inverts():
+    from axonn_b200 import ops
+    from axonn_b200.ops.rope import _rope_torch
+
+    torch.manual_seed(2)
+    B, S, G, n, D = 2, 96, 3, 4, 128
+    table = ops.rope_table(S, D, 500000.0, torch.device(DEV))
+    qkv = torch.randn(B, S, G, n + 2, D, device=DEV).bfloat16()
+    ref = _rope_torch(qkv[:, :, :, : n + 1].float().cpu(), table.cpu(), False)
+    src = qkv.clone().requires_grad_(True)
+    work = src * 1.0
+    ops.apply_rope(work[:, :, :, : n + 1], table)
+    _close(work[:, :, :, : n + 1].cpu(), ref, 1e-2)
+    assert torch.equal(work[:, :, :, n + 1], qkv[:, :, :, n + 1])  # v untouched
+    # backward is the inverse rotation
+    gout = torch.randn_like(work)
+    work.backward(gout)
+    gref = gout.clone().float().cpu()
+    gref[:, :, :, : n + 1] = _rope_torch(gref[:, :, :, : n + 1], table.cpu(), True)
+    _close(src.grad.cpu(), gref, 1e-2)
+    # 4-D form
+    q = torch.randn(B, S, 8, 64, device=DEV).bfloat16()
+    t64 = ops.rope_table(S, 64, 10000.0, torch.device(DEV))
+    r4 = _rope_torch(q.float().cpu(), t64.cpu(), False)
+    q2 = (q * 1.0)
+    from axonn_b200.ops.rope import _rope_apply
+    _rope_apply(q2, t64, False)
+    _close(q2.cpu(), r4, 1e-2)
+
+
+@pytest.mark.parametrize("V", [512, 50304 // 2])
+def test_cross_entropy(V):
+    from axonn_b200 import ops
+
+    torch.manual_seed(3)
+    rows = 300
+    z = (torch.randn(rows, V, device=DEV) * 2).bfloat16()
+    t = torch.randint(0, V, (rows,), device=DEV)
+    t[5] = -100
+    zr = z.float().requires_grad_(True)
+    lr = F.cross_entropy(zr, t, ignore_index=-100)
+    lr.backward()
+    zz = z.clone().requires_grad_(True)
+    zin = zz * 1.0
+    loss = ops.cross_entropy(zin, t)
+    loss.backward()
+    assert abs(loss.item() - lr.item()) < 2e-3 * abs(lr.item())
+    _close(zz.grad, zr.grad, 2e-2, 1e-5)
+
+
+def test_fused_adamw_matches_torch():
+    from axonn_b200.optim import FusedAdamW
+
+    torch.manual_seed(4)
+    shapes = [(1000,), (257, 33), (70000,), (8,)]
+    ps = [torch.randn(s, device=DEV).bfloat16().requires_grad_(True) for s in shapes]
+    ref = [p.detach().float().clone().requires_grad_(True) for p in ps]
+    opt = FusedAdamW(ps, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ropt = torch.optim.AdamW(ref, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for _ in range(4):
+        for p, r in zip(ps, ref):
+            g = torch.randn_like(r)
+            p.grad = g.bfloat16()
+            r.grad = g.bfloat16().float()
+        opt.step()
+        ropt.step()
+    for p, r in zip(ps, ref):
+        _close(opt.state[p]["master"], r, 1e-5, 1e-6)
+        _close(p, r, 1e-2)
+
+
+def test_multi_tensor_norm_and_scale():
+    from axonn_b200 import ops
+
+    torch.manual_seed(5)
+    ts = [torch.randn(n, device=DEV).to(dt) for n, dt in
+          [(100000, torch.bfloat16), (7, torch.float32), (65537, torch.float32), (131072, torch.bfloat16)]]
+    got = ops.multi_tensor_l2norm_sq(ts).item()
+    want = sum(t.float().pow(2).sum().item() for t in ts)
+    assert abs(got - want) <= 1e-4 * want
+    before = [t.clone() for t in ts]
+    ops.multi_tensor_scale_(ts, 0.5)
+    for a, b in zip(ts, before):
+        _close(a, b.float() * 0.5, 1e-2, 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [4096, 1_000_003, 14336 * 512])
+def test_prune_topk(dtype, n):
+    from axonn_b200 import ops
+
+    torch.manual_seed(6)
+    g = torch.randn(n, device=DEV).to(dtype)
+    k = max(1, int(round(n * 0.1)))
+    ref = g.clone()
+    thr = ref.abs().float().kthvalue(n - k + 1).values
+    ref = ref * (ref.abs().float() >= thr).to(dtype)
+    out = ops.prune_topk_(g.clone(), 0.1)
+    assert torch.equal(out, ref), f"kept {(out != 0).sum().item()} vs {(ref != 0).sum().item()}"

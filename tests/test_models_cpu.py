@@ -23,7 +23,7 @@ def _train(rank, world, grid, family, steps):
     else:
         cfg = LlamaConfig.tiny()
         model = Llama(cfg, dtype=torch.float32)
-    opt = FusedAdamW(model.parameters(), lr=1e-2, weight_decay=0.0)
+    opt = FusedAdamW(model.parameters(), lr=2e-3, weight_decay=0.0)
     tr = Trainer(model, opt, micro_batch_size=2, clip_grad=1.0)
     g = torch.Generator().manual_seed(7)
     B = 8
