@@ -66,6 +66,9 @@ def init(
     from .parallel import symm as _symm
 
     _symm.reset()
+    from .parallel import fused as _fused
+
+    _fused.reset()
 
 
 def finalize() -> None:

@@ -29,6 +29,29 @@ int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias
              int M, int N, int K, int in_dtype, int out_dtype, int epilogue, int accumulate,
              int device, void* stream);
 
+/* Peer-memory context of the fused GEMM + all-reduce epilogue.  All pointers are device addresses:
+ * the *_local ones in this rank's symmetric buffer, the *_peer[j] ones the same regions of rank j mapped
+ * into this process.  Inboxes and flag arrays are indexed [source rank][slot]; `epoch` increases by one per
+ * call on the group and selects (by parity, done by the caller) which of two inbox/flag sets is used. */
+typedef struct AxbArCtx {
+  int n;                      /* ranks in the group (2..8) */
+  int rank;                   /* this rank's index in the group */
+  unsigned int epoch;         /* call sequence number (>= 2) */
+  int bn;                     /* tile width all ranks agreed on: 128 or 256 */
+  void* inbox_local;          /* my inbox: partial tiles written by peers */
+  void* inbox_peer[8];        /* peer j's inbox */
+  unsigned int* flags_local;  /* per (source, tile, warp) arrival flags written by peers */
+  unsigned int* flags_peer[8];
+  unsigned int* done_local;   /* [source] last call the peer has completed */
+  unsigned int* done_peer[8];
+  unsigned int* counter;      /* local CTA completion counter (zero between calls) */
+  unsigned long long inbox_vecs_per_src; /* 16-byte words per source in an inbox */
+  unsigned long long flags_per_src;      /* flags per source */
+} AxbArCtx;
+
+int axb_gemm_ar(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N, int K,
+                int in_dtype, int out_dtype, int epilogue, int device, void* stream, const AxbArCtx* ar);
+
 #ifdef __cplusplus
 }
 #endif

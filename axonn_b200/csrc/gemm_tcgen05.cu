@@ -45,6 +45,7 @@ struct GemmParams {
   int accumulate;
   unsigned int* status;
   unsigned long long timeout_ns;
+  AxbArCtx ar;  // ar.n <= 1: plain GEMM; otherwise the epilogue all-reduces C over ar.n ranks
 };
 
 template <int BN>
@@ -134,6 +135,30 @@ __device__ __forceinline__ void store_row32(void* base, int out_dtype, size_t ro
   }
 }
 
+// ---- peer-memory helpers of the fused all-reduce epilogue
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded spin until *flag >= want (flags are monotonically increasing epochs).
+__device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned int want, volatile int* abort_flag,
+                                             uint64_t timeout_ns) {
+  uint64_t start = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (static_cast<int>(ld_acquire_sys(flag) - want) >= 0) return true;
+    if ((it & 0x3f) == 0x3f) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (start == 0) start = now;
+      else if (now - start > timeout_ns) { *abort_flag = 1; return false; }
+    }
+  }
+}
+
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -167,6 +192,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (p.ar.n > 1 && threadIdx.x == 64) {
+    // The inbox (double-buffered by call parity) was last read by the peers in call epoch-2:
+    // do not overwrite it before they are done with that call.
+    for (int j = 0; j < p.ar.n; ++j) {
+      if (j == p.ar.rank) continue;
+      if (!wait_flag_ge(p.ar.done_local + j, p.ar.epoch - 2u, abort_flag, timeout)) {
+        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x108u;
+        break;
+      }
+    }
+  }
+  if (p.ar.n > 1) __syncthreads();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -262,6 +300,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const size_t row = static_cast<size_t>(tm) * BM + q * 32 + lane;
       const bool row_ok = row < static_cast<size_t>(p.M);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      // slot of this (tile, warp) in every inbox: [chunk][vec 0..3][lane] 16-byte words
+      const size_t slot_vec = (static_cast<size_t>(tile) * 4 + q) * (BN / 32) * 4 * 32;
+      if (p.ar.n > 1) {
+        // ---- phase A: push this warp's bf16 partial (32 rows x BN cols) into every peer's inbox
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (tn * BN + c * 32 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          uint4 w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            w[i].x = pack2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]), p.in_dtype);
+            w[i].y = pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]), p.in_dtype);
+            w[i].z = pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]), p.in_dtype);
+            w[i].w = pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]), p.in_dtype);
+          }
+          for (int j = 0; j < p.ar.n; ++j) {
+            if (j == p.ar.rank) continue;
+            uint4* dst = reinterpret_cast<uint4*>(p.ar.inbox_peer[j]) +
+                         static_cast<size_t>(p.ar.rank) * p.ar.inbox_vecs_per_src + slot_vec + (c * 4) * 32 + lane;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i * 32] = w[i];
+          }
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          for (int j = 0; j < p.ar.n; ++j) {
+            if (j == p.ar.rank) continue;
+            st_release_sys(p.ar.flags_peer[j] + static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + q,
+                           p.ar.epoch);
+          }
+          // ---- phase B: wait for every peer's partial of the same (tile, warp)
+          for (int j = 0; j < p.ar.n && ok; ++j) {
+            if (j == p.ar.rank) continue;
+            ok = wait_flag_ge(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q,
+                              p.ar.epoch, abort_flag, timeout);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col = tn * BN + c * 32;
@@ -272,6 +354,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        if (p.ar.n > 1) {
+          // sum the bf16-rounded partials of all ranks in rank order: every rank gets the same bits
+          float acc[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+          for (int j = 0; j < p.ar.n; ++j) {
+            if (j == p.ar.rank) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                float a, b;
+                unpack2(pack2(v[2 * i], v[2 * i + 1], p.in_dtype), p.in_dtype, a, b);
+                acc[2 * i] += a; acc[2 * i + 1] += b;
+              }
+            } else {
+              const uint4* src = reinterpret_cast<const uint4*>(p.ar.inbox_local) +
+                                 static_cast<size_t>(j) * p.ar.inbox_vecs_per_src + slot_vec + (c * 4) * 32 + lane;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint4 u = __ldcv(src + i * 32);
+                float a, b;
+                unpack2(u.x, p.in_dtype, a, b); acc[8 * i + 0] += a; acc[8 * i + 1] += b;
+                unpack2(u.y, p.in_dtype, a, b); acc[8 * i + 2] += a; acc[8 * i + 3] += b;
+                unpack2(u.z, p.in_dtype, a, b); acc[8 * i + 4] += a; acc[8 * i + 5] += b;
+                unpack2(u.w, p.in_dtype, a, b); acc[8 * i + 6] += a; acc[8 * i + 7] += b;
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = acc[i];
+        }
         if (p.epilogue == 1 || p.epilogue == 2) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -300,6 +412,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+  if (p.ar.n > 1 && threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.ar.counter, 1u) == gridDim.x - 1) {
+      *p.ar.counter = 0;
+      __threadfence_system();
+      for (int j = 0; j < p.ar.n; ++j)
+        if (j != p.ar.rank) st_release_sys(p.ar.done_peer[j] + p.ar.rank, p.ar.epoch);
+    }
+  }
 }
 
 // ----------------------------------------------------------------------------- host side
@@ -370,8 +491,9 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
 
 }  // namespace axb
 
-extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,
-                        int K, int in_dtype, int out_dtype, int epilogue, int accumulate, int device, void* stream) {
+static int gemm_common(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,
+                       int K, int in_dtype, int out_dtype, int epilogue, int accumulate, int device, void* stream,
+                       const AxbArCtx* ar) {
   using namespace axb;
   if (M <= 0 || N <= 0 || K <= 0) { set_error("axb_gemm: empty problem"); return -1; }
   if (layout < 0 || layout > 2) { set_error("axb_gemm: bad layout %d", layout); return -1; }
@@ -383,7 +505,7 @@ extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const
 
   const int tiles_m = (M + BM - 1) / BM;
   const bool wide = static_cast<long long>(tiles_m) * ((N + 255) / 256) >= sm_count(device);
-  const int BN = wide ? 256 : 128;
+  const int BN = (ar && ar->n > 1) ? ar->bn : (wide ? 256 : 128);
   const int a_mn = (layout == 2) ? 1 : 0;
   const int b_mn = (layout == 0) ? 0 : 1;
 
@@ -398,6 +520,16 @@ extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const
   p.C = C; p.bias = bias; p.aux = aux; p.M = M; p.N = N; p.K = K;
   p.out_dtype = out_dtype; p.in_dtype = in_dtype; p.epilogue = epilogue; p.accumulate = accumulate;
   p.status = status_dev; p.timeout_ns = 2000000000ull;
+  if (ar && ar->n > 1) {
+    p.ar = *ar;
+    const long long tiles = static_cast<long long>(tiles_m) * ((N + BN - 1) / BN);
+    if (tiles * 4 > ar->flags_per_src || tiles * 4 * (BN / 32) * 128 > ar->inbox_vecs_per_src) {
+      set_error("axb_gemm_ar: communication buffers too small for %lld tiles", tiles);
+      return -1;
+    }
+  } else {
+    p.ar.n = 1;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define AXB_DISPATCH(BN_, A_, B_) return launch<BN_, A_, B_>(tmA, tmB, p, device, s)
   if (BN == 256) {
@@ -410,4 +542,20 @@ extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const
     AXB_DISPATCH(128, 1, 1);
   }
 #undef AXB_DISPATCH
+}
+
+extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,
+                        int K, int in_dtype, int out_dtype, int epilogue, int accumulate, int device, void* stream) {
+  return gemm_common(layout, A, B, C, bias, aux, M, N, K, in_dtype, out_dtype, epilogue, accumulate, device, stream,
+                     nullptr);
+}
+
+// C = allreduce_over_ranks(op(A) op(B)) (+bias, GELU): every rank of the group calls this with its partial
+// operands; the epilogue exchanges bf16 partial tiles through peer-mapped inboxes (see AxbArCtx).
+extern "C" int axb_gemm_ar(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M,
+                           int N, int K, int in_dtype, int out_dtype, int epilogue, int device, void* stream,
+                           const AxbArCtx* ar) {
+  if (!ar || ar->n < 2 || ar->n > 8) { axb::set_error("axb_gemm_ar: group size must be 2..8"); return -1; }
+  if (ar->bn != 128 && ar->bn != 256) { axb::set_error("axb_gemm_ar: bn must be 128 or 256"); return -1; }
+  return gemm_common(layout, A, B, C, bias, aux, M, N, K, in_dtype, out_dtype, epilogue, 0, device, stream, ar);
 }

@@ -192,18 +192,26 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
   }
 }
 
-// out[c] = sum_b part[b, c]   (optionally two tables at once)
+// out[c] = sum_b part[b, c]   (optionally two tables at once).  Block = 32 columns x 8 row-groups.
 __global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb, float* __restrict__ oa,
                                      float* __restrict__ ob, int nblocks, int H) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+  __shared__ float sa[8][33], sb[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
-  for (int r = 0; r < nblocks; ++r) {
-    a += pa[static_cast<size_t>(r) * H + c];
-    if (pb) b += pb[static_cast<size_t>(r) * H + c];
+  if (c < H) {
+    for (int r = threadIdx.y; r < nblocks; r += 8) {
+      a += pa[static_cast<size_t>(r) * H + c];
+      if (pb) b += pb[static_cast<size_t>(r) * H + c];
+    }
   }
-  oa[c] = a;
-  if (pb) ob[c] = b;
+  sa[threadIdx.y][threadIdx.x] = a; sb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < H) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) { a += sa[k][threadIdx.x]; b += sb[k][threadIdx.x]; }
+    oa[c] = a;
+    if (pb) ob[c] = b;
+  }
 }
 
 int sm_count(int device);
@@ -245,7 +253,7 @@ static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const fl
 }  // namespace axb
 
 extern "C" int axb_norm_grid(int device, int rows) {
-  int g = 4 * axb::sm_count(device);
+  int g = 6 * axb::sm_count(device);
   return rows < g ? rows : g;
 }
 
@@ -276,8 +284,8 @@ extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, co
   else rc = norm_bwd_t<float>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s);
   if (rc) return rc;
   if (mode != 1 && dgamma_part && dgamma) {
-    fold_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(dgamma_part, rms ? nullptr : dbeta_part, dgamma,
-                                                        rms ? nullptr : dbeta, grid, H);
+    fold_partials_kernel<<<(H + 31) / 32, dim3(32, 8), 0, s>>>(dgamma_part, rms ? nullptr : dbeta_part, dgamma,
+                                                              rms ? nullptr : dbeta, grid, H);
     AXB_CUDA(cudaGetLastError());
   }
   return 0;

@@ -126,7 +126,51 @@ multi_adamw_kernel(const long long* __restrict__ table, int n, long long total_c
     const int gdtype = (int)row[6];
     const long long begin = (chunk - row[7]) * MT_CHUNK;
     const long long end = begin + MT_CHUNK < numel ? begin + MT_CHUNK : numel;
-    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
+                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(grad) |
+                           reinterpret_cast<uintptr_t>(model)) & 15) == 0;
+    long long scalar_from = begin;
+    if (aligned && gdtype != 2) {
+      // 4 elements per thread per iteration: 16-byte accesses to the fp32 state, 8-byte to bf16 tensors
+      const long long nv = (end - begin) / 4;
+      for (long long q = threadIdx.x; q < nv; q += blockDim.x) {
+        const long long i = begin + q * 4;
+        float4 p4 = *reinterpret_cast<const float4*>(master + i);
+        float4 m4 = *reinterpret_cast<const float4*>(m + i);
+        float4 v4 = *reinterpret_cast<const float4*>(v + i);
+        float g4[4];
+        if (gdtype == 0) {
+          const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grad) + i);
+          g4[0] = t.x; g4[1] = t.y; g4[2] = t.z; g4[3] = t.w;
+        } else {
+          const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(grad) + i);
+          const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+          const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+          g4[0] = __bfloat162float(a.x); g4[1] = __bfloat162float(a.y);
+          g4[2] = __bfloat162float(b.x); g4[3] = __bfloat162float(b.y);
+        }
+        float pp[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float g = g4[k] * gs;
+          mm[k] = a.beta1 * mm[k] + (1.f - a.beta1) * g;
+          vv[k] = a.beta2 * vv[k] + (1.f - a.beta2) * g * g;
+          const float denom = sqrtf(vv[k]) * inv_sqrt_c2 + a.eps;
+          pp[k] = pp[k] * decay - step * mm[k] / denom;
+        }
+        *reinterpret_cast<float4*>(master + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+        *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+        *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        if (model) {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
+          uint2 o;
+          o.x = *reinterpret_cast<const uint32_t*>(&lo); o.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(model + i) = o;
+        }
+      }
+      scalar_from = begin + nv * 4;
+    }
+    for (long long i = scalar_from + threadIdx.x; i < end; i += blockDim.x) {
       const float g = load_as_f32(grad, i, gdtype) * gs;
       const float mi = a.beta1 * m[i] + (1.f - a.beta1) * g;
       const float vi = a.beta2 * v[i] + (1.f - a.beta2) * g * g;
@@ -140,7 +184,7 @@ multi_adamw_kernel(const long long* __restrict__ table, int n, long long total_c
 }
 
 int sm_count(int device);
-static inline int mt_grid(long long chunks) { return (int)(chunks < 148 * 4 ? (chunks < 1 ? 1 : chunks) : 148 * 4); }
+static inline int mt_grid(long long chunks) { return (int)(chunks < 148 * 8 ? (chunks < 1 ? 1 : chunks) : 148 * 8); }
 
 }  // namespace axb
 

@@ -29,6 +29,7 @@ from torch.autograd import Function
 
 from .. import axonn as ax
 from .. import ops
+from ..parallel import fused
 from ..utils import divide
 from . import overlap_communication as oc
 from .asym_communication import (
@@ -100,7 +101,17 @@ class AsyncLinear(Function):
         inner_n = dist.get_world_size(forward_all_reduce_group)
         b = None if bias is None else bias.to(compute_dtype)
         pre_act = None
-        if inner_n == 1 and x2.is_cuda and (b is not None or activation):
+        if inner_n > 1 and fused.usable(forward_all_reduce_group, x2):
+            # GEMM whose epilogue all-reduces the output tiles over NVLink peer memory,
+            # then applies bias / GELU to the reduced values
+            epi = ops.EPI_NONE
+            if activation == "gelu":
+                pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype, device=x2.device)
+                epi = ops.EPI_BIAS_GELU if b is not None else ops.EPI_GELU
+            elif b is not None:
+                epi = ops.EPI_BIAS
+            out = fused.gemm_all_reduce(0, x2, w, forward_all_reduce_group, bias=b, epilogue=epi, aux=pre_act)
+        elif inner_n == 1 and x2.is_cuda and (b is not None or activation):
             if activation == "gelu":
                 pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype, device=x2.device)
                 epi = ops.EPI_BIAS_GELU if b is not None else ops.EPI_GELU
@@ -161,9 +172,16 @@ class AsyncLinear(Function):
         if outer_n > 1 or not overlap_rs:
             # dgrad first so that its all-reduce hides under the wgrad GEMM
             if ctx.needs_input_grad[0]:
-                grad_input = dgrad()
-                if outer_n > 1:
-                    handle = dist.all_reduce(grad_input, group=ctx.backward_all_reduce_group, async_op=overlap_ar)
+                if outer_n > 1 and fused.usable(ctx.backward_all_reduce_group, go2):
+                    w = _gathered_weight(w_shard, ctx.depth_parallel_group, ctx.shape, cache=False)
+                    if w.dtype != ctx.compute_dtype:
+                        w = w.to(ctx.compute_dtype)
+                    grad_input = fused.gemm_all_reduce(1, go2.contiguous(), w, ctx.backward_all_reduce_group)
+                else:
+                    grad_input = dgrad()
+                    if outer_n > 1:
+                        handle = dist.all_reduce(grad_input, group=ctx.backward_all_reduce_group,
+                                                 async_op=overlap_ar)
             if ctx.needs_input_grad[1]:
                 grad_weight = wgrad()
             if ctx.has_bias and ctx.needs_input_grad[2]:

@@ -1,0 +1,72 @@
+"""Fused GEMM + all-reduce over NVLink peer memory against NCCL + a plain
+PyTorch fp32 reference, on 2 GPUs (child processes, NVLS off)."""
+
+import os
+
+import pytest
+import torch
+
+from _dist import run_distributed
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _gemm_ar_case(rank, world):
+    import torch.distributed as dist
+
+    from axonn_b200.ops import _lib
+    from axonn_b200.parallel import fused
+
+    dev = torch.device("cuda", rank)
+    group = dist.group.WORLD
+    results = []
+    for layout, (M, N, K) in [(0, (512, 512, 256)), (0, (1000, 1288, 520)), (1, (2048, 1024, 512)),
+                              (0, (4096, 4096, 1024)), (1, (640, 264, 136))]:
+        for rep in range(3):  # repeated calls exercise inbox parity and epochs
+            g = torch.Generator(device=dev).manual_seed(17 * rank + M + rep)
+            a = (torch.randn(M, K, device=dev, generator=g) * 0.5).bfloat16()
+            bshape = (N, K) if layout == 0 else (K, N)
+            b = (torch.randn(bshape, device=dev, generator=g) * 0.5).bfloat16()
+            out = fused.gemm_all_reduce(layout, a, b, group)
+            part = (a.float() @ b.float().t()) if layout == 0 else (a.float() @ b.float())
+            # reference: sum of the bf16-rounded partials of both ranks (what an NCCL bf16 all-reduce adds)
+            ref = part.bfloat16().float()
+            dist.all_reduce(ref)
+            torch.cuda.synchronize()
+            status = _lib.lib().axb_device_status(rank, 1)
+            err = (out.float() - ref).abs().max().item()
+            scale = ref.abs().max().item()
+            results.append((layout, M, N, K, rep, status, err, scale))
+            # both ranks must hold identical bits
+            other = out.clone()
+            dist.broadcast(other, src=0)
+            assert torch.equal(other, out), "ranks disagree bitwise"
+    # fused bias + GELU after the reduction
+    M, N, K = 768, 512, 256
+    a = torch.randn(M, K, device=dev).bfloat16()
+    b = torch.randn(N, K, device=dev).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    dist.broadcast(bias, src=0)
+    aux = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    from axonn_b200 import ops
+    out = fused.gemm_all_reduce(0, a, b, group, bias=bias, epilogue=ops.EPI_BIAS_GELU, aux=aux)
+    ref = (a.float() @ b.float().t()).bfloat16().float()
+    dist.all_reduce(ref)
+    z = ref + bias.float()
+    gz = torch.nn.functional.gelu(z, approximate="tanh")
+    torch.cuda.synchronize()
+    results.append(("gelu", (aux.float() - z).abs().max().item() / z.abs().max().item(),
+                    (out.float() - gz).abs().max().item() / gz.abs().max().item()))
+    return results
+
+
+def test_gemm_all_reduce_two_gpus():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    res = run_distributed(_gemm_ar_case, 2, backend="nccl", timeout=300)
+    for per_rank in res:
+        for r in per_rank[:-1]:
+            layout, M, N, K, rep, status, err, scale = r
+            assert status == 0, f"kernel reported an expired wait: {r}"
+            assert err <= 1.6e-2 * scale, f"{r}"
+        _, e1, e2 = per_rank[-1]
+        assert e1 < 2e-2 and e2 < 2e-2
