@@ -69,6 +69,9 @@ def init(
     from .parallel import fused as _fused
 
     _fused.reset()
+    from .parallel import moe_kernels as _mk
+
+    _mk.reset()
 
 
 def finalize() -> None:

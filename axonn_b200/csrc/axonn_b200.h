@@ -52,6 +52,27 @@ typedef struct AxbArCtx {
 int axb_gemm_ar(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N, int K,
                 int in_dtype, int out_dtype, int epilogue, int device, void* stream, const AxbArCtx* ar);
 
+/* Peer-memory context of the MoE token exchange kernels.  `wait_local[j]` must reach `wait_value` before the
+ * kernel touches remote memory; when the kernel has finished it writes `epoch` to `signal_peer[j][rank]`. */
+typedef struct AxbMoeCtx {
+  int n, rank;
+  unsigned int epoch;
+  int n_local;
+  void* buf_peer[8];
+  unsigned int* wait_local;
+  unsigned int wait_value;
+  unsigned int* signal_peer[8];
+  unsigned int* counter;
+} AxbMoeCtx;
+
+int axb_moe_dispatch(const void* x, int x_by_token, const long long* dest, const unsigned char* keep,
+                     const long long* counts, int T, int k, int E, int C, int H, const AxbMoeCtx* ctx, int device,
+                     void* stream);
+int axb_moe_gather(void* out, const long long* dest, const unsigned char* keep, int T, int k, int C, int H,
+                   const AxbMoeCtx* ctx, int device, void* stream);
+int axb_moe_signal(const AxbMoeCtx* ctx, int device, void* stream);
+int axb_moe_wait(const AxbMoeCtx* ctx, int device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

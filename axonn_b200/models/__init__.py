@@ -2,6 +2,7 @@
 
 from .gpt import GPT, GPTConfig  # noqa: F401
 from .llama import Llama, LlamaConfig  # noqa: F401
+from .mixtral import Mixtral, MixtralConfig  # noqa: F401
 from .mlp import MLP  # noqa: F401
 from .vgg import DistributedVGG16  # noqa: F401
 from .vit import DistributedViT  # noqa: F401

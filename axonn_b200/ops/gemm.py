@@ -27,7 +27,12 @@ _DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
 def _cuda_ok(a, b):
-    return a.is_cuda and b.is_cuda and a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16)
+    """Kernel path: 16-bit CUDA operands whose dimensions give 16-byte aligned TMA
+    row pitches.  Odd shapes (e.g. a router with 4 outputs) use torch.matmul."""
+    if not (a.is_cuda and b.is_cuda and a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16)):
+        return False
+    # every dimension that is a contiguous (innermost) extent or the output width
+    return a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0 and b.shape[0] % 8 == 0
 
 
 def _rowmajor(t):
@@ -60,7 +65,7 @@ def matmul_nt(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None, out=None, accu
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
         return _launch(0, a, b, M, N, K, out, bias, epilogue, accumulate, aux)
-    if a.is_cuda and a.dtype in (torch.bfloat16, torch.float16):
+    if a.is_cuda and a.dtype != b.dtype:
         raise TypeError("matmul_nt: operand dtypes differ")
     y = torch.matmul(a, b.t())
     if epilogue in (EPI_BIAS, EPI_BIAS_GELU):

@@ -1,0 +1,103 @@
+"""Failure detection without touching a GPU: a rank that stops participating
+is reported by its peers' watchdogs, the pipeline engine's receive loop gives
+up with PipelineTimeout instead of hanging, and training resumes from the
+sharded checkpoint with the same loss."""
+
+import os
+import time
+
+import pytest
+import torch
+
+from _dist import run_distributed
+
+
+def _silent_rank(rank, world, tmp):
+    import torch.distributed as dist
+
+    from axonn_b200.parallel.watchdog import RankFailure, Watchdog
+
+    wd = Watchdog(interval_s=0.1, timeout_s=1.0).start()
+    time.sleep(0.5)
+    wd.check()  # everybody alive
+    if rank == 1:
+        wd.stop()      # rank 1 goes silent (its process stays so that the test can finish cleanly)
+        time.sleep(3.0)
+        return "silent"
+    time.sleep(2.5)
+    try:
+        wd.check()
+    except RankFailure as e:
+        wd.stop()
+        return str(e)
+    wd.stop()
+    return "not detected"
+
+
+def test_watchdog_reports_silent_rank(tmp_path):
+    out = run_distributed(_silent_rank, 3, str(tmp_path))
+    assert out[1] == "silent"
+    assert "rank 1" in out[0] and "rank 1" in out[2]
+
+
+def _pipeline_timeout(rank, world):
+    from axonn_b200 import axonn as ax
+    from axonn_b200.inter_layer import AxoNN_Inter_Layer_Engine, PipelineTimeout
+    from axonn_b200.models import DistributedViT
+
+    ax.init(G_inter=2, G_data=1)
+    torch.manual_seed(0)
+    model = DistributedViT(image_size=8, patch_size=4, num_classes=4, dim=16, depth=2, heads=2, mlp_dim=32, channels=1)
+    eng = AxoNN_Inter_Layer_Engine(model, torch.nn.functional.cross_entropy, computation_dtype=torch.float32,
+                                   timeout_s=1.5)
+    ax.config.micro_batch_size = 2
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    if rank == 0:
+        return "never joined the step"   # stage 0 does not send anything
+    t0 = time.time()
+    try:
+        eng.forward_backward_optimizer(torch.zeros(4, 1, 8, 8), torch.zeros(4, dtype=torch.long), opt)
+    except PipelineTimeout as e:
+        return f"timeout after {time.time() - t0:.1f}s: {e}"
+    return "no timeout"
+
+
+def test_pipeline_receive_has_deadline():
+    out = run_distributed(_pipeline_timeout, 2)
+    assert out[1].startswith("timeout after") and "stage 1" in out[1]
+
+
+def _ckpt_resume(rank, world, folder, phase):
+    from axonn_b200 import axonn as ax
+    from axonn_b200 import checkpoint
+    from axonn_b200.models import GPT, GPTConfig
+    from axonn_b200.optim import FusedAdamW
+    from axonn_b200.trainer import Trainer
+
+    r, c, d = (2, 1, 1) if phase != "resume_other_grid" else (1, 1, 2)
+    ax.init(G_inter=1, G_data=world // (r * c * d), G_intra_r=r, G_intra_c=c, G_intra_d=d)
+    torch.manual_seed(3)
+    cfg = GPTConfig.tiny()
+    model = GPT(cfg, dtype=torch.float32)
+    opt = FusedAdamW(model.parameters(), lr=1e-3, weight_decay=0.0)
+    tr = Trainer(model, opt)
+    g = torch.Generator().manual_seed(9)
+    data = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=g)
+    x, y = data[:, :-1].contiguous(), data[:, 1:].contiguous()
+    if phase == "train":
+        losses = [tr.train_step(x, y) for _ in range(2)]
+        checkpoint.save({"model": model.state_dict(), "optimizer": opt.state_dict()}, folder, "step2")
+        losses += [tr.train_step(x, y) for _ in range(2)]
+        return losses
+    state = checkpoint.load(None, folder, "step2")
+    model.load_state_dict(state["model"])
+    opt.load_state_dict(state["optimizer"])
+    return [tr.train_step(x, y) for _ in range(2)]
+
+
+def test_resume_from_sharded_checkpoint_reproduces_loss(tmp_path):
+    folder = str(tmp_path / "ckpt")
+    full = run_distributed(_ckpt_resume, 2, folder, "train")[0]
+    assert sorted(os.listdir(folder)) == ["tp_row_0_col_0_depth_0", "tp_row_1_col_0_depth_0"]
+    resumed = run_distributed(_ckpt_resume, 2, folder, "resume")[0]
+    assert resumed == pytest.approx(full[2:], rel=1e-5)

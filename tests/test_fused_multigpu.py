@@ -70,3 +70,48 @@ def test_gemm_all_reduce_two_gpus():
             assert err <= 1.6e-2 * scale, f"{r}"
         _, e1, e2 = per_rank[-1]
         assert e1 < 2e-2 and e2 < 2e-2
+
+
+def _moe_case(rank, world):
+    import torch.distributed as dist
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200.ops import _lib
+    from axonn_b200.parallel import moe_kernels, symm
+    from axonn_b200.parallel.moe import ExpertParallelMoE
+
+    ax.init(G_inter=1, G_data=world)
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(5)
+    layer = ExpertParallelMoE(hidden=256, ffn=512, n_experts=4, top_k=2, capacity_factor=1.0, dtype=torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    outs = []
+    for it in range(3):
+        x = (torch.randn(4, 64, 256, device=dev, generator=g)).bfloat16().requires_grad_(True)
+        gy = torch.randn(4, 64, 256, device=dev, generator=g).bfloat16()
+        res = {}
+        for mode in ("nccl", "fused"):
+            os.environ["AXONN_BACKEND"] = mode
+            for p in layer.parameters():
+                p.grad = None
+            x.grad = None
+            y = layer(x)
+            y.backward(gy)
+            res[mode] = (y.detach().float(), x.grad.float().clone(), layer.w1.grad.float().clone(),
+                         layer.router.grad.float().clone(), float(layer.last_drop_fraction))
+        torch.cuda.synchronize()
+        status = _lib.lib().axb_device_status(rank, 1)
+        errs = [((a - b).abs().max() / (b.abs().max() + 1e-6)).item() for a, b in zip(res["fused"][:4], res["nccl"][:4])]
+        outs.append((status, errs, res["fused"][4]))
+    os.environ["AXONN_BACKEND"] = "fused"
+    return outs
+
+
+def test_moe_peer_memory_exchange_matches_all_to_all():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    res = run_distributed(_moe_case, 2, backend="nccl", timeout=300)
+    for per_rank in res:
+        for status, errs, drop in per_rank:
+            assert status == 0
+            assert max(errs) < 3e-2, errs
+            assert drop > 0.0  # capacity factor 1.0 with random routing drops some assignments

@@ -1,0 +1,72 @@
+"""Expert-parallel MoE on CPU ranks: with a capacity large enough to drop
+nothing, 4 expert-parallel ranks must reproduce the single-rank layer (same
+seed => same experts) in output, input gradient and expert gradients."""
+
+import pytest
+import torch
+
+from _dist import run_distributed
+
+
+def _moe(rank, world, ep):
+    import torch.distributed as dist
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200.intra_layer import sync_gradients
+    from axonn_b200.parallel.moe import ExpertParallelMoE
+
+    ax.init(G_inter=1, G_data=world)
+    torch.manual_seed(5)
+    layer = ExpertParallelMoE(hidden=32, ffn=64, n_experts=4, top_k=2, capacity_factor=4.0, dtype=torch.float32)
+    g = torch.Generator().manual_seed(11)
+    X = torch.randn(4, 8, 32, generator=g)          # 4 "ranks worth" of tokens
+    G = torch.randn(4, 8, 32, generator=g)
+    per = 4 // world
+    x = X[rank * per:(rank + 1) * per].clone().requires_grad_(True)
+    y = layer(x)
+    (y * G[rank * per:(rank + 1) * per]).sum().backward()
+    assert float(layer.last_drop_fraction) == 0.0
+    sync_gradients(layer, expert_mode=True)  # router is replicated: summed over the data group
+    # gather everything for comparison
+    ys = [torch.zeros_like(y) for _ in range(world)]
+    dist.all_gather(ys, y.detach())
+    gxs = [torch.zeros_like(x) for _ in range(world)]
+    dist.all_gather(gxs, x.grad)
+    w1s = [torch.zeros_like(layer.w1.grad) for _ in range(world)]
+    dist.all_gather(w1s, layer.w1.grad)
+    return (torch.cat(ys).numpy(), torch.cat(gxs).numpy(), torch.cat(w1s).numpy(), layer.router.grad.numpy(),
+            float(layer.last_aux_loss))
+
+
+def test_expert_parallel_matches_single_rank():
+    import numpy as np
+
+    ref = run_distributed(_moe, 1, 1)[0]
+    out = run_distributed(_moe, 4, 4)
+    for r in out:
+        for a, b in zip(r[:4], ref[:4]):
+            assert np.allclose(a, b, rtol=1e-4, atol=1e-5), np.abs(a - b).max()
+
+
+def test_router_capacity_and_aux_loss():
+    from axonn_b200.parallel.moe import route_top_k
+
+    torch.manual_seed(0)
+    logits = torch.randn(64, 8)
+    idx, gate, slot, keep, aux = route_top_k(logits, 2, capacity=4)
+    assert torch.allclose(gate.sum(-1), torch.ones(64))
+    # no two kept assignments share a slot of the same expert
+    pairs = set()
+    for t in range(64):
+        for j in range(2):
+            if keep[t, j]:
+                key = (int(idx[t, j]), int(slot[t, j]))
+                assert key not in pairs and slot[t, j] < 4
+                pairs.add(key)
+    assert len(pairs) <= 8 * 4
+    # perfectly uniform routing gives aux == 1
+    u = torch.zeros(8, 8)
+    for i in range(8):
+        u[i, i] = 10.0
+    _, _, _, _, aux_u = route_top_k(u, 1, capacity=8)
+    assert abs(float(aux_u) - 1.0) < 0.05
