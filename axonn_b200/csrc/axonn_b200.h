@@ -73,6 +73,15 @@ int axb_moe_gather(void* out, const long long* dest, const unsigned char* keep, 
 int axb_moe_signal(const AxbMoeCtx* ctx, int device, void* stream);
 int axb_moe_wait(const AxbMoeCtx* ctx, int device, void* stream);
 
+/* Top-k gradient pruning for callers that cannot allocate device memory (programs that own the whole GPU
+ * through their own pool, or that forbid allocation after start-up).  This entry point has no counterpart
+ * in the reference project.  Same result as axb_prune_topk, but the radix-select scratch is a 393,248-byte
+ * array inside the library image, held on every GPU that loads the library until the process exits.
+ * The first call on a device (with that device current) resolves the array's address: make it before any
+ * stream capture.  n is limited to 2,147,483,647 elements.  Calls share the scratch: they must not overlap
+ * on the GPU. */
+int axb_prune_topk_static(void* g, long long n, int dtype, long long k, int device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -168,3 +168,60 @@ extern "C" int axb_prune_topk(void* g, long long n, int dtype, long long k, void
   if (!work) { axb::set_error("prune: workspace is null"); return -1; }
   return axb::prune_topk_launch(g, n, dtype, k, static_cast<unsigned int*>(work), device, (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Entry point for callers that must not allocate.
+//
+// Some programs that embed this library own every byte of device memory themselves (a serving
+// process that hands the whole GPU to its own pool at start-up, or one that runs under a
+// "nothing is allocated after initialisation" rule): asking the driver for a workspace in the
+// middle of their step can fail or fragment their pool, so they cannot supply freshly allocated
+// scratch and do not want this library to allocate it behind their back.  For them the
+// radix-select scratch lives in the library image itself, in the array below.
+//
+// The array takes PR_WORK_WORDS * 4 bytes (32768 + 65536 + 8 words = 393,248 bytes) of every
+// GPU that loads the library, from load until the process exits.
+static __device__ __align__(256) unsigned int g_prune_static_scratch[axb::PR_WORK_WORDS];
+
+namespace axb {
+// Largest tensor the static entry point accepts: the histogram counters are 32-bit.
+constexpr long long PR_STATIC_MAX_NUMEL = 2147483647LL;
+// Device address of g_prune_static_scratch per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use, so the address is looked up once per
+// device with cudaGetSymbolAddress while that device is current.
+static unsigned int* g_prune_static_ptr[64] = {nullptr};
+}  // namespace axb
+
+// Keep the k largest-magnitude entries of g (dtype 0 fp32, 1 bf16, 2 fp16), zero the rest, in place,
+// like axb_prune_topk, but with no workspace argument and without allocating anything: no cudaMalloc,
+// no cudaFree, no allocating library call.
+//
+// * The first call on a device looks up the scratch array's device address (the device must be the
+//   current one, as it is for the launch itself).  Make that first call before starting any stream
+//   capture on the device.
+// * n must not exceed 2,147,483,647 elements; larger tensors are rejected with an error.
+// * All calls on a device share one scratch array.  It is cleared at the start of each call, so
+//   nothing needs to be reset between calls, but two calls whose kernels may overlap on the GPU
+//   (different streams without an ordering between them) race on it: serialise them.
+extern "C" int axb_prune_topk_static(void* g, long long n, int dtype, long long k, int device, void* stream) {
+  using namespace axb;
+  if (n > PR_STATIC_MAX_NUMEL) {
+    set_error("axb_prune_topk_static: %lld elements exceed the supported maximum of %lld", n, PR_STATIC_MAX_NUMEL);
+    return -1;
+  }
+  if (device < 0 || device >= 64) { set_error("axb_prune_topk_static: bad device index %d", device); return -1; }
+  if (dtype < 0 || dtype > 2) { set_error("axb_prune_topk_static: bad dtype %d", dtype); return -1; }
+  if (g_prune_static_ptr[device] == nullptr) {
+    int current = -1;
+    AXB_CUDA(cudaGetDevice(&current));
+    if (current != device) {
+      set_error("axb_prune_topk_static: device %d must be current on first use (current is %d)", device, current);
+      return -1;
+    }
+    unsigned int* p = nullptr;
+    AXB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_prune_static_scratch));
+    if (p == nullptr) { set_error("axb_prune_topk_static: scratch symbol has no device address"); return -1; }
+    g_prune_static_ptr[device] = p;
+  }
+  return prune_topk_launch(g, n, dtype, k, g_prune_static_ptr[device], device, (cudaStream_t)stream);
+}
