@@ -1,0 +1,204 @@
+// Gradient all-reduce over NVLink peer memory with fused scale and dtype handling.
+//
+//   pack     a list of gradient tensors is copied into this rank's symmetric bucket (one launch over a
+//            pointer table); the last CTA publishes READY = epoch to every peer;
+//   reduce   two-shot in one kernel: rank k owns slice k of the bucket, loads that slice from every rank
+//            (P2P loads, fp32 accumulation in rank order so that all ranks see identical bits), multiplies
+//            by `scale` and stores the result into every rank's bucket (P2P stores).  Nobody else touches
+//            slice k, so no further ordering is needed inside the kernel.  The last CTA publishes DONE;
+//   unpack   waits for every peer's DONE (all slices of my bucket are final) and copies the bucket back
+//            into the gradient tensors.
+//
+// Bytes on the wire per rank and direction: 2 (n-1)/n of the bucket, the two-shot optimum.  All waits
+// are bounded and report through the device status word.
+#include "common.cuh"
+
+namespace axb {
+
+struct CommCtx {
+  int n, rank;
+  unsigned int epoch;
+  void* buf_peer[8];
+  unsigned int* wait_local;      // [n] flags to wait on
+  unsigned int* signal_peer[8];  // flag array on rank j (indexed by my rank) to publish completion
+  unsigned int* counter;
+  unsigned int* status;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ void c_st_release(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int c_ld_acquire(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool comm_wait_all(const CommCtx& c, int* sh_ok) {
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const uint64_t t0 = globaltimer_ns();
+    for (int j = 0; j < c.n && ok; ++j) {
+      if (j == c.rank) continue;
+      while (static_cast<int>(c_ld_acquire(c.wait_local + j) - c.epoch) < 0) {
+        if (globaltimer_ns() - t0 > c.timeout_ns) {
+          ok = 0;
+          *reinterpret_cast<volatile unsigned int*>(c.status) = 0x301u;
+          break;
+        }
+      }
+    }
+    *sh_ok = ok;
+  }
+  __syncthreads();
+  return *sh_ok != 0;
+}
+__device__ __forceinline__ void comm_signal_when_last(const CommCtx& c) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(c.counter, 1u) == gridDim.x - 1) {
+      *c.counter = 0;
+      __threadfence_system();
+      for (int j = 0; j < c.n; ++j)
+        if (j != c.rank) c_st_release(c.signal_peer[j] + c.rank, c.epoch);
+    }
+  }
+}
+
+constexpr int PK_CHUNK = 1 << 15;
+
+// table rows: {tensor ptr, numel, dtype (unused: all tensors share the bucket dtype), element offset in bucket,
+//              chunk prefix}
+__device__ __forceinline__ int pk_find(const long long* table, int n, long long chunk) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (table[(size_t)mid * 5 + 4] <= chunk) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <typename T, bool TO_BUCKET>
+__global__ void __launch_bounds__(256)
+bucket_copy_kernel(const long long* __restrict__ table, int ntensors, long long total_chunks, T* bucket, CommCtx c,
+                   int wait_first, int signal_last) {
+  __shared__ int sh_ok;
+  if (wait_first && c.n > 1 && !comm_wait_all(c, &sh_ok)) return;
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    const int t = pk_find(table, ntensors, chunk);
+    const long long* row = table + (size_t)t * 5;
+    T* tensor = reinterpret_cast<T*>(row[0]);
+    const long long numel = row[1];
+    T* slot = bucket + row[3];
+    const long long begin = (chunk - row[4]) * PK_CHUNK;
+    const long long end = begin + PK_CHUNK < numel ? begin + PK_CHUNK : numel;
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      if (TO_BUCKET) slot[i] = tensor[i]; else tensor[i] = slot[i];
+    }
+  }
+  if (signal_last && c.n > 1) comm_signal_when_last(c);
+}
+
+template <typename T> struct V16;  // 16-byte vector of T <-> floats
+template <> struct V16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+template <> struct V16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+  }
+};
+
+// nvec: number of 16-byte vectors in the bucket (padded so that nvec % n == 0)
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_twoshot_kernel(long long nvec, float scale, CommCtx c) {
+  __shared__ int sh_ok;
+  if (!comm_wait_all(c, &sh_ok)) return;
+  const long long per = nvec / c.n;
+  const long long lo = per * c.rank;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
+    float acc[V16<T>::N];
+#pragma unroll
+    for (int e = 0; e < V16<T>::N; ++e) acc[e] = 0.f;
+    for (int j = 0; j < c.n; ++j) {
+      const uint4 u = *(reinterpret_cast<const uint4*>(c.buf_peer[j]) + lo + i);
+      float f[V16<T>::N];
+      V16<T>::unpack(u, f);
+#pragma unroll
+      for (int e = 0; e < V16<T>::N; ++e) acc[e] += f[e];
+    }
+#pragma unroll
+    for (int e = 0; e < V16<T>::N; ++e) acc[e] *= scale;
+    const uint4 o = V16<T>::pack(acc);
+    for (int j = 0; j < c.n; ++j) *(reinterpret_cast<uint4*>(c.buf_peer[j]) + lo + i) = o;
+  }
+  comm_signal_when_last(c);
+}
+
+}  // namespace axb
+
+using namespace axb;
+
+static int fill_comm(CommCtx& c, const AxbCommCtx* h, int device) {
+  if (!h || h->n < 1 || h->n > 8) { set_error("allreduce: group size must be 1..8"); return -1; }
+  c.n = h->n; c.rank = h->rank; c.epoch = h->epoch;
+  for (int j = 0; j < 8; ++j) { c.buf_peer[j] = h->buf_peer[j]; c.signal_peer[j] = h->signal_peer[j]; }
+  c.wait_local = h->wait_local; c.counter = h->counter;
+  unsigned int* st = nullptr;
+  if (!device_status_word(device, &st)) { set_error("allreduce: no status word"); return -1; }
+  c.status = st;
+  c.timeout_ns = 5000000000ull;
+  return 0;
+}
+
+// direction 0: tensors -> bucket (then publish READY); direction 1: wait DONE, bucket -> tensors.
+extern "C" int axb_bucket_copy(const long long* table, int ntensors, long long total_chunks, void* bucket, int dtype,
+                               int direction, const AxbCommCtx* ctx, int device, void* stream) {
+  CommCtx c;
+  if (fill_comm(c, ctx, device)) return -1;
+  const int grid = (int)(total_chunks < 148 * 8 ? (total_chunks < 1 ? 1 : total_chunks) : 148 * 8);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == 0) {
+    if (direction == 0) bucket_copy_kernel<float, true><<<grid, 256, 0, s>>>(table, ntensors, total_chunks, (float*)bucket, c, 0, 1);
+    else bucket_copy_kernel<float, false><<<grid, 256, 0, s>>>(table, ntensors, total_chunks, (float*)bucket, c, 1, 0);
+  } else {
+    if (direction == 0) bucket_copy_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(table, ntensors, total_chunks, (__nv_bfloat16*)bucket, c, 0, 1);
+    else bucket_copy_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(table, ntensors, total_chunks, (__nv_bfloat16*)bucket, c, 1, 0);
+  }
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// In-place two-shot all-reduce of every rank's bucket (nbytes, padded to a multiple of 16 * n), times `scale`.
+extern "C" int axb_allreduce_twoshot(long long nbytes, int dtype, float scale, const AxbCommCtx* ctx, int device,
+                                     void* stream) {
+  CommCtx c;
+  if (fill_comm(c, ctx, device)) return -1;
+  if (nbytes % (16 * c.n)) { set_error("allreduce: bucket bytes must be a multiple of 16 * group size"); return -1; }
+  const long long nvec = nbytes / 16;
+  const long long per = nvec / c.n;
+  long long blocks = (per + 511) / 512;
+  const int grid = (int)(blocks < 1 ? 1 : (blocks > 148 * 4 ? 148 * 4 : blocks));
+  if (dtype == 0) allreduce_twoshot_kernel<float><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, c);
+  else allreduce_twoshot_kernel<__nv_bfloat16><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, c);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}

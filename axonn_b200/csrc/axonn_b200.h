@@ -47,7 +47,12 @@ typedef struct AxbArCtx {
   unsigned int* counter;      /* local CTA completion counter (zero between calls) */
   unsigned long long inbox_vecs_per_src; /* 16-byte words per source in an inbox */
   unsigned long long flags_per_src;      /* flags per source */
+  int mode;                   /* 0: all-reduce of C; 1: reduce-scatter of C by row blocks */
+  int rows_per_shard;         /* mode 1: rows of C owned by each rank (multiple of 32) */
 } AxbArCtx;
+
+int axb_gemm_rs(int layout, const void* A, const void* B, void* C_shard, int M, int N, int K, int in_dtype,
+                int out_dtype, int accumulate, int device, void* stream, const AxbArCtx* ar);
 
 int axb_gemm_ar(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N, int K,
                 int in_dtype, int out_dtype, int epilogue, int device, void* stream, const AxbArCtx* ar);
@@ -72,6 +77,21 @@ int axb_moe_gather(void* out, const long long* dest, const unsigned char* keep, 
                    const AxbMoeCtx* ctx, int device, void* stream);
 int axb_moe_signal(const AxbMoeCtx* ctx, int device, void* stream);
 int axb_moe_wait(const AxbMoeCtx* ctx, int device, void* stream);
+
+/* Peer-memory context of the gradient all-reduce kernels (see AxbMoeCtx for the flag conventions). */
+typedef struct AxbCommCtx {
+  int n, rank;
+  unsigned int epoch;
+  int pad;
+  void* buf_peer[8];
+  unsigned int* wait_local;
+  unsigned int* signal_peer[8];
+  unsigned int* counter;
+} AxbCommCtx;
+
+int axb_bucket_copy(const long long* table, int ntensors, long long total_chunks, void* bucket, int dtype, int direction,
+                    const AxbCommCtx* ctx, int device, void* stream);
+int axb_allreduce_twoshot(long long nbytes, int dtype, float scale, const AxbCommCtx* ctx, int device, void* stream);
 
 /* Top-k gradient pruning for callers that cannot allocate device memory (programs that own the whole GPU
  * through their own pool, or that forbid allocation after start-up).  This entry point has no counterpart

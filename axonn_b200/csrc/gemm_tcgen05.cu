@@ -302,8 +302,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       // slot of this (tile, warp) in every inbox: [chunk][vec 0..3][lane] 16-byte words
       const size_t slot_vec = (static_cast<size_t>(tile) * 4 + q) * (BN / 32) * 4 * 32;
-      if (p.ar.n > 1) {
-        // ---- phase A: push this warp's bf16 partial (32 rows x BN cols) into every peer's inbox
+      // Reduce-scatter mode: rows [o * rows_per_shard, (o + 1) * rows_per_shard) of C belong to rank o; a warp's
+      // 32 rows always have one owner (rows_per_shard is a multiple of 32).
+      int owner = -1;
+      bool do_final = true;
+      size_t out_row = row;
+      if (p.ar.n > 1 && p.ar.mode == 1) {
+        owner = (tm * BM + q * 32) / p.ar.rows_per_shard;
+        do_final = owner == p.ar.rank;
+        out_row = row - static_cast<size_t>(p.ar.rank) * p.ar.rows_per_shard;
+      }
+      if (p.ar.n > 1 && (p.ar.mode == 0 || (owner != p.ar.rank && owner < p.ar.n))) {
+        // ---- phase A: push this warp's bf16 partial (32 rows x BN cols) into the inbox of every peer
+        // (all-reduce) or of the rows' owner (reduce-scatter)
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           if (tn * BN + c * 32 >= p.N) break;
@@ -319,7 +330,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             w[i].w = pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]), p.in_dtype);
           }
           for (int j = 0; j < p.ar.n; ++j) {
-            if (j == p.ar.rank) continue;
+            if (j == p.ar.rank || (p.ar.mode == 1 && j != owner)) continue;
             uint4* dst = reinterpret_cast<uint4*>(p.ar.inbox_peer[j]) +
                          static_cast<size_t>(p.ar.rank) * p.ar.inbox_vecs_per_src + slot_vec + (c * 4) * 32 + lane;
 #pragma unroll
@@ -330,11 +341,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         __syncwarp();
         if (lane == 0) {
           for (int j = 0; j < p.ar.n; ++j) {
-            if (j == p.ar.rank) continue;
+            if (j == p.ar.rank || (p.ar.mode == 1 && j != owner)) continue;
             st_release_sys(p.ar.flags_peer[j] + static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + q,
                            p.ar.epoch);
           }
-          // ---- phase B: wait for every peer's partial of the same (tile, warp)
+        }
+      }
+      if (p.ar.n > 1 && do_final) {
+        // ---- phase B: wait for every peer's partial of the same (tile, warp)
+        if (lane == 0) {
           for (int j = 0; j < p.ar.n && ok; ++j) {
             if (j == p.ar.rank) continue;
             ok = wait_flag_ge(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q,
@@ -344,6 +359,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
       }
+      const bool store_ok = row_ok && do_final;
+      if (do_final)
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col = tn * BN + c * 32;
@@ -396,11 +413,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         if (p.epilogue >= 2) {
-          if (p.aux != nullptr && row_ok) store_row32(p.aux, p.out_dtype, row, p.N, col, p.N, v, false);
+          if (p.aux != nullptr && store_ok) store_row32(p.aux, p.out_dtype, out_row, p.N, col, p.N, v, false);
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
         }
-        if (row_ok) store_row32(p.C, p.out_dtype, row, p.N, col, p.N, v, p.accumulate != 0);
+        if (store_ok) store_row32(p.C, p.out_dtype, out_row, p.N, col, p.N, v, p.accumulate != 0);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -552,10 +569,26 @@ extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const
 
 // C = allreduce_over_ranks(op(A) op(B)) (+bias, GELU): every rank of the group calls this with its partial
 // operands; the epilogue exchanges bf16 partial tiles through peer-mapped inboxes (see AxbArCtx).
+// C_shard[rows_per_shard, N] (+)= reduce_scatter_over_ranks(op(A) op(B)) along the rows of the product:
+// rank o receives rows [o * rows_per_shard, (o + 1) * rows_per_shard).  M must equal n * rows_per_shard.
+extern "C" int axb_gemm_rs(int layout, const void* A, const void* B, void* C_shard, int M, int N, int K, int in_dtype,
+                           int out_dtype, int accumulate, int device, void* stream, const AxbArCtx* ar) {
+  if (!ar || ar->n < 2 || ar->n > 8) { axb::set_error("axb_gemm_rs: group size must be 2..8"); return -1; }
+  if (ar->mode != 1 || ar->rows_per_shard <= 0 || ar->rows_per_shard % 32 != 0 ||
+      static_cast<long long>(ar->rows_per_shard) * ar->n != M) {
+    axb::set_error("axb_gemm_rs: rows_per_shard must be a multiple of 32 with n * rows_per_shard == M");
+    return -1;
+  }
+  if (ar->bn != 128 && ar->bn != 256) { axb::set_error("axb_gemm_rs: bn must be 128 or 256"); return -1; }
+  return gemm_common(layout, A, B, C_shard, nullptr, nullptr, M, N, K, in_dtype, out_dtype, 0, accumulate, device,
+                     stream, ar);
+}
+
 extern "C" int axb_gemm_ar(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M,
                            int N, int K, int in_dtype, int out_dtype, int epilogue, int device, void* stream,
                            const AxbArCtx* ar) {
   if (!ar || ar->n < 2 || ar->n > 8) { axb::set_error("axb_gemm_ar: group size must be 2..8"); return -1; }
   if (ar->bn != 128 && ar->bn != 256) { axb::set_error("axb_gemm_ar: bn must be 128 or 256"); return -1; }
+  if (ar->mode != 0) { axb::set_error("axb_gemm_ar: context is not in all-reduce mode"); return -1; }
   return gemm_common(layout, A, B, C, bias, aux, M, N, K, in_dtype, out_dtype, epilogue, 0, device, stream, ar);
 }

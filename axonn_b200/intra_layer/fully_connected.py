@@ -154,6 +154,12 @@ class AsyncLinear(Function):
         handle = None
 
         def wgrad():
+            if depth_n > 1 and fused.reduce_scatter_usable(ctx.depth_parallel_group, go2, ctx.shape[0]) \
+                    and go2.dtype == w_shard.dtype:
+                # weight-gradient GEMM whose epilogue reduce-scatters the row blocks (= depth shards of the
+                # flattened weight) over NVLink peer memory
+                return fused.gemm_reduce_scatter(2, go2, x2, ctx.depth_parallel_group,
+                                                 out_dtype=w_shard.dtype).reshape(-1)
             gw = ops.matmul_tn(go2, x2, out_dtype=w_shard.dtype).reshape(-1)
             if depth_n > 1:
                 gw = _reduce_scatter(gw, 0, ctx.depth_parallel_group, overlap_comm=overlap_rs)

@@ -33,6 +33,7 @@ class AxbArCtx(ctypes.Structure):
         ("done_local", ctypes.c_void_p), ("done_peer", ctypes.c_void_p * 8),
         ("counter", ctypes.c_void_p),
         ("inbox_vecs_per_src", ctypes.c_ulonglong), ("flags_per_src", ctypes.c_ulonglong),
+        ("mode", ctypes.c_int), ("rows_per_shard", ctypes.c_int),
     ]
 
 
@@ -77,7 +78,7 @@ class _ArChannel:
         dist.barrier(group=self.group)
         self.epoch = 1
 
-    def context(self, bn):
+    def context(self, bn, mode=0, rows_per_shard=0):
         self.epoch += 1
         parity = self.epoch & 1
         f0, fbytes, i0, ibytes, _ = self._layout()
@@ -95,6 +96,7 @@ class _ArChannel:
             c.done_peer[j] = base[j]
         c.inbox_vecs_per_src = self.inbox_vecs_per_src
         c.flags_per_src = self.flags_per_src
+        c.mode, c.rows_per_shard = mode, rows_per_shard
         return c
 
 
@@ -135,6 +137,48 @@ def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, aux=None,
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]),
         ctypes.c_int(epilogue), ctypes.c_int(a.device.index), _lib.stream_ptr(), ctypes.byref(ctx))
     _lib.check(st, "axb_gemm_ar")
+    return out
+
+
+def reduce_scatter_usable(group, tensor, rows) -> bool:
+    n = dist.get_world_size(group)
+    return usable(group, tensor) and rows % n == 0 and (rows // n) % 32 == 0
+
+
+def gemm_reduce_scatter(layout, a, b, group, out_dtype=None, out=None, accumulate=False):
+    """Row-wise ``reduce_scatter(op(a) @ op(b))`` over ``group`` in one kernel: rank ``o`` receives rows
+    ``[o*R, (o+1)*R)`` of the summed product (``R = M / n``), optionally accumulated into ``out``.
+
+    layout 2 (``a[K,M]``, ``b[K,N]`` -> ``a.T @ b``) is the weight-gradient product whose row blocks are
+    exactly the depth shards of the flattened weight."""
+    if layout == 2:
+        K, M = a.shape
+        N = b.shape[1]
+    elif layout == 0:
+        M, K = a.shape
+        N = b.shape[0]
+    else:
+        M, K = a.shape
+        N = b.shape[1]
+    a = a if a.is_contiguous() else a.contiguous()
+    b = b if b.is_contiguous() else b.contiguous()
+    ch = _channels.get(id(group))
+    if ch is None:
+        ch = _channels[id(group)] = _ArChannel(group)
+    R = M // ch.n
+    tiles_m = (M + _BM - 1) // _BM
+    bn = 256 if tiles_m * ((N + 255) // 256) >= 148 else 128
+    tiles = tiles_m * ((N + bn - 1) // bn)
+    ch.ensure(tiles, bn)
+    ctx = ch.context(bn, mode=1, rows_per_shard=R)
+    if out is None:
+        out = torch.empty((R, N), dtype=out_dtype or a.dtype, device=a.device)
+        accumulate = False
+    st = _lib.lib().axb_gemm_rs(
+        ctypes.c_int(layout), _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), ctypes.c_int(M), ctypes.c_int(N),
+        ctypes.c_int(K), ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]), ctypes.c_int(1 if accumulate else 0),
+        ctypes.c_int(a.device.index), _lib.stream_ptr(), ctypes.byref(ctx))
+    _lib.check(st, "axb_gemm_rs")
     return out
 
 

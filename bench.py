@@ -8,7 +8,7 @@ prints one JSON line.  Configuration: GPT-style decoder 1.3B (24 layers,
 d_model 2048, 16 heads, FFN 8192 GELU, LayerNorm, learned positions, vocab
 50304, seq 2048), bf16 compute with fp32 master weights, AdamW, synthetic
 uniform-random tokens, random-init weights; weak scaling with 8 sequences per
-GPU (global batch 64 at 8 GPUs) in microbatches of 8 sequences; the
+GPU (global batch 64 at 8 GPUs), each replica's batch in one microbatch (at most 32 sequences); the
 tensor-parallel grid grows towards r=c=d=2: 1 -> (1,1,1), 2 -> d=2,
 4 -> r=2,d=2, 8 -> r=c=d=2.
 
@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 
 GRIDS = {1: (1, 1, 1), 2: (1, 1, 2), 4: (2, 1, 2), 8: (2, 2, 2)}  # (r, c, d)
 SEQS_PER_GPU = 8
-MICRO_BATCH = 8
+MICRO_BATCH = 32  # sequences per microbatch (upper bound; a replica's whole batch when it is smaller)
 
 
 def parse():

@@ -60,6 +60,47 @@ def _gemm_ar_case(rank, world):
     return results
 
 
+def _gemm_rs_case(rank, world):
+    import torch.distributed as dist
+
+    from axonn_b200.ops import _lib
+    from axonn_b200.parallel import fused
+
+    dev = torch.device("cuda", rank)
+    group = dist.group.WORLD
+    out = []
+    for (M, N, K) in [(512, 256, 1024), (2048, 1024, 4096), (4096, 2048, 512), (192, 136, 264)]:
+        for rep in range(2):
+            g = torch.Generator(device=dev).manual_seed(31 * rank + M + rep)
+            a = (torch.randn(K, M, device=dev, generator=g) * 0.5).bfloat16()   # dY  [tokens, out]
+            b = (torch.randn(K, N, device=dev, generator=g) * 0.5).bfloat16()   # X   [tokens, in]
+            assert fused.reduce_scatter_usable(group, a, M)
+            shard = fused.gemm_reduce_scatter(2, a, b, group)
+            full = (a.float().t() @ b.float()).bfloat16().float()
+            dist.all_reduce(full)
+            R = M // world
+            want = full[rank * R:(rank + 1) * R]
+            torch.cuda.synchronize()
+            status = _lib.lib().axb_device_status(rank, 1)
+            err = (shard.float() - want).abs().max().item()
+            out.append((M, N, K, status, err, want.abs().max().item()))
+            # accumulate into an fp32 buffer
+            acc = torch.ones(R, N, device=dev)
+            fused.gemm_reduce_scatter(2, a, b, group, out=acc, accumulate=True)
+            torch.cuda.synchronize()
+            err2 = (acc - (want + 1)).abs().max().item()
+            out.append((M, N, K, _lib.lib().axb_device_status(rank, 1), err2, want.abs().max().item()))
+    return out
+
+
+def test_gemm_reduce_scatter_two_gpus():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    for per_rank in run_distributed(_gemm_rs_case, 2, backend="nccl", timeout=300):
+        for M, N, K, status, err, scale in per_rank:
+            assert status == 0
+            assert err <= 1.6e-2 * scale + 1e-3, (M, N, K, err, scale)
+
+
 def test_gemm_all_reduce_two_gpus():
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     res = run_distributed(_gemm_ar_case, 2, backend="nccl", timeout=300)
