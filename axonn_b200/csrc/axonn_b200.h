@@ -29,10 +29,12 @@ int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias
              int M, int N, int K, int in_dtype, int out_dtype, int epilogue, int accumulate,
              int device, void* stream);
 
-/* Peer-memory context of the fused GEMM + all-reduce epilogue.  All pointers are device addresses:
+/* Peer-memory context of the fused GEMM + all-reduce / reduce-scatter.  All pointers are device addresses:
  * the *_local ones in this rank's symmetric buffer, the *_peer[j] ones the same regions of rank j mapped
- * into this process.  Inboxes and flag arrays are indexed [source rank][slot]; `epoch` increases by one per
- * call on the group and selects (by parity, done by the caller) which of two inbox/flag sets is used. */
+ * into this process.  `inbox_*` is each rank's outbox of bf16 partial tiles ([tile][128 rows][bn columns]),
+ * written locally by the GEMM CTAs and read by the comm CTAs of every rank that reduces those rows.  Flag
+ * arrays are indexed [source rank][tile * 4 + warp]; `epoch` increases by one per call on the group and
+ * selects (by parity, done by the caller) which of two outbox/flag sets is used. */
 typedef struct AxbArCtx {
   int n;                      /* ranks in the group (2..8) */
   int rank;                   /* this rank's index in the group */
@@ -49,7 +51,31 @@ typedef struct AxbArCtx {
   unsigned long long flags_per_src;      /* flags per source */
   int mode;                   /* 0: all-reduce of C; 1: reduce-scatter of C by row blocks */
   int rows_per_shard;         /* mode 1: rows of C owned by each rank (multiple of 32) */
+  int comm_ctas;              /* CTAs of the launch dedicated to the reduction over peer memory (0: default 32) */
+  int pad_;
 } AxbArCtx;
+
+/* Peer-memory context of the fused all-gather -> GEMM: B's row blocks ("shards", one per rank) are pulled
+ * from the owners' outboxes into a local staging copy of B by the first `n_copy` CTAs while the other tiles
+ * compute.  `wait_local[j]` reaches `epoch` when rank j has published its shard; `shard_ready[z]` is a local
+ * counter that reaches `ready_target` when all copy CTAs have landed shard z. */
+typedef struct AxbAgCtx {
+  int n, rank;
+  unsigned int epoch;
+  int n_copy;
+  const void* outbox_peer[8];
+  void* staging;
+  unsigned long long shard_bytes;
+  unsigned int* shard_ready;
+  unsigned int ready_target;
+  int rows_per_shard;
+  unsigned int* wait_local;
+  unsigned int* done_peer[8];
+  unsigned int* counter;
+} AxbAgCtx;
+
+int axb_ag_gemm(int layout, const void* A, void* C, const void* bias, void* aux, int M, int N, int K, int in_dtype,
+                int out_dtype, int epilogue, int device, void* stream, const AxbAgCtx* ag, const AxbArCtx* ar);
 
 int axb_gemm_rs(int layout, const void* A, const void* B, void* C_shard, int M, int N, int K, int in_dtype,
                 int out_dtype, int accumulate, int device, void* stream, const AxbArCtx* ar);

@@ -1,0 +1,336 @@
+// Causal flash attention forward on tcgen05 tensor cores (sm_100a), grouped-query aware.
+//
+// Input is the fused projection output, packed [B, S, G, q_per_kv + 2, D]: for every KV group its query
+// heads, then its key head, then its value head.  One CTA handles one (batch, query head, 128-row query
+// tile) and walks the KV tiles up to the diagonal:
+//
+//   warp 0   TMA: Q once, then K_j / V_j into a 2-stage shared-memory ring (128-byte swizzle)
+//   warp 1   MMA: S_j = Q K_j^T into one of two TMEM score buffers (issued one tile ahead), then
+//            PV_j = P_j V_j into one of two TMEM output buffers; P_j is read from shared memory
+//            (K-major), V_j is consumed in place as an MN-major operand - no transposes
+//   warps 2-5 softmax: one thread per query row; tcgen05.ld the scores, online max / exp2 / row sum,
+//            write P_j (bf16) into shared memory in the tensor core's canonical swizzled layout,
+//            and fold the previous tile's PV product into the register-resident output row
+//            (o = o * alpha + PV), so score MMAs, exponentials and PV MMAs of neighbouring tiles
+//            overlap.
+//
+// Outputs: O [B, S, heads, D] bf16 and the per-row log-sum-exp (natural log, of the scaled scores)
+// [B, heads, S] fp32 for the backward pass.  All waits are bounded.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace axb {
+
+int make_tmap_2d_16bit(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, int dtype);
+
+struct FaParams {
+  __nv_bfloat16* out;
+  float* lse;
+  int B, S, G, qpk;
+  float scale_log2;
+  unsigned int* status;
+  unsigned long long timeout_ns;
+};
+
+constexpr int FA_BQ = 128, FA_BKV = 128, FA_THREADS = 192;
+
+template <int HD>
+struct FaSmem {
+  static constexpr int TILE = 128 * HD * 2;       // Q, K or V tile bytes
+  static constexpr int P_BYTES = 128 * 128 * 2;
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = TILE;               // 2 stages
+  static constexpr int V_OFF = 3 * TILE;           // 2 stages
+  static constexpr int P_OFF = 5 * TILE;
+  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int NBARS = 1 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 2 + 2;
+  static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
+  using S_ = FaSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S_::BAR_OFF);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = bars + 3;
+  uint64_t* kv_empty = bars + 5;
+  uint64_t* s_full = bars + 7;
+  uint64_t* s_empty = bars + 9;
+  uint64_t* p_full = bars + 11;
+  uint64_t* p_empty = bars + 12;
+  uint64_t* o_full = bars + 13;
+  uint64_t* o_empty = bars + 15;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + S_::NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = p.S / FA_BQ;
+  const int qt = nq - 1 - static_cast<int>(blockIdx.x);  // heaviest tiles first
+  const int head = blockIdx.y;
+  const int b = blockIdx.z;
+  const int g = head / p.qpk, jq = head % p.qpk;
+  const int n_kv = qt + 1;                               // causal: tiles 0..qt
+  const int row0 = b * p.S + qt * FA_BQ;                 // row in the [B*S, G*(qpk+2)*HD] view
+  const int col_q = (g * (p.qpk + 2) + jq) * HD;
+  const int col_k = (g * (p.qpk + 2) + p.qpk) * HD;
+  const int col_v = col_k + HD;
+  const uint64_t timeout = p.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4);
+    }
+    mbar_init(p_full, 4); mbar_init(p_empty, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) tma_prefetch_desc(&tmQKV);
+  if (warp == 1) { tmem_alloc(tmem_ptr_smem, 512); tmem_relinquish(); }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t tmem_s = tmem_base;          // 2 x 128 columns
+  const uint32_t tmem_o = tmem_base + 256;    // 2 x HD columns
+
+  if (warp == 0) {
+    if (elect_one()) {
+      bool ok = true;
+      mbar_expect_tx(q_full, S_::TILE);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + S_::Q_OFF + c * 16384, &tmQKV, q_full, col_q + 64 * c, row0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+        const int krow = b * p.S + j * FA_BKV;
+        mbar_expect_tx(&k_full[st], S_::TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_2d(smem + S_::K_OFF + st * S_::TILE + c * 16384, &tmQKV, &k_full[st], col_k + 64 * c, krow);
+        mbar_expect_tx(&v_full[st], S_::TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_2d(smem + S_::V_OFF + st * S_::TILE + c * 16384, &tmQKV, &v_full[st], col_v + 64 * c, krow);
+      }
+      if (!ok) {
+        // drain: give in-flight copies time to land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {}
+        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x401u;
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      bool ok = true;
+      const uint32_t idesc_s = umma_idesc(1, 0, 0, 128, 128);
+      const uint32_t idesc_o = umma_idesc(1, 0, 1, 128, HD);
+      const uint32_t q_addr = smem_u32(smem + S_::Q_OFF);
+      const uint32_t p_addr = smem_u32(smem + S_::P_OFF);
+      auto issue_s = [&](int j) {
+        const uint32_t k_addr = smem_u32(smem + S_::K_OFF + (j & 1) * S_::TILE);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_f16(tmem_s + (j & 1) * 128, umma_smem_desc(q_addr + off, 16, 1024), umma_smem_desc(k_addr + off, 16, 1024),
+                   idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[j & 1]);
+      };
+      ok = mbar_wait(q_full, 0, abort_flag, timeout) && mbar_wait(&k_full[0], 0, abort_flag, timeout);
+      if (ok) { tcgen05_fence_after(); issue_s(0); }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          const int u = j + 1;
+          if (!mbar_wait(&k_full[u & 1], (u >> 1) & 1, abort_flag, timeout) ||
+              !mbar_wait(&s_empty[u & 1], ((u >> 1) & 1) ^ 1, abort_flag, timeout)) { ok = false; break; }
+          tcgen05_fence_after();
+          issue_s(u);
+        }
+        if (!mbar_wait(p_full, j & 1, abort_flag, timeout) || !mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag, timeout) ||
+            !mbar_wait(&o_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag, timeout)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t v_addr = smem_u32(smem + S_::V_OFF + (j & 1) * S_::TILE);
+#pragma unroll
+        for (int kk = 0; kk < FA_BKV / 16; ++kk) {
+          const uint64_t adesc = umma_smem_desc(p_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+          // V: MN-major, 64-wide column chunks 16 KB apart (leading), 8-row groups 1 KB apart (stride)
+          const uint64_t bdesc = umma_smem_desc(v_addr + kk * 2048, 16384, 1024);
+          umma_f16(tmem_o + (j & 1) * HD, adesc, bdesc, idesc_o, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&o_full[j & 1]);
+        umma_commit(p_empty);
+        umma_commit(&kv_empty[j & 1]);
+      }
+      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x402u;
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output accumulation
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;                 // query row inside the tile
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    bool ok = true;
+    uint8_t* p_row = smem + S_::P_OFF + (r >> 3) * 1024 + (r & 7) * 128;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
+      tcgen05_fence_after();
+      const uint32_t s_addr = tmem_s + lane_base + (j & 1) * 128;
+      const bool diag = (j == qt);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = __uint_as_float(v[i]) * p.scale_log2;
+          if (!diag || (c * 32 + i) <= r) mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float alpha = exp2f(m - m_new);
+      if (!mbar_wait(p_empty, (j & 1) ^ 1, abort_flag, timeout)) { ok = false; break; }
+      // pass 2: exponentials, row sum, P tile (bf16, swizzled K-major layout)
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float e0 = exp2f(__uint_as_float(v[2 * i]) * p.scale_log2 - m_new);
+          float e1 = exp2f(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - m_new);
+          if (diag) {
+            if (c * 32 + 2 * i > r) e0 = 0.f;
+            if (c * 32 + 2 * i + 1 > r) e1 = 0.f;
+          }
+          const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+          // accumulate what the tensor core will actually see (bf16-rounded probabilities)
+          rowsum += __bfloat162float(h.x) + __bfloat162float(h.y);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        // columns [c*32, c*32+32): 64-column block (c >> 1), 16-byte chunks ((c & 1) * 4 + t), t = 0..3
+        uint8_t* blk = p_row + (c >> 1) * 16384;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int chunk = ((c & 1) * 4 + t) ^ (r & 7);
+          *reinterpret_cast<uint4*>(blk + chunk * 16) =
+              make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
+        }
+      }
+      tcgen05_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&s_empty[j & 1]); mbar_arrive(p_full); }
+      l = l * alpha + rowsum;
+      m = m_new;
+      // fold the previous tile's PV product into the output row
+      if (j > 0) {
+        const int u = j - 1;
+        if (!mbar_wait(&o_full[u & 1], (u >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t o_addr = tmem_o + lane_base + (u & 1) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(o_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_empty[u & 1]);
+      }
+      alpha_prev = alpha;
+    }
+    if (ok) {
+      const int u = n_kv - 1;
+      if (mbar_wait(&o_full[u & 1], (u >> 1) & 1, abort_flag, timeout)) {
+        tcgen05_fence_after();
+        const uint32_t o_addr = tmem_o + lane_base + (u & 1) * HD;
+        const float inv_l = 1.f / l;
+        const size_t heads = static_cast<size_t>(p.G) * p.qpk;
+        __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + qt * FA_BQ + r) * heads + head) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(o_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int e = t * 8 + i * 2;
+              const float a0 = (o[c * 32 + e] * alpha_prev + __uint_as_float(v[e])) * inv_l;
+              const float a1 = (o[c * 32 + e + 1] * alpha_prev + __uint_as_float(v[e + 1])) * inv_l;
+              const __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
+              w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        p.lse[(static_cast<size_t>(b) * heads + head) * p.S + qt * FA_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
+      } else {
+        ok = false;
+      }
+    }
+    if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x404u;
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+template <int HD>
+static int fa_launch(const CUtensorMap& tm, const FaParams& p, int device, cudaStream_t s) {
+  using S_ = FaSmem<HD>;
+  static bool configured[64] = {false};
+  auto kern = fa_fwd_kernel<HD>;
+  if (!configured[device & 63]) {
+    AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_::TOTAL));
+    configured[device & 63] = true;
+  }
+  dim3 grid(p.S / FA_BQ, p.G * p.qpk, p.B);
+  kern<<<grid, FA_THREADS, S_::TOTAL, s>>>(tm, p);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace axb
+
+// qkv: [B, S, G, qpk + 2, D] bf16 contiguous; out: [B, S, G*qpk, D] bf16; lse: [B, G*qpk, S] fp32.
+extern "C" int axb_flash_attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int G, int qpk, int D,
+                                  float scale, int device, void* stream) {
+  using namespace axb;
+  if (D != 64 && D != 128) { set_error("flash attention: head_dim must be 64 or 128"); return -1; }
+  if (S % 128) { set_error("flash attention: sequence length must be a multiple of 128"); return -1; }
+  CUtensorMap tm;
+  if (make_tmap_2d_16bit(&tm, qkv, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(G) * (qpk + 2) * D, 128, 0))
+    return -1;
+  FaParams p;
+  p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse; p.B = B; p.S = S; p.G = G; p.qpk = qpk;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  unsigned int* st = nullptr;
+  if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
+  p.status = st; p.timeout_ns = 2000000000ull;
+  if (D == 128) return fa_launch<128>(tm, p, device, static_cast<cudaStream_t>(stream));
+  return fa_launch<64>(tm, p, device, static_cast<cudaStream_t>(stream));
+}

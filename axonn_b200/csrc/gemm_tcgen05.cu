@@ -22,6 +22,7 @@
 // Every wait is bounded; on expiry the CTA raises an abort flag, records the
 // reason in the device status word, drains its TMA copies, frees TMEM and
 // returns.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -46,6 +47,11 @@ struct GemmParams {
   unsigned int* status;
   unsigned long long timeout_ns;
   AxbArCtx ar;  // ar.n <= 1: plain GEMM; otherwise the epilogue all-reduces C over ar.n ranks
+  AxbAgCtx ag;  // ag.n <= 1: B is complete; otherwise B's row blocks are gathered from the peers in-kernel
+  int tn_offset;  // rotation of the N-tile order (all-gather mode: tiles of the local shard first)
+  int kb_offset;  // rotation of the K-block order (all-gather mode, B rows = K: local shard first)
+  int gemm_ctas;  // number of CTAs computing tiles; the remaining CTAs of the grid reduce over peer memory
+  int debug;      // timing experiments only (AXB_AR_DEBUG): 1 no system fence, 2 no peer stores, 4 no inbox loads
 };
 
 template <int BN>
@@ -94,6 +100,36 @@ __device__ __forceinline__ void unpack2(uint32_t u, int dtype, float& a, float& 
   }
 }
 
+// Store 8 consecutive elements starting at element offset `off` (16-byte aligned for 16-bit outputs).
+__device__ __forceinline__ void store_vec8(void* base, int out_dtype, size_t off, const float* v, bool accumulate) {
+  if (out_dtype == 2) {
+    float* p = reinterpret_cast<float*>(base) + off;
+    float4 a = make_float4(v[0], v[1], v[2], v[3]), b = make_float4(v[4], v[5], v[6], v[7]);
+    if (accumulate) {
+      const float4 oa = *reinterpret_cast<float4*>(p), ob = *reinterpret_cast<float4*>(p + 4);
+      a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w; b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
+    }
+    *reinterpret_cast<float4*>(p) = a; *reinterpret_cast<float4*>(p + 4) = b;
+  } else {
+    uint16_t* p = reinterpret_cast<uint16_t*>(base) + off;
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = v[i];
+    if (accumulate) {
+      const uint4 old = *reinterpret_cast<uint4*>(p);
+      float a, b;
+      unpack2(old.x, out_dtype, a, b); f[0] += a; f[1] += b;
+      unpack2(old.y, out_dtype, a, b); f[2] += a; f[3] += b;
+      unpack2(old.z, out_dtype, a, b); f[4] += a; f[5] += b;
+      unpack2(old.w, out_dtype, a, b); f[6] += a; f[7] += b;
+    }
+    uint4 o;
+    o.x = pack2(f[0], f[1], out_dtype); o.y = pack2(f[2], f[3], out_dtype);
+    o.z = pack2(f[4], f[5], out_dtype); o.w = pack2(f[6], f[7], out_dtype);
+    *reinterpret_cast<uint4*>(p) = o;
+  }
+}
+
 // Store 32 consecutive columns of one output row (fp32 values in v).
 __device__ __forceinline__ void store_row32(void* base, int out_dtype, size_t row, int ld, int col, int N,
                                             const float (&v)[32], bool accumulate) {
@@ -135,6 +171,16 @@ __device__ __forceinline__ void store_row32(void* base, int out_dtype, size_t ro
   }
 }
 
+// Named-barrier OR-reduction over the 128 epilogue threads (barrier 1): returns true if all passed true.
+__device__ __forceinline__ bool __syncthreads_or_named(bool ok) {
+  __shared__ int sh_fail;
+  if ((threadIdx.x - 64) == 0) sh_fail = 0;
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (!ok) sh_fail = 1;
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  return sh_fail == 0;
+}
+
 // ---- peer-memory helpers of the fused all-reduce epilogue
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -159,6 +205,223 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
   }
 }
 
+// 1-D bulk async copy global -> shared (no multicast), completion counted in bytes on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               : : "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// Finish 8 consecutive reduced values of one output row: bias / GELU / store.
+__device__ __forceinline__ void comm_finish8(const GemmParams& p, float* v, size_t row, int col) {
+  if (p.epilogue == 1 || p.epilogue == 2) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      v[e] += (p.in_dtype == 0) ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + e])
+                                : __half2float(reinterpret_cast<const __half*>(p.bias)[col + e]);
+  }
+  const size_t out_row = (p.ar.mode == 1) ? row - static_cast<size_t>(p.ar.rank) * p.ar.rows_per_shard : row;
+  if (p.epilogue >= 2) {
+    if (p.aux != nullptr) store_vec8(p.aux, p.out_dtype, out_row * p.N + col, v, false);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+  }
+  store_vec8(p.C, p.out_dtype, out_row * p.N + col, v, p.accumulate != 0);
+}
+
+__device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) {
+  float a, b;
+  unpack2(u.x, dtype, a, b); acc[0] += a; acc[1] += b;
+  unpack2(u.y, dtype, a, b); acc[2] += a; acc[3] += b;
+  unpack2(u.z, dtype, a, b); acc[4] += a; acc[5] += b;
+  unpack2(u.w, dtype, a, b); acc[6] += a; acc[7] += b;
+}
+
+// ---- comm CTA: reduces finished tiles over peer memory while the other CTAs of the same kernel compute.
+// Warp 0 is the fetcher: for every tile of this CTA (in the order the GEMM CTAs produce them) it waits until
+// this rank's and the peers' (tile, warp) flags are up and then pulls the peers' bf16 partial rows over
+// NVLink with bulk asynchronous copies (cp.async.bulk, no multicast) into a ring of shared-memory stages -
+// several tiles, i.e. hundreds of KB per CTA, are in flight at once.  Warps 1-5 are the reducers: they add
+// this rank's partial (local memory) and the peers' (shared memory) in rank order - identical bits on every
+// rank -, apply bias / GELU and write C.  In reduce-scatter mode only the 32-row groups owned by this rank
+// are fetched and reduced.
+template <int BN>
+__device__ __forceinline__ void comm_cta(const GemmParams& p, int group, int num_tiles, uint8_t* smem) {
+  __shared__ int sh_fail;
+  using S = GemmSmem<BN>;
+  constexpr int VPR = BN / 8;                       // 16-byte vectors per tile row
+  constexpr int TILE_BYTES = BM * BN * 2;
+  constexpr int GROUP_BYTES = 32 * BN * 2;          // one warp's 32 rows
+  const int ncomm = gridDim.x - p.gemm_ctas;
+  const int cid = blockIdx.x - p.gemm_ctas;
+  const int P = p.ar.n - 1;
+  const int stage_bytes = P * TILE_BYTES;
+  int D = S::BAR_OFFSET / stage_bytes;
+  if (D > 4) D = 4;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty = full + 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    sh_fail = 0;
+    for (int i = 0; i < 4; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 5); }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  volatile int* failp = &sh_fail;
+  auto mine_of = [&](int tile, int& tm, int& tn) -> unsigned {
+    tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+    unsigned mine = 0;
+    for (int q = 0; q < 4; ++q)
+      if (p.ar.mode == 0 || (tm * BM + q * 32) / p.ar.rows_per_shard == p.ar.rank) mine |= 1u << q;
+    return mine;
+  };
+  if (D >= 1) {
+    if (warp == 0) {
+      if (lane == 0) {
+        int k = 0;
+        bool ok = true;
+        for (int tile = cid; tile < num_tiles && ok; tile += ncomm) {
+          int tm, tn;
+          const unsigned mine = mine_of(tile, tm, tn);
+          if (mine == 0) continue;
+          const int st = k % D;
+          const uint32_t ph = (k / D) & 1;
+          if (!mbar_wait(&empty[st], ph ^ 1, failp, p.timeout_ns)) { ok = false; break; }
+          for (int j = 0; j < p.ar.n && ok; ++j)
+            for (int q = 0; q < 4 && ok; ++q)
+              if (mine & (1u << q))
+                ok = wait_flag_ge(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q,
+                                  p.ar.epoch, failp, p.timeout_ns);
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+          mbar_expect_tx(&full[st], static_cast<uint32_t>(__popc(mine) * P * GROUP_BYTES));
+          int pi = 0;
+          for (int j = 0; j < p.ar.n; ++j) {
+            if (j == p.ar.rank) continue;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ar.inbox_peer[j]) + static_cast<size_t>(tile) * TILE_BYTES;
+            uint8_t* dst = smem + st * stage_bytes + pi * TILE_BYTES;
+            if (!(p.debug & 4)) {
+              for (int q = 0; q < 4; ++q)
+                if (mine & (1u << q)) bulk_load_1d(dst + q * GROUP_BYTES, src + q * GROUP_BYTES, GROUP_BYTES, &full[st]);
+            } else {
+              // timing experiment: no NVLink traffic (local source)
+              const uint8_t* lsrc = reinterpret_cast<const uint8_t*>(p.ar.inbox_local) + static_cast<size_t>(tile) * TILE_BYTES;
+              for (int q = 0; q < 4; ++q)
+                if (mine & (1u << q)) bulk_load_1d(dst + q * GROUP_BYTES, lsrc + q * GROUP_BYTES, GROUP_BYTES, &full[st]);
+            }
+            ++pi;
+          }
+          ++k;
+        }
+        if (!ok) {
+          sh_fail = 1;
+          const uint64_t t0 = globaltimer_ns();
+          while (globaltimer_ns() - t0 < 200000ull) {}   // let copies in flight land before the CTA exits
+          *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
+        }
+      }
+    } else {
+      const int rid = threadIdx.x - 32, nred = blockDim.x - 32;
+      int k = 0;
+      bool ok = true;
+      for (int tile = cid; tile < num_tiles && ok; tile += ncomm) {
+        int tm, tn;
+        const unsigned mine = mine_of(tile, tm, tn);
+        if (mine == 0) continue;
+        const int st = k % D;
+        const uint32_t ph = (k / D) & 1;
+        if (!mbar_wait(&full[st], ph, failp, p.timeout_ns)) { ok = false; break; }
+        const uint4* local = reinterpret_cast<const uint4*>(p.ar.inbox_local) + static_cast<size_t>(tile) * BM * VPR;
+        const uint4* staged = reinterpret_cast<const uint4*>(smem + st * stage_bytes);
+        // batches of 8 vectors per thread: the 8 local loads are independent and overlap their latency
+        for (int base = rid; base < BM * VPR; base += nred * 8) {
+          uint4 loc[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int idx = base + k * nred;
+            loc[k] = (idx < BM * VPR && (mine & (1u << (idx / (32 * VPR))))) ? __ldcv(local + idx)
+                                                                            : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int idx = base + k * nred;
+            if (idx >= BM * VPR) continue;
+            const int r = idx / VPR, cv = idx - r * VPR;
+            if (!(mine & (1u << (r >> 5)))) continue;
+            const size_t row = static_cast<size_t>(tm) * BM + r;
+            const int col = tn * BN + cv * 8;
+            if (row >= static_cast<size_t>(p.M) || col >= p.N) continue;
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+            int pi = 0;
+            for (int j = 0; j < p.ar.n; ++j) {
+              if (j == p.ar.rank) acc_vec8(acc, loc[k], p.in_dtype);
+              else { acc_vec8(acc, staged[pi * (TILE_BYTES / 16) + idx], p.in_dtype); ++pi; }
+            }
+            comm_finish8(p, acc, row, col);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+        ++k;
+      }
+    }
+  } else {
+    // peers' tiles do not fit in shared memory (large groups with wide tiles): direct P2P loads
+    for (int tile = cid; tile < num_tiles; tile += ncomm) {
+      int tm, tn;
+      const unsigned mine = mine_of(tile, tm, tn);
+      if (mine == 0) continue;
+      if (threadIdx.x < 4 * p.ar.n) {
+        const int q = threadIdx.x & 3, j = threadIdx.x >> 2;
+        if ((mine & (1u << q)) &&
+            !wait_flag_ge(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q, p.ar.epoch,
+                          failp, p.timeout_ns))
+          sh_fail = 1;
+      }
+      __syncthreads();
+      if (sh_fail) break;
+      const size_t tile_vec0 = static_cast<size_t>(tile) * BM * VPR;
+      for (int idx = threadIdx.x; idx < BM * VPR; idx += blockDim.x) {
+        const int r = idx / VPR, cv = idx - r * VPR;
+        if (!(mine & (1u << (r >> 5)))) continue;
+        const size_t row = static_cast<size_t>(tm) * BM + r;
+        const int col = tn * BN + cv * 8;
+        if (row >= static_cast<size_t>(p.M) || col >= p.N) continue;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int j = 0; j < p.ar.n; ++j) {
+          const uint4* src = reinterpret_cast<const uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + tile_vec0;
+          acc_vec8(acc, __ldcv(src + idx), p.in_dtype);
+        }
+        comm_finish8(p, acc, row, col);
+      }
+    }
+    if (sh_fail && threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x121u;
+  }
+  // take part in the end-of-kernel completion count
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.ar.counter, 1u) == gridDim.x - 1) {
+      *p.ar.counter = 0;
+      __threadfence_system();
+      for (int j = 0; j < p.ar.n; ++j)
+        if (j != p.ar.rank) st_release_sys(p.ar.done_peer[j] + p.ar.rank, p.ar.epoch);
+    }
+  }
+  if (p.ag.n > 1 && threadIdx.x == 32) {
+    __threadfence();
+    if (atomicAdd(p.ag.counter, 1u) == gridDim.x - 1) {
+      *p.ag.counter = 0;
+      __threadfence_system();
+      for (int j = 0; j < p.ag.n; ++j)
+        if (j != p.ag.rank) st_release_sys(p.ag.done_peer[j] + p.ag.rank, p.ag.epoch);
+    }
+  }
+}
+
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -179,6 +442,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int group = (BN == 256) ? 16 : 8;
   const uint64_t timeout = p.timeout_ns;
+  const int gemm_ctas = p.gemm_ctas;   // CTAs [gemm_ctas, gridDim.x) are comm CTAs (reduction over peer memory)
+
+  if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
+    comm_cta<BN>(p, group, num_tiles, smem);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -211,11 +480,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (elect_one()) {
       int stage = 0; uint32_t phase = 0;
       uint32_t armed_mask = 0, armed_parity = 0;
+      uint32_t ag_ready_mask = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas) {
         int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+        tn += p.tn_offset; if (tn >= p.tiles_n) tn -= p.tiles_n;
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kbi = 0; kbi < num_kb; ++kbi) {
+          int kb = kbi + p.kb_offset; if (kb >= num_kb) kb -= num_kb;
+          if (p.ag.n > 1) {
+            // B row block needed by this load: rows n0.. (B is [N,K]) or rows k0.. (B is [K,N])
+            const int brow = (B_MN == 0) ? n0 : kb * BK;
+            const int shard = brow / p.ag.rows_per_shard;
+            if (!(ag_ready_mask & (1u << shard))) {
+              uint64_t t0 = 0;
+              for (uint32_t it = 0;; ++it) {
+                unsigned int v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ag.shard_ready + shard) : "memory");
+                if (static_cast<int>(v - p.ag.ready_target) >= 0) break;
+                if ((it & 0x3f) == 0x3f) {
+                  const uint64_t now = globaltimer_ns();
+                  if (t0 == 0) t0 = now;
+                  else if (*abort_flag || now - t0 > timeout) { *abort_flag = 1; ok = false; break; }
+                }
+              }
+              if (!ok) break;
+              asm volatile("fence.proxy.async;" ::: "memory");
+              ag_ready_mask |= 1u << shard;
+            }
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, timeout)) { ok = false; break; }
           uint8_t* sA = smem + stage * S::STAGE_BYTES;
           uint8_t* sB = sA + S::A_BYTES;
@@ -262,7 +555,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++t) {
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
         if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, timeout)) { ok = false; break; }
@@ -291,8 +584,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     bool ok = true;
     int t = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+    if (p.ag.n > 1 && static_cast<int>(blockIdx.x) < p.ag.n_copy) {
+      // ---- all-gather stage: pull this CTA's slice of every shard of B (own shard first) from the owners'
+      // outboxes over NVLink into the local staging copy of B, then count the slice as arrived.
+      const int tid = threadIdx.x - 64;  // 0..127
+      const size_t vecs = p.ag.shard_bytes / 16;
+      const size_t per = (vecs + p.ag.n_copy - 1) / p.ag.n_copy;
+      const size_t lo = per * blockIdx.x, hi = (lo + per < vecs) ? lo + per : vecs;
+      for (int s = 0; s < p.ag.n && ok; ++s) {
+        const int z = (p.ag.rank + s) % p.ag.n;
+        if (z != p.ag.rank) {
+          if (tid == 0) ok = wait_flag_ge(p.ag.wait_local + z, p.ag.epoch, abort_flag, timeout);
+          ok = __syncthreads_or_named(ok);
+          if (!ok) break;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(p.ag.outbox_peer[z]);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.ag.staging) + static_cast<size_t>(z) * p.ag.shard_bytes);
+        for (size_t i = lo + tid; i < hi; i += 128) dst[i] = src[i];
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid == 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag.shard_ready + z) : "memory");
+        }
+      }
+      if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x110u;
+    }
+    // Finish one tile: values v (one row, 32 columns) -> bias / GELU -> C.
+    auto finish_chunk = [&](float (&v)[32], size_t out_row, int col, bool store_ok) {
+      if (p.epilogue == 1 || p.epilogue == 2) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (col + i < p.N) {
+            float b = (p.in_dtype == 0)
+                          ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + i])
+                          : __half2float(reinterpret_cast<const __half*>(p.bias)[col + i]);
+            v[i] += b;
+          }
+        }
+      }
+      if (p.epilogue >= 2) {
+        if (p.aux != nullptr && store_ok) store_row32(p.aux, p.out_dtype, out_row, p.N, col, p.N, v, false);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+      }
+      if (store_ok) store_row32(p.C, p.out_dtype, out_row, p.N, col, p.N, v, p.accumulate != 0);
+    };
+
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++t) {
       int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+      tn += p.tn_offset; if (tn >= p.tiles_n) tn -= p.tiles_n;
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
       if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, timeout)) { ok = false; break; }
@@ -300,128 +641,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const size_t row = static_cast<size_t>(tm) * BM + q * 32 + lane;
       const bool row_ok = row < static_cast<size_t>(p.M);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-      // slot of this (tile, warp) in every inbox: [chunk][vec 0..3][lane] 16-byte words
-      const size_t slot_vec = (static_cast<size_t>(tile) * 4 + q) * (BN / 32) * 4 * 32;
-      // Reduce-scatter mode: rows [o * rows_per_shard, (o + 1) * rows_per_shard) of C belong to rank o; a warp's
-      // 32 rows always have one owner (rows_per_shard is a multiple of 32).
-      int owner = -1;
-      bool do_final = true;
-      size_t out_row = row;
-      if (p.ar.n > 1 && p.ar.mode == 1) {
-        owner = (tm * BM + q * 32) / p.ar.rows_per_shard;
-        do_final = owner == p.ar.rank;
-        out_row = row - static_cast<size_t>(p.ar.rank) * p.ar.rows_per_shard;
-      }
-      if (p.ar.n > 1 && (p.ar.mode == 0 || (owner != p.ar.rank && owner < p.ar.n))) {
-        // ---- phase A: push this warp's bf16 partial (32 rows x BN cols) into the inbox of every peer
-        // (all-reduce) or of the rows' owner (reduce-scatter)
+      if (p.ar.n <= 1) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          if (tn * BN + c * 32 >= p.N) break;
+          const int col = tn * BN + c * 32;
+          if (col >= p.N) break;  // uniform across the warp
           uint32_t r[32];
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
-          uint4 w[4];
+          float v[32];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            w[i].x = pack2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]), p.in_dtype);
-            w[i].y = pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]), p.in_dtype);
-            w[i].z = pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]), p.in_dtype);
-            w[i].w = pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]), p.in_dtype);
-          }
-          for (int j = 0; j < p.ar.n; ++j) {
-            if (j == p.ar.rank || (p.ar.mode == 1 && j != owner)) continue;
-            uint4* dst = reinterpret_cast<uint4*>(p.ar.inbox_peer[j]) +
-                         static_cast<size_t>(p.ar.rank) * p.ar.inbox_vecs_per_src + slot_vec + (c * 4) * 32 + lane;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i * 32] = w[i];
-          }
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          finish_chunk(v, row, col, row_ok);
         }
-        __threadfence_system();
+        tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          for (int j = 0; j < p.ar.n; ++j) {
-            if (j == p.ar.rank || (p.ar.mode == 1 && j != owner)) continue;
-            st_release_sys(p.ar.flags_peer[j] + static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + q,
-                           p.ar.epoch);
-          }
-        }
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        continue;
       }
-      if (p.ar.n > 1 && do_final) {
-        // ---- phase B: wait for every peer's partial of the same (tile, warp)
-        if (lane == 0) {
-          for (int j = 0; j < p.ar.n && ok; ++j) {
-            if (j == p.ar.rank) continue;
-            ok = wait_flag_ge(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q,
-                              p.ar.epoch, abort_flag, timeout);
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-      }
-      const bool store_ok = row_ok && do_final;
-      if (do_final)
+      // ---- communication mode: the epilogue only parks this warp's bf16 partial (32 rows x BN columns) in
+      // this rank's peer-readable outbox ([tile][128 rows][BN columns]) and raises the (tile, warp) flag on
+      // the ranks that will reduce these rows; the comm CTAs of those ranks do the rest.
+      const int owner = (p.ar.mode == 1) ? (tm * BM + q * 32) / p.ar.rows_per_shard : -1;
+      uint16_t* part = reinterpret_cast<uint16_t*>(p.ar.inbox_local) +
+                       (static_cast<size_t>(tile) * BM + q * 32 + lane) * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
-        const int col = tn * BN + c * 32;
-        if (col >= p.N) break;  // uniform across the warp
+        if (tn * BN + c * 32 >= p.N) break;
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        if (p.ar.n > 1) {
-          // sum the bf16-rounded partials of all ranks in rank order: every rank gets the same bits
-          float acc[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-          for (int j = 0; j < p.ar.n; ++j) {
-            if (j == p.ar.rank) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                float a, b;
-                unpack2(pack2(v[2 * i], v[2 * i + 1], p.in_dtype), p.in_dtype, a, b);
-                acc[2 * i] += a; acc[2 * i + 1] += b;
-              }
-            } else {
-              const uint4* src = reinterpret_cast<const uint4*>(p.ar.inbox_local) +
-                                 static_cast<size_t>(j) * p.ar.inbox_vecs_per_src + slot_vec + (c * 4) * 32 + lane;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const uint4 u = __ldcv(src + i * 32);
-                float a, b;
-                unpack2(u.x, p.in_dtype, a, b); acc[8 * i + 0] += a; acc[8 * i + 1] += b;
-                unpack2(u.y, p.in_dtype, a, b); acc[8 * i + 2] += a; acc[8 * i + 3] += b;
-                unpack2(u.z, p.in_dtype, a, b); acc[8 * i + 4] += a; acc[8 * i + 5] += b;
-                unpack2(u.w, p.in_dtype, a, b); acc[8 * i + 6] += a; acc[8 * i + 7] += b;
-              }
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = acc[i];
+        for (int i = 0; i < 4; ++i) {
+          uint4 w;
+          w.x = pack2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]), p.in_dtype);
+          w.y = pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]), p.in_dtype);
+          w.z = pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]), p.in_dtype);
+          w.w = pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]), p.in_dtype);
+          *reinterpret_cast<uint4*>(part + c * 32 + i * 8) = w;
         }
-        if (p.epilogue == 1 || p.epilogue == 2) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (col + i < p.N) {
-              float b = (p.in_dtype == 0)
-                            ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + i])
-                            : __half2float(reinterpret_cast<const __half*>(p.bias)[col + i]);
-              v[i] += b;
-            }
-          }
-        }
-        if (p.epilogue >= 2) {
-          if (p.aux != nullptr && store_ok) store_row32(p.aux, p.out_dtype, out_row, p.N, col, p.N, v, false);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-        }
-        if (store_ok) store_row32(p.C, p.out_dtype, out_row, p.N, col, p.N, v, p.accumulate != 0);
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      if (lane == 0) {
+        mbar_arrive(&tmem_empty[buf]);   // accumulator is free: the MMA warp runs ahead
+        __threadfence_system();          // the partial (local memory) is visible before any flag
+        for (int j = 0; j < p.ar.n; ++j) {
+          if (p.ar.mode == 1 && j != owner) continue;
+          unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
+                            static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + q;
+          st_release_sys(f, p.ar.epoch);
+        }
+      }
     }
     if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x104u;
   }
@@ -429,6 +700,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+  if (p.ag.n > 1 && threadIdx.x == 32) {
+    __threadfence();
+    if (atomicAdd(p.ag.counter, 1u) == gridDim.x - 1) {
+      *p.ag.counter = 0;
+      __threadfence_system();
+      for (int j = 0; j < p.ag.n; ++j)
+        if (j != p.ag.rank) st_release_sys(p.ag.done_peer[j] + p.ag.rank, p.ag.epoch);
+    }
+  }
   if (p.ar.n > 1 && threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(p.ar.counter, 1u) == gridDim.x - 1) {
@@ -500,7 +780,17 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+  const int sms = sm_count(device);
+  // every CTA must be resident at once (comm CTAs wait for GEMM CTAs of the same launch): grid <= #SMs
+  int n_comm = 0;
+  if (p.ar.n > 1) {
+    n_comm = p.ar.comm_ctas > 0 ? p.ar.comm_ctas : 32;
+    if (n_comm > sms / 2) n_comm = sms / 2;
+    if (n_comm > tiles) n_comm = tiles;
+  }
+  p.gemm_ctas = tiles < sms - n_comm ? tiles : sms - n_comm;
+  if (p.ag.n > 1 && p.ag.n_copy > p.gemm_ctas) { p.ag.n_copy = p.gemm_ctas; p.ag.ready_target = p.ag.n_copy; }
+  const int grid = p.gemm_ctas + n_comm;
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
   AXB_CUDA(cudaGetLastError());
   return 0;
@@ -510,7 +800,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
 
 static int gemm_common(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,
                        int K, int in_dtype, int out_dtype, int epilogue, int accumulate, int device, void* stream,
-                       const AxbArCtx* ar) {
+                       const AxbArCtx* ar, const AxbAgCtx* ag = nullptr) {
   using namespace axb;
   if (M <= 0 || N <= 0 || K <= 0) { set_error("axb_gemm: empty problem"); return -1; }
   if (layout < 0 || layout > 2) { set_error("axb_gemm: bad layout %d", layout); return -1; }
@@ -522,7 +812,8 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
 
   const int tiles_m = (M + BM - 1) / BM;
   const bool wide = static_cast<long long>(tiles_m) * ((N + 255) / 256) >= sm_count(device);
-  const int BN = (ar && ar->n > 1) ? ar->bn : (wide ? 256 : 128);
+  int BN = (ar && ar->n > 1) ? ar->bn : (wide ? 256 : 128);
+  if (ag && ag->n > 1 && layout == 0 && ag->rows_per_shard % BN != 0) BN = 128;
   const int a_mn = (layout == 2) ? 1 : 0;
   const int b_mn = (layout == 0) ? 0 : 1;
 
@@ -540,12 +831,45 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
   if (ar && ar->n > 1) {
     p.ar = *ar;
     const long long tiles = static_cast<long long>(tiles_m) * ((N + BN - 1) / BN);
-    if (tiles * 4 > ar->flags_per_src || tiles * 4 * (BN / 32) * 128 > ar->inbox_vecs_per_src) {
+    if (tiles * 4 > ar->flags_per_src || tiles * BM * (BN / 8) > ar->inbox_vecs_per_src) {
       set_error("axb_gemm_ar: communication buffers too small for %lld tiles", tiles);
       return -1;
     }
   } else {
     p.ar.n = 1;
+  }
+  p.tn_offset = 0; p.kb_offset = 0;
+  { const char* dbg = getenv("AXB_AR_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
+  if (ag && ag->n > 1) {
+    p.ag = *ag;
+    {
+      // every copy CTA must be resident: never more of them than CTAs in the grid
+      const long long tiles = static_cast<long long>(tiles_m) * ((N + BN - 1) / BN);
+      const long long grid = tiles < sm_count(device) ? tiles : sm_count(device);
+      if (p.ag.n_copy > grid) p.ag.n_copy = static_cast<int>(grid);
+      p.ag.ready_target = static_cast<unsigned int>(p.ag.n_copy);
+      AXB_CUDA(cudaMemsetAsync(p.ag.shard_ready, 0, 8 * sizeof(unsigned int), static_cast<cudaStream_t>(stream)));
+    }
+    if (layout == 0) {
+      if (ag->rows_per_shard % BN != 0 || static_cast<long long>(ag->rows_per_shard) * ag->n != N) {
+        set_error("axb_ag_gemm: shard rows (%d) must be a multiple of the tile width %d and n*rows == N", ag->rows_per_shard, BN);
+        return -1;
+      }
+      // With the all-reduce epilogue every rank must walk the tiles in the same order (partials are matched
+      // by tile index and a rank waits for its peers' partial of the tile it finished one step earlier).
+      p.tn_offset = (ar && ar->n > 1) ? 0 : ag->rank * (ag->rows_per_shard / BN);
+    } else if (layout == 1) {
+      if (ag->rows_per_shard % BK != 0 || static_cast<long long>(ag->rows_per_shard) * ag->n != K) {
+        set_error("axb_ag_gemm: shard rows (%d) must be a multiple of %d and n*rows == K", ag->rows_per_shard, BK);
+        return -1;
+      }
+      p.kb_offset = ag->rank * (ag->rows_per_shard / BK);
+    } else {
+      set_error("axb_ag_gemm: layout must be 0 or 1");
+      return -1;
+    }
+  } else {
+    p.ag.n = 1;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define AXB_DISPATCH(BN_, A_, B_) return launch<BN_, A_, B_>(tmA, tmB, p, device, s)
@@ -569,6 +893,19 @@ extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const
 
 // C = allreduce_over_ranks(op(A) op(B)) (+bias, GELU): every rank of the group calls this with its partial
 // operands; the epilogue exchanges bf16 partial tiles through peer-mapped inboxes (see AxbArCtx).
+// C = op(A) op(B) where B ([N,K] for layout 0, [K,N] for layout 1) is the concatenation along its rows of one
+// shard per rank: the kernel pulls the shards from the ranks' outboxes into `ag->staging` (which holds the
+// complete B afterwards) while the tiles that only need already-present shards are being computed.  The B
+// argument of the GEMM is `ag->staging`.  May be combined with the all-reduce epilogue (`ar`, optional).
+extern "C" int axb_ag_gemm(int layout, const void* A, void* C, const void* bias, void* aux, int M, int N, int K,
+                           int in_dtype, int out_dtype, int epilogue, int device, void* stream, const AxbAgCtx* ag,
+                           const AxbArCtx* ar) {
+  if (!ag || ag->n < 2 || ag->n > 8) { axb::set_error("axb_ag_gemm: group size must be 2..8"); return -1; }
+  if (ag->n_copy < 1 || ag->shard_bytes % 16) { axb::set_error("axb_ag_gemm: bad copy configuration"); return -1; }
+  return gemm_common(layout, A, ag->staging, C, bias, aux, M, N, K, in_dtype, out_dtype, epilogue, 0, device, stream,
+                     (ar && ar->n > 1) ? ar : nullptr, ag);
+}
+
 // C_shard[rows_per_shard, N] (+)= reduce_scatter_over_ranks(op(A) op(B)) along the rows of the product:
 // rank o receives rows [o * rows_per_shard, (o + 1) * rows_per_shard).  M must equal n * rows_per_shard.
 extern "C" int axb_gemm_rs(int layout, const void* A, const void* B, void* C_shard, int M, int N, int K, int in_dtype,

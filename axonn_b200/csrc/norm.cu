@@ -161,7 +161,7 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
     T* dxr = dx + static_cast<size_t>(row) * H;
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
-      const int c = threadIdx.x + k * NORM_THREADS;
+      const int c = threadIdx.x + k * blockDim.x;
       if (c < nchunk) {
         float f[8], d[8], g[8], o[8];
         Vec8<T>::load(xr + c * 8, f); Vec8<T>::load(dyr + c * 8, d); Vec8<T>::load(gamma + c * 8, g);
@@ -178,7 +178,7 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
   if (mode != 1 && dgamma_part) {
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
-      const int c = threadIdx.x + k * NORM_THREADS;
+      const int c = threadIdx.x + k * blockDim.x;
       if (c >= nchunk) continue;
       float* pg = dgamma_part + static_cast<size_t>(blockIdx.x) * H + c * 8;
 #pragma unroll
@@ -219,12 +219,13 @@ int sm_count(int device);
 template <typename T>
 static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
                       int H_total, float eps, int rms, int mode, int grid, cudaStream_t s) {
+  const int threads = (H / 8 <= 128) ? 128 : NORM_THREADS;  // no idle threads for narrow (sharded) rows
   if (rms)
-    norm_fwd_kernel<T, true><<<grid, NORM_THREADS, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
-                                                          stats, rows, H, H_total, eps, mode);
+    norm_fwd_kernel<T, true><<<grid, threads, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
+                                                     stats, rows, H, H_total, eps, mode);
   else
-    norm_fwd_kernel<T, false><<<grid, NORM_THREADS, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
-                                                           stats, rows, H, H_total, eps, mode);
+    norm_fwd_kernel<T, false><<<grid, threads, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
+                                                      stats, rows, H, H_total, eps, mode);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }
@@ -234,9 +235,10 @@ static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const fl
                       float* dgp, float* dbp, int rows, int H, int H_total, int rms, int mode, int grid,
                       cudaStream_t s) {
   const int nchunk = H / 8;
-  const int ch = (nchunk + NORM_THREADS - 1) / NORM_THREADS;
+  const int threads = (nchunk <= 128) ? 128 : NORM_THREADS;
+  const int ch = (nchunk + threads - 1) / threads;
 #define AXB_NORM_BWD(RMS_, CH_)                                                                              \
-  norm_bwd_kernel<T, RMS_, CH_><<<grid, NORM_THREADS, 0, s>>>((const T*)dy, (const T*)x, (const T*)gamma, stats, \
+  norm_bwd_kernel<T, RMS_, CH_><<<grid, threads, 0, s>>>((const T*)dy, (const T*)x, (const T*)gamma, stats, \
                                                               (T*)dx, sums, dgp, dbp, rows, H, H_total, mode)
   if (rms) {
     if (ch <= 1) AXB_NORM_BWD(true, 1); else if (ch <= 2) AXB_NORM_BWD(true, 2);
@@ -253,7 +255,7 @@ static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const fl
 }  // namespace axb
 
 extern "C" int axb_norm_grid(int device, int rows) {
-  int g = 6 * axb::sm_count(device);
+  int g = 8 * axb::sm_count(device);
   return rows < g ? rows : g;
 }
 

@@ -94,41 +94,54 @@ class AsyncLinear(Function):
         if torch.is_autocast_enabled(input_.device.type):
             compute_dtype = torch.get_autocast_dtype(input_.device.type)
             input_ = input_.to(compute_dtype)
-        w = _gathered_weight(w_shard, depth_parallel_group, local_weight_shape, cache)
-        if w.dtype != compute_dtype:
-            w = w.to(compute_dtype)
         x2 = input_.reshape(-1, input_.shape[-1])
         inner_n = dist.get_world_size(forward_all_reduce_group)
+        depth_n = dist.get_world_size(depth_parallel_group)
         b = None if bias is None else bias.to(compute_dtype)
         pre_act = None
-        if inner_n > 1 and fused.usable(forward_all_reduce_group, x2):
-            # GEMM whose epilogue all-reduces the output tiles over NVLink peer memory,
-            # then applies bias / GELU to the reduced values
-            epi = ops.EPI_NONE
-            if activation == "gelu":
-                pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype, device=x2.device)
-                epi = ops.EPI_BIAS_GELU if b is not None else ops.EPI_GELU
-            elif b is not None:
-                epi = ops.EPI_BIAS
-            out = fused.gemm_all_reduce(0, x2, w, forward_all_reduce_group, bias=b, epilogue=epi, aux=pre_act)
-        elif inner_n == 1 and x2.is_cuda and (b is not None or activation):
-            if activation == "gelu":
-                pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype, device=x2.device)
-                epi = ops.EPI_BIAS_GELU if b is not None else ops.EPI_GELU
-                out = ops.matmul_nt(x2, w, bias=b, epilogue=epi, aux=pre_act)
-            else:
-                out = ops.matmul_nt(x2, w, bias=b, epilogue=ops.EPI_BIAS)
-        else:
-            out = ops.matmul_nt(x2, w)
-            if inner_n > 1:
-                dist.all_reduce(out, group=forward_all_reduce_group)
-            if b is not None:
-                out = out.add_(b)
-            if activation == "gelu":
-                pre_act = out
-                out = ops.gelu(out.detach())
         if activation not in (None, "gelu"):
             raise ValueError(f"unsupported fused activation {activation!r}")
+        epi = ops.EPI_NONE
+        if activation == "gelu":
+            epi = ops.EPI_BIAS_GELU if b is not None else ops.EPI_GELU
+        elif b is not None:
+            epi = ops.EPI_BIAS
+        prefetched = id(w_shard) in oc.weights_cache
+        if (depth_n > 1 and not prefetched and (inner_n == 1 or fused.usable(forward_all_reduce_group, x2))
+                and fused.all_gather_usable(depth_parallel_group, x2, w_shard, local_weight_shape, 0)):
+            # one kernel: pull the depth shards of W over NVLink while computing, multiply, (all-reduce), epilogue
+            if activation == "gelu":
+                pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype, device=x2.device)
+            out, w = fused.all_gather_gemm(0, x2, w_shard, depth_parallel_group, local_weight_shape,
+                                           ar_group=forward_all_reduce_group if inner_n > 1 else None,
+                                           bias=b, epilogue=epi, aux=pre_act)
+            if cache:
+                oc.weights_cache[id(w_shard)] = [w_shard, w.reshape(-1), None]
+        else:
+            w = _gathered_weight(w_shard, depth_parallel_group, local_weight_shape, cache)
+            if w.dtype != compute_dtype:
+                w = w.to(compute_dtype)
+            if inner_n > 1 and fused.usable(forward_all_reduce_group, x2):
+                # GEMM whose epilogue all-reduces the output tiles over NVLink peer memory,
+                # then applies bias / GELU to the reduced values
+                if activation == "gelu":
+                    pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype,
+                                          device=x2.device)
+                out = fused.gemm_all_reduce(0, x2, w, forward_all_reduce_group, bias=b, epilogue=epi, aux=pre_act)
+            elif inner_n == 1 and x2.is_cuda and epi != ops.EPI_NONE:
+                if activation == "gelu":
+                    pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype,
+                                          device=x2.device)
+                out = ops.matmul_nt(x2, w, bias=b, epilogue=epi, aux=pre_act)
+            else:
+                out = ops.matmul_nt(x2, w)
+                if inner_n > 1:
+                    dist.all_reduce(out, group=forward_all_reduce_group)
+                if b is not None:
+                    out = out.add_(b)
+                if activation == "gelu":
+                    pre_act = out
+                    out = ops.gelu(out.detach())
         ctx.save_for_backward(input_, w_shard, pre_act)
         ctx.has_bias = bias is not None
         ctx.bias_dtype = None if bias is None else bias.dtype
@@ -178,7 +191,13 @@ class AsyncLinear(Function):
         if outer_n > 1 or not overlap_rs:
             # dgrad first so that its all-reduce hides under the wgrad GEMM
             if ctx.needs_input_grad[0]:
-                if outer_n > 1 and fused.usable(ctx.backward_all_reduce_group, go2):
+                if (depth_n > 1 and id(w_shard) not in oc.weights_cache
+                        and (outer_n == 1 or fused.usable(ctx.backward_all_reduce_group, go2))
+                        and fused.all_gather_usable(ctx.depth_parallel_group, go2, w_shard, ctx.shape, 1)):
+                    grad_input, _ = fused.all_gather_gemm(
+                        1, go2.contiguous(), w_shard, ctx.depth_parallel_group, ctx.shape,
+                        ar_group=ctx.backward_all_reduce_group if outer_n > 1 else None)
+                elif outer_n > 1 and fused.usable(ctx.backward_all_reduce_group, go2):
                     w = _gathered_weight(w_shard, ctx.depth_parallel_group, ctx.shape, cache=False)
                     if w.dtype != ctx.compute_dtype:
                         w = w.to(ctx.compute_dtype)

@@ -32,11 +32,12 @@ def flash_attention(q, k, v, causal=True, scale=None):
     if q.is_cuda and not _IMPL["force_torch"]:
         from . import attention_cuda
 
-        if attention_cuda.available():
+        if attention_cuda.available() and causal:
             B, S, hq, D = q.shape
             G = k.shape[2]
             qkv = torch.cat([q.reshape(B, S, G, hq // G, D), k.unsqueeze(3), v.unsqueeze(3)], 3)
-            return attention_cuda.flash_attention_packed_cuda(qkv, causal, scale)
+            if attention_cuda.supported(qkv):
+                return attention_cuda.flash_attention_packed_cuda(qkv, causal, scale)
     return _sdpa(q, k, v, causal, scale)
 
 
@@ -48,7 +49,7 @@ def flash_attention_packed(qkv, causal=True, scale=None):
     if qkv.is_cuda and not _IMPL["force_torch"]:
         from . import attention_cuda
 
-        if attention_cuda.available():
+        if attention_cuda.available() and attention_cuda.supported(qkv) and causal:
             return attention_cuda.flash_attention_packed_cuda(qkv, causal, scale)
     q = qkv[:, :, :, :qpk].reshape(B, S, G * qpk, D)
     return _sdpa(q, qkv[:, :, :, qpk], qkv[:, :, :, qpk + 1], causal, scale)

@@ -13,6 +13,7 @@ size); the caller then uses ``torch.distributed``.
 """
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -34,6 +35,7 @@ class AxbArCtx(ctypes.Structure):
         ("counter", ctypes.c_void_p),
         ("inbox_vecs_per_src", ctypes.c_ulonglong), ("flags_per_src", ctypes.c_ulonglong),
         ("mode", ctypes.c_int), ("rows_per_shard", ctypes.c_int),
+        ("comm_ctas", ctypes.c_int), ("pad_", ctypes.c_int),
     ]
 
 
@@ -42,8 +44,8 @@ class _ArChannel:
 
     Layout of the symmetric allocation (same on every rank):
       [0, 4096)        control: done[n] (u32) at 0, CTA counter (u32) at 256
-      flags[parity]    n * flags_per_src u32
-      inbox[parity]    n * inbox_vecs_per_src 16-byte words
+      flags[parity]    n * flags_per_src u32   (indexed [source rank][tile * 4 + warp])
+      outbox[parity]   inbox_vecs_per_src 16-byte words: this rank's bf16 partial tiles, read by the peers
     """
 
     def __init__(self, group):
@@ -57,7 +59,7 @@ class _ArChannel:
 
     def _layout(self):
         fbytes = self.n * self.flags_per_src * 4
-        ibytes = self.n * self.inbox_vecs_per_src * 16
+        ibytes = self.inbox_vecs_per_src * 16
         f0 = _CTRL_BYTES
         i0 = (f0 + 2 * fbytes + 1023) // 1024 * 1024
         return f0, fbytes, i0, ibytes, i0 + 2 * ibytes
@@ -97,6 +99,7 @@ class _ArChannel:
         c.inbox_vecs_per_src = self.inbox_vecs_per_src
         c.flags_per_src = self.flags_per_src
         c.mode, c.rows_per_shard = mode, rows_per_shard
+        c.comm_ctas = int(os.environ.get("AXONN_COMM_CTAS", "0"))
         return c
 
 
@@ -105,6 +108,8 @@ _channels = {}
 
 def reset():
     _channels.clear()
+    _grad_channels.clear()
+    _ag_channels.clear()
 
 
 def usable(group, tensor) -> bool:
@@ -182,5 +187,212 @@ def gemm_reduce_scatter(layout, a, b, group, out_dtype=None, out=None, accumulat
     return out
 
 
+class AxbAgCtx(ctypes.Structure):
+    _fields_ = [("n", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint), ("n_copy", ctypes.c_int),
+                ("outbox_peer", ctypes.c_void_p * 8), ("staging", ctypes.c_void_p),
+                ("shard_bytes", ctypes.c_ulonglong), ("shard_ready", ctypes.c_void_p),
+                ("ready_target", ctypes.c_uint), ("rows_per_shard", ctypes.c_int),
+                ("wait_local", ctypes.c_void_p), ("done_peer", ctypes.c_void_p * 8), ("counter", ctypes.c_void_p)]
+
+
+class _AgChannel:
+    """Outboxes and flags of the fused all-gather -> GEMM for one (depth) group.
+    Control block: READY[n] at 0, DONE[n] at 64, CTA counter at 256, shard arrival counters at 320;
+    two outboxes (call parity) follow at 4096."""
+
+    _READY, _DONE, _COUNTER, _SHARD_READY = 0, 64, 256, 320
+
+    def __init__(self, group, shard_bytes):
+        from .moe_kernels import AxbMoeCtx  # same flag-kernel context layout
+
+        self._flag_ctx = AxbMoeCtx
+        self.group, self.n, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.capacity = (int(shard_bytes) + (1 << 20) - 1) // (1 << 20) * (1 << 20)
+        torch.cuda.synchronize()
+        self.buf = symm.SymmBuffer(group, _CTRL_BYTES + 2 * self.capacity, "ag_gemm")
+        self.buf.local.zero_()
+        torch.cuda.synchronize()
+        self.buf.barrier()
+        dist.barrier(group=group)
+        self.epoch = 1
+
+    def publish(self, shard):
+        """Copy my shard into this call's outbox and raise READY on every peer."""
+        L = _lib.lib()
+        self.epoch += 1
+        e, parity = self.epoch, self.epoch & 1
+        base = self.buf.peer_ptrs
+        dev = shard.device.index
+        c = self._flag_ctx()
+        c.n, c.rank, c.epoch, c.n_local = self.n, self.rank, e, 1
+        c.wait_local = base[self.rank] + self._DONE
+        c.wait_value = max(0, e - 2)
+        c.counter = base[self.rank] + self._COUNTER
+        for j in range(self.n):
+            c.buf_peer[j] = base[j]
+            c.signal_peer[j] = base[j] + self._READY
+        # the outbox of this parity was last read by the peers in call e-2
+        _lib.check(L.axb_moe_wait(ctypes.byref(c), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_wait")
+        nbytes = shard.numel() * shard.element_size()
+        off = _CTRL_BYTES + parity * self.capacity
+        self.buf.local[off:off + nbytes].view(shard.dtype).copy_(shard.reshape(-1))
+        _lib.check(L.axb_moe_signal(ctypes.byref(c), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_signal")
+        return e, parity, nbytes
+
+    def context(self, e, parity, nbytes, staging, rows_per_shard, n_copy):
+        base = self.buf.peer_ptrs
+        c = AxbAgCtx()
+        c.n, c.rank, c.epoch, c.n_copy = self.n, self.rank, e, n_copy
+        for j in range(self.n):
+            c.outbox_peer[j] = base[j] + _CTRL_BYTES + parity * self.capacity
+            c.done_peer[j] = base[j] + self._DONE
+        c.staging = staging.data_ptr()
+        c.shard_bytes = nbytes
+        c.shard_ready = base[self.rank] + self._SHARD_READY
+        c.ready_target = n_copy
+        c.rows_per_shard = rows_per_shard
+        c.wait_local = base[self.rank] + self._READY
+        c.counter = base[self.rank] + self._COUNTER
+        return c
+
+
+_ag_channels = {}
+
+
+def all_gather_usable(group, x, w_shard, local_shape, layout) -> bool:
+    if not usable(group, x) or w_shard.dtype != x.dtype or x.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    n = dist.get_world_size(group)
+    rows = local_shape[0]
+    if rows % n:
+        return False
+    R = rows // n
+    if (w_shard.numel() * w_shard.element_size()) % 16:
+        return False
+    return R % 128 == 0 if layout == 0 else R % 64 == 0
+
+
+def all_gather_gemm(layout, a, w_shard, depth_group, local_shape, ar_group=None, bias=None, epilogue=EPI_NONE,
+                    aux=None):
+    """``op(a) @ op(W)`` where ``W [out_l, in_l]`` is the row-wise concatenation of the depth group's flat
+    shards: the gather runs inside the GEMM kernel.  layout 0: ``a[M,in_l] @ W.T``; layout 1:
+    ``a[M,out_l] @ W``.  With ``ar_group`` the product is additionally all-reduced in the epilogue.
+    Returns ``(product, W)`` — ``W`` is the gathered weight left behind by the kernel."""
+    out_l, in_l = local_shape
+    M = a.shape[0]
+    N, K = (out_l, in_l) if layout == 0 else (in_l, out_l)
+    a = a if a.is_contiguous() else a.contiguous()
+    ch = _ag_channels.get(id(depth_group))
+    nbytes = w_shard.numel() * w_shard.element_size()
+    if ch is None or ch.capacity < nbytes:
+        ch = _ag_channels[id(depth_group)] = _AgChannel(depth_group, nbytes)
+    e, parity, nbytes = ch.publish(w_shard.detach())
+    staging = torch.empty((out_l, in_l), dtype=w_shard.dtype, device=a.device)
+    ag = ch.context(e, parity, nbytes, staging, out_l // ch.n, n_copy=16)
+    ar_ref = None
+    if ar_group is not None and dist.get_world_size(ar_group) > 1:
+        arch = _channels.get(id(ar_group))
+        if arch is None:
+            arch = _channels[id(ar_group)] = _ArChannel(ar_group)
+        tiles_m = (M + _BM - 1) // _BM
+        bn = 128 if (layout == 0 and (out_l // ch.n) % 256) else (256 if tiles_m * ((N + 255) // 256) >= 148 else 128)
+        arch.ensure(tiles_m * ((N + bn - 1) // bn), bn)
+        ar_ref = ctypes.byref(arch.context(bn))
+    out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    st = _lib.lib().axb_ag_gemm(
+        ctypes.c_int(layout), _lib.ptr(a), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux), ctypes.c_int(M),
+        ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]),
+        ctypes.c_int(epilogue), ctypes.c_int(a.device.index), _lib.stream_ptr(), ctypes.byref(ag), ar_ref)
+    _lib.check(st, "axb_ag_gemm")
+    return out, staging
+
+
+class AxbCommCtx(ctypes.Structure):
+    _fields_ = [("n", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint), ("pad", ctypes.c_int),
+                ("buf_peer", ctypes.c_void_p * 8), ("wait_local", ctypes.c_void_p),
+                ("signal_peer", ctypes.c_void_p * 8), ("counter", ctypes.c_void_p)]
+
+
+class _GradChannel:
+    """Symmetric bucket + flags of the peer-memory gradient all-reduce for one group.
+    Control block: READY[n] at 0, DONE[n] at 64, CTA counter at 256; the bucket starts at 4096."""
+
+    _READY, _DONE, _COUNTER = 0, 64, 256
+
+    def __init__(self, group, nbytes):
+        self.group, self.n, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.capacity = (int(nbytes) + (1 << 22) - 1) // (1 << 22) * (1 << 22)
+        torch.cuda.synchronize()
+        self.buf = symm.SymmBuffer(group, _CTRL_BYTES + self.capacity, "grad_ar")
+        self.buf.local.zero_()
+        torch.cuda.synchronize()
+        self.buf.barrier()
+        dist.barrier(group=group)
+        self.epoch = 0
+        self.tables = {}
+
+    def ctx(self, wait_off, signal_off):
+        c = AxbCommCtx()
+        c.n, c.rank, c.epoch = self.n, self.rank, self.epoch
+        base = self.buf.peer_ptrs
+        for j in range(self.n):
+            c.buf_peer[j] = base[j] + _CTRL_BYTES
+            c.signal_peer[j] = base[j] + signal_off
+        c.wait_local = base[self.rank] + wait_off
+        c.counter = base[self.rank] + self._COUNTER
+        return c
+
+
+_grad_channels = {}
+_PK_CHUNK = 1 << 15
+
+
+def _grad_table(ch, grads):
+    key = tuple((g.data_ptr(), g.numel()) for g in grads)
+    tab = ch.tables.get(key)
+    if tab is None:
+        rows, off, prefix = [], 0, 0
+        for g in grads:
+            rows.append((g.data_ptr(), g.numel(), 0, off, prefix))
+            off += (g.numel() + 7) // 8 * 8
+            prefix += (g.numel() + _PK_CHUNK - 1) // _PK_CHUNK
+        dev_tab = torch.tensor(rows, dtype=torch.int64).to(grads[0].device)
+        ch.tables.clear()
+        tab = ch.tables[key] = (dev_tab, len(rows), prefix, off)
+    return tab
+
+
 def try_all_reduce_scale_(grads, group, scale) -> bool:
-    return False
+    """Sum ``grads`` over ``group`` and multiply by ``scale`` with the peer-memory kernels
+    (pack -> two-shot reduce with fused scale -> unpack).  Returns False when not applicable."""
+    if not grads or not usable(group, grads[0]):
+        return False
+    dtype = grads[0].dtype
+    if dtype not in (torch.float32, torch.bfloat16) or any(g.dtype != dtype or not g.is_contiguous() for g in grads):
+        return False
+    es = 4 if dtype == torch.float32 else 2
+    total_elems = sum((g.numel() + 7) // 8 * 8 for g in grads)
+    n = dist.get_world_size(group)
+    nbytes = (total_elems * es + 16 * n - 1) // (16 * n) * (16 * n)
+    ch = _grad_channels.get(id(group))
+    if ch is None or ch.capacity < nbytes:
+        ch = _grad_channels[id(group)] = _GradChannel(group, nbytes)
+    tab, ntens, chunks, _ = _grad_table(ch, grads)
+    L = _lib.lib()
+    dev = grads[0].device.index
+    code = 0 if dtype == torch.float32 else 1
+    bucket = ch.buf.peer_ptrs[ch.rank] + _CTRL_BYTES
+    ch.epoch += 1
+    pack = ch.ctx(ch._DONE, ch._READY)      # publishes READY
+    _lib.check(L.axb_bucket_copy(_lib.ptr(tab), ctypes.c_int(ntens), ctypes.c_longlong(chunks),
+                                 ctypes.c_void_p(bucket), ctypes.c_int(code), ctypes.c_int(0), ctypes.byref(pack),
+                                 ctypes.c_int(dev), _lib.stream_ptr()), "axb_bucket_copy")
+    red = ch.ctx(ch._READY, ch._DONE)       # waits READY, publishes DONE
+    _lib.check(L.axb_allreduce_twoshot(ctypes.c_longlong(nbytes), ctypes.c_int(code),
+                                       ctypes.c_float(1.0 if scale is None else float(scale)), ctypes.byref(red),
+                                       ctypes.c_int(dev), _lib.stream_ptr()), "axb_allreduce_twoshot")
+    unpack = ch.ctx(ch._DONE, ch._READY)    # waits DONE
+    _lib.check(L.axb_bucket_copy(_lib.ptr(tab), ctypes.c_int(ntens), ctypes.c_longlong(chunks),
+                                 ctypes.c_void_p(bucket), ctypes.c_int(code), ctypes.c_int(1), ctypes.byref(unpack),
+                                 ctypes.c_int(dev), _lib.stream_ptr()), "axb_bucket_copy")
+    return True

@@ -75,9 +75,117 @@ def bench_gemm(shapes=GEMM_SHAPES, iters=10):
     return rows
 
 
+def bench_attention(small=False):
+    """tcgen05 flash-attention forward vs cuDNN SDPA forward on packed QKV."""
+    import math
+
+    import torch.nn.functional as F
+
+    from axonn_b200.ops.attention_cuda import flash_fwd_packed
+
+    dev = torch.device("cuda", 0)
+    cases = [(2, 2048, 4, 1, 128)] if small else [(8, 2048, 16, 1, 128), (4, 4096, 8, 4, 128), (8, 2048, 16, 1, 64)]
+    for B, S, G, qpk, D in cases:
+        qkv = torch.randn(B, S, G, qpk + 2, D, device=dev, dtype=torch.bfloat16)
+        scale = 1.0 / math.sqrt(D)
+        q = qkv[:, :, :, :qpk].reshape(B, S, G * qpk, D).transpose(1, 2).contiguous()
+        k = qkv[:, :, :, qpk].transpose(1, 2).repeat_interleave(qpk, dim=1).contiguous()
+        v = qkv[:, :, :, qpk + 1].transpose(1, 2).repeat_interleave(qpk, dim=1).contiguous()
+        t_ours, _ = time_cuda(lambda: flash_fwd_packed(qkv, scale), iters=3 if small else 10)
+        t_lib, _ = time_cuda(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True), iters=3 if small else 10)
+        fl = 4.0 * B * G * qpk * S * S * D / 2
+        print(json.dumps(dict(B=B, S=S, heads=G * qpk, kv_heads=G, D=D, ms=round(t_ours, 4),
+                              tflops=round(fl / t_ours / 1e9, 1), cudnn_ms=round(t_lib, 4),
+                              cudnn_tflops=round(fl / t_lib / 1e9, 1))), flush=True)
+
+
+FUSED_SHAPES = [
+    # (M, N, K, label) per-rank GEMM of the GPT-1.3B r=c=d=2 configuration, one 32-sequence microbatch
+    (65536, 4096, 1024, "fc1 fwd + AR(c)"),
+    (65536, 3072, 1024, "qkv fwd + AR(c)"),
+    (65536, 1024, 4096, "fc2 fwd + AR(r)"),
+    (65536, 1024, 1024, "proj fwd + AR(r)"),
+    (16384, 4096, 1024, "fc1 fwd + AR, 8 sequences"),
+]
+
+
+def bench_fused(iters=8):
+    """Fused GEMM+all-reduce vs GEMM followed by an NCCL all-reduce, on the ranks of the default group.
+    Roofline: max(FLOPs / measured bf16 peak, bytes over NVLink / 770 GB/s), bytes = M*N*2 per direction."""
+    import torch.distributed as dist
+
+    from axonn_b200 import ops
+    from axonn_b200.metrics import measured_peaks
+    from axonn_b200.parallel import fused
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peak, _, kind = measured_peaks()
+    group = dist.group.WORLD
+    import os
+
+    shapes = FUSED_SHAPES[:1] if os.environ.get("AXB_AR_DEBUG") else FUSED_SHAPES
+    for M, N, K, label in shapes:
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+
+        def run_fused():
+            return fused.gemm_all_reduce(0, a, b, group)
+
+        def run_unfused():
+            out = ops.matmul_nt(a, b)
+            dist.all_reduce(out, group=group)
+            return out
+
+        def run_gemm_only():
+            return ops.matmul_nt(a, b)
+
+        res = {}
+        for name, fn in (("fused", run_fused), ("gemm+nccl", run_unfused), ("gemm", run_gemm_only)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[name] = float(t.item())
+        flops, nbytes = 2.0 * M * N * K, 2.0 * M * N * (world - 1)
+        roof_ms = max(flops / (peak * 1e12), nbytes / 770e9) * 1e3
+        if rank == 0:
+            print(json.dumps(dict(label=label, M=M, N=N, K=K, ranks=world, fused_ms=round(res["fused"], 4),
+                                  gemm_nccl_ms=round(res["gemm+nccl"], 4), gemm_ms=round(res["gemm"], 4),
+                                  roofline_ms=round(roof_ms, 4), fraction=round(roof_ms / res["fused"], 3),
+                                  nvlink_gbs=round(nbytes / res["fused"] / 1e6, 1), peak=f"{peak} TFLOP/s {kind}")),
+                  flush=True)
+        del a, b
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
         bench_gemm()
+    elif what == "gemm_small":
+        # one mid-size shape (working set 192 MB > L2), a handful of launches: the case profiled with ncu
+        bench_gemm(shapes=[("nt", 8192, 8192, 2048, "profile case")], iters=3)
+    elif what == "attn_small":
+        bench_attention(small=True)
+    elif what == "attn":
+        bench_attention()
+    elif what == "fused":
+        import os
+
+        import torch.distributed as dist
+
+        local = int(os.environ.get("LOCAL_RANK", 0))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        bench_fused()
+        dist.destroy_process_group()
     else:
         raise SystemExit(f"unknown benchmark {what}")

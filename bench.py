@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="gpt1.3b", choices=["gpt1.3b", "tiny"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile", default=None, help="diagnostic: write a torch.profiler kernel table of one step "
+                    "(rank 0) to this file and exit; no benchmark number is produced")
     return ap.parse_args()
 
 
@@ -194,6 +196,19 @@ def main():
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
+
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            step_device(dev_x[0], dev_y[0])
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.profile, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=90))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
 
     sampler = ClockSampler(local)
     if rank == 0:

@@ -101,6 +101,88 @@ def test_gemm_reduce_scatter_two_gpus():
             assert err <= 1.6e-2 * scale + 1e-3, (M, N, K, err, scale)
 
 
+def _grad_ar_case(rank, world):
+    import torch.distributed as dist
+
+    from axonn_b200 import ops
+    from axonn_b200.ops import _lib
+
+    dev = torch.device("cuda", rank)
+    out = []
+    for dtype in (torch.bfloat16, torch.float32):
+        for rep in range(3):
+            g = torch.Generator(device=dev).manual_seed(5 * rank + rep)
+            grads = [torch.randn(n, device=dev, generator=g).to(dtype) for n in (1000, 7, 123457, 2048 * 513)]
+            ref = [t.float().clone() for t in grads]
+            for t in ref:
+                dist.all_reduce(t)
+            ops.all_reduce_bucketed_(grads, dist.group.WORLD, scale=0.5)
+            torch.cuda.synchronize()
+            status = _lib.lib().axb_device_status(rank, 1)
+            tol = 2e-2 if dtype == torch.bfloat16 else 1e-6
+            err = max(((a.float() - 0.5 * b).abs().max() / (b.abs().max() + 1e-9)).item() for a, b in zip(grads, ref))
+            same = []
+            for a in grads:
+                o = a.clone()
+                dist.broadcast(o, src=0)
+                same.append(bool(torch.equal(o, a)))
+            out.append((str(dtype), status, err, tol, all(same)))
+    return out
+
+
+def test_gradient_all_reduce_two_gpus():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    for per_rank in run_distributed(_grad_ar_case, 2, backend="nccl", timeout=300):
+        for name, status, err, tol, same in per_rank:
+            assert status == 0 and err <= tol and same, (name, status, err)
+
+
+def _ag_gemm_case(rank, world):
+    import torch.distributed as dist
+
+    from axonn_b200.ops import _lib
+    from axonn_b200.parallel import fused
+
+    dev = torch.device("cuda", rank)
+    group = dist.group.WORLD
+    out = []
+    for layout, (M, out_l, in_l) in [(0, (1024, 512, 256)), (0, (4096, 2048, 1024)), (1, (2048, 1024, 512)),
+                                     (1, (512, 256, 136)), (0, (640, 256, 72))]:
+        for rep in range(3):
+            g = torch.Generator(device=dev).manual_seed(1000 + rep + out_l)       # same full weight on all ranks
+            W = (torch.randn(out_l, in_l, device=dev, generator=g) * 0.3).bfloat16()
+            R = out_l // world
+            shard = W[rank * R:(rank + 1) * R].reshape(-1).clone()
+            ga = torch.Generator(device=dev).manual_seed(7 * rank + rep)
+            a = (torch.randn(M, in_l if layout == 0 else out_l, device=dev, generator=ga) * 0.5).bfloat16()
+            assert fused.all_gather_usable(group, a, shard, (out_l, in_l), layout)
+            y, Wg = fused.all_gather_gemm(layout, a, shard, group, (out_l, in_l))
+            torch.cuda.synchronize()
+            status = _lib.lib().axb_device_status(rank, 1)
+            ref = a.float() @ (W.float().t() if layout == 0 else W.float())
+            err = (y.float() - ref).abs().max().item() / ref.abs().max().item()
+            out.append((layout, M, out_l, in_l, status, err, bool(torch.equal(Wg, W))))
+    # all-gather over one group combined with the all-reduce epilogue over the same ranks
+    W = (torch.randn(512, 256, device=dev, generator=torch.Generator(device=dev).manual_seed(3)) * 0.3).bfloat16()
+    shard = W[rank * 256:(rank + 1) * 256].reshape(-1).clone()
+    a = torch.randn(1024, 256, device=dev).bfloat16()
+    y, _ = fused.all_gather_gemm(0, a, shard, group, (512, 256), ar_group=group)
+    ref = (a.float() @ W.float().t()).bfloat16().float()
+    dist.all_reduce(ref)
+    torch.cuda.synchronize()
+    out.append((9, 0, 0, 0, _lib.lib().axb_device_status(rank, 1),
+                (y.float() - ref).abs().max().item() / ref.abs().max().item(), True))
+    return out
+
+
+def test_all_gather_gemm_two_gpus():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    for per_rank in run_distributed(_ag_gemm_case, 2, backend="nccl", timeout=300):
+        for layout, M, out_l, in_l, status, err, same in per_rank:
+            assert status == 0, (layout, M, out_l, in_l, status)
+            assert err < 1.6e-2 and same, (layout, M, out_l, in_l, err, same)
+
+
 def test_gemm_all_reduce_two_gpus():
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     res = run_distributed(_gemm_ar_case, 2, backend="nccl", timeout=300)

@@ -166,3 +166,27 @@ def test_prune_topk(dtype, n):
     ref = ref * (ref.abs().float() >= thr).to(dtype)
     out = ops.prune_topk_(g.clone(), 0.1)
     assert torch.equal(out, ref), f"kept {(out != 0).sum().item()} vs {(ref != 0).sum().item()}"
+
+
+@pytest.mark.parametrize("cfg", [(2, 256, 2, 1, 128), (1, 512, 2, 4, 128), (2, 384, 3, 1, 64), (1, 1024, 1, 2, 64)])
+def test_flash_attention_forward(cfg):
+    from axonn_b200.ops import _lib
+    from axonn_b200.ops.attention_cuda import flash_fwd_packed
+
+    B, S, G, qpk, D = cfg
+    torch.manual_seed(7)
+    qkv = torch.randn(B, S, G, qpk + 2, D, device=DEV).bfloat16()
+    scale = D ** -0.5
+    out, lse = flash_fwd_packed(qkv, scale)
+    torch.cuda.synchronize()
+    assert _lib.lib().axb_device_status(0, 1) == 0
+    q = qkv[:, :, :, :qpk].reshape(B, S, G * qpk, D).float().transpose(1, 2)
+    k = qkv[:, :, :, qpk].float().transpose(1, 2).repeat_interleave(qpk, dim=1)
+    v = qkv[:, :, :, qpk + 1].float().transpose(1, 2).repeat_interleave(qpk, dim=1)
+    s = (q @ k.transpose(-1, -2)) * scale
+    mask = torch.ones(S, S, device=DEV, dtype=torch.bool).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    ref = (s.softmax(-1) @ v).transpose(1, 2)
+    _close(out, ref, 2e-2, 2e-2)
+    lse_ref = torch.logsumexp(s, -1)
+    assert (lse - lse_ref).abs().max().item() < 2e-2
