@@ -334,3 +334,326 @@ extern "C" int axb_flash_attn_fwd(const void* qkv, void* out, float* lse, int B,
   if (D == 128) return fa_launch<128>(tm, p, device, static_cast<cudaStream_t>(stream));
   return fa_launch<64>(tm, p, device, static_cast<cudaStream_t>(stream));
 }
+
+// =====================================================================================================
+// Backward.  One CTA owns one (batch, KV group, 128-row KV tile): K and V stay in shared memory, dK and dV
+// accumulate in TMEM, and the CTA walks every (query tile on or below the diagonal, query head of the
+// group).  Per step:
+//   MMA      S = Q K^T and dP = dO V^T into TMEM
+//   softmax  P = exp2(S * scale_log2 - lse * log2e), dS = P * (dP - delta) * scale, both written as bf16
+//            tiles in the canonical swizzled layout (one thread per query row)
+//   MMA      dV += P^T dO, dK += dS^T Q (A operands read MN-major: the same bytes, transposed by the
+//            descriptor), dQ_partial = dS K into the TMEM columns S occupied
+//   softmax  dQ_partial -> fp32 global accumulator with vector reductions (red.global.add.v4.f32)
+// delta = rowsum(dO * O) comes from a small pre-kernel.  dK/dV are written straight into the packed
+// gradient tensor; dQ is converted from the fp32 accumulator by the caller.
+namespace axb {
+
+struct FaBwdParams {
+  const float* lse;     // [B, heads, S]
+  const float* delta;   // [B, heads, S]
+  float* dq_acc;        // [B, S, heads, D] fp32, zero-initialised
+  __nv_bfloat16* dqkv;  // [B, S, G, qpk + 2, D]
+  int B, S, G, qpk;
+  float scale, scale_log2;
+  unsigned int* status;
+  unsigned long long timeout_ns;
+};
+
+template <int HD>
+struct FaBwdSmem {
+  static constexpr int TILE = 128 * HD * 2;
+  static constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = 3 * TILE;
+  static constexpr int P_OFF = 4 * TILE, DS_OFF = P_OFF + 32768;
+  static constexpr int BAR_OFF = DS_OFF + 32768;
+  static constexpr int NBARS = 7;
+  static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, const FaBwdParams p) {
+  using S_ = FaBwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S_::BAR_OFF);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* pds_full = bars + 4;
+  uint64_t* dq_full = bars + 5;
+  uint64_t* s_free = bars + 6;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + S_::NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = p.S / 128;
+  const int jt = blockIdx.x;            // KV tile (tile 0 has the most work and is scheduled first)
+  const int g = blockIdx.y, b = blockIdx.z;
+  const int heads = p.G * p.qpk;
+  const int n_iter = (nq - jt) * p.qpk;  // (query tile, query head) pairs
+  const int col_k = (g * (p.qpk + 2) + p.qpk) * HD, col_v = col_k + HD;
+  const int kvrow = b * p.S + jt * 128;
+  const uint64_t timeout = p.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(s_free, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmQKV); tma_prefetch_desc(&tmDO); }
+  if (warp == 1) { tmem_alloc(tmem_ptr_smem, 512); tmem_relinquish(); }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dk = tmem_base + 256, tm_dv = tmem_base + 384;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      bool ok = true;
+      mbar_expect_tx(kv_full, 2 * S_::TILE);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_2d(smem + S_::K_OFF + c * 16384, &tmQKV, kv_full, col_k + 64 * c, kvrow);
+        tma_load_2d(smem + S_::V_OFF + c * 16384, &tmQKV, kv_full, col_v + 64 * c, kvrow);
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int i = jt + it / p.qpk, jq = it % p.qpk;
+        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag, timeout)) { ok = false; break; }
+        const int qrow = b * p.S + i * 128;
+        const int col_q = (g * (p.qpk + 2) + jq) * HD;
+        const int col_do = (g * p.qpk + jq) * HD;
+        mbar_expect_tx(qdo_full, 2 * S_::TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_2d(smem + S_::Q_OFF + c * 16384, &tmQKV, qdo_full, col_q + 64 * c, qrow);
+          tma_load_2d(smem + S_::DO_OFF + c * 16384, &tmDO, qdo_full, col_do + 64 * c, qrow);
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {}
+        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x411u;
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      bool ok = mbar_wait(kv_full, 0, abort_flag, timeout);
+      const uint32_t idesc_s = umma_idesc(1, 0, 0, 128, 128);      // S, dP: K-major x K-major
+      const uint32_t idesc_t = umma_idesc(1, 1, 1, 128, HD);       // dV, dK: A^T (MN-major) x MN-major
+      const uint32_t idesc_q = umma_idesc(1, 0, 1, 128, HD);       // dQ: K-major x MN-major
+      const uint32_t k_addr = smem_u32(smem + S_::K_OFF), v_addr = smem_u32(smem + S_::V_OFF);
+      const uint32_t q_addr = smem_u32(smem + S_::Q_OFF), do_addr = smem_u32(smem + S_::DO_OFF);
+      const uint32_t p_addr = smem_u32(smem + S_::P_OFF), ds_addr = smem_u32(smem + S_::DS_OFF);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(qdo_full, ph, abort_flag, timeout) || !mbar_wait(s_free, ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_f16(tm_s, umma_smem_desc(q_addr + off, 16, 1024), umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_f16(tm_dp, umma_smem_desc(do_addr + off, 16, 1024), umma_smem_desc(v_addr + off, 16, 1024), idesc_s, kk != 0);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, ph, abort_flag, timeout)) { ok = false; break; }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {   // reduction over the 128 query rows, 16 per step
+          umma_f16(tm_dv, umma_smem_desc(p_addr + kk * 2048, 16384, 1024), umma_smem_desc(do_addr + kk * 2048, 16384, 1024),
+                   idesc_t, (it | kk) != 0);
+          umma_f16(tm_dk, umma_smem_desc(ds_addr + kk * 2048, 16384, 1024), umma_smem_desc(q_addr + kk * 2048, 16384, 1024),
+                   idesc_t, (it | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {   // reduction over the 128 KV rows
+          umma_f16(tm_s, umma_smem_desc(ds_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                   umma_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_q, kk != 0);
+        }
+        umma_commit(dq_full);
+        umma_commit(qdo_empty);
+      }
+      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x412u;
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+    uint8_t* p_row = smem + S_::P_OFF + (r >> 3) * 1024 + (r & 7) * 128;
+    uint8_t* ds_row = smem + S_::DS_OFF + (r >> 3) * 1024 + (r & 7) * 128;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const uint32_t ph = it & 1;
+      const int i = jt + it / p.qpk, jq = it % p.qpk;
+      const int head = g * p.qpk + jq;
+      const size_t srow = static_cast<size_t>(i) * 128 + r;   // query position of this thread's row
+      const float lse2 = p.lse[(static_cast<size_t>(b) * heads + head) * p.S + srow] * 1.4426950408889634f;
+      const float dl = p.delta[(static_cast<size_t>(b) * heads + head) * p.S + srow];
+      if (!mbar_wait(sdp_full, ph, abort_flag, timeout)) { ok = false; break; }
+      tcgen05_fence_after();
+      const bool diag = (i == jt);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tm_s + lane_base + c * 32, sv);
+        tmem_ld_32x32(tm_dp + lane_base + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float p0 = exp2f(__uint_as_float(sv[2 * k]) * p.scale_log2 - lse2);
+          float p1 = exp2f(__uint_as_float(sv[2 * k + 1]) * p.scale_log2 - lse2);
+          if (diag) {   // key position (column) beyond the query position (row) is masked
+            if (c * 32 + 2 * k > r) p0 = 0.f;
+            if (c * 32 + 2 * k + 1 > r) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dv[2 * k]) - dl) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dv[2 * k + 1]) - dl) * p.scale;
+          const __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+          pp[k] = *reinterpret_cast<const uint32_t*>(&hp);
+          dd[k] = *reinterpret_cast<const uint32_t*>(&hd);
+        }
+        const int blk = (c >> 1) * 16384;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int chunk = ((c & 1) * 4 + t) ^ (r & 7);
+          *reinterpret_cast<uint4*>(p_row + blk + chunk * 16) = make_uint4(pp[4 * t], pp[4 * t + 1], pp[4 * t + 2], pp[4 * t + 3]);
+          *reinterpret_cast<uint4*>(ds_row + blk + chunk * 16) = make_uint4(dd[4 * t], dd[4 * t + 1], dd[4 * t + 2], dd[4 * t + 3]);
+        }
+      }
+      tcgen05_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      // dQ partial of this (query tile, head): TMEM -> fp32 accumulator in global memory
+      if (!mbar_wait(dq_full, ph, abort_flag, timeout)) { ok = false; break; }
+      tcgen05_fence_after();
+      float* dq = p.dq_acc + ((static_cast<size_t>(b) * p.S + srow) * heads + head) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_s + lane_base + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          red_add_v4(dq + c * 32 + k * 4, __uint_as_float(v[4 * k]), __uint_as_float(v[4 * k + 1]),
+                     __uint_as_float(v[4 * k + 2]), __uint_as_float(v[4 * k + 3]));
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+    }
+    if (ok) {
+      // dK, dV of this KV tile: thread r holds KV row r
+      const size_t kvpos = static_cast<size_t>(b) * p.S + jt * 128 + r;
+      __nv_bfloat16* dk = p.dqkv + (kvpos * p.G + g) * (p.qpk + 2) * HD + static_cast<size_t>(p.qpk) * HD;
+      __nv_bfloat16* dvp = dk + HD;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = (which == 0 ? tm_dk : tm_dv) + lane_base;
+        __nv_bfloat16* dst = which == 0 ? dk : dvp;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(src + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[t * 8 + 2 * k]), __uint_as_float(v[t * 8 + 2 * k + 1]));
+              w[k] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    } else if (lane == 0) {
+      *reinterpret_cast<volatile unsigned int*>(p.status) = 0x414u;
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (b, s, h) row
+__global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                float* __restrict__ delta, int B, int S, int H, int D) {
+  const long long rows = static_cast<long long>(B) * S * H;
+  const int lane = threadIdx.x & 31;
+  for (long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; row < rows;
+       row += ((long long)gridDim.x * blockDim.x) >> 5) {
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(o + row * D);
+    const __nv_bfloat162* c = reinterpret_cast<const __nv_bfloat162*>(d_o + row * D);
+    float acc = 0.f;
+    for (int i = lane; i < D / 2; i += 32) {
+      const float2 x = __bfloat1622float2(a[i]), y = __bfloat1622float2(c[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) {
+      const long long h = row % H, bs = row / H, s = bs % S, bb = bs / S;
+      delta[(bb * H + h) * S + s] = acc;
+    }
+  }
+}
+
+template <int HD>
+static int fa_bwd_launch(const CUtensorMap& tq, const CUtensorMap& td, const FaBwdParams& p, int device, cudaStream_t s) {
+  using S_ = FaBwdSmem<HD>;
+  static bool configured[64] = {false};
+  auto kern = fa_bwd_kernel<HD>;
+  if (!configured[device & 63]) {
+    AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_::TOTAL));
+    configured[device & 63] = true;
+  }
+  dim3 grid(p.S / 128, p.G, p.B);
+  kern<<<grid, FA_THREADS, S_::TOTAL, s>>>(tq, td, p);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace axb
+
+// Backward of axb_flash_attn_fwd.  qkv [B,S,G,qpk+2,D], out / d_out [B,S,G*qpk,D] bf16, lse [B,G*qpk,S];
+// delta [B,G*qpk,S] fp32 scratch; dq_acc [B,S,G*qpk,D] fp32, zero on entry, holds dQ on return;
+// dqkv [B,S,G,qpk+2,D]: its K and V slots receive dK and dV (the Q slots are left to the caller).
+extern "C" int axb_flash_attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta,
+                                  float* dq_acc, void* dqkv, int B, int S, int G, int qpk, int D, float scale,
+                                  int device, void* stream) {
+  using namespace axb;
+  if (D != 64 && D != 128) { set_error("flash attention: head_dim must be 64 or 128"); return -1; }
+  if (S % 128) { set_error("flash attention: sequence length must be a multiple of 128"); return -1; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int H = G * qpk;
+  const long long rows = static_cast<long long>(B) * S * H;
+  const int blocks = static_cast<int>(rows / 8 < 148 * 16 ? (rows / 8 < 1 ? 1 : rows / 8) : 148 * 16);
+  fa_delta_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out),
+                                         delta, B, S, H, D);
+  AXB_CUDA(cudaGetLastError());
+  CUtensorMap tq, td;
+  if (make_tmap_2d_16bit(&tq, qkv, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(G) * (qpk + 2) * D, 128, 0)) return -1;
+  if (make_tmap_2d_16bit(&td, d_out, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(H) * D, 128, 0)) return -1;
+  FaBwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
+  p.B = B; p.S = S; p.G = G; p.qpk = qpk; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  unsigned int* st = nullptr;
+  if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
+  p.status = st; p.timeout_ns = 2000000000ull;
+  if (D == 128) return fa_bwd_launch<128>(tq, td, p, device, s);
+  return fa_bwd_launch<64>(tq, td, p, device, s);
+}

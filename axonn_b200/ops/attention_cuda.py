@@ -1,9 +1,7 @@
 """Bindings of the flash-attention kernels (``csrc/flash_attn.cu``).
 
-Forward runs on the package's tcgen05 kernel directly on the packed QKV
-tensor; backward recomputes through ``F.scaled_dot_product_attention`` (cuDNN)
-until the native backward kernel lands, which needs q/k/v split out of the
-packed tensor.
+Forward and backward run on the package's tcgen05 kernels directly on the packed
+QKV tensor (no split, no head repetition for grouped-query attention).
 """
 
 import ctypes
@@ -37,27 +35,37 @@ def flash_fwd_packed(qkv, scale):
     return out, lse
 
 
+def flash_bwd_packed(qkv, out, d_out, lse, scale):
+    """Gradient of the packed QKV tensor for ``flash_fwd_packed``."""
+    B, S, G, n, D = qkv.shape
+    qpk = n - 2
+    H = G * qpk
+    d_out = d_out if d_out.is_contiguous() else d_out.contiguous()
+    delta = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
+    dq_acc = torch.zeros((B, S, H, D), dtype=torch.float32, device=qkv.device)
+    dqkv = torch.empty_like(qkv)
+    st = _lib.lib().axb_flash_attn_bwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(d_out), _lib.ptr(lse), _lib.ptr(delta),
+                                       _lib.ptr(dq_acc), _lib.ptr(dqkv), ctypes.c_int(B), ctypes.c_int(S),
+                                       ctypes.c_int(G), ctypes.c_int(qpk), ctypes.c_int(D), ctypes.c_float(scale),
+                                       ctypes.c_int(qkv.device.index), _lib.stream_ptr())
+    _lib.check(st, "axb_flash_attn_bwd")
+    _lib.add_launches(1)
+    dqkv[:, :, :, :qpk].copy_(dq_acc.view(B, S, G, qpk, D))
+    return dqkv
+
+
 class _FlashPacked(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, scale):
         out, lse = flash_fwd_packed(qkv, scale)
-        ctx.save_for_backward(qkv)
+        ctx.save_for_backward(qkv, out, lse)
         ctx.scale = scale
         return out
 
     @staticmethod
     def backward(ctx, g):
-        (qkv,) = ctx.saved_tensors
-        B, S, G, n, D = qkv.shape
-        qpk = n - 2
-        with torch.enable_grad():
-            x = qkv.detach().requires_grad_(True)
-            q = x[:, :, :, :qpk].reshape(B, S, G * qpk, D).transpose(1, 2)
-            k = x[:, :, :, qpk].transpose(1, 2).repeat_interleave(qpk, dim=1)
-            v = x[:, :, :, qpk + 1].transpose(1, 2).repeat_interleave(qpk, dim=1)
-            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=ctx.scale).transpose(1, 2)
-            (gx,) = torch.autograd.grad(o, x, g)
-        return gx, None
+        qkv, out, lse = ctx.saved_tensors
+        return flash_bwd_packed(qkv, out, g, lse, ctx.scale), None
 
 
 def flash_attention_packed_cuda(qkv, causal, scale):

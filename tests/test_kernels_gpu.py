@@ -190,3 +190,31 @@ def test_flash_attention_forward(cfg):
     _close(out, ref, 2e-2, 2e-2)
     lse_ref = torch.logsumexp(s, -1)
     assert (lse - lse_ref).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("cfg", [(2, 256, 2, 1, 128), (1, 512, 2, 4, 128), (2, 384, 3, 1, 64), (1, 640, 1, 2, 64)])
+def test_flash_attention_backward(cfg):
+    from axonn_b200.ops import _lib
+    from axonn_b200.ops.attention_cuda import flash_bwd_packed, flash_fwd_packed
+
+    B, S, G, qpk, D = cfg
+    torch.manual_seed(11)
+    qkv = torch.randn(B, S, G, qpk + 2, D, device=DEV).bfloat16()
+    d_out = torch.randn(B, S, G * qpk, D, device=DEV).bfloat16()
+    scale = D ** -0.5
+    out, lse = flash_fwd_packed(qkv, scale)
+    dqkv = flash_bwd_packed(qkv, out, d_out, lse, scale)
+    torch.cuda.synchronize()
+    assert _lib.lib().axb_device_status(0, 1) == 0
+    x = qkv.float().requires_grad_(True)
+    q = x[:, :, :, :qpk].reshape(B, S, G * qpk, D).transpose(1, 2)
+    k = x[:, :, :, qpk].transpose(1, 2).repeat_interleave(qpk, dim=1)
+    v = x[:, :, :, qpk + 1].transpose(1, 2).repeat_interleave(qpk, dim=1)
+    s = (q @ k.transpose(-1, -2)) * scale
+    mask = torch.ones(S, S, device=DEV, dtype=torch.bool).tril()
+    ref = (s.masked_fill(~mask, float("-inf")).softmax(-1) @ v).transpose(1, 2)
+    ref.backward(d_out.float())
+    for name, sl in (("dq", slice(0, qpk)), ("dk", slice(qpk, qpk + 1)), ("dv", slice(qpk + 1, qpk + 2))):
+        got, want = dqkv[:, :, :, sl].float(), x.grad[:, :, :, sl]
+        err = (got - want).abs().max().item()
+        assert err <= 3e-2 * want.abs().max().item() + 2e-2, f"{name}: {err} vs {want.abs().max().item()}"
