@@ -31,8 +31,9 @@ int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias
 
 /* Peer-memory context of the fused GEMM + all-reduce / reduce-scatter.  All pointers are device addresses:
  * the *_local ones in this rank's symmetric buffer, the *_peer[j] ones the same regions of rank j mapped
- * into this process.  `inbox_*` is each rank's outbox of bf16 partial tiles ([tile][128 rows][bn columns]),
- * written locally by the GEMM CTAs and read by the comm CTAs of every rank that reduces those rows.  Flag
+ * into this process.  `inbox_*` holds bf16 partial tiles indexed [source rank][tile][warp]: every rank's
+ * GEMM epilogue pushes its partial into the inbox of the ranks that reduce those rows (posted stores over
+ * NVLink for peers), whose comm CTAs sum the slots locally.  Flag
  * arrays are indexed [source rank][tile * 4 + warp]; `epoch` increases by one per call on the group and
  * selects (by parity, done by the caller) which of two outbox/flag sets is used. */
 typedef struct AxbArCtx {

@@ -55,3 +55,12 @@ extern "C" unsigned int axb_device_status(int device, int clear) {
   if (clear) w[0] = 0;
   return v;
 }
+
+// Diagnostic words next to the status word (index 1..15); reading clears when asked.
+extern "C" unsigned int axb_debug_word(int device, int index, int clear) {
+  volatile unsigned int* w = axb::device_status_word(device, nullptr);
+  if (!w || index < 0 || index > 15) return 0;
+  unsigned int v = w[index];
+  if (clear) w[index] = 0;
+  return v;
+}

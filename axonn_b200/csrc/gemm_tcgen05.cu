@@ -236,170 +236,81 @@ __device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) 
   unpack2(u.w, dtype, a, b); acc[6] += a; acc[7] += b;
 }
 
-// ---- comm CTA: reduces finished tiles over peer memory while the other CTAs of the same kernel compute.
-// Warp 0 is the fetcher: for every tile of this CTA (in the order the GEMM CTAs produce them) it waits until
-// this rank's and the peers' (tile, warp) flags are up and then pulls the peers' bf16 partial rows over
-// NVLink with bulk asynchronous copies (cp.async.bulk, no multicast) into a ring of shared-memory stages -
-// several tiles, i.e. hundreds of KB per CTA, are in flight at once.  Warps 1-5 are the reducers: they add
-// this rank's partial (local memory) and the peers' (shared memory) in rank order - identical bits on every
-// rank -, apply bias / GELU and write C.  In reduce-scatter mode only the 32-row groups owned by this rank
-// are fetched and reduced.
+// ---- comm CTA: reduces finished tiles while the other CTAs of the same kernel compute.  For every tile
+// (in the order the GEMM CTAs produce them) it waits until the (tile, warp) flags of all ranks are up - the
+// peers' partials were pushed into this rank's inbox over NVLink by their epilogues -, then sums the inbox
+// slots of all ranks in rank order (local, coalesced 16-byte loads, 8 in flight per thread; identical bits
+// on every rank), applies bias / GELU and writes C.  In reduce-scatter mode only the 32-row groups owned by
+// this rank exist in the inbox and are reduced.
 template <int BN>
 __device__ __forceinline__ void comm_cta(const GemmParams& p, int group, int num_tiles, uint8_t* smem) {
   __shared__ int sh_fail;
-  using S = GemmSmem<BN>;
-  constexpr int VPR = BN / 8;                       // 16-byte vectors per tile row
-  constexpr int TILE_BYTES = BM * BN * 2;
-  constexpr int GROUP_BYTES = 32 * BN * 2;          // one warp's 32 rows
+  constexpr int CH = BN / 32;                 // 32-column chunks per tile row
+  constexpr int WVEC = CH * 4 * 32;           // 16-byte words per (tile, warp) slot
+  constexpr int TVEC = 4 * WVEC;              // per tile
   const int ncomm = gridDim.x - p.gemm_ctas;
   const int cid = blockIdx.x - p.gemm_ctas;
-  const int P = p.ar.n - 1;
-  const int stage_bytes = P * TILE_BYTES;
-  int D = S::BAR_OFFSET / stage_bytes;
-  if (D > 4) D = 4;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
-  uint64_t* empty = full + 4;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    sh_fail = 0;
-    for (int i = 0; i < 4; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 5); }
-    fence_mbar_init();
-  }
+  if (threadIdx.x == 0) sh_fail = 0;
   __syncthreads();
   volatile int* failp = &sh_fail;
-  auto mine_of = [&](int tile, int& tm, int& tn) -> unsigned {
-    tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+  for (int tile = cid; tile < num_tiles; tile += ncomm) {
+    int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
     unsigned mine = 0;
     for (int q = 0; q < 4; ++q)
       if (p.ar.mode == 0 || (tm * BM + q * 32) / p.ar.rows_per_shard == p.ar.rank) mine |= 1u << q;
-    return mine;
-  };
-  if (D >= 1) {
-    if (warp == 0) {
-      if (lane == 0) {
-        int k = 0;
-        bool ok = true;
-        for (int tile = cid; tile < num_tiles && ok; tile += ncomm) {
-          int tm, tn;
-          const unsigned mine = mine_of(tile, tm, tn);
-          if (mine == 0) continue;
-          const int st = k % D;
-          const uint32_t ph = (k / D) & 1;
-          if (!mbar_wait(&empty[st], ph ^ 1, failp, p.timeout_ns)) { ok = false; break; }
-          for (int j = 0; j < p.ar.n && ok; ++j)
-            for (int q = 0; q < 4 && ok; ++q)
-              if (mine & (1u << q))
-                ok = wait_flag_ge(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q,
-                                  p.ar.epoch, failp, p.timeout_ns);
-          if (!ok) break;
-          asm volatile("fence.proxy.async;" ::: "memory");
-          mbar_expect_tx(&full[st], static_cast<uint32_t>(__popc(mine) * P * GROUP_BYTES));
-          int pi = 0;
-          for (int j = 0; j < p.ar.n; ++j) {
-            if (j == p.ar.rank) continue;
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ar.inbox_peer[j]) + static_cast<size_t>(tile) * TILE_BYTES;
-            uint8_t* dst = smem + st * stage_bytes + pi * TILE_BYTES;
-            if (!(p.debug & 4)) {
-              for (int q = 0; q < 4; ++q)
-                if (mine & (1u << q)) bulk_load_1d(dst + q * GROUP_BYTES, src + q * GROUP_BYTES, GROUP_BYTES, &full[st]);
-            } else {
-              // timing experiment: no NVLink traffic (local source)
-              const uint8_t* lsrc = reinterpret_cast<const uint8_t*>(p.ar.inbox_local) + static_cast<size_t>(tile) * TILE_BYTES;
-              for (int q = 0; q < 4; ++q)
-                if (mine & (1u << q)) bulk_load_1d(dst + q * GROUP_BYTES, lsrc + q * GROUP_BYTES, GROUP_BYTES, &full[st]);
-            }
-            ++pi;
-          }
-          ++k;
-        }
-        if (!ok) {
-          sh_fail = 1;
-          const uint64_t t0 = globaltimer_ns();
-          while (globaltimer_ns() - t0 < 200000ull) {}   // let copies in flight land before the CTA exits
-          *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
-        }
-      }
-    } else {
-      const int rid = threadIdx.x - 32, nred = blockDim.x - 32;
-      int k = 0;
-      bool ok = true;
-      for (int tile = cid; tile < num_tiles && ok; tile += ncomm) {
-        int tm, tn;
-        const unsigned mine = mine_of(tile, tm, tn);
-        if (mine == 0) continue;
-        const int st = k % D;
-        const uint32_t ph = (k / D) & 1;
-        if (!mbar_wait(&full[st], ph, failp, p.timeout_ns)) { ok = false; break; }
-        const uint4* local = reinterpret_cast<const uint4*>(p.ar.inbox_local) + static_cast<size_t>(tile) * BM * VPR;
-        const uint4* staged = reinterpret_cast<const uint4*>(smem + st * stage_bytes);
-        // batches of 8 vectors per thread: the 8 local loads are independent and overlap their latency
-        for (int base = rid; base < BM * VPR; base += nred * 8) {
-          uint4 loc[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int idx = base + k * nred;
-            loc[k] = (idx < BM * VPR && (mine & (1u << (idx / (32 * VPR))))) ? __ldcv(local + idx)
-                                                                            : make_uint4(0u, 0u, 0u, 0u);
-          }
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int idx = base + k * nred;
-            if (idx >= BM * VPR) continue;
-            const int r = idx / VPR, cv = idx - r * VPR;
-            if (!(mine & (1u << (r >> 5)))) continue;
-            const size_t row = static_cast<size_t>(tm) * BM + r;
-            const int col = tn * BN + cv * 8;
-            if (row >= static_cast<size_t>(p.M) || col >= p.N) continue;
-            float acc[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-            int pi = 0;
-            for (int j = 0; j < p.ar.n; ++j) {
-              if (j == p.ar.rank) acc_vec8(acc, loc[k], p.in_dtype);
-              else { acc_vec8(acc, staged[pi * (TILE_BYTES / 16) + idx], p.in_dtype); ++pi; }
-            }
-            comm_finish8(p, acc, row, col);
+    if (mine == 0) continue;
+    if (threadIdx.x < 4 * p.ar.n) {
+      const int q = threadIdx.x & 3, j = threadIdx.x >> 2;
+      if (mine & (1u << q)) {
+        const volatile unsigned int* f = p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q;
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
+          if (static_cast<int>(*f - p.ar.epoch) >= 0) break;
+          if ((it & 0xff) == 0xff) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (sh_fail || now - t0 > p.timeout_ns) { sh_fail = 1; break; }
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[st]);
-        ++k;
+        __threadfence_system();   // acquire: the flagged data is visible to the loads below
       }
     }
-  } else {
-    // peers' tiles do not fit in shared memory (large groups with wide tiles): direct P2P loads
-    for (int tile = cid; tile < num_tiles; tile += ncomm) {
-      int tm, tn;
-      const unsigned mine = mine_of(tile, tm, tn);
-      if (mine == 0) continue;
-      if (threadIdx.x < 4 * p.ar.n) {
-        const int q = threadIdx.x & 3, j = threadIdx.x >> 2;
-        if ((mine & (1u << q)) &&
-            !wait_flag_ge(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q, p.ar.epoch,
-                          failp, p.timeout_ns))
-          sh_fail = 1;
+    __syncthreads();
+    if (sh_fail) break;
+    const uint4* inbox = reinterpret_cast<const uint4*>(p.ar.inbox_local) + static_cast<size_t>(tile) * TVEC;
+    for (int base = threadIdx.x; base < TVEC; base += blockDim.x * 8) {
+      float acc[8][8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
+      for (int j = 0; j < p.ar.n; ++j) {
+        const uint4* src = inbox + static_cast<size_t>(j) * p.ar.inbox_vecs_per_src;
+        uint4 in[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int v = base + k * blockDim.x;
+          in[k] = (v < TVEC && (mine & (1u << (v / WVEC)))) ? __ldcg(src + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc_vec8(acc[k], in[k], p.in_dtype);
       }
-      __syncthreads();
-      if (sh_fail) break;
-      const size_t tile_vec0 = static_cast<size_t>(tile) * BM * VPR;
-      for (int idx = threadIdx.x; idx < BM * VPR; idx += blockDim.x) {
-        const int r = idx / VPR, cv = idx - r * VPR;
-        if (!(mine & (1u << (r >> 5)))) continue;
-        const size_t row = static_cast<size_t>(tm) * BM + r;
-        const int col = tn * BN + cv * 8;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int v = base + k * blockDim.x;
+        if (v >= TVEC) continue;
+        const int q = v / WVEC;
+        if (!(mine & (1u << q))) continue;
+        const int w = v - q * WVEC;
+        const int c = w >> 7, i = (w >> 5) & 3, ln = w & 31;
+        const size_t row = static_cast<size_t>(tm) * BM + q * 32 + ln;
+        const int col = tn * BN + c * 32 + i * 8;
         if (row >= static_cast<size_t>(p.M) || col >= p.N) continue;
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (int j = 0; j < p.ar.n; ++j) {
-          const uint4* src = reinterpret_cast<const uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + tile_vec0;
-          acc_vec8(acc, __ldcv(src + idx), p.in_dtype);
-        }
-        comm_finish8(p, acc, row, col);
+        comm_finish8(p, acc[k], row, col);
       }
     }
-    if (sh_fail && threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x121u;
   }
+  if (sh_fail && threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
   // take part in the end-of-kernel completion count
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -659,33 +570,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         continue;
       }
-      // ---- communication mode: the epilogue only parks this warp's bf16 partial (32 rows x BN columns) in
-      // this rank's peer-readable outbox ([tile][128 rows][BN columns]) and raises the (tile, warp) flag on
-      // the ranks that will reduce these rows; the comm CTAs of those ranks do the rest.
+      // ---- communication mode: the epilogue moves this warp's bf16 partial (32 rows x BN columns) out of
+      // TMEM into the inbox of every rank that reduces these rows - with posted 16-byte stores over NVLink
+      // for the peers, plain stores for this rank - then raises the (tile, warp) flags; the comm CTAs of the
+      // reducing ranks sum the inbox slots locally.  Slot layout of a (tile, warp): [chunk][vec 0..3][lane]
+      // 16-byte words, so every store instruction of a warp covers 512 contiguous bytes.
       const int owner = (p.ar.mode == 1) ? (tm * BM + q * 32) / p.ar.rows_per_shard : -1;
-      uint16_t* part = reinterpret_cast<uint16_t*>(p.ar.inbox_local) +
-                       (static_cast<size_t>(tile) * BM + q * 32 + lane) * BN;
+      const size_t slot_vec = static_cast<size_t>(p.ar.rank) * p.ar.inbox_vecs_per_src +
+                              (static_cast<size_t>(tile) * 4 + q) * (BN / 32) * 4 * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         if (tn * BN + c * 32 >= p.N) break;
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
+        uint4 w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          uint4 w;
-          w.x = pack2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]), p.in_dtype);
-          w.y = pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]), p.in_dtype);
-          w.z = pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]), p.in_dtype);
-          w.w = pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]), p.in_dtype);
-          *reinterpret_cast<uint4*>(part + c * 32 + i * 8) = w;
+          w[i].x = pack2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]), p.in_dtype);
+          w[i].y = pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]), p.in_dtype);
+          w[i].z = pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]), p.in_dtype);
+          w[i].w = pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]), p.in_dtype);
+        }
+        for (int j = 0; j < p.ar.n; ++j) {
+          if (p.ar.mode == 1 && j != owner) continue;
+          if ((p.debug & 2) && j != p.ar.rank) continue;
+          uint4* dst = reinterpret_cast<uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + slot_vec + (c * 4) * 32;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i * 32] = w[i];
         }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&tmem_empty[buf]);   // accumulator is free: the MMA warp runs ahead
-        __threadfence_system();          // the partial (local memory) is visible before any flag
+        if (!(p.debug & 1)) __threadfence_system();   // all 32 lanes' stores (ordered by the warp sync) before the flags
         for (int j = 0; j < p.ar.n; ++j) {
           if (p.ar.mode == 1 && j != owner) continue;
           unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
@@ -831,7 +750,7 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
   if (ar && ar->n > 1) {
     p.ar = *ar;
     const long long tiles = static_cast<long long>(tiles_m) * ((N + BN - 1) / BN);
-    if (tiles * 4 > ar->flags_per_src || tiles * BM * (BN / 8) > ar->inbox_vecs_per_src) {
+    if (tiles * 4 > ar->flags_per_src || tiles * 4 * (BN / 32) * 128 > ar->inbox_vecs_per_src) {
       set_error("axb_gemm_ar: communication buffers too small for %lld tiles", tiles);
       return -1;
     }

@@ -14,7 +14,7 @@ from . import _lib
 
 
 def available():
-    return hasattr(_lib.lib(), "axb_flash_attn_fwd") and os.environ.get("AXONN_FLASH", "0") == "1"
+    return hasattr(_lib.lib(), "axb_flash_attn_fwd") and os.environ.get("AXONN_FLASH", "1") == "1"
 
 
 def supported(qkv):

@@ -45,7 +45,8 @@ class _ArChannel:
     Layout of the symmetric allocation (same on every rank):
       [0, 4096)        control: done[n] (u32) at 0, CTA counter (u32) at 256
       flags[parity]    n * flags_per_src u32   (indexed [source rank][tile * 4 + warp])
-      outbox[parity]   inbox_vecs_per_src 16-byte words: this rank's bf16 partial tiles, read by the peers
+      inbox[parity]    n * inbox_vecs_per_src 16-byte words, indexed [source rank][tile][warp]: bf16 partial
+                       tiles pushed by every rank's GEMM epilogue (the own ones stored locally)
     """
 
     def __init__(self, group):
@@ -59,7 +60,7 @@ class _ArChannel:
 
     def _layout(self):
         fbytes = self.n * self.flags_per_src * 4
-        ibytes = self.inbox_vecs_per_src * 16
+        ibytes = self.n * self.inbox_vecs_per_src * 16
         f0 = _CTRL_BYTES
         i0 = (f0 + 2 * fbytes + 1023) // 1024 * 1024
         return f0, fbytes, i0, ibytes, i0 + 2 * ibytes

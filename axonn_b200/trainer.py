@@ -11,6 +11,7 @@ It packages the loop the reference leaves to user scripts and to its Lightning
 strategy (``axonn/lightning/axonn_strategy.py:148-164,241-256``).
 """
 
+import os
 from typing import Callable, Optional
 
 import torch
@@ -25,7 +26,8 @@ from .intra_layer import (clip_grad_norm_, no_grad_sync, optimize_communication,
 class Trainer:
     def __init__(self, model, optimizer, micro_batch_size: Optional[int] = None, clip_grad: float = 0.0,
                  prune_keep_fraction: Optional[float] = None, overlap: bool = True,
-                 loss_fn: Optional[Callable] = None, expert_mode: bool = True):
+                 loss_fn: Optional[Callable] = None, expert_mode: bool = True,
+                 prefetch_all_gather: Optional[bool] = None):
         assert ax.is_initialized
         if ax.config.G_inter != 1:
             raise ValueError("Trainer drives non-pipelined models; use AxoNN_Inter_Layer_Engine for G_inter > 1")
@@ -34,6 +36,11 @@ class Trainer:
         self.clip_grad = clip_grad
         self.prune_keep_fraction = prune_keep_fraction
         self.overlap = overlap
+        # depth all-gathers: either prefetched one layer ahead on the collective library's stream, or (False)
+        # left to the GEMM kernels that gather their weight shards themselves over peer memory
+        if prefetch_all_gather is None:
+            prefetch_all_gather = os.environ.get("AXONN_AG_PREFETCH", "1") == "1"
+        self.prefetch_all_gather = prefetch_all_gather and overlap
         self.loss_fn = loss_fn
         self.expert_mode = expert_mode
         self.device = ax.comm_handle.device
@@ -61,7 +68,7 @@ class Trainer:
         for i in range(n_micro):
             x, y = inputs[i * mbs:(i + 1) * mbs], targets[i * mbs:(i + 1) * mbs]
             with optimize_communication(overlap_all_reduce=self.overlap, overlap_reduce_scatter=self.overlap,
-                                        cache_weights=False, overlap_all_gather=self.overlap,
+                                        cache_weights=False, overlap_all_gather=self.prefetch_all_gather,
                                         model_object_for_overlapping_allgathers=self.model):
                 loss = self._forward_loss(x, y)
                 # backward consumes the layers in reverse: prefetch depth all-gathers in that order

@@ -94,9 +94,21 @@ def bench_attention(small=False):
         t_ours, _ = time_cuda(lambda: flash_fwd_packed(qkv, scale), iters=3 if small else 10)
         t_lib, _ = time_cuda(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True), iters=3 if small else 10)
         fl = 4.0 * B * G * qpk * S * S * D / 2
+        from axonn_b200.ops.attention_cuda import flash_bwd_packed
+
+        out, lse = flash_fwd_packed(qkv, scale)
+        d_out = torch.randn_like(out)
+        t_bwd, _ = time_cuda(lambda: flash_bwd_packed(qkv, out, d_out, lse, scale), iters=3 if small else 10)
+        qr, kr, vr = (t.detach().requires_grad_(True) for t in (q, k, v))
+        o_ref = F.scaled_dot_product_attention(qr, kr, vr, is_causal=True)
+        g_ref = torch.randn_like(o_ref)
+        t_lib_bwd, _ = time_cuda(lambda: torch.autograd.grad(o_ref, (qr, kr, vr), g_ref, retain_graph=True),
+                                 iters=3 if small else 10)
         print(json.dumps(dict(B=B, S=S, heads=G * qpk, kv_heads=G, D=D, ms=round(t_ours, 4),
                               tflops=round(fl / t_ours / 1e9, 1), cudnn_ms=round(t_lib, 4),
-                              cudnn_tflops=round(fl / t_lib / 1e9, 1))), flush=True)
+                              cudnn_tflops=round(fl / t_lib / 1e9, 1), bwd_ms=round(t_bwd, 4),
+                              bwd_tflops=round(2.5 * fl / t_bwd / 1e9, 1), cudnn_bwd_ms=round(t_lib_bwd, 4))),
+              flush=True)
 
 
 FUSED_SHAPES = [
@@ -155,6 +167,15 @@ def bench_fused(iters=8):
             t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             res[name] = float(t.item())
+        if os.environ.get("AXB_AR_DEBUG") and rank == 0:
+            from axonn_b200.ops import _lib
+
+            L = _lib.lib()
+            words = [L.axb_debug_word(dev.index, i, 1) for i in range(2, 7)]
+            tiles = max(1, words[2])
+            print("comm CTA 0 per tile (us): wait_stage %.2f wait_flags %.2f | wait_data %.2f reduce %.2f (tiles %d)" % (
+                words[0] / tiles / 1e3, words[1] / tiles / 1e3, words[3] / tiles / 1e3, words[4] / tiles / 1e3, tiles),
+                flush=True)
         flops, nbytes = 2.0 * M * N * K, 2.0 * M * N * (world - 1)
         roof_ms = max(flops / (peak * 1e12), nbytes / 770e9) * 1e3
         if rank == 0:
