@@ -32,7 +32,7 @@ namespace axb {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 352;   // TMA warp, MMA warp, 4 epilogue warps, 4 reducer warps, flagger warp
 
 struct GemmParams {
   void* C;
@@ -205,12 +205,6 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
   }
 }
 
-// 1-D bulk async copy global -> shared (no multicast), completion counted in bytes on an mbarrier.
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               : : "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-
 // Finish 8 consecutive reduced values of one output row: bias / GELU / store.
 __device__ __forceinline__ void comm_finish8(const GemmParams& p, float* v, size_t row, int col) {
   if (p.epilogue == 1 || p.epilogue == 2) {
@@ -236,101 +230,96 @@ __device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) 
   unpack2(u.w, dtype, a, b); acc[6] += a; acc[7] += b;
 }
 
-// ---- comm CTA: reduces finished tiles while the other CTAs of the same kernel compute.  For every tile
-// (in the order the GEMM CTAs produce them) it waits until the (tile, warp) flags of all ranks are up - the
-// peers' partials were pushed into this rank's inbox over NVLink by their epilogues -, then sums the inbox
-// slots of all ranks in rank order (local, coalesced 16-byte loads, 8 in flight per thread; identical bits
-// on every rank), applies bias / GELU and writes C.  In reduce-scatter mode only the 32-row groups owned by
-// this rank exist in the inbox and are reduced.
-template <int BN>
-__device__ __forceinline__ void comm_cta(const GemmParams& p, int group, int num_tiles, uint8_t* smem) {
-  __shared__ int sh_fail;
+// ---- reducer warps (warps 6-9 of every CTA): second half of the fused all-reduce / reduce-scatter.
+// They follow the CTA's own tile sequence: for each tile they wait (bounded) until the (tile, warp) flags of
+// all ranks are up - the peers' partials were pushed into this rank's inbox over NVLink by their epilogues,
+// this CTA's epilogue stored its own -, then sum the inbox slots of all ranks in rank order (identical bits
+// on every rank; loads of all ranks are issued before any is used), apply bias / GELU and write C.  They
+// only wait on memory, so they run beside the MMA and epilogue warps of the same SM: the reduction of every
+// tile is spread over all SMs without taking any away from the GEMM.  In reduce-scatter mode only the
+// 32-row groups owned by this rank exist in the inbox and are reduced.
+template <int BN, int NR>
+__device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag) {
   constexpr int CH = BN / 32;                 // 32-column chunks per tile row
   constexpr int WVEC = CH * 4 * 32;           // 16-byte words per (tile, warp) slot
-  constexpr int TVEC = 4 * WVEC;              // per tile
-  const int ncomm = gridDim.x - p.gemm_ctas;
-  const int cid = blockIdx.x - p.gemm_ctas;
-  if (threadIdx.x == 0) sh_fail = 0;
-  __syncthreads();
-  volatile int* failp = &sh_fail;
-  for (int tile = cid; tile < num_tiles; tile += ncomm) {
+  constexpr int TVEC = 4 * WVEC;
+  constexpr int KB = 32 / NR;                 // vectors per thread and batch: 32 16-byte loads in flight per thread
+  const int tid = threadIdx.x - 192;          // 0..127
+  bool ok = true;
+  for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
     int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
     unsigned mine = 0;
     for (int q = 0; q < 4; ++q)
       if (p.ar.mode == 0 || (tm * BM + q * 32) / p.ar.rows_per_shard == p.ar.rank) mine |= 1u << q;
     if (mine == 0) continue;
-    if (threadIdx.x < 4 * p.ar.n) {
-      const int q = threadIdx.x & 3, j = threadIdx.x >> 2;
-      if (mine & (1u << q)) {
-        const volatile unsigned int* f = p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4 + q;
-        uint64_t t0 = 0;
-        for (uint32_t it = 0;; ++it) {
-          if (static_cast<int>(*f - p.ar.epoch) >= 0) break;
-          if ((it & 0xff) == 0xff) {
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (sh_fail || now - t0 > p.timeout_ns) { sh_fail = 1; break; }
+    if (tid == 0) {
+      // the four (tile, warp) flags of a rank are one aligned 16-byte word
+      uint64_t t0 = 0;
+      for (uint32_t it = 0;; ++it) {
+        bool all = true;
+        for (int j = 0; j < p.ar.n; ++j) {
+          const uint4 f = __ldcv(reinterpret_cast<const uint4*>(p.ar.flags_local + static_cast<size_t>(j) * p.ar.flags_per_src + tile * 4));
+          const unsigned int fv[4] = {f.x, f.y, f.z, f.w};
+          for (int q = 0; q < 4; ++q)
+            if ((mine & (1u << q)) && static_cast<int>(fv[q] - p.ar.epoch) < 0) all = false;
+        }
+        if (all) break;
+        if ((it & 0x3f) == 0x3f) {
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (*abort_flag || now - t0 > p.timeout_ns) { *abort_flag = 1; break; }
+        }
+      }
+      __threadfence_system();   // acquire side of the flags, once per tile
+    }
+    asm volatile("bar.sync 3, 128;" ::: "memory");
+    if (*abort_flag) { ok = false; break; }
+    const uint4* inbox = reinterpret_cast<const uint4*>(p.ar.inbox_local) + static_cast<size_t>(tile) * TVEC;
+    // A unit is one output row segment of 32 columns (4 vectors of one lane of one chunk): the thread that
+    // reduces it writes 64 contiguous bytes of C, so every 32-byte sector of C is written in one piece.
+    constexpr int UNITS = TVEC / 4;
+    constexpr int UB = KB / 4;                  // units per thread and batch (KB vectors per rank in flight)
+    for (int base = tid; base < UNITS; base += 128 * UB) {
+      uint4 in[NR][UB][4];
+#pragma unroll
+      for (int j = 0; j < NR; ++j) {
+        if (j < p.ar.n) {
+          const uint4* src = inbox + static_cast<size_t>(j) * p.ar.inbox_vecs_per_src;
+#pragma unroll
+          for (int k = 0; k < UB; ++k) {
+            const int u = base + k * 128;
+            const int q = u / (CH * 32), c = (u >> 5) % CH, ln = u & 31;
+            const bool live = u < UNITS && (mine & (1u << q));
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              in[j][k][i] = live ? __ldcg(src + q * WVEC + (c * 4 + i) * 32 + ln) : make_uint4(0u, 0u, 0u, 0u);
           }
         }
-        __threadfence_system();   // acquire: the flagged data is visible to the loads below
-      }
-    }
-    __syncthreads();
-    if (sh_fail) break;
-    const uint4* inbox = reinterpret_cast<const uint4*>(p.ar.inbox_local) + static_cast<size_t>(tile) * TVEC;
-    for (int base = threadIdx.x; base < TVEC; base += blockDim.x * 8) {
-      float acc[8][8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
-      for (int j = 0; j < p.ar.n; ++j) {
-        const uint4* src = inbox + static_cast<size_t>(j) * p.ar.inbox_vecs_per_src;
-        uint4 in[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int v = base + k * blockDim.x;
-          in[k] = (v < TVEC && (mine & (1u << (v / WVEC)))) ? __ldcg(src + v) : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc_vec8(acc[k], in[k], p.in_dtype);
       }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int v = base + k * blockDim.x;
-        if (v >= TVEC) continue;
-        const int q = v / WVEC;
+      for (int k = 0; k < UB; ++k) {
+        const int u = base + k * 128;
+        if (u >= UNITS) continue;
+        const int q = u / (CH * 32), c = (u >> 5) % CH, ln = u & 31;
         if (!(mine & (1u << q))) continue;
-        const int w = v - q * WVEC;
-        const int c = w >> 7, i = (w >> 5) & 3, ln = w & 31;
         const size_t row = static_cast<size_t>(tm) * BM + q * 32 + ln;
-        const int col = tn * BN + c * 32 + i * 8;
-        if (row >= static_cast<size_t>(p.M) || col >= p.N) continue;
-        comm_finish8(p, acc[k], row, col);
+        if (row >= static_cast<size_t>(p.M)) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = tn * BN + c * 32 + i * 8;
+          if (col >= p.N) continue;
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+          for (int j = 0; j < NR; ++j)
+            if (j < p.ar.n) acc_vec8(acc, in[j][k][i], p.in_dtype);
+          comm_finish8(p, acc, row, col);
+        }
       }
     }
   }
-  if (sh_fail && threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
-  // take part in the end-of-kernel completion count
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(p.ar.counter, 1u) == gridDim.x - 1) {
-      *p.ar.counter = 0;
-      __threadfence_system();
-      for (int j = 0; j < p.ar.n; ++j)
-        if (j != p.ar.rank) st_release_sys(p.ar.done_peer[j] + p.ar.rank, p.ar.epoch);
-    }
-  }
-  if (p.ag.n > 1 && threadIdx.x == 32) {
-    __threadfence();
-    if (atomicAdd(p.ag.counter, 1u) == gridDim.x - 1) {
-      *p.ag.counter = 0;
-      __threadfence_system();
-      for (int j = 0; j < p.ag.n; ++j)
-        if (j != p.ag.rank) st_release_sys(p.ag.done_peer[j] + p.ag.rank, p.ag.epoch);
-    }
-  }
+  if (!ok && tid == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
 }
 
 template <int BN, int A_MN, int B_MN>
@@ -346,6 +335,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  volatile unsigned int* parts_done = reinterpret_cast<volatile unsigned int*>(tmem_ptr_smem + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -355,15 +345,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint64_t timeout = p.timeout_ns;
   const int gemm_ctas = p.gemm_ctas;   // CTAs [gemm_ctas, gridDim.x) are comm CTAs (reduction over peer memory)
 
-  if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
-    comm_cta<BN>(p, group, num_tiles, smem);
-    return;
-  }
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
     *abort_flag = 0;
+    *parts_done = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
@@ -490,6 +476,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x102u;
     }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ flagger: publishes finished partials
+    // One thread waits until the four epilogue warps have stored a tile's partial (shared counter), runs
+    // the single system-scope fence the tile needs and raises its flags on the reducing ranks, so that the
+    // fence latency is off the epilogue's path.
+    if (p.ar.n > 1 && lane == 0) {
+      int t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gemm_ctas, ++t) {
+        int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+        uint64_t t0 = 0;
+        bool good = true;
+        for (uint32_t it = 0; static_cast<int>(*parts_done - 4u * (t + 1)) < 0; ++it) {
+          if ((it & 0xff) == 0xff) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (*abort_flag || now - t0 > timeout) { good = false; break; }
+          }
+        }
+        if (!good) break;
+        if (!(p.debug & 1)) __threadfence_system();
+        for (int qq = 0; qq < 4; ++qq) {
+          const int own = (p.ar.mode == 1) ? (tm * BM + qq * 32) / p.ar.rows_per_shard : -1;
+          for (int j = 0; j < p.ar.n; ++j) {
+            if (p.ar.mode == 1 && j != own) continue;
+            unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
+                              static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + qq;
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar.epoch) : "memory");
+          }
+        }
+      }
+    }
+  } else if (warp >= 6) {
+    if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag);
+    else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4>(p, group, num_tiles, abort_flag);
+    else if (p.ar.n > 4) reducer_warps<BN, 8>(p, group, num_tiles, abort_flag);
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -602,15 +623,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tcgen05_fence_before();
       __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);   // accumulator is free: the MMA warp runs ahead
+      // hand the stored partial to the flagger warp (release at CTA scope on a monotonic counter)
       if (lane == 0) {
-        mbar_arrive(&tmem_empty[buf]);   // accumulator is free: the MMA warp runs ahead
-        if (!(p.debug & 1)) __threadfence_system();   // all 32 lanes' stores (ordered by the warp sync) before the flags
-        for (int j = 0; j < p.ar.n; ++j) {
-          if (p.ar.mode == 1 && j != owner) continue;
-          unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
-                            static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + q;
-          st_release_sys(f, p.ar.epoch);
-        }
+        __threadfence_block();
+        atomicAdd(const_cast<unsigned int*>(parts_done), 1u);
       }
     }
     if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x104u;
@@ -701,12 +718,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
   const int tiles = p.tiles_m * p.tiles_n;
   const int sms = sm_count(device);
   // every CTA must be resident at once (comm CTAs wait for GEMM CTAs of the same launch): grid <= #SMs
-  int n_comm = 0;
-  if (p.ar.n > 1) {
-    n_comm = p.ar.comm_ctas > 0 ? p.ar.comm_ctas : 32;
-    if (n_comm > sms / 2) n_comm = sms / 2;
-    if (n_comm > tiles) n_comm = tiles;
-  }
+  const int n_comm = 0;   // the reduction runs on warps 6-9 of every CTA
   p.gemm_ctas = tiles < sms - n_comm ? tiles : sms - n_comm;
   if (p.ag.n > 1 && p.ag.n_copy > p.gemm_ctas) { p.ag.n_copy = p.gemm_ctas; p.ag.ready_target = p.ag.n_copy; }
   const int grid = p.gemm_ctas + n_comm;

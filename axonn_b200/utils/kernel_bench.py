@@ -171,11 +171,11 @@ def bench_fused(iters=8):
             from axonn_b200.ops import _lib
 
             L = _lib.lib()
-            words = [L.axb_debug_word(dev.index, i, 1) for i in range(2, 7)]
-            tiles = max(1, words[2])
-            print("comm CTA 0 per tile (us): wait_stage %.2f wait_flags %.2f | wait_data %.2f reduce %.2f (tiles %d)" % (
-                words[0] / tiles / 1e3, words[1] / tiles / 1e3, words[3] / tiles / 1e3, words[4] / tiles / 1e3, tiles),
-                flush=True)
+            w = {i: L.axb_debug_word(dev.index, i, 1) for i in range(2, 8)}
+            tiles = max(1, w[7])
+            print("comm CTA 0, us per tile: fetcher poll %.2f fence %.2f stage-wait+issue %.2f | reducer wait %.2f reduce %.2f "
+                  "(tiles %d)" % (w[2] / tiles / 1e3, w[3] / tiles / 1e3, w[4] / tiles / 1e3, w[5] / tiles / 1e3,
+                                  w[6] / tiles / 1e3, tiles), flush=True)
         flops, nbytes = 2.0 * M * N * K, 2.0 * M * N * (world - 1)
         roof_ms = max(flops / (peak * 1e12), nbytes / 770e9) * 1e3
         if rank == 0:
