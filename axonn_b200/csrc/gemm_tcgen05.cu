@@ -32,7 +32,10 @@ namespace axb {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 352;   // TMA warp, MMA warp, 4 epilogue warps, 4 reducer warps, flagger warp
+constexpr int REDUCER_THREADS = 256;
+constexpr int GEMM_THREADS = 192 + REDUCER_THREADS + 64;   // TMA warp, MMA warp, 4 epilogue warps, 8 reducer warps, flagger warp, watcher warp
+constexpr int FLAGGER_WARP = (192 + REDUCER_THREADS) / 32;
+constexpr int WATCHER_WARP = FLAGGER_WARP + 1;
 
 struct GemmParams {
   void* C;
@@ -51,7 +54,7 @@ struct GemmParams {
   int tn_offset;  // rotation of the N-tile order (all-gather mode: tiles of the local shard first)
   int kb_offset;  // rotation of the K-block order (all-gather mode, B rows = K: local shard first)
   int gemm_ctas;  // number of CTAs computing tiles; the remaining CTAs of the grid reduce over peer memory
-  int debug;      // timing experiments only (AXB_AR_DEBUG): 1 no system fence, 2 no peer stores, 4 no inbox loads
+  int debug;      // timing experiments only (AXB_AR_DEBUG): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores
 };
 
 template <int BN>
@@ -238,23 +241,23 @@ __device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) 
 // only wait on memory, so they run beside the MMA and epilogue warps of the same SM: the reduction of every
 // tile is spread over all SMs without taking any away from the GEMM.  In reduce-scatter mode only the
 // 32-row groups owned by this rank exist in the inbox and are reduced.
-template <int BN, int NR>
-__device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag) {
-  constexpr int CH = BN / 32;                 // 32-column chunks per tile row
-  constexpr int WVEC = CH * 4 * 32;           // 16-byte words per (tile, warp) slot
-  constexpr int TVEC = 4 * WVEC;
-  constexpr int KB = 32 / NR;                 // vectors per thread and batch: 32 16-byte loads in flight per thread
-  const int tid = threadIdx.x - 192;          // 0..127
-  bool ok = true;
-  for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
+// ---- watcher (one thread per CTA): runs ahead of the reducer warps over the CTA's tile sequence, waits
+// (bounded) until the (tile, warp) flags of all ranks are up, performs the acquire fence once per tile and
+// publishes the count of ready tiles in shared memory, so that polling global memory and the system-scope
+// fence overlap the reduction of the previous tile instead of preceding each one.
+template <int BN>
+__device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
+                                               volatile unsigned int* ready_tiles) {
+  int t = 0;
+  for (int tile = blockIdx.x; tile < num_tiles; tile += p.gemm_ctas, ++t) {
     int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
     unsigned mine = 0;
     for (int q = 0; q < 4; ++q)
       if (p.ar.mode == 0 || (tm * BM + q * 32) / p.ar.rows_per_shard == p.ar.rank) mine |= 1u << q;
-    if (mine == 0) continue;
-    if (tid == 0) {
+    if (mine != 0) {
       // the four (tile, warp) flags of a rank are one aligned 16-byte word
       uint64_t t0 = 0;
+      bool good = true;
       for (uint32_t it = 0;; ++it) {
         bool all = true;
         for (int j = 0; j < p.ar.n; ++j) {
@@ -267,38 +270,114 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
         if ((it & 0x3f) == 0x3f) {
           const uint64_t now = globaltimer_ns();
           if (t0 == 0) t0 = now;
-          else if (*abort_flag || now - t0 > p.timeout_ns) { *abort_flag = 1; break; }
+          else if (*abort_flag || now - t0 > p.timeout_ns) { *abort_flag = 1; good = false; break; }
         }
       }
-      __threadfence_system();   // acquire side of the flags, once per tile
+      if (!good) {
+        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x121u;
+        return;
+      }
+      if (!(p.debug & 4)) __threadfence_system();   // acquire side of the flags, once per tile
     }
-    asm volatile("bar.sync 3, 128;" ::: "memory");
+    __threadfence_block();
+    *ready_tiles = static_cast<unsigned>(t + 1);
+  }
+}
+
+// 16-byte L2 load whose position among the other loads and the pins below is fixed for the compiler
+__device__ __forceinline__ uint4 ld_cg_ordered(const uint4* ptr) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
+// keeps a loaded word from being consumed before every load that precedes this statement was issued
+__device__ __forceinline__ void pin(uint4& v) { asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)); }
+
+template <int BN, int NR>
+__device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
+                                              volatile unsigned int* ready_tiles) {
+  constexpr int CH = BN / 32;                 // 32-column chunks per tile row
+  constexpr int WVEC = CH * 4 * 32;           // 16-byte words per (tile, warp) slot
+  constexpr int TVEC = 4 * WVEC;
+  constexpr int RG = NR < 4 ? NR : 4;         // ranks whose words are in flight together
+  constexpr int UB = 4 / RG;                  // units per thread and batch: RG * UB * 4 = 16 loads in flight
+  constexpr int UNITS = TVEC / 4;
+  const int tid = threadIdx.x - 192;          // 0 .. REDUCER_THREADS-1
+  bool ok = true;
+  int t = -1;
+  const bool probe = (p.debug & 64) && blockIdx.x == 0 && tid == 0;
+  uint64_t ns_wait = 0, ns_work = 0, ns_mark = probe ? globaltimer_ns() : 0;
+  for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
+    ++t;
+    int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+    unsigned mine = 0;
+    for (int q = 0; q < 4; ++q)
+      if (p.ar.mode == 0 || (tm * BM + q * 32) / p.ar.rows_per_shard == p.ar.rank) mine |= 1u << q;
+    if (mine == 0) continue;
+    if (tid == 0) {
+      // the watcher warp has seen (and acquired) the flags of all ranks for tiles [0, *ready_tiles)
+      uint64_t t0 = 0;
+      for (uint32_t it = 0; static_cast<int>(*ready_tiles - static_cast<unsigned>(t + 1)) < 0; ++it) {
+        if (*abort_flag) break;
+        if ((it & 0xfff) == 0xfff) {
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > p.timeout_ns) { *abort_flag = 1; break; }
+        }
+      }
+      __threadfence_block();
+    }
+    asm volatile("bar.sync 3, %0;" ::"n"(REDUCER_THREADS) : "memory");
     if (*abort_flag) { ok = false; break; }
+    if (probe) { const uint64_t now = globaltimer_ns(); ns_wait += now - ns_mark; ns_mark = now; }
+    if (p.debug & 8) continue;
     const uint4* inbox = reinterpret_cast<const uint4*>(p.ar.inbox_local) + static_cast<size_t>(tile) * TVEC;
     // A unit is one output row segment of 32 columns (4 vectors of one lane of one chunk): the thread that
     // reduces it writes 64 contiguous bytes of C, so every 32-byte sector of C is written in one piece.
-    constexpr int UNITS = TVEC / 4;
-    constexpr int UB = KB / 4;                  // units per thread and batch (KB vectors per rank in flight)
-    for (int base = tid; base < UNITS; base += 128 * UB) {
-      uint4 in[NR][UB][4];
+    for (int base = tid; base < UNITS; base += REDUCER_THREADS * UB) {
+      float acc[UB][4][8];
 #pragma unroll
-      for (int j = 0; j < NR; ++j) {
-        if (j < p.ar.n) {
-          const uint4* src = inbox + static_cast<size_t>(j) * p.ar.inbox_vecs_per_src;
+      for (int k = 0; k < UB; ++k)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[k][i][e] = 0.f;
+#pragma unroll
+      for (int j0 = 0; j0 < NR; j0 += RG) {
+        if (j0 >= p.ar.n) break;
+        uint4 in[RG][UB][4];
+#pragma unroll
+        for (int jj = 0; jj < RG; ++jj) {
+          const int j = j0 + jj;
+          const uint4* src = inbox + static_cast<size_t>(j < p.ar.n ? j : 0) * p.ar.inbox_vecs_per_src;
 #pragma unroll
           for (int k = 0; k < UB; ++k) {
-            const int u = base + k * 128;
+            const int u = base + k * REDUCER_THREADS;
             const int q = u / (CH * 32), c = (u >> 5) % CH, ln = u & 31;
-            const bool live = u < UNITS && (mine & (1u << q));
+            const bool live = j < p.ar.n && u < UNITS && (mine & (1u << q));
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              in[j][k][i] = live ? __ldcg(src + q * WVEC + (c * 4 + i) * 32 + ln) : make_uint4(0u, 0u, 0u, 0u);
+            for (int i = 0; i < 4; ++i) {
+              if (live) in[jj][k][i] = ld_cg_ordered(src + q * WVEC + (c * 4 + i) * 32 + ln);
+              else in[jj][k][i] = make_uint4(0u, 0u, 0u, 0u);
+            }
           }
         }
+#pragma unroll
+        for (int jj = 0; jj < RG; ++jj)
+#pragma unroll
+          for (int k = 0; k < UB; ++k)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pin(in[jj][k][i]);
+#pragma unroll
+        for (int jj = 0; jj < RG; ++jj)   // rank order: identical bits on every rank
+#pragma unroll
+          for (int k = 0; k < UB; ++k)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc_vec8(acc[k][i], in[jj][k][i], p.in_dtype);
       }
 #pragma unroll
       for (int k = 0; k < UB; ++k) {
-        const int u = base + k * 128;
+        const int u = base + k * REDUCER_THREADS;
         if (u >= UNITS) continue;
         const int q = u / (CH * 32), c = (u >> 5) % CH, ln = u & 31;
         if (!(mine & (1u << q))) continue;
@@ -308,16 +387,15 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
         for (int i = 0; i < 4; ++i) {
           const int col = tn * BN + c * 32 + i * 8;
           if (col >= p.N) continue;
-          float acc[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-          for (int j = 0; j < NR; ++j)
-            if (j < p.ar.n) acc_vec8(acc, in[j][k][i], p.in_dtype);
-          comm_finish8(p, acc, row, col);
+          comm_finish8(p, acc[k][i], row, col);
         }
       }
     }
+    if (probe) { const uint64_t now = globaltimer_ns(); ns_work += now - ns_mark; ns_mark = now; }
+  }
+  if (probe) {
+    volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(p.status);
+    w[2] = static_cast<unsigned>(ns_wait); w[3] = static_cast<unsigned>(ns_work); w[7] = static_cast<unsigned>(t + 1);
   }
   if (!ok && tid == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
 }
@@ -336,6 +414,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   volatile unsigned int* parts_done = reinterpret_cast<volatile unsigned int*>(tmem_ptr_smem + 2);
+  volatile unsigned int* ready_tiles = reinterpret_cast<volatile unsigned int*>(tmem_ptr_smem + 3);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -350,6 +429,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
     *abort_flag = 0;
     *parts_done = 0;
+    *ready_tiles = 0;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
@@ -476,7 +556,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x102u;
     }
-  } else if (warp == 10) {
+  } else if (warp == FLAGGER_WARP) {
     // ------------------------------------------------------------------ flagger: publishes finished partials
     // One thread waits until the four epilogue warps have stored a tile's partial (shared counter), runs
     // the single system-scope fence the tile needs and raises its flags on the reducing ranks, so that the
@@ -507,10 +587,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
+  } else if (warp == WATCHER_WARP) {
+    if (p.ar.n > 1 && lane == 0) watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles);
   } else if (warp >= 6) {
-    if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag);
-    else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4>(p, group, num_tiles, abort_flag);
-    else if (p.ar.n > 4) reducer_warps<BN, 8>(p, group, num_tiles, abort_flag);
+    if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag, ready_tiles);
+    else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4>(p, group, num_tiles, abort_flag, ready_tiles);
+    else if (p.ar.n > 4) reducer_warps<BN, 8>(p, group, num_tiles, abort_flag, ready_tiles);
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -616,7 +698,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int j = 0; j < p.ar.n; ++j) {
           if (p.ar.mode == 1 && j != owner) continue;
           if ((p.debug & 2) && j != p.ar.rank) continue;
+          if (p.debug & 16) continue;
           uint4* dst = reinterpret_cast<uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + slot_vec + (c * 4) * 32;
+          if ((p.debug & 32) && j == p.ar.rank) {
+            uint64_t pol;
+            asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(dst + i * 32), "r"(w[i].x),
+                           "r"(w[i].y), "r"(w[i].z), "r"(w[i].w), "l"(pol) : "memory");
+            continue;
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) dst[i * 32] = w[i];
         }

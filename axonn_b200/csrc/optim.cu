@@ -10,6 +10,7 @@ namespace axb {
 
 constexpr int MT_CHUNK = 1 << 16;
 constexpr int MT_THREADS = 512;
+constexpr int ADAM_UNROLL = 4;
 
 // table row for norm/scale: {ptr, numel, dtype (0 fp32, 1 bf16, 2 fp16), chunk_prefix}
 // table row for adamw:      {master fp32, model bf16 or 0, grad, exp_avg, exp_avg_sq, numel, grad dtype, chunk_prefix}
@@ -131,41 +132,57 @@ multi_adamw_kernel(const long long* __restrict__ table, int n, long long total_c
                            reinterpret_cast<uintptr_t>(model)) & 15) == 0;
     long long scalar_from = begin;
     if (aligned && gdtype != 2) {
-      // 4 elements per thread per iteration: 16-byte accesses to the fp32 state, 8-byte to bf16 tensors
+      // 4 elements per vector: 16-byte accesses to the fp32 state, 8-byte to bf16 tensors.  Every thread
+      // loads ADAM_UNROLL vectors of all four streams before it computes, so that enough bytes are in
+      // flight per SM to cover the DRAM latency; the state is touched once per step, hence streaming hints.
       const long long nv = (end - begin) / 4;
-      for (long long q = threadIdx.x; q < nv; q += blockDim.x) {
-        const long long i = begin + q * 4;
-        float4 p4 = *reinterpret_cast<const float4*>(master + i);
-        float4 m4 = *reinterpret_cast<const float4*>(m + i);
-        float4 v4 = *reinterpret_cast<const float4*>(v + i);
-        float g4[4];
-        if (gdtype == 0) {
-          const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grad) + i);
-          g4[0] = t.x; g4[1] = t.y; g4[2] = t.z; g4[3] = t.w;
-        } else {
-          const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(grad) + i);
-          const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
-          const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
-          g4[0] = __bfloat162float(a.x); g4[1] = __bfloat162float(a.y);
-          g4[2] = __bfloat162float(b.x); g4[3] = __bfloat162float(b.y);
-        }
-        float pp[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+      for (long long q0 = threadIdx.x; q0 < nv; q0 += (long long)blockDim.x * ADAM_UNROLL) {
+        float4 p4[ADAM_UNROLL], m4[ADAM_UNROLL], v4[ADAM_UNROLL];
+        float g4[ADAM_UNROLL][4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float g = g4[k] * gs;
-          mm[k] = a.beta1 * mm[k] + (1.f - a.beta1) * g;
-          vv[k] = a.beta2 * vv[k] + (1.f - a.beta2) * g * g;
-          const float denom = sqrtf(vv[k]) * inv_sqrt_c2 + a.eps;
-          pp[k] = pp[k] * decay - step * mm[k] / denom;
+        for (int u = 0; u < ADAM_UNROLL; ++u) {
+          const long long q = q0 + (long long)u * blockDim.x;
+          if (q < nv) {
+            const long long i = begin + q * 4;
+            p4[u] = __ldcs(reinterpret_cast<const float4*>(master + i));
+            m4[u] = __ldcs(reinterpret_cast<const float4*>(m + i));
+            v4[u] = __ldcs(reinterpret_cast<const float4*>(v + i));
+            if (gdtype == 0) {
+              const float4 t = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grad) + i));
+              g4[u][0] = t.x; g4[u][1] = t.y; g4[u][2] = t.z; g4[u][3] = t.w;
+            } else {
+              const uint2 t = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(grad) + i));
+              const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+              const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+              g4[u][0] = __bfloat162float(lo.x); g4[u][1] = __bfloat162float(lo.y);
+              g4[u][2] = __bfloat162float(hi.x); g4[u][3] = __bfloat162float(hi.y);
+            }
+          }
         }
-        *reinterpret_cast<float4*>(master + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
-        *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
-        *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-        if (model) {
-          const __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
-          uint2 o;
-          o.x = *reinterpret_cast<const uint32_t*>(&lo); o.y = *reinterpret_cast<const uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(model + i) = o;
+#pragma unroll
+        for (int u = 0; u < ADAM_UNROLL; ++u) {
+          const long long q = q0 + (long long)u * blockDim.x;
+          if (q >= nv) continue;
+          const long long i = begin + q * 4;
+          float pp[4] = {p4[u].x, p4[u].y, p4[u].z, p4[u].w}, mm[4] = {m4[u].x, m4[u].y, m4[u].z, m4[u].w},
+                vv[4] = {v4[u].x, v4[u].y, v4[u].z, v4[u].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float g = g4[u][k] * gs;
+            mm[k] = a.beta1 * mm[k] + (1.f - a.beta1) * g;
+            vv[k] = a.beta2 * vv[k] + (1.f - a.beta2) * g * g;
+            const float denom = sqrtf(vv[k]) * inv_sqrt_c2 + a.eps;
+            pp[k] = pp[k] * decay - step * mm[k] / denom;
+          }
+          __stcs(reinterpret_cast<float4*>(master + i), make_float4(pp[0], pp[1], pp[2], pp[3]));
+          __stcs(reinterpret_cast<float4*>(m + i), make_float4(mm[0], mm[1], mm[2], mm[3]));
+          __stcs(reinterpret_cast<float4*>(v + i), make_float4(vv[0], vv[1], vv[2], vv[3]));
+          if (model) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
+            uint2 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&lo); o.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(model + i) = o;
+          }
         }
       }
       scalar_from = begin + nv * 4;

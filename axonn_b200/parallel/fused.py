@@ -146,6 +146,56 @@ def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, aux=None,
     return out
 
 
+_loopback = {}
+
+
+def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None):
+    """Single-GPU emulation of a two-rank ``gemm_all_reduce`` (layout 0): the "peer" inbox, flags and done
+    words are aliased onto this GPU's own slots of source rank 1, so one launch pushes its partial twice,
+    reduces both copies and returns ``2 * (a @ b.T)`` (+bias, +GELU).  The kernel only ever waits on flags
+    that its own CTAs raise.  It exercises the whole communication path of the kernel - epilogue pushes,
+    flag publication, reducer warps, end-of-call handshake - with NVLink replaced by local stores, which is
+    what a one-GPU test or a profiler capture of that path needs."""
+    M, K = a.shape
+    N = b.shape[0]
+    dev = a.device
+    tiles_m = (M + _BM - 1) // _BM
+    bn = 256 if tiles_m * ((N + 255) // 256) >= 148 else 128
+    tiles = tiles_m * ((N + bn - 1) // bn)
+    flags_per_src = (tiles * 4 + 1023) // 1024 * 1024
+    vecs_per_src = tiles * 4 * (bn // 32) * 128
+    fbytes, ibytes = 2 * flags_per_src * 4, 2 * vecs_per_src * 16
+    f0 = _CTRL_BYTES
+    i0 = (f0 + 2 * fbytes + 1023) // 1024 * 1024
+    total = i0 + 2 * ibytes
+    st = _loopback.get(dev)
+    if st is None or st["buf"].numel() < total or st["key"] != (flags_per_src, vecs_per_src):
+        st = _loopback[dev] = {"buf": torch.zeros(total, dtype=torch.uint8, device=dev), "epoch": 1,
+                               "key": (flags_per_src, vecs_per_src)}
+    st["epoch"] += 1
+    parity = st["epoch"] & 1
+    me = st["buf"].data_ptr()
+    c = AxbArCtx()
+    c.n, c.rank, c.epoch, c.bn = 2, 0, st["epoch"], bn
+    c.inbox_local = me + i0 + parity * ibytes
+    c.flags_local = me + f0 + parity * fbytes
+    c.done_local = me
+    c.counter = me + 256
+    c.inbox_peer[0], c.flags_peer[0], c.done_peer[0] = c.inbox_local, c.flags_local, me
+    c.inbox_peer[1] = c.inbox_local + vecs_per_src * 16   # peer's slot of source 0 == own slot of source 1
+    c.flags_peer[1] = c.flags_local + flags_per_src * 4
+    c.done_peer[1] = me + 4                                # peer's done[0] == own done[1]
+    c.inbox_vecs_per_src, c.flags_per_src = vecs_per_src, flags_per_src
+    c.mode, c.rows_per_shard, c.comm_ctas = 0, 0, 0
+    out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=dev)
+    rc = _lib.lib().axb_gemm_ar(
+        ctypes.c_int(0), _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(None),
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]),
+        ctypes.c_int(epilogue), ctypes.c_int(dev.index), _lib.stream_ptr(), ctypes.byref(c))
+    _lib.check(rc, "axb_gemm_ar")
+    return out
+
+
 def reduce_scatter_usable(group, tensor, rows) -> bool:
     n = dist.get_world_size(group)
     return usable(group, tensor) and rows % n == 0 and (rows // n) % 32 == 0

@@ -187,6 +187,32 @@ def bench_fused(iters=8):
         del a, b
 
 
+def bench_fused_loopback(M=16384, N=4096, K=1024, iters=3):
+    """One-GPU emulation of the two-rank fused GEMM+all-reduce (peer slots aliased onto local memory): the
+    local cost of the communication path - epilogue pushes, flags, reducer warps - without NVLink."""
+    from axonn_b200 import ops
+    from axonn_b200.parallel import fused
+
+    dev = torch.device("cuda", 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    t_loop, _ = time_cuda(lambda: fused.gemm_all_reduce_loopback(a, b), iters=iters, flush=flush)
+    t_gemm, _ = time_cuda(lambda: ops.matmul_nt(a, b), iters=iters, flush=flush)
+    ref = 2.0 * (a.float() @ b.float().t())
+    err = float((fused.gemm_all_reduce_loopback(a, b).float() - ref).abs().max() / ref.abs().max())
+    import os
+
+    if int(os.environ.get("AXB_AR_DEBUG", "0")) & 64:
+        from axonn_b200.ops import _lib
+
+        w = {i: _lib.lib().axb_debug_word(0, i, 1) for i in (2, 3, 7)}
+        print("reducer of CTA 0, last call: wait %.2f us/tile, work %.2f us/tile, %d tiles" % (
+            w[2] / max(1, w[7]) / 1e3, w[3] / max(1, w[7]) / 1e3, w[7]), flush=True)
+    print(json.dumps(dict(label="fused GEMM+AR, two ranks emulated on one GPU", M=M, N=N, K=K,
+                          loopback_ms=round(t_loop, 4), gemm_ms=round(t_gemm, 4), rel_err=round(err, 5))), flush=True)
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
@@ -198,6 +224,8 @@ if __name__ == "__main__":
         bench_attention(small=True)
     elif what == "attn":
         bench_attention()
+    elif what == "fused_loopback":
+        bench_fused_loopback()
     elif what == "fused":
         import os
 

@@ -87,3 +87,22 @@ def test_gemm_bias_gelu_epilogue():
     g_ref = torch.nn.functional.gelu(z_ref, approximate="tanh")
     assert (aux.float() - z_ref).abs().max().item() <= 1e-2 * z_ref.abs().max().item() + 1e-2
     assert (out.float() - g_ref).abs().max().item() <= 1e-2 * g_ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(1024, 512, 256), (4096, 4096, 1024), (300, 136, 64)])
+def test_fused_all_reduce_loopback(shape):
+    """Two-rank GEMM+all-reduce emulated on one GPU (peer slots aliased to local memory): 2 * A B^T."""
+    from axonn_b200.parallel import fused
+
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = 2.0 * (a.float() @ b.float().t()) + bias.float()
+    for _ in range(3):   # three calls: both parities of the double-buffered inbox and the done handshake
+        out = fused.gemm_all_reduce_loopback(a, b, bias=bias, epilogue=1)
+    torch.cuda.synchronize()
+    err = (out.float() - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, err
