@@ -748,6 +748,186 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+// ----------------------------------------------------------------------------- CTA-pair GEMM (cta_group::2)
+// Plain GEMM (no in-kernel communication) on pairs of CTAs: a cluster of two CTAs computes one 256x256 output
+// tile with tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128 of the 256
+// rows/columns of B per K block (32 KB per stage instead of 48 KB, six stages), the leader CTA issues the
+// MMAs for both, and each CTA's epilogue drains the 128 accumulator rows held in its own TMEM.  Shared-memory
+// traffic per SM and flop drops by a third against the single-CTA 128x256 tile, which is what bounds that
+// kernel's tensor-pipe utilisation.  TMA loads carry no multicast; the only cluster-wide signals are the
+// tcgen05.commit arrivals and plain remote mbarrier arrivals.
+constexpr int PAIR_THREADS = 192;   // TMA warp, MMA warp, 4 epilogue warps
+constexpr int PAIR_BN = 256;
+struct PairSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = (PAIR_BN / 2) * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024 /* alignment slack */;
+};
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using S = PairSmem;
+  constexpr int BN = PAIR_BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + S::STAGES;
+  uint64_t* tmem_full = empty_bar + S::STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();         // 0: leader (issues the MMAs), 1: peer
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles_m2 = (p.tiles_m + 1) >> 1;         // 256-row tile rows
+  const int total = tiles_m2 * p.tiles_n;
+  const uint64_t timeout = p.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 8); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 1) { tmem_alloc_pair(tmem_ptr_smem, 2 * BN); tmem_relinquish_pair(); }
+  tcgen05_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();     // both CTAs' barriers are initialised before any remote arrival or TMA signal
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int it = pair_id; it < total && ok; it += num_pairs) {
+        int tm2, tn; tile_coords(it, tiles_m2, p.tiles_n, 8, tm2, tn);
+        const int m0 = (2 * tm2 + static_cast<int>(rank)) * BM;
+        const int n0 = tn * BN + static_cast<int>(rank) * (BN / 2);   // this CTA's half of the B tile
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, timeout)) { ok = false; break; }
+          uint8_t* sA = smem + stage * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          // the leader's barrier counts the bytes of both CTAs' loads of this stage
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d_pair(sA, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sA + j * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * j, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d_pair(sB, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0);
+          }
+          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x141u;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      const uint32_t idesc = umma_idesc(p.in_dtype == 0 ? 1 : 0, A_MN, B_MN, 2 * BM, BN);
+      const uint32_t a_lbo = A_MN ? BK * 128 : 16, a_sbo = 1024, a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t b_lbo = B_MN ? BK * 128 : 16, b_sbo = 1024, b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      int t = 0;
+      for (int it = pair_id; it < total && ok; it += num_pairs, ++t) {
+        const int buf = t & 1;
+        const uint32_t acc_phase = (t >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, timeout)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, timeout)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = umma_smem_desc(a_addr + k * a_kstep, a_lbo, a_sbo);
+            const uint64_t bdesc = umma_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
+            umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);      // frees this stage in both CTAs
+          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tmem_full[buf]);   // accumulator complete: both epilogues may read
+      }
+      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x142u;
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    bool ok = true;
+    int t = 0;
+    for (int it = pair_id; it < total && ok; it += num_pairs, ++t) {
+      int tm2, tn; tile_coords(it, tiles_m2, p.tiles_n, 8, tm2, tn);
+      const int tm = 2 * tm2 + static_cast<int>(rank);
+      const int buf = t & 1;
+      const uint32_t acc_phase = (t >> 1) & 1;
+      if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, timeout)) { ok = false; break; }
+      tcgen05_fence_after();
+      const size_t row = static_cast<size_t>(tm) * BM + q * 32 + lane;
+      const bool row_ok = row < static_cast<size_t>(p.M);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col = tn * BN + c * 32;
+        if (col >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        if (p.epilogue == 1 || p.epilogue == 2) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col + i < p.N) {
+              v[i] += (p.in_dtype == 0) ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + i])
+                                        : __half2float(reinterpret_cast<const __half*>(p.bias)[col + i]);
+            }
+          }
+        }
+        if (p.epilogue >= 2) {
+          if (p.aux != nullptr && row_ok) store_row32(p.aux, p.out_dtype, row, p.N, col, p.N, v, false);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        }
+        if (row_ok) store_row32(p.C, p.out_dtype, row, p.N, col, p.N, v, p.accumulate != 0);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);   // 8 arrivals (4 warps x 2 CTAs) free the buffer
+    }
+    if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x144u;
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();     // the peer's shared memory and TMEM stay valid until every MMA and arrival is done
+  if (warp == 1) { tcgen05_fence_after(); tmem_dealloc_pair(tmem_base, 2 * BN); }
+}
+
 // ----------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -819,6 +999,33 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
   return 0;
 }
 
+template <int A_MN, int B_MN>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int device, cudaStream_t stream) {
+  using S = PairSmem;
+  static bool configured[64] = {false};
+  auto kern = gemm_pair_kernel<A_MN, B_MN>;
+  if (!configured[device & 63]) {
+    AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured[device & 63] = true;
+  }
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + PAIR_BN - 1) / PAIR_BN;
+  const int total = ((p.tiles_m + 1) / 2) * p.tiles_n;
+  const int pairs = sm_count(device) / 2;
+  const int grid = 2 * (total < pairs ? total : pairs);
+  p.gemm_ctas = grid;
+  kern<<<grid, PAIR_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// CTA pairs are used for plain GEMMs wide enough to fill the GPU with 256x256 tiles (AXONN_GEMM_2CTA=0 disables).
+static bool pair_mode_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("AXONN_GEMM_2CTA"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v == 1;
+}
+
 }  // namespace axb
 
 static int gemm_common(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,
@@ -844,7 +1051,10 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
   // K-major operand [R, K]: box 64(K) x tile rows.  MN-major operand [K, R]: box 64(R) x 64(K).
   if (a_mn == 0) { if (make_tmap_2d_16bit(&tmA, A, M, K, BM, in_dtype)) return -1; }
   else           { if (make_tmap_2d_16bit(&tmA, A, K, M, BK, in_dtype)) return -1; }
-  if (b_mn == 0) { if (make_tmap_2d_16bit(&tmB, B, N, K, BN, in_dtype)) return -1; }
+  const bool comm = (ar && ar->n > 1) || (ag && ag->n > 1);
+  const bool pair = !comm && BN == 256 && pair_mode_enabled() &&
+                    static_cast<long long>((tiles_m + 1) / 2) * ((N + 255) / 256) >= sm_count(device) / 2;
+  if (b_mn == 0) { if (make_tmap_2d_16bit(&tmB, B, N, K, pair ? BN / 2 : BN, in_dtype)) return -1; }
   else           { if (make_tmap_2d_16bit(&tmB, B, K, N, BK, in_dtype)) return -1; }
 
   GemmParams p;
@@ -895,6 +1105,11 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
     p.ag.n = 1;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair) {
+    if (layout == 0) return launch_pair<0, 0>(tmA, tmB, p, device, s);
+    if (layout == 1) return launch_pair<0, 1>(tmA, tmB, p, device, s);
+    return launch_pair<1, 1>(tmA, tmB, p, device, s);
+  }
 #define AXB_DISPATCH(BN_, A_, B_) return launch<BN_, A_, B_>(tmA, tmB, p, device, s)
   if (BN == 256) {
     if (layout == 0) AXB_DISPATCH(256, 0, 0);

@@ -89,6 +89,43 @@ def test_gemm_bias_gelu_epilogue():
     assert (out.float() - g_ref).abs().max().item() <= 1e-2 * g_ref.abs().max().item() + 1e-2
 
 
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_gemm_cta_pair_path_ragged(layout):
+    """Shapes wide enough for the CTA-pair (256x256 tile) kernel: odd number of 128-row tiles, ragged N and K."""
+    from axonn_b200 import ops
+    from axonn_b200.ops import _lib
+
+    M, N, K = 4104, 4360, 520
+    dev = torch.device("cuda", 0)
+    a, b = _operands(layout, M, N, K, torch.bfloat16, dev)
+    fn = {"nt": ops.matmul_nt, "nn": ops.matmul_nn, "tn": ops.matmul_tn}[layout]
+    ref = _ref(layout, a, b)
+    scale = ref.abs().max().item()
+    for _ in range(2):
+        out32 = fn(a, b, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert _lib.lib().axb_device_status(0, 1) == 0
+    assert (out32 - ref).abs().max().item() <= 2e-4 * scale + 1e-4
+    acc = torch.full((M, N), 3.0, device=dev)
+    fn(a, b, out=acc, accumulate=True)
+    assert (acc - (ref + 3)).abs().max().item() <= 2e-4 * scale + 1e-4
+
+
+def test_gemm_cta_pair_path_epilogue():
+    from axonn_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    M, N, K = 8192, 4096, 1024
+    a, b = _operands("nt", M, N, K, torch.bfloat16, dev)
+    bias = (torch.randn(N, device=dev) * 0.5).bfloat16()
+    z_ref = _ref("nt", a, b) + bias.float()
+    aux = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    out = ops.matmul_nt(a, b, bias=bias, epilogue=ops.EPI_BIAS_GELU, aux=aux)
+    g_ref = torch.nn.functional.gelu(z_ref, approximate="tanh")
+    assert (aux.float() - z_ref).abs().max().item() <= 1e-2 * z_ref.abs().max().item() + 1e-2
+    assert (out.float() - g_ref).abs().max().item() <= 1e-2 * g_ref.abs().max().item() + 1e-2
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("shape", [(1024, 512, 256), (4096, 4096, 1024), (300, 136, 64)])
 def test_fused_all_reduce_loopback(shape):
