@@ -24,6 +24,7 @@ from .conv import Conv2d  # noqa: F401
 from .embedding import Embedding  # noqa: F401
 from .fully_connected import Linear  # noqa: F401
 from .gradient_normalization import clip_grad_norm_  # noqa: F401
+from .gradient_pruning import prune_gradients_, register_pruning_hooks  # noqa: F401
 from .overlap_communication import (  # noqa: F401
     clear_weights_cache,
     optimize_communication,

@@ -1,6 +1,6 @@
 """Model zoo built on the tensor-parallel layers and sm_100a kernels."""
 
-from .gpt import GPT, GPTConfig  # noqa: F401
+from .gpt import GPT, DistributedGPT, GPTConfig  # noqa: F401
 from .llama import Llama, LlamaConfig  # noqa: F401
 from .mixtral import Mixtral, MixtralConfig  # noqa: F401
 from .mlp import MLP  # noqa: F401

@@ -73,3 +73,75 @@ class GPT(nn.Module):
 
     def num_parameters(self):
         return count_parameters(self)
+
+
+class DistributedGPT(nn.Module):
+    """One pipeline stage of the GPT above, for the inter-layer engine.
+
+    Stage ``s`` of ``G_inter`` owns ``n_layers // G_inter`` consecutive blocks; the first stage also owns the
+    token / position embeddings, the last one the final norm and the LM head (logits out; the engine's loss
+    function gets ``[microbatch, seq, vocab_local]``).  Activation checkpointing wraps every ``ckp_coeff``
+    blocks when enabled.  ``get_input_shape`` / ``get_output_shape`` use ``-1`` for the microbatch dimension,
+    which is the engine's contract.  Same role as ``DistributedGPT`` in
+    ``external/models/nvidia_transformer.py`` of the reference (there ``[seq, -1, hidden]``; here
+    batch-first ``[-1, seq, hidden]``, the layout of this package's attention kernels).
+    """
+
+    def __init__(self, cfg: GPTConfig, dtype=torch.bfloat16, ckp_coeff=1, G_inter=None, stage=None):
+        super().__init__()
+        G_inter = ax.config.G_inter if G_inter is None else G_inter
+        stage = ax.config.inter_layer_parallel_rank if stage is None else stage
+        assert cfg.n_layers % G_inter == 0, "n_layers must be divisible by the number of pipeline stages"
+        self.cfg, self.ckp_coeff = cfg, max(1, int(ckp_coeff))
+        self.first, self.last = stage == 0, stage == G_inter - 1
+        init = lambda w: nn.init.normal_(w, std=0.02)  # noqa: E731
+        if self.first:
+            self.tok_emb = Embedding(cfg.vocab, cfg.hidden, expert_mode=True, transpose=True, init_method=init,
+                                     dtype=dtype)
+            self.pos_emb = Embedding(cfg.seq_len, cfg.hidden, expert_mode=True, transpose=True, init_method=init,
+                                     dtype=dtype)
+        self.blocks = nn.ModuleList([
+            TransformerBlock(cfg.hidden, cfg.n_heads, cfg.ffn, activation="gelu", rms=False, bias=True,
+                             max_seq=cfg.seq_len, dtype=dtype, n_layers=cfg.n_layers)
+            for _ in range(cfg.n_layers // G_inter)])
+        if self.last:
+            self.norm_f = TPNorm(cfg.hidden, dtype=dtype)
+            self.head = ParallelLMHead(cfg.hidden, cfg.vocab, dtype=dtype)
+        self._dtype = dtype
+
+    def _hidden_local(self):
+        return self.blocks[0].norm1.local
+
+    def get_input_shape(self):
+        if self.first:
+            return [-1, self.cfg.seq_len]
+        return [-1, self.cfg.seq_len, self._hidden_local()]
+
+    def get_output_shape(self):
+        if self.last:
+            return [-1, self.cfg.seq_len, self.head.proj.local_out_features]
+        return [-1, self.cfg.seq_len, self._hidden_local()]
+
+    def input_dtype(self):
+        return torch.long if self.first else self._dtype
+
+    def _run_blocks(self, x, lo, hi):
+        for blk in self.blocks[lo:hi]:
+            x = blk(x)
+        return x
+
+    def forward(self, x):
+        if self.first:
+            tokens = x.long()
+            pos = torch.arange(tokens.shape[1], device=tokens.device)
+            x = self.tok_emb(tokens) + self.pos_emb(pos)[None]
+        n = len(self.blocks)
+        for lo in range(0, n, self.ckp_coeff):
+            hi = min(n, lo + self.ckp_coeff)
+            if self.cfg.activation_checkpointing and self.training:
+                x = checkpoint(self._run_blocks, x, lo, hi, use_reentrant=False)
+            else:
+                x = self._run_blocks(x, lo, hi)
+        if self.last:
+            x = self.head(self.norm_f(x))
+        return x

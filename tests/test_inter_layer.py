@@ -94,3 +94,54 @@ def test_vgg_partition_and_shapes():
         assert list(x.shape[1:]) == m.get_output_shape()[1:]
         prev_out = m.get_output_shape()[1:]
     assert x.shape == (2, 10)
+
+
+def _gpt_run(rank, world, G_inter, steps):
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200.inter_layer import AxoNN_Inter_Layer_Engine
+    from axonn_b200.models import DistributedGPT, GPTConfig
+
+    ax.init(G_inter=G_inter, G_data=1)
+    cfg = GPTConfig(n_layers=4, hidden=32, n_heads=4, ffn=64, vocab=64, seq_len=16)
+    torch.manual_seed(7)
+    full = DistributedGPT(cfg, dtype=torch.float32, G_inter=1, stage=0)
+    mine = DistributedGPT(cfg, dtype=torch.float32, ckp_coeff=2)
+    per = cfg.n_layers // G_inter
+    stage = ax.config.inter_layer_parallel_rank
+    new = {}
+    for k, v in full.state_dict().items():
+        if k.startswith("blocks."):
+            idx = int(k.split(".")[1])
+            if stage * per <= idx < (stage + 1) * per:
+                new["blocks.%d.%s" % (idx - stage * per, k.split(".", 2)[2])] = v
+        elif k in mine.state_dict():
+            new[k] = v
+    mine.load_state_dict(new)
+    assert mine.get_input_shape() == ([-1, 16] if stage == 0 else [-1, 16, 32])
+    assert mine.get_output_shape() == ([-1, 16, 64] if stage == G_inter - 1 else [-1, 16, 32])
+    opt = torch.optim.SGD(mine.parameters(), lr=0.1)
+    loss_fn = lambda logits, y: F.cross_entropy(logits.reshape(-1, logits.shape[-1]), y.reshape(-1))  # noqa: E731
+    engine = AxoNN_Inter_Layer_Engine(mine, loss_fn, computation_dtype=torch.float32)
+    ax.config.micro_batch_size = 2
+    g = torch.Generator().manual_seed(5)
+    X = torch.randint(0, 64, (8, 16), generator=g)
+    Y = torch.randint(0, 64, (8, 16), generator=g)
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        losses.append(engine.forward_backward_optimizer(X, Y, opt))
+    t = torch.tensor(losses, dtype=torch.float64)
+    if stage != G_inter - 1:
+        t.zero_()
+    dist.all_reduce(t)
+    return t.tolist()
+
+
+def test_gpt_pipeline_stages_match_single_stage():
+    ref = run_distributed(_gpt_run, 1, 1, 3)[0]
+    two = run_distributed(_gpt_run, 2, 2, 3)[0]
+    assert ref[-1] < ref[0]
+    assert all(abs(a - b) < 1e-4 for a, b in zip(ref, two)), (ref, two)

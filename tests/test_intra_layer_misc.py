@@ -148,3 +148,33 @@ def _hf(rank, world):
 def test_transformers_shim_llama():
     pytest.importorskip("transformers")
     assert all(run_distributed(_hf, 2, timeout=400))
+
+
+def _prune_run(rank, world):
+    import torch
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200.intra_layer import Linear, prune_gradients_, register_pruning_hooks
+
+    ax.init(G_inter=1, G_data=1, G_intra_r=1, G_intra_c=1, G_intra_d=2)
+    torch.manual_seed(0)
+    lin = Linear(32, 16, expert_mode=True)
+    x = torch.randn(4, 32)
+    lin(x).square().sum().backward()
+    n = lin.weight.grad.numel()
+    assert prune_gradients_(lin, 0.25) == 1
+    kept = int((lin.weight.grad != 0).sum())
+    assert abs(kept - round(0.25 * n)) <= 1, (kept, n)
+    assert lin.bias is None or (lin.bias.grad != 0).any()   # biases stay dense
+    lin.zero_grad()
+    handles = register_pruning_hooks(lin, 0.5)
+    lin(x).square().sum().backward()
+    kept = int((lin.weight.grad != 0).sum())
+    assert abs(kept - round(0.5 * n)) <= 1, (kept, n)
+    for h in handles:
+        h.remove()
+    return kept
+
+
+def test_gradient_pruning_explicit_and_hooks():
+    run_distributed(_prune_run, 2)
