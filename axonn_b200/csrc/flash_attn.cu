@@ -16,6 +16,7 @@
 //
 // Outputs: O [B, S, heads, D] bf16 and the per-row log-sum-exp (natural log, of the scaled scores)
 // [B, heads, S] fp32 for the backward pass.  All waits are bounded.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -70,9 +71,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = p.S / FA_BQ;
-  const int qt = nq - 1 - static_cast<int>(blockIdx.x);  // heaviest tiles first
-  const int head = blockIdx.y;
-  const int b = blockIdx.z;
+  const int qt = nq - 1 - static_cast<int>(blockIdx.z);  // heaviest tiles first, over the whole grid
+  const int head = blockIdx.x;
+  const int b = blockIdx.y;
   const int g = head / p.qpk, jq = head % p.qpk;
   const int n_kv = qt + 1;                               // causal: tiles 0..qt
   const int row0 = b * p.S + qt * FA_BQ;                 // row in the [B*S, G*(qpk+2)*HD] view
@@ -308,7 +309,7 @@ static int fa_launch(const CUtensorMap& tm, const FaParams& p, int device, cudaS
     AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_::TOTAL));
     configured[device & 63] = true;
   }
-  dim3 grid(p.S / FA_BQ, p.G * p.qpk, p.B);
+  dim3 grid(p.G * p.qpk, p.B, p.S / FA_BQ);   // z (slowest) = query tile, heaviest tiles first
   kern<<<grid, FA_THREADS, S_::TOTAL, s>>>(tm, p);
   AXB_CUDA(cudaGetLastError());
   return 0;
@@ -358,6 +359,7 @@ struct FaBwdParams {
   float scale, scale_log2;
   unsigned int* status;
   unsigned long long timeout_ns;
+  int debug;   // timing experiments only (AXB_FA_DEBUG): 1 no dQ reductions, 2 no exponentials
 };
 
 template <int HD>
@@ -365,7 +367,11 @@ struct FaBwdSmem {
   static constexpr int TILE = 128 * HD * 2;
   static constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = 3 * TILE;
   static constexpr int P_OFF = 4 * TILE, DS_OFF = P_OFF + 32768;
-  static constexpr int BAR_OFF = DS_OFF + 32768;
+  // After the MMAs of an iteration the P / dS tiles are dead until the next iteration writes them; the dQ
+  // partial (fp32, one padded row per query row) is staged there for the bulk reductions into global memory.
+  static constexpr int DQ_ROW_BYTES = HD * 4 + 16;            // +16: consecutive rows start 4 banks apart
+  static constexpr int DQ_STAGE_BYTES = 128 * DQ_ROW_BYTES;
+  static constexpr int BAR_OFF = P_OFF + (DQ_STAGE_BYTES > 65536 ? DQ_STAGE_BYTES : 65536);
   static constexpr int NBARS = 7;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16 + 1024;
 };
@@ -374,8 +380,33 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// thread r holds KV row r of the dK (which = 0) or dV (which = 1) accumulator: TMEM -> packed gradient tensor
 template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__device__ __forceinline__ void fa_store_kv_grad(const FaBwdParams& p, uint32_t src, int b, int jt, int g, int r, int which) {
+  const size_t kvpos = static_cast<size_t>(b) * p.S + jt * 128 + r;
+  __nv_bfloat16* dst = p.dqkv + (kvpos * p.G + g) * (p.qpk + 2) * HD + static_cast<size_t>(p.qpk + which) * HD;
+#pragma unroll 1
+  for (int c = 0; c < HD / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(src + c * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      uint32_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[t * 8 + 2 * k]), __uint_as_float(v[t * 8 + 2 * k + 1]));
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+constexpr int FA_BWD_THREADS = 320;   // TMA warp, MMA warp, 8 softmax / reduction warps
+
+template <int HD>
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, const FaBwdParams p) {
   using S_ = FaBwdSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
@@ -393,8 +424,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = p.S / 128;
-  const int jt = blockIdx.x;            // KV tile (tile 0 has the most work and is scheduled first)
-  const int g = blockIdx.y, b = blockIdx.z;
+  const int jt = blockIdx.z;            // KV tile; tile 0 has the most work and its CTAs are scheduled first
+  const int g = blockIdx.x, b = blockIdx.y;
   const int heads = p.G * p.qpk;
   const int n_iter = (nq - jt) * p.qpk;  // (query tile, query head) pairs
   const int col_k = (g * (p.qpk + 2) + p.qpk) * HD, col_v = col_k + HD;
@@ -403,7 +434,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4); mbar_init(dq_full, 1); mbar_init(s_free, 4);
+    mbar_init(pds_full, 8); mbar_init(dq_full, 1); mbar_init(s_free, 8);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -452,22 +483,34 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       const uint32_t k_addr = smem_u32(smem + S_::K_OFF), v_addr = smem_u32(smem + S_::V_OFF);
       const uint32_t q_addr = smem_u32(smem + S_::Q_OFF), do_addr = smem_u32(smem + S_::DO_OFF);
       const uint32_t p_addr = smem_u32(smem + S_::P_OFF), ds_addr = smem_u32(smem + S_::DS_OFF);
+      const bool probe = (p.debug & 4) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+      uint64_t w_qdo = 0, w_sfree = 0, w_pds = 0, t_mark = probe ? globaltimer_ns() : 0;
       for (int it = 0; it < n_iter && ok; ++it) {
         const uint32_t ph = it & 1;
-        if (!mbar_wait(qdo_full, ph, abort_flag, timeout) || !mbar_wait(s_free, ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+        if (probe) t_mark = globaltimer_ns();
+        if (!mbar_wait(qdo_full, ph, abort_flag, timeout)) { ok = false; break; }
+        if (probe) { const uint64_t now = globaltimer_ns(); w_qdo += now - t_mark; t_mark = now; }
+        tcgen05_fence_after();
+        // dP first: its TMEM columns are free already, while the S columns still hold the previous
+        // iteration's dQ until the reduction warps have drained it
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_f16(tm_dp, umma_smem_desc(do_addr + off, 16, 1024), umma_smem_desc(v_addr + off, 16, 1024), idesc_s, kk != 0);
+        }
+        if (probe) t_mark = globaltimer_ns();
+        if (!mbar_wait(s_free, ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+        if (probe) { const uint64_t now = globaltimer_ns(); w_sfree += now - t_mark; t_mark = now; }
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_f16(tm_s, umma_smem_desc(q_addr + off, 16, 1024), umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0);
         }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_f16(tm_dp, umma_smem_desc(do_addr + off, 16, 1024), umma_smem_desc(v_addr + off, 16, 1024), idesc_s, kk != 0);
-        }
         umma_commit(sdp_full);
+        if (probe) t_mark = globaltimer_ns();
         if (!mbar_wait(pds_full, ph, abort_flag, timeout)) { ok = false; break; }
+        if (probe) { const uint64_t now = globaltimer_ns(); w_pds += now - t_mark; t_mark = now; }
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // reduction over the 128 query rows, 16 per step
@@ -476,35 +519,47 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
           umma_f16(tm_dk, umma_smem_desc(ds_addr + kk * 2048, 16384, 1024), umma_smem_desc(q_addr + kk * 2048, 16384, 1024),
                    idesc_t, (it | kk) != 0);
         }
+        umma_commit(qdo_empty);            // Q and dO are free once dV / dK are done: the next loads overlap dQ
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // reduction over the 128 KV rows
           umma_f16(tm_s, umma_smem_desc(ds_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
                    umma_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_q, kk != 0);
         }
         umma_commit(dq_full);
-        umma_commit(qdo_empty);
+      }
+      if (probe) {
+        volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(p.status);
+        w[2] = static_cast<unsigned>(w_qdo); w[3] = static_cast<unsigned>(w_sfree); w[4] = static_cast<unsigned>(w_pds);
+        w[7] = static_cast<unsigned>(n_iter);
       }
       if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x412u;
     }
   } else {
+    // ---- 8 softmax / reduction warps: thread = (query row r, column half): two warps share each TMEM lane
+    // quarter and split the 128 score columns (and the HD columns of dQ) between them
     const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = q4 * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     uint8_t* p_row = smem + S_::P_OFF + (r >> 3) * 1024 + (r & 7) * 128;
     uint8_t* ds_row = smem + S_::DS_OFF + (r >> 3) * 1024 + (r & 7) * 128;
     bool ok = true;
+    const bool probe = (p.debug & 4) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
+    uint64_t w_sdp = 0, t_a = 0, w_dq = 0, t_b = 0, t_mark = 0;
     for (int it = 0; it < n_iter; ++it) {
       const uint32_t ph = it & 1;
       const int i = jt + it / p.qpk, jq = it % p.qpk;
       const int head = g * p.qpk + jq;
       const size_t srow = static_cast<size_t>(i) * 128 + r;   // query position of this thread's row
+      if (probe) t_mark = globaltimer_ns();
       const float lse2 = p.lse[(static_cast<size_t>(b) * heads + head) * p.S + srow] * 1.4426950408889634f;
       const float dl = p.delta[(static_cast<size_t>(b) * heads + head) * p.S + srow];
       if (!mbar_wait(sdp_full, ph, abort_flag, timeout)) { ok = false; break; }
+      if (probe) { const uint64_t now = globaltimer_ns(); w_sdp += now - t_mark; t_mark = now; }
       tcgen05_fence_after();
       const bool diag = (i == jt);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(tm_s + lane_base + c * 32, sv);
         tmem_ld_32x32(tm_dp + lane_base + c * 32, dv);
@@ -512,8 +567,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
         uint32_t pp[16], dd[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
-          float p0 = exp2f(__uint_as_float(sv[2 * k]) * p.scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(sv[2 * k + 1]) * p.scale_log2 - lse2);
+          float p0 = (p.debug & 2) ? __uint_as_float(sv[2 * k]) : exp2f(__uint_as_float(sv[2 * k]) * p.scale_log2 - lse2);
+          float p1 = (p.debug & 2) ? __uint_as_float(sv[2 * k + 1]) : exp2f(__uint_as_float(sv[2 * k + 1]) * p.scale_log2 - lse2);
           if (diag) {   // key position (column) beyond the query position (row) is masked
             if (c * 32 + 2 * k > r) p0 = 0.f;
             if (c * 32 + 2 * k + 1 > r) p1 = 0.f;
@@ -536,50 +591,46 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if (probe) { const uint64_t now = globaltimer_ns(); t_a += now - t_mark; t_mark = now; }
       // dQ partial of this (query tile, head): TMEM -> fp32 accumulator in global memory
       if (!mbar_wait(dq_full, ph, abort_flag, timeout)) { ok = false; break; }
+      if (probe) { const uint64_t now = globaltimer_ns(); w_dq += now - t_mark; t_mark = now; }
       tcgen05_fence_after();
       float* dq = p.dq_acc + ((static_cast<size_t>(b) * p.S + srow) * heads + head) * HD;
+      // this thread's half row: TMEM -> staging row in shared memory -> one bulk reduce-add into global memory
+      uint8_t* stage = smem + S_::P_OFF + r * S_::DQ_ROW_BYTES + half * (HD * 2);
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tm_s + lane_base + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          red_add_v4(dq + c * 32 + k * 4, __uint_as_float(v[4 * k]), __uint_as_float(v[4 * k + 1]),
-                     __uint_as_float(v[4 * k + 2]), __uint_as_float(v[4 * k + 3]));
+          *reinterpret_cast<uint4*>(stage + (c - half * (HD / 64)) * 128 + k * 16) =
+              make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
       }
       tcgen05_fence_before();
+      if (!(p.debug & 1)) {
+        fence_proxy_async_smem();
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                     ::"l"(dq + half * (HD / 2)), "r"(smem_u32(stage)), "r"(HD * 2) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        // the staging bytes are the next iteration's P / dS tiles: wait until the copy engine has read them
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
+      if (probe) { const uint64_t now = globaltimer_ns(); t_b += now - t_mark; t_mark = now; }
     }
+    if (probe) {
+      volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(p.status);
+      w[8] = static_cast<unsigned>(w_sdp); w[9] = static_cast<unsigned>(t_a); w[10] = static_cast<unsigned>(w_dq);
+      w[11] = static_cast<unsigned>(t_b);
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    // dK (column half 0) and dV (half 1) of this KV tile: every MMA has completed (last dq_full seen)
     if (ok) {
-      // dK, dV of this KV tile: thread r holds KV row r
-      const size_t kvpos = static_cast<size_t>(b) * p.S + jt * 128 + r;
-      __nv_bfloat16* dk = p.dqkv + (kvpos * p.G + g) * (p.qpk + 2) * HD + static_cast<size_t>(p.qpk) * HD;
-      __nv_bfloat16* dvp = dk + HD;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t src = (which == 0 ? tm_dk : tm_dv) + lane_base;
-        __nv_bfloat16* dst = which == 0 ? dk : dvp;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(src + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            uint32_t w[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[t * 8 + 2 * k]), __uint_as_float(v[t * 8 + 2 * k + 1]));
-              w[k] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-      }
+      fa_store_kv_grad<HD>(p, (half == 0 ? tm_dk : tm_dv) + lane_base, b, jt, g, r, half);
     } else if (lane == 0) {
       *reinterpret_cast<volatile unsigned int*>(p.status) = 0x414u;
     }
@@ -621,8 +672,8 @@ static int fa_bwd_launch(const CUtensorMap& tq, const CUtensorMap& td, const FaB
     AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_::TOTAL));
     configured[device & 63] = true;
   }
-  dim3 grid(p.S / 128, p.G, p.B);
-  kern<<<grid, FA_THREADS, S_::TOTAL, s>>>(tq, td, p);
+  dim3 grid(p.G, p.B, p.S / 128);   // z (slowest) = KV tile: all CTAs with the most iterations are scheduled first
+  kern<<<grid, FA_BWD_THREADS, S_::TOTAL, s>>>(tq, td, p);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }
@@ -654,6 +705,7 @@ extern "C" int axb_flash_attn_bwd(const void* qkv, const void* out, const void* 
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
   p.status = st; p.timeout_ns = 2000000000ull;
+  { const char* dbg = getenv("AXB_FA_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
   if (D == 128) return fa_bwd_launch<128>(tq, td, p, device, s);
   return fa_bwd_launch<64>(tq, td, p, device, s);
 }

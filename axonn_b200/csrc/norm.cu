@@ -192,25 +192,203 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
   }
 }
 
-// out[c] = sum_b part[b, c]   (optionally two tables at once).  Block = 32 columns x 8 row-groups.
-__global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb, float* __restrict__ oa,
-                                     float* __restrict__ ob, int nblocks, int H) {
-  __shared__ float sa[8][33], sb[8][33];
-  const int c = blockIdx.x * 32 + threadIdx.x;
-  float a = 0.f, b = 0.f;
-  if (c < H) {
-    for (int r = threadIdx.y; r < nblocks; r += 8) {
-      a += pa[static_cast<size_t>(r) * H + c];
-      if (pb) b += pb[static_cast<size_t>(r) * H + c];
+// ---- mode-0 fast path (statistics local, hidden <= 256 * 8 * CH): a block handles R rows per iteration with one
+// 8-element chunk per thread and CH, keeps the rows in registers between the statistics and the apply step
+// (one global read per element) and needs a single block barrier per iteration: the loads of R rows are in
+// flight together and the cross-warp sums of all R rows share the barrier.
+template <int NV>
+__device__ __forceinline__ void block_sum_n(float (&v)[NV], float* red /* [2][NV][8] */, int it) {
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float* buf = red + (it & 1) * NV * 8;     // double-buffered by iteration: one barrier per iteration
+  if (l == 0) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) buf[k * 8 + w] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    float t = 0.f;
+    for (int i = 0; i < nw; ++i) t += buf[k * 8 + i];
+    v[k] = t;
+  }
+}
+
+template <typename T, bool RMS, int CH, int R>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                     T* __restrict__ y, float* __restrict__ stats, int rows, int H, float eps) {
+  __shared__ float red[2 * 2 * R * 8];
+  const int nchunk = H / 8;
+  float g[CH][8], b[CH][8];
+#pragma unroll
+  for (int k = 0; k < CH; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { g[k][i] = 0.f; b[k][i] = 0.f; }
+    if (c < nchunk) {
+      Vec8<T>::load(gamma + c * 8, g[k]);
+      if (!RMS && beta) Vec8<T>::load(beta + c * 8, b[k]);
     }
   }
-  sa[threadIdx.y][threadIdx.x] = a; sb[threadIdx.y][threadIdx.x] = b;
+  int it = 0;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, ++it) {
+    float f[R][CH][8];
+    float sm[2 * R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      sm[2 * r] = 0.f; sm[2 * r + 1] = 0.f;
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (row0 + r < rows && c < nchunk) Vec8<T>::load(x + static_cast<size_t>(row0 + r) * H + c * 8, f[r][k]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[r][k][i] = 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int k = 0; k < CH; ++k)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { sm[2 * r] += f[r][k][i]; sm[2 * r + 1] += f[r][k][i] * f[r][k][i]; }
+    block_sum_n<2 * R>(sm, red, it);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= rows) break;
+      float mean, rstd;
+      if (RMS) { mean = 0.f; rstd = rsqrtf(sm[2 * r + 1] / H + eps); }
+      else { mean = sm[2 * r] / H; rstd = rsqrtf(fmaxf(sm[2 * r + 1] / H - mean * mean, 0.f) + eps); }
+      if (threadIdx.x == 0) { stats[2 * (row0 + r)] = mean; stats[2 * (row0 + r) + 1] = rstd; }
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c >= nchunk) continue;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (f[r][k][i] - mean) * rstd * g[k][i] + b[k][i];
+        Vec8<T>::store(y + static_cast<size_t>(row0 + r) * H + c * 8, o);
+      }
+    }
+  }
+}
+
+template <typename T, bool RMS, int CH, int R>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_rows_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                     const float* __restrict__ stats, T* __restrict__ dx, float* __restrict__ dgamma_part,
+                     float* __restrict__ dbeta_part, int rows, int H) {
+  __shared__ float red[2 * 2 * R * 8];
+  const int nchunk = H / 8;
+  float g[CH][8], ag[CH][8], ab[CH][8];
+#pragma unroll
+  for (int k = 0; k < CH; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { g[k][i] = 0.f; ag[k][i] = 0.f; ab[k][i] = 0.f; }
+    if (c < nchunk) Vec8<T>::load(gamma + c * 8, g[k]);
+  }
+  int it = 0;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, ++it) {
+    float xh[R][CH][8], d[R][CH][8];
+    float rstd[R];
+    float sm[2 * R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool live = row0 + r < rows;
+      const float mean = live ? stats[2 * (row0 + r)] : 0.f;
+      rstd[r] = live ? stats[2 * (row0 + r) + 1] : 0.f;
+      sm[2 * r] = 0.f; sm[2 * r + 1] = 0.f;
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (live && c < nchunk) {
+          Vec8<T>::load(x + static_cast<size_t>(row0 + r) * H + c * 8, xh[r][k]);
+          Vec8<T>::load(dy + static_cast<size_t>(row0 + r) * H + c * 8, d[r][k]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) xh[r][k][i] = (xh[r][k][i] - mean) * rstd[r];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { xh[r][k][i] = 0.f; d[r][k][i] = 0.f; }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int k = 0; k < CH; ++k)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float gd = g[k][i] * d[r][k][i];
+          sm[2 * r] += gd; sm[2 * r + 1] += gd * xh[r][k][i];
+          ag[k][i] += d[r][k][i] * xh[r][k][i]; ab[k][i] += d[r][k][i];
+        }
+    block_sum_n<2 * R>(sm, red, it);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= rows) break;
+      const float m1 = RMS ? 0.f : sm[2 * r] / H, m2 = sm[2 * r + 1] / H;
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c >= nchunk) continue;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd[r] * (g[k][i] * d[r][k][i] - m1 - xh[r][k][i] * m2);
+        Vec8<T>::store(dx + static_cast<size_t>(row0 + r) * H + c * 8, o);
+      }
+    }
+  }
+  if (dgamma_part) {
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      if (c >= nchunk) continue;
+      float4* pg = reinterpret_cast<float4*>(dgamma_part + static_cast<size_t>(blockIdx.x) * H + c * 8);
+      pg[0] = make_float4(ag[k][0], ag[k][1], ag[k][2], ag[k][3]);
+      pg[1] = make_float4(ag[k][4], ag[k][5], ag[k][6], ag[k][7]);
+      if (!RMS && dbeta_part) {
+        float4* pb = reinterpret_cast<float4*>(dbeta_part + static_cast<size_t>(blockIdx.x) * H + c * 8);
+        pb[0] = make_float4(ab[k][0], ab[k][1], ab[k][2], ab[k][3]);
+        pb[1] = make_float4(ab[k][4], ab[k][5], ab[k][6], ab[k][7]);
+      }
+    }
+  }
+}
+
+// out[c] = sum_b part[b, c]   (optionally two tables at once).  Block = 32 columns x 32 row-groups; every
+// thread keeps four independent loads in flight.
+__global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb, float* __restrict__ oa,
+                                     float* __restrict__ ob, int nblocks, int H) {
+  __shared__ float sa[32][33], sb[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+  if (c < H) {
+    for (int r = threadIdx.y; r < nblocks; r += 128) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + 32 * u;
+        if (rr < nblocks) {
+          a[u] += pa[static_cast<size_t>(rr) * H + c];
+          if (pb) b[u] += pb[static_cast<size_t>(rr) * H + c];
+        }
+      }
+    }
+  }
+  sa[threadIdx.y][threadIdx.x] = (a[0] + a[1]) + (a[2] + a[3]);
+  sb[threadIdx.y][threadIdx.x] = (b[0] + b[1]) + (b[2] + b[3]);
   __syncthreads();
   if (threadIdx.y == 0 && c < H) {
+    float ta = 0.f, tb = 0.f;
 #pragma unroll
-    for (int k = 1; k < 8; ++k) { a += sa[k][threadIdx.x]; b += sb[k][threadIdx.x]; }
-    oa[c] = a;
-    if (pb) ob[c] = b;
+    for (int k = 0; k < 32; ++k) { ta += sa[k][threadIdx.x]; tb += sb[k][threadIdx.x]; }
+    oa[c] = ta;
+    if (pb) ob[c] = tb;
   }
 }
 
@@ -220,6 +398,17 @@ template <typename T>
 static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
                       int H_total, float eps, int rms, int mode, int grid, cudaStream_t s) {
   const int threads = (H / 8 <= 128) ? 128 : NORM_THREADS;  // no idle threads for narrow (sharded) rows
+  if (mode == 0 && H == H_total && H / 8 <= 2 * NORM_THREADS && H / 8 > 128) {
+    const int ch = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+#define AXB_NORM_FWD_ROWS(RMS_, CH_, R_)                                                                         \
+  norm_fwd_rows_kernel<T, RMS_, CH_, R_><<<min(grid, (rows + R_ - 1) / R_), NORM_THREADS, 0, s>>>(              \
+      (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, stats, rows, H, eps)
+    if (rms) { if (ch == 1) AXB_NORM_FWD_ROWS(true, 1, 4); else AXB_NORM_FWD_ROWS(true, 2, 2); }
+    else { if (ch == 1) AXB_NORM_FWD_ROWS(false, 1, 4); else AXB_NORM_FWD_ROWS(false, 2, 2); }
+#undef AXB_NORM_FWD_ROWS
+    AXB_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (rms)
     norm_fwd_kernel<T, true><<<grid, threads, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
                                                      stats, rows, H, H_total, eps, mode);
@@ -233,10 +422,22 @@ static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* 
 template <typename T>
 static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const float* stats, void* dx, float* sums,
                       float* dgp, float* dbp, int rows, int H, int H_total, int rms, int mode, int grid,
-                      cudaStream_t s) {
+                      cudaStream_t s, int* blocks_launched) {
+  *blocks_launched = grid;
   const int nchunk = H / 8;
   const int threads = (nchunk <= 128) ? 128 : NORM_THREADS;
   const int ch = (nchunk + threads - 1) / threads;
+  if (mode == 0 && H == H_total && nchunk <= 2 * NORM_THREADS && nchunk > 128) {
+#define AXB_NORM_BWD_ROWS(RMS_, CH_, R_)                                                                       \
+  *blocks_launched = min(grid, (rows + R_ - 1) / R_);                                                          \
+  norm_bwd_rows_kernel<T, RMS_, CH_, R_><<<*blocks_launched, NORM_THREADS, 0, s>>>(                            \
+      (const T*)dy, (const T*)x, (const T*)gamma, stats, (T*)dx, dgp, dbp, rows, H)
+    if (rms) { if (ch == 1) { AXB_NORM_BWD_ROWS(true, 1, 2); } else { AXB_NORM_BWD_ROWS(true, 2, 1); } }
+    else { if (ch == 1) { AXB_NORM_BWD_ROWS(false, 1, 2); } else { AXB_NORM_BWD_ROWS(false, 2, 1); } }
+#undef AXB_NORM_BWD_ROWS
+    AXB_CUDA(cudaGetLastError());
+    return 0;
+  }
 #define AXB_NORM_BWD(RMS_, CH_)                                                                              \
   norm_bwd_kernel<T, RMS_, CH_><<<grid, threads, 0, s>>>((const T*)dy, (const T*)x, (const T*)gamma, stats, \
                                                               (T*)dx, sums, dgp, dbp, rows, H, H_total, mode)
@@ -280,14 +481,14 @@ extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, co
   if (rows <= 0) return 0;
   const int grid = axb_norm_grid(device, rows);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int rc;
-  if (dtype == 0) rc = norm_bwd_t<__nv_bfloat16>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s);
-  else if (dtype == 1) rc = norm_bwd_t<__half>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s);
-  else rc = norm_bwd_t<float>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s);
+  int rc, nblocks = grid;
+  if (dtype == 0) rc = norm_bwd_t<__nv_bfloat16>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks);
+  else if (dtype == 1) rc = norm_bwd_t<__half>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks);
+  else rc = norm_bwd_t<float>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks);
   if (rc) return rc;
   if (mode != 1 && dgamma_part && dgamma) {
-    fold_partials_kernel<<<(H + 31) / 32, dim3(32, 8), 0, s>>>(dgamma_part, rms ? nullptr : dbeta_part, dgamma,
-                                                              rms ? nullptr : dbeta, grid, H);
+    fold_partials_kernel<<<(H + 31) / 32, dim3(32, 32), 0, s>>>(dgamma_part, rms ? nullptr : dbeta_part, dgamma,
+                                                              rms ? nullptr : dbeta, nblocks, H);
     AXB_CUDA(cudaGetLastError());
   }
   return 0;

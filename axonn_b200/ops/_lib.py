@@ -77,3 +77,36 @@ def add_launches(n: int):
 def reset_launch_count():
     global launch_count
     launch_count = 0
+
+
+_STATUS_NAMES = {
+    0x101: "GEMM producer: shared-memory stage never freed",
+    0x102: "GEMM MMA issuer: operand stage or accumulator never arrived",
+    0x104: "GEMM epilogue: accumulator never completed",
+    0x108: "fused GEMM: a peer never finished the previous call on this buffer",
+    0x110: "all-gather stage: a peer never published its weight shard",
+    0x120: "fused reduction: aborted while waiting for partial tiles",
+    0x121: "fused reduction: partial tiles of a peer never arrived",
+    0x141: "CTA-pair GEMM producer timed out",
+    0x142: "CTA-pair GEMM MMA issuer timed out",
+    0x144: "CTA-pair GEMM epilogue timed out",
+}
+
+
+def device_status(device=None, clear=True) -> int:
+    """Status word that kernels write when one of their bounded waits gave up (0: none did).  The word lives
+    in mapped host memory, so reading it needs no synchronisation; it is meaningful once the kernels in
+    question have finished (e.g. after reading the loss)."""
+    import torch
+
+    if not available() or not torch.cuda.is_available():
+        return 0
+    dev = torch.cuda.current_device() if device is None else int(device)
+    return int(lib().axb_device_status(ctypes.c_int(dev), ctypes.c_int(1 if clear else 0)))
+
+
+def check_status(device=None):
+    """Raise ``KernelError`` if a kernel on ``device`` reported a timed-out wait since the last check."""
+    st = device_status(device, clear=True)
+    if st not in (0, 0xFFFFFFFF):
+        raise KernelError(f"device-side wait timed out (status 0x{st:x}: {_STATUS_NAMES.get(st, 'unknown')})")

@@ -19,6 +19,7 @@ import torch.distributed as dist
 
 from . import axonn as ax
 from . import ops
+from .ops import _lib
 from .intra_layer import (clip_grad_norm_, no_grad_sync, optimize_communication,
                           overlap_all_gathers_for_checkpointed_forward, sync_gradients)
 
@@ -102,7 +103,9 @@ class Trainer:
     def train_step(self, inputs, targets) -> float:
         """One optimizer step from host tensors; returns the loss as a float."""
         loss = self.train_step_device(self._to_device(inputs), self._to_device(targets))
-        return float(loss.item())
+        value = float(loss.item())
+        _lib.check_status()   # a bounded device-side wait that gave up surfaces here, after the sync above
+        return value
 
 
 def replica_index() -> int:

@@ -104,6 +104,17 @@ def bench_attention(small=False):
         g_ref = torch.randn_like(o_ref)
         t_lib_bwd, _ = time_cuda(lambda: torch.autograd.grad(o_ref, (qr, kr, vr), g_ref, retain_graph=True),
                                  iters=3 if small else 10)
+        import os
+
+        if int(os.environ.get("AXB_FA_DEBUG", "0")) & 4:
+            from axonn_b200.ops import _lib
+
+            w = {i: _lib.lib().axb_debug_word(0, i, 1) for i in (2, 3, 4, 7, 8, 9, 10, 11)}
+            n = max(1, w[7])
+            print("bwd CTA (0,0,0), us per iteration: MMA warp waits: Q/dO %.2f, S columns free %.2f, P/dS %.2f | "
+                  "softmax warp: wait S/dP %.2f, P/dS math %.2f, wait dQ %.2f, dQ reduction %.2f (%d iterations)" % (
+                      w[2] / n / 1e3, w[3] / n / 1e3, w[4] / n / 1e3, w[8] / n / 1e3, w[9] / n / 1e3,
+                      w[10] / n / 1e3, w[11] / n / 1e3, n), flush=True)
         print(json.dumps(dict(B=B, S=S, heads=G * qpk, kv_heads=G, D=D, ms=round(t_ours, 4),
                               tflops=round(fl / t_ours / 1e9, 1), cudnn_ms=round(t_lib, 4),
                               cudnn_tflops=round(fl / t_lib / 1e9, 1), bwd_ms=round(t_bwd, 4),
@@ -187,6 +198,45 @@ def bench_fused(iters=8):
         del a, b
 
 
+def bench_memory_bound(rows=16384, H=2048):
+    """Memory-bound kernels against the measured copy bandwidth: algorithmic bytes / CUDA-event time."""
+    from axonn_b200 import ops
+    from axonn_b200.metrics import measured_peaks
+
+    dev = torch.device("cuda", 0)
+    _, hbm, kind = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    x = torch.randn(rows, H, device=dev).bfloat16().requires_grad_(True)
+    g = torch.ones(H, device=dev).bfloat16().requires_grad_(True)
+    b = torch.zeros(H, device=dev).bfloat16().requires_grad_(True)
+    dy = torch.randn(rows, H, device=dev).bfloat16()
+    out = []
+
+    def report(label, ms, nbytes):
+        gbs = nbytes / ms / 1e6
+        out.append(dict(label=label, rows=rows, H=H, ms=round(ms, 4), gbs=round(gbs, 1),
+                        fraction=round(gbs / hbm, 3), peak=f"{hbm} GB/s {kind}"))
+        print(json.dumps(out[-1]), flush=True)
+
+    nb = rows * H * 2
+    for name, fn in (("layernorm", lambda: ops.layer_norm(x, g, b, 1e-5)), ("rmsnorm", lambda: ops.rms_norm(x, g, 1e-5))):
+        with torch.no_grad():
+            t, _ = time_cuda(fn, flush=flush)
+        report(name + " fwd", t, 2 * nb)
+        y = fn()
+        t, _ = time_cuda(lambda: torch.autograd.grad(y, (x, g), dy, retain_graph=True), flush=flush)
+        report(name + " bwd (dx, dgamma, dbeta)", t, 3 * nb)
+    h = torch.randn(rows, 4 * H, device=dev).bfloat16().requires_grad_(True)
+    dh = torch.randn_like(h)
+    with torch.no_grad():
+        t, _ = time_cuda(lambda: ops.gelu(h), flush=flush)
+    report("gelu fwd", t, 2 * 4 * nb)
+    yh = ops.gelu(h)
+    t, _ = time_cuda(lambda: torch.autograd.grad(yh, h, dh, retain_graph=True), flush=flush)
+    report("gelu bwd", t, 3 * 4 * nb)
+    return out
+
+
 def bench_fused_loopback(M=16384, N=4096, K=1024, iters=3):
     """One-GPU emulation of the two-rank fused GEMM+all-reduce (peer slots aliased onto local memory): the
     local cost of the communication path - epilogue pushes, flags, reducer warps - without NVLink."""
@@ -224,6 +274,8 @@ if __name__ == "__main__":
         bench_attention(small=True)
     elif what == "attn":
         bench_attention()
+    elif what == "memory":
+        bench_memory_bound()
     elif what == "fused_loopback":
         bench_fused_loopback()
     elif what == "fused":

@@ -15,7 +15,7 @@ def _close(a, b, rel, abs_=1e-3):
 
 
 @pytest.mark.parametrize("rms", [False, True])
-@pytest.mark.parametrize("shape", [(512, 2048), (333, 1024), (64, 4096), (1000, 256)])
+@pytest.mark.parametrize("shape", [(512, 2048), (333, 1024), (64, 4096), (1000, 256), (5003, 2048), (2501, 3072)])
 def test_norm_fwd_bwd(rms, shape):
     from axonn_b200 import ops
 
