@@ -33,7 +33,7 @@ int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias
  * the *_local ones in this rank's symmetric buffer, the *_peer[j] ones the same regions of rank j mapped
  * into this process.  `inbox_*` holds bf16 partial tiles indexed [source rank][tile][warp]: every rank's
  * GEMM epilogue pushes its partial into the inbox of the ranks that reduce those rows (posted stores over
- * NVLink for peers), whose comm CTAs sum the slots locally.  Flag
+ * NVLink for peers), whose reducer warps sum the slots locally.  Flag
  * arrays are indexed [source rank][tile * 4 + warp]; `epoch` increases by one per call on the group and
  * selects (by parity, done by the caller) which of two outbox/flag sets is used. */
 typedef struct AxbArCtx {
@@ -52,7 +52,7 @@ typedef struct AxbArCtx {
   unsigned long long flags_per_src;      /* flags per source */
   int mode;                   /* 0: all-reduce of C; 1: reduce-scatter of C by row blocks */
   int rows_per_shard;         /* mode 1: rows of C owned by each rank (multiple of 32) */
-  int comm_ctas;              /* CTAs of the launch dedicated to the reduction over peer memory (0: default 32) */
+  int comm_ctas;              /* reserved, must be 0 */
   int pad_;
 } AxbArCtx;
 

@@ -1,6 +1,8 @@
 // bf16/fp16 GEMM on 5th-generation tensor cores (tcgen05) for sm_100a.
 //
-// One persistent CTA per SM, 192 threads, warp-specialised:
+// Two kernels share the pipeline below.
+//
+// gemm_tcgen05_kernel: one persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer: streams 128xBK (A) and BNxBK (B) tiles into a
 //               multi-stage shared-memory ring (128-byte swizzle, mbarrier
 //               transaction counts);
@@ -11,7 +13,14 @@
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM
 //               lanes), apply bias / GELU / accumulate, convert and store; runs
 //               concurrently with the next tile's main loop thanks to the
-//               double-buffered accumulator.
+//               double-buffered accumulator;
+//   warps 6-15  only active when the GEMM carries an all-reduce / reduce-scatter
+//               over peer memory: eight reducer warps, a flagger and a watcher
+//               (described at reducer_warps / watcher_thread below).
+//
+// gemm_pair_kernel: clusters of two CTAs (tcgen05.mma.cta_group::2) compute
+// 256x256 tiles for plain GEMMs; warps 0-5 as above in each CTA, MMAs issued
+// by the even CTA for both.
 //
 // Operand layouts: each of A and B is either K-major (row = M/N index, K
 // contiguous) or MN-major (row = K index, M/N contiguous); both are expressed
@@ -422,7 +431,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int group = (BN == 256) ? 16 : 8;
   const uint64_t timeout = p.timeout_ns;
-  const int gemm_ctas = p.gemm_ctas;   // CTAs [gemm_ctas, gridDim.x) are comm CTAs (reduction over peer memory)
+  const int gemm_ctas = p.gemm_ctas;   // == gridDim.x: every CTA computes tiles (and reduces them in comm mode)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -675,7 +684,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       // ---- communication mode: the epilogue moves this warp's bf16 partial (32 rows x BN columns) out of
       // TMEM into the inbox of every rank that reduces these rows - with posted 16-byte stores over NVLink
-      // for the peers, plain stores for this rank - then raises the (tile, warp) flags; the comm CTAs of the
+      // for the peers, plain stores for this rank - then the flagger raises the (tile, warp) flags; the reducer warps of the
       // reducing ranks sum the inbox slots locally.  Slot layout of a (tile, warp): [chunk][vec 0..3][lane]
       // 16-byte words, so every store instruction of a warp covers 512 contiguous bytes.
       const int owner = (p.ar.mode == 1) ? (tm * BM + q * 32) / p.ar.rows_per_shard : -1;
@@ -989,11 +998,10 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int sms = sm_count(device);
-  // every CTA must be resident at once (comm CTAs wait for GEMM CTAs of the same launch): grid <= #SMs
-  const int n_comm = 0;   // the reduction runs on warps 6-9 of every CTA
-  p.gemm_ctas = tiles < sms - n_comm ? tiles : sms - n_comm;
+  // every CTA must be resident at once (reducer warps wait for partials of the same launch): grid <= #SMs
+  p.gemm_ctas = tiles < sms ? tiles : sms;
   if (p.ag.n > 1 && p.ag.n_copy > p.gemm_ctas) { p.ag.n_copy = p.gemm_ctas; p.ag.ready_target = p.ag.n_copy; }
-  const int grid = p.gemm_ctas + n_comm;
+  const int grid = p.gemm_ctas;
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
   AXB_CUDA(cudaGetLastError());
   return 0;

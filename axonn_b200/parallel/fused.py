@@ -100,7 +100,7 @@ class _ArChannel:
         c.inbox_vecs_per_src = self.inbox_vecs_per_src
         c.flags_per_src = self.flags_per_src
         c.mode, c.rows_per_shard = mode, rows_per_shard
-        c.comm_ctas = int(os.environ.get("AXONN_COMM_CTAS", "0"))
+        c.comm_ctas = 0
         return c
 
 

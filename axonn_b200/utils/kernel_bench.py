@@ -178,15 +178,6 @@ def bench_fused(iters=8):
             t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             res[name] = float(t.item())
-        if os.environ.get("AXB_AR_DEBUG") and rank == 0:
-            from axonn_b200.ops import _lib
-
-            L = _lib.lib()
-            w = {i: L.axb_debug_word(dev.index, i, 1) for i in range(2, 8)}
-            tiles = max(1, w[7])
-            print("comm CTA 0, us per tile: fetcher poll %.2f fence %.2f stage-wait+issue %.2f | reducer wait %.2f reduce %.2f "
-                  "(tiles %d)" % (w[2] / tiles / 1e3, w[3] / tiles / 1e3, w[4] / tiles / 1e3, w[5] / tiles / 1e3,
-                                  w[6] / tiles / 1e3, tiles), flush=True)
         flops, nbytes = 2.0 * M * N * K, 2.0 * M * N * (world - 1)
         roof_ms = max(flops / (peak * 1e12), nbytes / 770e9) * 1e3
         if rank == 0:
