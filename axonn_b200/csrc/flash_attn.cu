@@ -34,7 +34,7 @@ struct FaParams {
   unsigned long long timeout_ns;
 };
 
-constexpr int FA_BQ = 128, FA_BKV = 128, FA_THREADS = 192;
+constexpr int FA_BQ = 128, FA_BKV = 128, FA_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps
 
 template <int HD>
 struct FaSmem {
@@ -46,8 +46,25 @@ struct FaSmem {
   static constexpr int P_OFF = 5 * TILE;
   static constexpr int BAR_OFF = P_OFF + P_BYTES;
   static constexpr int NBARS = 1 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 2 + 2;
-  static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16 + 1024;
+  // exchange between the two threads of a query row: maxima [2][2][128], row sums [2][128], sequence tags [2][128]
+  static constexpr int XCH_OFF = BAR_OFF + NBARS * 8 + 16;
+  static constexpr int TOTAL = XCH_OFF + 8 * 128 * 4 + 1024;
 };
+
+// Bounded wait until the other thread of a query row has published sequence number `want`.
+__device__ __forceinline__ bool wait_partner(volatile int* flag, int want, volatile int* abort_flag, uint64_t timeout_ns) {
+  uint64_t start = 0;
+  for (uint32_t it = 0; *flag < want; ++it) {
+    if ((it & 0xff) == 0xff) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (start == 0) start = now;
+      else if (now - start > timeout_ns) { *abort_flag = 1; return false; }
+    }
+  }
+  __threadfence_block();
+  return true;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
@@ -86,10 +103,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
-      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
+      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 8);
     }
-    mbar_init(p_full, 4); mbar_init(p_empty, 1);
+    mbar_init(p_full, 8); mbar_init(p_empty, 1);
+    for (int i = 0; i < 256; ++i) reinterpret_cast<volatile int*>(smem + S_::XCH_OFF + 6 * 128 * 4)[i] = 0;
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -175,70 +193,80 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
     }
   } else {
     // ------------------------------------------------------------------ softmax + output accumulation
+    // Eight warps: two share each TMEM lane quarter; thread = (query row r, column half).  A thread owns 64 of
+    // the 128 score columns of its row and HD/2 of the output columns, so that a KV tile costs it one TMEM
+    // read of the scores (kept in registers between the max and the exponentials) and one of the PV product.
+    // The two threads of a row exchange their partial row maxima through shared memory (one 64-thread named
+    // barrier per tile); the partial row sums are only combined at the end.
     const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = q4 * 32 + lane;                 // query row inside the tile
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
-    float o[HD];
+    constexpr int OC = HD / 2;                    // output columns per thread
+    float o[OC];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < OC; ++i) o[i] = 0.f;
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
     bool ok = true;
-    uint8_t* p_row = smem + S_::P_OFF + (r >> 3) * 1024 + (r & 7) * 128;
+    uint8_t* p_row = smem + S_::P_OFF + (r >> 3) * 1024 + (r & 7) * 128 + half * 16384;
+    volatile float* xch = reinterpret_cast<volatile float*>(smem + S_::XCH_OFF);   // [2 tile parities][2 halves][128 rows]
+    volatile int* xflag = reinterpret_cast<volatile int*>(smem + S_::XCH_OFF + 6 * 128 * 4);   // [2 halves][128 rows]
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
       tcgen05_fence_after();
-      const uint32_t s_addr = tmem_s + lane_base + (j & 1) * 128;
+      const uint32_t s_addr = tmem_s + lane_base + (j & 1) * 128 + half * 64;
       const bool diag = (j == qt);
-      // pass 1: row maximum
+      uint32_t sv[64];
+      tmem_ld_32x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_wait();
+      // the score buffer can be reused by the MMA warp as soon as both halves hold it in registers
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[j & 1]);
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(v[i]) * p.scale_log2;
-          if (!diag || (c * 32 + i) <= r) mx = fmaxf(mx, s);
-        }
+      for (int i = 0; i < 64; ++i) {
+        const float sc = __uint_as_float(sv[i]) * p.scale_log2;
+        if (!diag || (half * 64 + i) <= r) mx = fmaxf(mx, sc);
       }
+      xch[((j & 1) * 2 + half) * 128 + r] = mx;
+      __threadfence_block();
+      xflag[half * 128 + r] = j + 1;
+      if (!wait_partner(xflag + (half ^ 1) * 128 + r, j + 1, abort_flag, timeout)) { ok = false; break; }
+      mx = fmaxf(mx, xch[((j & 1) * 2 + (half ^ 1)) * 128 + r]);
       const float m_new = fmaxf(m, mx);
       const float alpha = exp2f(m - m_new);
       if (!mbar_wait(p_empty, (j & 1) ^ 1, abort_flag, timeout)) { ok = false; break; }
-      // pass 2: exponentials, row sum, P tile (bf16, swizzled K-major layout)
+      // exponentials, partial row sum, this thread's half of the P row (bf16, swizzled K-major layout)
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float e0 = exp2f(__uint_as_float(v[2 * i]) * p.scale_log2 - m_new);
-          float e1 = exp2f(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - m_new);
+          float e0 = exp2f(__uint_as_float(sv[c * 32 + 2 * i]) * p.scale_log2 - m_new);
+          float e1 = exp2f(__uint_as_float(sv[c * 32 + 2 * i + 1]) * p.scale_log2 - m_new);
           if (diag) {
-            if (c * 32 + 2 * i > r) e0 = 0.f;
-            if (c * 32 + 2 * i + 1 > r) e1 = 0.f;
+            if (half * 64 + c * 32 + 2 * i > r) e0 = 0.f;
+            if (half * 64 + c * 32 + 2 * i + 1 > r) e1 = 0.f;
           }
           const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
           // accumulate what the tensor core will actually see (bf16-rounded probabilities)
           rowsum += __bfloat162float(h.x) + __bfloat162float(h.y);
           packed[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
-        // columns [c*32, c*32+32): 64-column block (c >> 1), 16-byte chunks ((c & 1) * 4 + t), t = 0..3
-        uint8_t* blk = p_row + (c >> 1) * 16384;
+        // columns half*64 + [c*32, c*32+32): 16-byte chunks (c * 4 + t), t = 0..3, of the 64-column block
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          const int chunk = ((c & 1) * 4 + t) ^ (r & 7);
-          *reinterpret_cast<uint4*>(blk + chunk * 16) =
+          const int chunk = (c * 4 + t) ^ (r & 7);
+          *reinterpret_cast<uint4*>(p_row + chunk * 16) =
               make_uint4(packed[4 * t], packed[4 * t + 1], packed[4 * t + 2], packed[4 * t + 3]);
         }
       }
-      tcgen05_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&s_empty[j & 1]); mbar_arrive(p_full); }
+      if (lane == 0) mbar_arrive(p_full);
       l = l * alpha + rowsum;
       m = m_new;
       // fold the previous tile's PV product into the output row
@@ -246,18 +274,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
         const int u = j - 1;
         if (!mbar_wait(&o_full[u & 1], (u >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
         tcgen05_fence_after();
-        const uint32_t o_addr = tmem_o + lane_base + (u & 1) * HD;
+        const uint32_t o_addr = tmem_o + lane_base + (u & 1) * HD + half * OC;
+        uint32_t v[OC];
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(o_addr + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
-        }
+        for (int c = 0; c < OC / 32; ++c) tmem_ld_32x32(o_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+        tmem_ld_wait();
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&o_empty[u & 1]);
+#pragma unroll
+        for (int i = 0; i < OC; ++i) o[i] = o[i] * alpha_prev + __uint_as_float(v[i]);
       }
       alpha_prev = alpha;
     }
@@ -265,12 +291,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
       const int u = n_kv - 1;
       if (mbar_wait(&o_full[u & 1], (u >> 1) & 1, abort_flag, timeout)) {
         tcgen05_fence_after();
-        const uint32_t o_addr = tmem_o + lane_base + (u & 1) * HD;
+        // total row sum = sum of the two halves' partial sums
+        volatile float* lx = xch + 4 * 128;        // [2 halves][128 rows], used once
+        lx[half * 128 + r] = l;
+        __threadfence_block();
+        xflag[half * 128 + r] = n_kv + 1;
+        if (!wait_partner(xflag + (half ^ 1) * 128 + r, n_kv + 1, abort_flag, timeout)) ok = false;
+        l += lx[(half ^ 1) * 128 + r];
+        const uint32_t o_addr = tmem_o + lane_base + (u & 1) * HD + half * OC;
         const float inv_l = 1.f / l;
         const size_t heads = static_cast<size_t>(p.G) * p.qpk;
-        __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + qt * FA_BQ + r) * heads + head) * HD;
+        __nv_bfloat16* dst = p.out + ((static_cast<size_t>(b) * p.S + qt * FA_BQ + r) * heads + head) * HD + half * OC;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32(o_addr + c * 32, v);
           tmem_ld_wait();
@@ -288,7 +321,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
             *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
-        p.lse[(static_cast<size_t>(b) * heads + head) * p.S + qt * FA_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
+        if (half == 0)
+          p.lse[(static_cast<size_t>(b) * heads + head) * p.S + qt * FA_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
       } else {
         ok = false;
       }
