@@ -392,6 +392,49 @@ __global__ void fold_partials_kernel(const float* __restrict__ pa, const float* 
   }
 }
 
+// Column sums of a row-major [rows, N] matrix (bias gradients): block = 32 column vectors (8 columns each)
+// x 8 row groups, grid = (column blocks, row splits); every thread keeps four 16-byte loads in flight and one
+// partial row per row split is written for fold_partials_kernel.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const T* __restrict__ x, float* __restrict__ part, int rows, int N) {
+  __shared__ float red[8][32][9];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * 8;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (c < N) {
+    const int stride = gridDim.y * 8;
+    for (int r = blockIdx.y * 8 + w; r < rows; r += 4 * stride) {
+      float f[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * stride;
+        if (rr < rows) Vec8<T>::load(x + static_cast<size_t>(rr) * N + c, f[u]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[u][i] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[u][i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[w][lane][i] = acc[i];
+  __syncthreads();
+  // thread (w, lane) folds column i = w of lane's vector over the 8 row groups
+  if (c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][lane][w];
+    part[static_cast<size_t>(blockIdx.y) * N + c + w] = t;
+  }
+}
+
 int sm_count(int device);
 
 template <typename T>
@@ -491,5 +534,29 @@ extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, co
                                                               rms ? nullptr : dbeta, nblocks, H);
     AXB_CUDA(cudaGetLastError());
   }
+  return 0;
+}
+
+extern "C" int axb_colsum_splits(int device, int rows, int N) {
+  const int col_blocks = (N / 8 + 31) / 32;
+  int splits = (4 * axb::sm_count(device) + col_blocks - 1) / col_blocks;
+  const int max_splits = (rows + 31) / 32;       // at least four rows per thread
+  if (splits > max_splits) splits = max_splits;
+  return splits < 1 ? 1 : splits;
+}
+
+// out[c] = sum_r x[r, c]; part: [axb_colsum_splits, N] fp32 scratch, out: [N] fp32.  N must be a multiple of 8.
+extern "C" int axb_colsum(const void* x, float* part, float* out, int rows, int N, int dtype, int device, void* stream) {
+  using namespace axb;
+  if (N % 8 || rows <= 0) { set_error("colsum: N must be a multiple of 8 and rows positive"); return -1; }
+  const int splits = axb_colsum_splits(device, rows, N);
+  dim3 grid((N / 8 + 31) / 32, splits);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0) colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, part, rows, N);
+  else if (dtype == 1) colsum_partial_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, part, rows, N);
+  else colsum_partial_kernel<float><<<grid, 256, 0, s>>>((const float*)x, part, rows, N);
+  AXB_CUDA(cudaGetLastError());
+  fold_partials_kernel<<<(N + 31) / 32, dim3(32, 32), 0, s>>>(part, nullptr, out, nullptr, splits, N);
+  AXB_CUDA(cudaGetLastError());
   return 0;
 }

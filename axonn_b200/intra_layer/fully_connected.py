@@ -210,7 +210,7 @@ class AsyncLinear(Function):
             if ctx.needs_input_grad[1]:
                 grad_weight = wgrad()
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                grad_bias = go2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+                grad_bias = ops.column_sum(go2).to(ctx.bias_dtype)
             if handle is not None and overlap_ar:
                 handle.wait()
         else:
@@ -220,7 +220,7 @@ class AsyncLinear(Function):
             if ctx.needs_input_grad[0]:
                 grad_input = dgrad()
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                grad_bias = go2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+                grad_bias = ops.column_sum(go2).to(ctx.bias_dtype)
         if grad_input is not None:
             grad_input = grad_input.reshape(input_.shape)
         return grad_input, grad_weight, grad_bias, None, None, None, None, None, None

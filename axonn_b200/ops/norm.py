@@ -140,3 +140,22 @@ def layer_norm(x, gamma, beta, eps=1e-5, group=None):
 
 def rms_norm(x, gamma, eps=1e-6, group=None):
     return _NormFn.apply(x, gamma, None, eps, True, group)
+
+
+def column_sum(x):
+    """``x.sum(0)`` of a 2-D tensor in fp32 (bias gradients).  One pass over ``x`` at memory bandwidth on
+    CUDA (partial sums per row split, then a fold); plain PyTorch elsewhere."""
+    if not (_lib.use_cuda_kernels(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.is_contiguous()
+            and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and x.shape[0] > 0):
+        return x.sum(0, dtype=torch.float32)
+    rows, n = x.shape
+    L = _lib.lib()
+    dev = x.device.index
+    splits = L.axb_colsum_splits(ctypes.c_int(dev), ctypes.c_int(rows), ctypes.c_int(n))
+    part = torch.empty((splits, n), dtype=torch.float32, device=x.device)
+    out = torch.empty(n, dtype=torch.float32, device=x.device)
+    dt = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[x.dtype]
+    _lib.check(L.axb_colsum(_lib.ptr(x), _lib.ptr(part), _lib.ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
+                            ctypes.c_int(dt), ctypes.c_int(dev), _lib.stream_ptr()), "axb_colsum")
+    _lib.add_launches(1)
+    return out

@@ -84,7 +84,7 @@ def bench_attention(small=False):
     from axonn_b200.ops.attention_cuda import flash_fwd_packed
 
     dev = torch.device("cuda", 0)
-    cases = [(2, 2048, 4, 1, 128)] if small else [(8, 2048, 16, 1, 128), (4, 4096, 8, 4, 128), (8, 2048, 16, 1, 64)]
+    cases = [(4, 2048, 8, 1, 128)] if small else [(8, 2048, 16, 1, 128), (4, 4096, 8, 4, 128), (8, 2048, 16, 1, 64)]
     for B, S, G, qpk, D in cases:
         qkv = torch.randn(B, S, G, qpk + 2, D, device=dev, dtype=torch.bfloat16)
         scale = 1.0 / math.sqrt(D)
@@ -217,6 +217,11 @@ def bench_memory_bound(rows=16384, H=2048):
         y = fn()
         t, _ = time_cuda(lambda: torch.autograd.grad(y, (x, g), dy, retain_graph=True), flush=flush)
         report(name + " bwd (dx, dgamma, dbeta)", t, 3 * nb)
+    with torch.no_grad():
+        t, _ = time_cuda(lambda: ops.column_sum(dy), flush=flush)
+        report("column sum (bias gradient)", t, nb)
+        t, _ = time_cuda(lambda: dy.sum(0, dtype=torch.float32), flush=flush)
+        report("column sum, torch reduce", t, nb)
     h = torch.randn(rows, 4 * H, device=dev).bfloat16().requires_grad_(True)
     dh = torch.randn_like(h)
     with torch.no_grad():

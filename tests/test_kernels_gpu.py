@@ -218,3 +218,17 @@ def test_flash_attention_backward(cfg):
         got, want = dqkv[:, :, :, sl].float(), x.grad[:, :, :, sl]
         err = (got - want).abs().max().item()
         assert err <= 3e-2 * want.abs().max().item() + 2e-2, f"{name}: {err} vs {want.abs().max().item()}"
+
+
+@pytest.mark.parametrize("shape", [(16384, 2048), (1000, 136), (7, 8), (4099, 6144)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_column_sum(shape, dtype):
+    from axonn_b200 import ops
+
+    torch.manual_seed(3)
+    x = torch.randn(*shape, device=DEV).to(dtype)
+    got = ops.column_sum(x)
+    ref = x.double().sum(0)
+    assert got.dtype == torch.float32
+    err = (got.double() - ref).abs().max().item()
+    assert err <= 1e-4 * shape[0] ** 0.5 + 1e-3 * ref.abs().max().item(), err
