@@ -226,10 +226,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
       if (lane == 0) mbar_arrive(&s_empty[j & 1]);
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float sc = __uint_as_float(sv[i]) * p.scale_log2;
-        if (!diag || (half * 64 + i) <= r) mx = fmaxf(mx, sc);
-      }
+      for (int i = 0; i < 64; ++i)
+        if (!diag || (half * 64 + i) <= r) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      mx *= p.scale_log2;                       // the scale is positive: scale the maximum once
       xch[((j & 1) * 2 + half) * 128 + r] = mx;
       __threadfence_block();
       xflag[half * 128 + r] = j + 1;
@@ -252,8 +251,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
             if (half * 64 + c * 32 + 2 * i + 1 > r) e1 = 0.f;
           }
           const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-          // accumulate what the tensor core will actually see (bf16-rounded probabilities)
-          rowsum += __bfloat162float(h.x) + __bfloat162float(h.y);
+          rowsum += e0 + e1;
           packed[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
         // columns half*64 + [c*32, c*32+32): 16-byte chunks (c * 4 + t), t = 0..3, of the 64-column block

@@ -435,6 +435,52 @@ colsum_partial_kernel(const T* __restrict__ x, float* __restrict__ part, int row
   }
 }
 
+// dx = dy * gelu'(x) together with the column sums of dx (the bias gradient of the layer that produced x):
+// same thread layout as colsum_partial_kernel, one extra load and one store per element.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gelu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx,
+                       float* __restrict__ part, int rows, int N) {
+  __shared__ float red[8][32][9];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * 8;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (c < N) {
+    const int stride = gridDim.y * 8;
+    for (int r = blockIdx.y * 8 + w; r < rows; r += 2 * stride) {
+      float fx[2][8], fd[2][8];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int rr = r + u * stride;
+        if (rr < rows) {
+          Vec8<T>::load(x + static_cast<size_t>(rr) * N + c, fx[u]);
+          Vec8<T>::load(dy + static_cast<size_t>(rr) * N + c, fd[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int rr = r + u * stride;
+        if (rr >= rows) continue;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { o[i] = fd[u][i] * gelu_tanh_grad(fx[u][i]); acc[i] += o[i]; }
+        Vec8<T>::store(dx + static_cast<size_t>(rr) * N + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[w][lane][i] = acc[i];
+  __syncthreads();
+  if (c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][lane][w];
+    part[static_cast<size_t>(blockIdx.y) * N + c + w] = t;
+  }
+}
+
 int sm_count(int device);
 
 template <typename T>
@@ -557,6 +603,26 @@ extern "C" int axb_colsum(const void* x, float* part, float* out, int rows, int 
   else colsum_partial_kernel<float><<<grid, 256, 0, s>>>((const float*)x, part, rows, N);
   AXB_CUDA(cudaGetLastError());
   fold_partials_kernel<<<(N + 31) / 32, dim3(32, 32), 0, s>>>(part, nullptr, out, nullptr, splits, N);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// dx = dy * gelu'(x) (tanh form) and colsum[c] = sum_r dx[r, c] in one pass.  part: [axb_colsum_splits, N] fp32.
+extern "C" int axb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, float* part, float* colsum, int rows,
+                                   int N, int dtype, int device, void* stream) {
+  using namespace axb;
+  if (N % 8 || rows <= 0) { set_error("gelu_bwd_colsum: N must be a multiple of 8 and rows positive"); return -1; }
+  if (dtype != 0 && dtype != 1) { set_error("gelu_bwd_colsum: bf16 or fp16 only"); return -1; }
+  const int splits = axb_colsum_splits(device, rows, N);
+  dim3 grid((N / 8 + 31) / 32, splits);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    gelu_bwd_colsum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                              (__nv_bfloat16*)dx, part, rows, N);
+  else
+    gelu_bwd_colsum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)dy, (const __half*)x, (__half*)dx, part, rows, N);
+  AXB_CUDA(cudaGetLastError());
+  fold_partials_kernel<<<(N + 31) / 32, dim3(32, 32), 0, s>>>(part, nullptr, colsum, nullptr, splits, N);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }

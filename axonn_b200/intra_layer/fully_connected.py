@@ -156,8 +156,12 @@ class AsyncLinear(Function):
         input_, w_shard, pre_act = ctx.saved_tensors
         grad_output = grad_output.to(ctx.compute_dtype)
         go2 = grad_output.reshape(-1, grad_output.shape[-1])
+        bias_sum = None
         if pre_act is not None:
-            go2 = ops.gelu_backward(go2, pre_act)
+            if ctx.has_bias and ctx.needs_input_grad[2]:
+                go2, bias_sum = ops.gelu_backward_colsum(go2, pre_act)   # bias gradient in the same pass
+            else:
+                go2 = ops.gelu_backward(go2, pre_act)
         x2 = input_.reshape(-1, input_.shape[-1])
         overlap_rs = oc.OVERLAP_REDUCE_SCATTER
         overlap_ar = oc.OVERLAP_ALL_REDUCE
@@ -210,7 +214,7 @@ class AsyncLinear(Function):
             if ctx.needs_input_grad[1]:
                 grad_weight = wgrad()
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                grad_bias = ops.column_sum(go2).to(ctx.bias_dtype)
+                grad_bias = (bias_sum if bias_sum is not None else ops.column_sum(go2)).to(ctx.bias_dtype)
             if handle is not None and overlap_ar:
                 handle.wait()
         else:
@@ -220,7 +224,7 @@ class AsyncLinear(Function):
             if ctx.needs_input_grad[0]:
                 grad_input = dgrad()
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                grad_bias = ops.column_sum(go2).to(ctx.bias_dtype)
+                grad_bias = (bias_sum if bias_sum is not None else ops.column_sum(go2)).to(ctx.bias_dtype)
         if grad_input is not None:
             grad_input = grad_input.reshape(input_.shape)
         return grad_input, grad_weight, grad_bias, None, None, None, None, None, None

@@ -5,7 +5,7 @@ kernel from ``axonn_b200/csrc`` reached through ``ops._lib`` and a plain
 PyTorch composition used on CPU (and as the numerical oracle in the tests).
 """
 
-from .activation import gelu, gelu_backward, swiglu  # noqa: F401
+from .activation import gelu_backward_colsum, gelu, gelu_backward, swiglu  # noqa: F401
 from .attention import flash_attention, flash_attention_packed  # noqa: F401
 from .gemm import (  # noqa: F401
     EPI_BIAS,

@@ -232,3 +232,15 @@ def test_column_sum(shape, dtype):
     assert got.dtype == torch.float32
     err = (got.double() - ref).abs().max().item()
     assert err <= 1e-4 * shape[0] ** 0.5 + 1e-3 * ref.abs().max().item(), err
+
+
+def test_gelu_backward_colsum():
+    from axonn_b200 import ops
+
+    torch.manual_seed(4)
+    x = torch.randn(4099, 1032, device=DEV).bfloat16()
+    dy = torch.randn_like(x)
+    dx, cs = ops.gelu_backward_colsum(dy, x)
+    ref = ops.gelu_backward(dy, x)
+    assert torch.equal(dx, ref)
+    _close(cs, ref.float().sum(0), 1e-3, 5e-2)
