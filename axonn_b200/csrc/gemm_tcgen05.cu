@@ -72,9 +72,16 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024 /* alignment slack */;
+  // Two-rank all-reduce with 128x256 tiles: the operand ring runs with RING_STAGES stages and the space
+  // behind them stages the inbox slots that the reducer warps sum (2 groups x 2 ranks x 16 KB, bulk copies).
+  static constexpr int RING_STAGES = 3;
+  static constexpr int RING_SLOT_BYTES = 32 * BN * 2;          // one (tile, warp) slot of one rank
+  static constexpr int RING_OFFSET = RING_STAGES * STAGE_BYTES;
+  static constexpr int RING_BYTES = (BN == 256) ? 4 * RING_SLOT_BYTES : 0;
+  static constexpr int BAR_OFFSET = (STAGES * STAGE_BYTES > RING_OFFSET + RING_BYTES) ? STAGES * STAGE_BYTES
+                                                                                      : RING_OFFSET + RING_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], ring_full[2], ring_empty[2], tmem ptr, flags
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 8) * 8 + 16 + 1024 /* alignment slack */;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group, int& tm, int& tn) {
@@ -256,7 +263,11 @@ __device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) 
 // fence overlap the reduction of the previous tile instead of preceding each one.
 template <int BN>
 __device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
-                                               volatile unsigned int* ready_tiles) {
+                                               volatile unsigned int* ready_tiles, uint8_t* ring = nullptr,
+                                               uint64_t* ring_full = nullptr, uint64_t* ring_empty = nullptr) {
+  constexpr int WVEC = (BN / 32) * 4 * 32;    // 16-byte words per (tile, warp) slot
+  constexpr int SLOT = WVEC * 16;
+  int issued = 0;                             // ring mode: units handed to the reducer warps so far
   int t = 0;
   for (int tile = blockIdx.x; tile < num_tiles; tile += p.gemm_ctas, ++t) {
     int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
@@ -287,6 +298,29 @@ __device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, i
         return;
       }
       if (!(p.debug & 4)) __threadfence_system();   // acquire side of the flags, once per tile
+      if (ring != nullptr) {
+        // two-rank ring mode: bring the tile's inbox slots (own partial and the peer's, 16 KB each per warp-row)
+        // into shared memory with bulk copies, one ring group per warp-row, as soon as the group is free
+        asm volatile("fence.proxy.async;" ::: "memory");   // the slots were written with ordinary stores
+        for (int q = 0; q < 4; ++q) {
+          if (!(mine & (1u << q))) continue;
+          const int g = issued & 1;
+          if (!mbar_wait(&ring_empty[g], ((issued >> 1) & 1) ^ 1, abort_flag, p.timeout_ns)) {
+            *reinterpret_cast<volatile unsigned int*>(p.status) = 0x123u;
+            return;
+          }
+          mbar_expect_tx(&ring_full[g], 2 * SLOT);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ar.inbox_local) +
+                                 (static_cast<size_t>(j) * p.ar.inbox_vecs_per_src + (static_cast<size_t>(tile) * 4 + q) * WVEC) * 16;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(ring + (g * 2 + j) * SLOT)), "l"(src), "r"(SLOT), "r"(smem_u32(&ring_full[g]))
+                         : "memory");
+          }
+          ++issued;
+        }
+      }
     }
     __threadfence_block();
     *ready_tiles = static_cast<unsigned>(t + 1);
@@ -409,6 +443,57 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
   if (!ok && tid == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
 }
 
+// ---- reducer warps, two ranks, 128x256 tiles: the inbox slots go through shared memory.
+// One (tile, warp-row q) unit = two 16 KB slots (own partial and the peer's), each contiguous in the inbox.  The
+// watcher thread copies them into a two-group ring behind the operand stages with bulk copies as soon as the
+// tile's flags are up (32 - 64 KB in flight per SM without holding registers); the eight reducer warps wait for
+// a group, read their 16-byte words from shared memory (warp = 32-column chunk, lane = row), sum them in rank
+// order, apply bias / GELU, store 64 contiguous bytes of C per thread and hand the group back.
+template <int BN>
+__device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
+                                             uint8_t* ring, uint64_t* ring_full, uint64_t* ring_empty) {
+  constexpr int CH = BN / 32;
+  constexpr int WVEC = CH * 4 * 32;           // 16-byte words per slot
+  constexpr int SLOT = WVEC * 16;
+  const int tid = threadIdx.x - 192;
+  const int wr = tid >> 5, ln = tid & 31;     // wr: 32-column chunk of the tile, ln: row inside the warp-row
+  bool ok = true;
+  int consumed = 0;                           // ring group = consumed & 1, phase = (consumed >> 1) & 1
+  for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
+    int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+    for (int q = 0; q < 4; ++q) {
+      if (p.ar.mode != 0 && (tm * BM + q * 32) / p.ar.rows_per_shard != p.ar.rank) continue;
+      const int g = consumed & 1;
+      if (!mbar_wait(&ring_full[g], (consumed >> 1) & 1, abort_flag, p.timeout_ns)) { ok = false; break; }
+      ++consumed;
+      if (!(p.debug & 8)) {
+        const size_t row = static_cast<size_t>(tm) * BM + q * 32 + ln;
+        const uint4* s0 = reinterpret_cast<const uint4*>(ring + (g * 2) * SLOT);
+        const uint4* s1 = reinterpret_cast<const uint4*>(ring + (g * 2 + 1) * SLOT);
+        uint4 a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { a[i] = s0[(wr * 4 + i) * 32 + ln]; b[i] = s1[(wr * 4 + i) * 32 + ln]; }
+        if (row < static_cast<size_t>(p.M)) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int col = tn * BN + wr * 32 + i * 8;
+            if (col >= p.N) continue;
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+            acc_vec8(acc, a[i], p.in_dtype);     // rank order: identical bits on both ranks
+            acc_vec8(acc, b[i], p.in_dtype);
+            comm_finish8(p, acc, row, col);
+          }
+        }
+      }
+      __syncwarp();
+      if (ln == 0) mbar_arrive(&ring_empty[g]);
+    }
+  }
+  if (!ok && tid == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x122u;
+}
+
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -420,7 +505,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* empty_bar = full_bar + S::STAGES;
   uint64_t* tmem_full = empty_bar + S::STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* ring_full = tmem_empty + 2;
+  uint64_t* ring_empty = ring_full + 2;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(ring_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   volatile unsigned int* parts_done = reinterpret_cast<volatile unsigned int*>(tmem_ptr_smem + 2);
   volatile unsigned int* ready_tiles = reinterpret_cast<volatile unsigned int*>(tmem_ptr_smem + 3);
@@ -432,10 +519,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int group = (BN == 256) ? 16 : 8;
   const uint64_t timeout = p.timeout_ns;
   const int gemm_ctas = p.gemm_ctas;   // == gridDim.x: every CTA computes tiles (and reduces them in comm mode)
+  // two ranks, 128x256 tiles: the reducer stages inbox slots in shared memory behind a 3-stage operand ring
+  const bool ring_mode = BN == 256 && p.ar.n == 2 && (p.debug & 128);
+  const int nstages = ring_mode ? S::RING_STAGES : S::STAGES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&ring_full[b], 1); mbar_init(&ring_empty[b], REDUCER_THREADS / 32); }
     *abort_flag = 0;
     *parts_done = 0;
     *ready_tiles = 0;
@@ -514,7 +605,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0);
           }
-          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok) {
@@ -559,7 +650,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
-          if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tmem_full[buf]);
       }
@@ -597,9 +688,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else if (warp == WATCHER_WARP) {
-    if (p.ar.n > 1 && lane == 0) watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles);
+    if (p.ar.n > 1 && lane == 0) {
+      if (ring_mode) watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles, smem + S::RING_OFFSET, ring_full, ring_empty);
+      else watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles);
+    }
   } else if (warp >= 6) {
-    if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag, ready_tiles);
+    bool done = false;
+    if constexpr (BN == 256) {
+      if (ring_mode) {
+        reducer_ring<BN>(p, group, num_tiles, abort_flag, smem + S::RING_OFFSET, ring_full, ring_empty);
+        done = true;
+      }
+    }
+    if (done) {
+    } else if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag, ready_tiles);
     else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4>(p, group, num_tiles, abort_flag, ready_tiles);
     else if (p.ar.n > 4) reducer_warps<BN, 8>(p, group, num_tiles, abort_flag, ready_tiles);
   } else {
