@@ -165,7 +165,7 @@ static int fill_comm(CommCtx& c, const AxbCommCtx* h, int device) {
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("allreduce: no status word"); return -1; }
   c.status = st;
-  c.timeout_ns = 5000000000ull;
+  c.timeout_ns = 2 * axb::wait_timeout_ns();
   return 0;
 }
 

@@ -44,7 +44,15 @@ volatile unsigned int* device_status_word(int device, unsigned int** dev_ptr) {
   return g_status_host[device];
 }
 
+static unsigned long long g_wait_timeout_ns = 2000000000ull;
+unsigned long long wait_timeout_ns() { return g_wait_timeout_ns; }
+
 }  // namespace axb
+
+// Deadline after which a device-side wait (mbarrier, peer flag) gives up and reports through the status word.
+extern "C" void axb_set_wait_timeout_ms(unsigned int ms) {
+  axb::g_wait_timeout_ns = (ms < 1 ? 1ull : static_cast<unsigned long long>(ms)) * 1000000ull;
+}
 
 extern "C" const char* axb_last_error(void) { return axb::g_err; }
 

@@ -19,6 +19,8 @@ int check_cuda(cudaError_t e, const char* what);
 // Per-device word that kernels set when a bounded wait expires (0 = clean).
 // Lives in mapped pinned host memory so the host can read it without a sync.
 volatile unsigned int* device_status_word(int device, unsigned int** dev_ptr);
+// Deadline of every device-side wait in nanoseconds (default 2 s; axb_set_wait_timeout_ms changes it).
+unsigned long long wait_timeout_ns();
 
 #define AXB_CUDA(call)                                   \
   do {                                                   \

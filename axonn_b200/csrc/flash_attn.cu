@@ -363,7 +363,7 @@ extern "C" int axb_flash_attn_fwd(const void* qkv, void* out, float* lse, int B,
   p.scale_log2 = scale * 1.4426950408889634f;
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
-  p.status = st; p.timeout_ns = 2000000000ull;
+  p.status = st; p.timeout_ns = wait_timeout_ns();
   if (D == 128) return fa_launch<128>(tm, p, device, static_cast<cudaStream_t>(stream));
   return fa_launch<64>(tm, p, device, static_cast<cudaStream_t>(stream));
 }
@@ -736,7 +736,7 @@ extern "C" int axb_flash_attn_bwd(const void* qkv, const void* out, const void* 
   p.B = B; p.S = S; p.G = G; p.qpk = qpk; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
-  p.status = st; p.timeout_ns = 2000000000ull;
+  p.status = st; p.timeout_ns = wait_timeout_ns();
   { const char* dbg = getenv("AXB_FA_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
   if (D == 128) return fa_bwd_launch<128>(tq, td, p, device, s);
   return fa_bwd_launch<64>(tq, td, p, device, s);

@@ -63,7 +63,7 @@ struct GemmParams {
   int tn_offset;  // rotation of the N-tile order (all-gather mode: tiles of the local shard first)
   int kb_offset;  // rotation of the K-block order (all-gather mode, B rows = K: local shard first)
   int gemm_ctas;  // number of CTAs computing tiles; the remaining CTAs of the grid reduce over peer memory
-  int debug;      // timing experiments only (AXB_AR_DEBUG): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores
+  int debug;      // timing experiments only (AXB_AR_DEBUG): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores, 128 register-path reducer instead of the shared-memory ring
 };
 
 template <int BN>
@@ -520,7 +520,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint64_t timeout = p.timeout_ns;
   const int gemm_ctas = p.gemm_ctas;   // == gridDim.x: every CTA computes tiles (and reduces them in comm mode)
   // two ranks, 128x256 tiles: the reducer stages inbox slots in shared memory behind a 3-stage operand ring
-  const bool ring_mode = BN == 256 && p.ar.n == 2 && (p.debug & 128);
+  const bool ring_mode = BN == 256 && p.ar.n == 2 && !(p.debug & 128);
   const int nstages = ring_mode ? S::RING_STAGES : S::STAGES;
 
   if (threadIdx.x == 0) {
@@ -1170,7 +1170,7 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
   GemmParams p;
   p.C = C; p.bias = bias; p.aux = aux; p.M = M; p.N = N; p.K = K;
   p.out_dtype = out_dtype; p.in_dtype = in_dtype; p.epilogue = epilogue; p.accumulate = accumulate;
-  p.status = status_dev; p.timeout_ns = 2000000000ull;
+  p.status = status_dev; p.timeout_ns = wait_timeout_ns();
   if (ar && ar->n > 1) {
     p.ar = *ar;
     const long long tiles = static_cast<long long>(tiles_m) * ((N + BN - 1) / BN);

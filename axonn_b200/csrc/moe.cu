@@ -160,7 +160,7 @@ static int fill_ctx(MoeCtx& c, const AxbMoeCtx* h, int device) {
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("moe: no status word"); return -1; }
   c.status = st;
-  c.timeout_ns = 2000000000ull;
+  c.timeout_ns = axb::wait_timeout_ns();
   return 0;
 }
 
