@@ -99,6 +99,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Record why a bounded wait gave up.  The first reason stays: later writers (warps that only notice the
+// abort flag of the first one) do not overwrite it.
+__device__ __forceinline__ void report_status(unsigned int* status, unsigned int code) {
+  volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(status);
+  if (*w == 0u) *w = code;
+}
+
 // 2-D tiled TMA load (no multicast) into CTA shared memory.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar,
                                             int32_t c0, int32_t c1) {

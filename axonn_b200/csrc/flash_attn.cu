@@ -144,7 +144,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
         // drain: give in-flight copies time to land before the CTA exits
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) {}
-        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x401u;
+        report_status(p.status, 0x401u);
       }
     }
   } else if (warp == 1) {
@@ -189,7 +189,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
         umma_commit(p_empty);
         umma_commit(&kv_empty[j & 1]);
       }
-      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x402u;
+      if (!ok) report_status(p.status, 0x402u);
     }
   } else {
     // ------------------------------------------------------------------ softmax + output accumulation
@@ -325,7 +325,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
         ok = false;
       }
     }
-    if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x404u;
+    if (!ok && lane == 0) report_status(p.status, 0x404u);
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -503,7 +503,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) {}
-        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x411u;
+        report_status(p.status, 0x411u);
       }
     }
   } else if (warp == 1) {
@@ -564,7 +564,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
         w[2] = static_cast<unsigned>(w_qdo); w[3] = static_cast<unsigned>(w_sfree); w[4] = static_cast<unsigned>(w_pds);
         w[7] = static_cast<unsigned>(n_iter);
       }
-      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x412u;
+      if (!ok) report_status(p.status, 0x412u);
     }
   } else {
     // ---- 8 softmax / reduction warps: thread = (query row r, column half): two warps share each TMEM lane
@@ -664,7 +664,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     if (ok) {
       fa_store_kv_grad<HD>(p, (half == 0 ? tm_dk : tm_dv) + lane_base, b, jt, g, r, half);
     } else if (lane == 0) {
-      *reinterpret_cast<volatile unsigned int*>(p.status) = 0x414u;
+      report_status(p.status, 0x414u);
     }
   }
   tcgen05_fence_before();

@@ -294,7 +294,7 @@ __device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, i
         }
       }
       if (!good) {
-        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x121u;
+        report_status(p.status, 0x121u);
         return;
       }
       if (!(p.debug & 4)) __threadfence_system();   // acquire side of the flags, once per tile
@@ -306,7 +306,7 @@ __device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, i
           if (!(mine & (1u << q))) continue;
           const int g = issued & 1;
           if (!mbar_wait(&ring_empty[g], ((issued >> 1) & 1) ^ 1, abort_flag, p.timeout_ns)) {
-            *reinterpret_cast<volatile unsigned int*>(p.status) = 0x123u;
+            report_status(p.status, 0x123u);
             return;
           }
           mbar_expect_tx(&ring_full[g], 2 * SLOT);
@@ -440,7 +440,7 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
     volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(p.status);
     w[2] = static_cast<unsigned>(ns_wait); w[3] = static_cast<unsigned>(ns_work); w[7] = static_cast<unsigned>(t + 1);
   }
-  if (!ok && tid == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x120u;
+  if (!ok && tid == 0) report_status(p.status, 0x120u);
 }
 
 // ---- reducer warps, two ranks, 128x256 tiles: the inbox slots go through shared memory.
@@ -491,7 +491,7 @@ __device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int
       if (ln == 0) mbar_arrive(&ring_empty[g]);
     }
   }
-  if (!ok && tid == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x122u;
+  if (!ok && tid == 0) report_status(p.status, 0x122u);
 }
 
 template <int BN, int A_MN, int B_MN>
@@ -545,7 +545,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int j = 0; j < p.ar.n; ++j) {
       if (j == p.ar.rank) continue;
       if (!wait_flag_ge(p.ar.done_local + j, p.ar.epoch - 2u, abort_flag, timeout)) {
-        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x108u;
+        report_status(p.status, 0x108u);
         break;
       }
     }
@@ -617,7 +617,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             while (!mbar_try_wait(&full_bar[s], par) && globaltimer_ns() - t0 < 2000000ull) {}
           }
         }
-        *reinterpret_cast<volatile unsigned int*>(p.status) = 0x101u;
+        report_status(p.status, 0x101u);
       }
     }
   } else if (warp == 1) {
@@ -654,7 +654,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (ok) umma_commit(&tmem_full[buf]);
       }
-      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x102u;
+      if (!ok) {
+        // MMAs issued before the abort may still be running: give them time before TMEM is released
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 50000ull) {}
+        report_status(p.status, 0x102u);
+      }
     }
   } else if (warp == FLAGGER_WARP) {
     // ------------------------------------------------------------------ flagger: publishes finished partials
@@ -733,7 +738,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag.shard_ready + z) : "memory");
         }
       }
-      if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x110u;
+      if (!ok && lane == 0) report_status(p.status, 0x110u);
     }
     // Finish one tile: values v (one row, 32 columns) -> bias / GELU -> C.
     auto finish_chunk = [&](float (&v)[32], size_t out_row, int col, bool store_ok) {
@@ -833,7 +838,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         atomicAdd(const_cast<unsigned int*>(parts_done), 1u);
       }
     }
-    if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x104u;
+    if (!ok && lane == 0) report_status(p.status, 0x104u);
   }
 
   tcgen05_fence_before();
@@ -949,7 +954,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x141u;
+      if (!ok) report_status(p.status, 0x141u);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -982,7 +987,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (ok) umma_commit_pair(&tmem_full[buf]);   // accumulator complete: both epilogues may read
       }
-      if (!ok) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x142u;
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 50000ull) {}   // let MMAs in flight finish before TMEM is released
+        report_status(p.status, 0x142u);
+      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
@@ -1029,7 +1038,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);   // 8 arrivals (4 warps x 2 CTAs) free the buffer
     }
-    if (!ok && lane == 0) *reinterpret_cast<volatile unsigned int*>(p.status) = 0x144u;
+    if (!ok && lane == 0) report_status(p.status, 0x144u);
   }
 
   tcgen05_fence_before();

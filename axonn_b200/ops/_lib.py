@@ -44,7 +44,17 @@ def lib():
                 build.build_library(verbose=False)
             _LIB = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
             _LIB.axb_last_error.restype = ctypes.c_char_p
+            ms = os.environ.get("AXONN_COMM_TIMEOUT_MS")
+            if ms:
+                _LIB.axb_set_wait_timeout_ms(ctypes.c_uint(int(ms)))
     return _LIB
+
+
+def set_wait_timeout_ms(ms: int):
+    """Deadline of every device-side wait (mbarrier, peer flag).  A kernel whose wait runs out returns and
+    reports through the status word (``check_status``).  Default 2000 ms; ``AXONN_COMM_TIMEOUT_MS`` sets it
+    at load time."""
+    lib().axb_set_wait_timeout_ms(ctypes.c_uint(int(ms)))
 
 
 def use_cuda_kernels(*tensors) -> bool:

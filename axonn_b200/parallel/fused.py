@@ -149,13 +149,17 @@ def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, aux=None,
 _loopback = {}
 
 
-def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None):
+def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None, silent_peer=False):
     """Single-GPU emulation of a two-rank ``gemm_all_reduce`` (layout 0): the "peer" inbox, flags and done
     words are aliased onto this GPU's own slots of source rank 1, so one launch pushes its partial twice,
     reduces both copies and returns ``2 * (a @ b.T)`` (+bias, +GELU).  The kernel only ever waits on flags
     that its own CTAs raise.  It exercises the whole communication path of the kernel - epilogue pushes,
     flag publication, reducer warps, end-of-call handshake - with NVLink replaced by local stores, which is
-    what a one-GPU test or a profiler capture of that path needs."""
+    what a one-GPU test or a profiler capture of that path needs.
+
+    ``silent_peer=True`` emulates a peer that never delivers: the flags of source rank 1 are redirected to a
+    scratch area that nothing reads, so the kernel's wait for them runs into its deadline, the kernel returns
+    and the status word reports it (``ops._lib.check_status``); the context stays usable."""
     M, K = a.shape
     N = b.shape[0]
     dev = a.device
@@ -184,6 +188,11 @@ def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None)
     c.inbox_peer[0], c.flags_peer[0], c.done_peer[0] = c.inbox_local, c.flags_local, me
     c.inbox_peer[1] = c.inbox_local + vecs_per_src * 16   # peer's slot of source 0 == own slot of source 1
     c.flags_peer[1] = c.flags_local + flags_per_src * 4
+    if silent_peer:
+        scratch = st.get("scratch")
+        if scratch is None or scratch.numel() < flags_per_src * 4 * 2:
+            scratch = st["scratch"] = torch.zeros(flags_per_src * 4 * 2, dtype=torch.uint8, device=dev)
+        c.flags_peer[1] = scratch.data_ptr()   # flags[rank 0] of the "peer" land here: never seen locally
     c.done_peer[1] = me + 4                                # peer's done[0] == own done[1]
     c.inbox_vecs_per_src, c.flags_per_src = vecs_per_src, flags_per_src
     c.mode, c.rows_per_shard, c.comm_ctas = 0, 0, 0

@@ -143,3 +143,36 @@ def test_fused_all_reduce_loopback(shape):
     torch.cuda.synchronize()
     err = (out.float() - ref).abs().max() / ref.abs().max()
     assert err < 2e-2, err
+
+
+def test_silent_peer_times_out_and_context_survives():
+    """A peer that never raises its flags: the bounded wait of the fused kernel runs out, the kernel returns,
+    the status word names the reason, and the next (healthy) call on the same buffers is correct."""
+    from axonn_b200.ops import _lib
+    from axonn_b200.parallel import fused
+
+    torch.manual_seed(1)
+    a = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16)
+    ref = 2.0 * (a.float() @ b.float().t())
+    fused.gemm_all_reduce_loopback(a, b)             # healthy call first
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    _lib.set_wait_timeout_ms(50)
+    try:
+        fused.gemm_all_reduce_loopback(a, b, silent_peer=True)
+        torch.cuda.synchronize()
+        st = _lib.device_status()
+        # the watcher (0x121 / 0x123) or the reducer warps waiting for it (0x120 / 0x122) run out first
+        assert st in (0x120, 0x121, 0x122, 0x123), hex(st)
+        with pytest.raises(_lib.KernelError):
+            fused.gemm_all_reduce_loopback(a, b, silent_peer=True)
+            torch.cuda.synchronize()
+            _lib.check_status()
+    finally:
+        _lib.set_wait_timeout_ms(2000)
+    for _ in range(2):
+        out = fused.gemm_all_reduce_loopback(a, b)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
