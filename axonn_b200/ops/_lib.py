@@ -97,6 +97,16 @@ _STATUS_NAMES = {
     0x110: "all-gather stage: a peer never published its weight shard",
     0x120: "fused reduction: aborted while waiting for partial tiles",
     0x121: "fused reduction: partial tiles of a peer never arrived",
+    0x122: "fused reduction (shared-memory ring): inbox slots never arrived",
+    0x123: "fused reduction (shared-memory ring): ring group never freed",
+    0x201: "expert dispatch / combine: a peer never signalled",
+    0x301: "gradient all-reduce: a peer never published its bucket",
+    0x401: "flash attention forward: producer timed out",
+    0x402: "flash attention forward: MMA issuer timed out",
+    0x404: "flash attention forward: softmax warps timed out",
+    0x411: "flash attention backward: producer timed out",
+    0x412: "flash attention backward: MMA issuer timed out",
+    0x414: "flash attention backward: softmax / reduction warps timed out",
     0x141: "CTA-pair GEMM producer timed out",
     0x142: "CTA-pair GEMM MMA issuer timed out",
     0x144: "CTA-pair GEMM epilogue timed out",
