@@ -13,7 +13,7 @@ import torch.nn.functional as F
 
 from .. import axonn as ax
 from ..utils import divide
-from .communication import Drop, ForwardGather_BackwardReduceScatter, Gather
+from .communication import ForwardGather_BackwardReduceScatter, Gather
 
 
 @torch.no_grad()

@@ -21,7 +21,7 @@ import torch.nn as nn
 
 from .. import axonn as ax
 from .. import ops
-from ..intra_layer import Embedding, Linear
+from ..intra_layer import Linear
 from ..utils import divide
 
 

@@ -7,7 +7,6 @@ implements the pipeline engine's stage contract.  Workload of the reference's
 classes) without depending on torchvision.
 """
 
-import torch
 import torch.nn as nn
 
 from .. import axonn as ax

@@ -8,7 +8,6 @@ import ctypes
 import os
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib
 

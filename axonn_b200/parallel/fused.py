@@ -13,7 +13,6 @@ size); the caller then uses ``torch.distributed``.
 """
 
 import ctypes
-import os
 
 import torch
 import torch.distributed as dist

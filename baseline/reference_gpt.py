@@ -12,7 +12,6 @@ the product's model: hidden split over the column group between blocks, heads
 over the row group, vocabulary over the row group.
 """
 
-import math
 
 import torch
 import torch.distributed as dist

@@ -13,8 +13,6 @@ from _dist import run_distributed
 
 
 def _silent_rank(rank, world, tmp):
-    import torch.distributed as dist
-
     from axonn_b200.parallel.watchdog import RankFailure, Watchdog
 
     wd = Watchdog(interval_s=0.1, timeout_s=1.0).start()

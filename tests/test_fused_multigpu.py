@@ -200,7 +200,6 @@ def _moe_case(rank, world):
 
     from axonn_b200 import axonn as ax
     from axonn_b200.ops import _lib
-    from axonn_b200.parallel import moe_kernels, symm
     from axonn_b200.parallel.moe import ExpertParallelMoE
 
     ax.init(G_inter=1, G_data=world)

@@ -14,7 +14,7 @@ def _conv_emb(rank, world, grid):
     import torch.distributed as dist
 
     from axonn_b200 import axonn as ax
-    from axonn_b200.intra_layer import Conv2d, Embedding, optimize_communication, sync_gradients
+    from axonn_b200.intra_layer import Conv2d, Embedding, optimize_communication
     from axonn_b200.intra_layer.communication import _gather
 
     r, c, d = grid

@@ -2,7 +2,6 @@
 nothing, 4 expert-parallel ranks must reproduce the single-rank layer (same
 seed => same experts) in output, input gradient and expert gradients."""
 
-import pytest
 import torch
 
 from _dist import run_distributed
