@@ -113,6 +113,14 @@ _STATUS_NAMES = {
 }
 
 
+class AxonnCommTimeout(KernelError):
+    """A device-side wait (mbarrier or peer flag) ran into its deadline; ``status`` is the kernel's reason code."""
+
+    def __init__(self, status: int):
+        self.status = status
+        super().__init__(f"device-side wait timed out (status 0x{status:x}: {_STATUS_NAMES.get(status, 'unknown')})")
+
+
 def device_status(device=None, clear=True) -> int:
     """Status word that kernels write when one of their bounded waits gave up (0: none did).  The word lives
     in mapped host memory, so reading it needs no synchronisation; it is meaningful once the kernels in
@@ -126,7 +134,8 @@ def device_status(device=None, clear=True) -> int:
 
 
 def check_status(device=None):
-    """Raise ``KernelError`` if a kernel on ``device`` reported a timed-out wait since the last check."""
+    """Raise ``AxonnCommTimeout`` (a ``KernelError``) if a kernel on ``device`` reported a timed-out wait since
+    the last check."""
     st = device_status(device, clear=True)
     if st not in (0, 0xFFFFFFFF):
-        raise KernelError(f"device-side wait timed out (status 0x{st:x}: {_STATUS_NAMES.get(st, 'unknown')})")
+        raise AxonnCommTimeout(st)
