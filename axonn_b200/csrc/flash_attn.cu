@@ -24,6 +24,7 @@
 namespace axb {
 
 int make_tmap_2d_16bit(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, int dtype);
+int make_tmap_2d_f32(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 struct FaParams {
   __nv_bfloat16* out;
@@ -391,7 +392,7 @@ struct FaBwdParams {
   float scale, scale_log2;
   unsigned int* status;
   unsigned long long timeout_ns;
-  int debug;   // timing experiments only (AXB_FA_DEBUG): 1 no dQ reductions, 2 no exponentials
+  int debug;   // timing experiments only (AXB_FA_DEBUG): 1 no dQ reductions, 2 no exponentials, 4 phase timers, 8 release Q/dO after the dQ MMAs
 };
 
 template <int HD>
@@ -400,10 +401,10 @@ struct FaBwdSmem {
   static constexpr int K_OFF = 0, V_OFF = TILE, Q_OFF = 2 * TILE, DO_OFF = 3 * TILE;
   static constexpr int P_OFF = 4 * TILE, DS_OFF = P_OFF + 32768;
   // After the MMAs of an iteration the P / dS tiles are dead until the next iteration writes them; the dQ
-  // partial (fp32, one padded row per query row) is staged there for the bulk reductions into global memory.
-  static constexpr int DQ_ROW_BYTES = HD * 4 + 16;            // +16: consecutive rows start 4 banks apart
-  static constexpr int DQ_STAGE_BYTES = 128 * DQ_ROW_BYTES;
-  static constexpr int BAR_OFF = P_OFF + (DQ_STAGE_BYTES > 65536 ? DQ_STAGE_BYTES : 65536);
+  // partial (fp32) is staged there as 32-row x 32-column boxes (4 KB, 128-byte swizzle), HD / 64 per warp,
+  // for the bulk tensor reductions into global memory.
+  static constexpr int DQ_BOX_BYTES = 32 * 32 * 4;
+  static constexpr int BAR_OFF = P_OFF + 65536;
   static constexpr int NBARS = 7;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16 + 1024;
 };
@@ -439,7 +440,8 @@ constexpr int FA_BWD_THREADS = 320;   // TMA warp, MMA warp, 8 softmax / reducti
 
 template <int HD>
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
-fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, const FaBwdParams p) {
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+              const __grid_constant__ CUtensorMap tmDQ, const FaBwdParams p) {
   using S_ = FaBwdSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -453,6 +455,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
   uint64_t* s_free = bars + 6;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + S_::NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  volatile int* reads_done = reinterpret_cast<volatile int*>(tmem_ptr_smem + 2);   // dQ staging boxes read back, per warp and iteration
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = p.S / 128;
@@ -468,9 +471,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
     mbar_init(pds_full, 8); mbar_init(dq_full, 1); mbar_init(s_free, 8);
     *abort_flag = 0;
+    *reads_done = 0;
     fence_mbar_init();
   }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmQKV); tma_prefetch_desc(&tmDO); }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmQKV); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmDQ); }
   if (warp == 1) { tmem_alloc(tmem_ptr_smem, 512); tmem_relinquish(); }
   tcgen05_fence_before();
   __syncthreads();
@@ -551,13 +555,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
           umma_f16(tm_dk, umma_smem_desc(ds_addr + kk * 2048, 16384, 1024), umma_smem_desc(q_addr + kk * 2048, 16384, 1024),
                    idesc_t, (it | kk) != 0);
         }
-        umma_commit(qdo_empty);            // Q and dO are free once dV / dK are done: the next loads overlap dQ
+        if (!(p.debug & 8)) umma_commit(qdo_empty);   // Q and dO are free once dV / dK are done: the next loads overlap dQ
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // reduction over the 128 KV rows
           umma_f16(tm_s, umma_smem_desc(ds_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
                    umma_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_q, kk != 0);
         }
         umma_commit(dq_full);
+        if (p.debug & 8) umma_commit(qdo_empty);
       }
       if (probe) {
         volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(p.status);
@@ -577,7 +582,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     uint8_t* ds_row = smem + S_::DS_OFF + (r >> 3) * 1024 + (r & 7) * 128;
     bool ok = true;
     const bool probe = (p.debug & 4) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
-    uint64_t w_sdp = 0, t_a = 0, w_dq = 0, t_b = 0, t_mark = 0;
+    uint64_t w_sdp = 0, t_a = 0, w_dq = 0, t_b = 0, t_b1 = 0, t_b2 = 0, t_mark = 0;
     for (int it = 0; it < n_iter; ++it) {
       const uint32_t ph = it & 1;
       const int i = jt + it / p.qpk, jq = it % p.qpk;
@@ -589,6 +594,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       if (!mbar_wait(sdp_full, ph, abort_flag, timeout)) { ok = false; break; }
       if (probe) { const uint64_t now = globaltimer_ns(); w_sdp += now - t_mark; t_mark = now; }
       tcgen05_fence_after();
+      if (it > 0) {
+        // the P / dS tiles still hold the previous iteration's dQ staging boxes until the copy engine has read
+        // them: every warp waits for its own reductions' reads and counts itself, all wait for the eight counts
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __threadfence_block();
+          atomicAdd(const_cast<int*>(reads_done), 1);
+        }
+        if (!wait_partner(reads_done, 8 * it, abort_flag, timeout)) { ok = false; break; }
+      }
       const bool diag = (i == jt);
 #pragma unroll 1
       for (int c = 2 * half; c < 2 * half + 2; ++c) {
@@ -628,27 +643,35 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       if (!mbar_wait(dq_full, ph, abort_flag, timeout)) { ok = false; break; }
       if (probe) { const uint64_t now = globaltimer_ns(); w_dq += now - t_mark; t_mark = now; }
       tcgen05_fence_after();
-      float* dq = p.dq_acc + ((static_cast<size_t>(b) * p.S + srow) * heads + head) * HD;
-      // this thread's half row: TMEM -> staging row in shared memory -> one bulk reduce-add into global memory
-      uint8_t* stage = smem + S_::P_OFF + r * S_::DQ_ROW_BYTES + half * (HD * 2);
+      // this warp's 32 rows x HD/2 columns: TMEM -> swizzled 32x32 fp32 boxes in shared memory -> one bulk
+      // tensor reduce-add per box into the fp32 accumulator (16 copy-engine operations per tile in all)
+      constexpr int NBOX = HD / 64;                 // boxes per warp
+      uint8_t* wstage = smem + S_::P_OFF + (warp - 2) * (NBOX * S_::DQ_BOX_BYTES);
 #pragma unroll 1
-      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
+      for (int cc = 0; cc < NBOX; ++cc) {
         uint32_t v[32];
-        tmem_ld_32x32(tm_s + lane_base + c * 32, v);
+        tmem_ld_32x32(tm_s + lane_base + (half * NBOX + cc) * 32, v);
         tmem_ld_wait();
+        uint8_t* row = wstage + cc * S_::DQ_BOX_BYTES + lane * 128;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          *reinterpret_cast<uint4*>(stage + (c - half * (HD / 64)) * 128 + k * 16) =
-              make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+          *reinterpret_cast<uint4*>(row + ((k ^ (lane & 7)) * 16)) = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
       }
       tcgen05_fence_before();
-      if (!(p.debug & 1)) {
-        fence_proxy_async_smem();
-        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
-                     ::"l"(dq + half * (HD / 2)), "r"(smem_u32(stage)), "r"(HD * 2) : "memory");
+      if (probe) { const uint64_t now = globaltimer_ns(); t_b1 += now - t_mark; }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && !(p.debug & 1)) {
+        const int y = b * p.S + i * 128 + q4 * 32;
+#pragma unroll
+        for (int cc = 0; cc < NBOX; ++cc) {
+          const int x = head * HD + (half * NBOX + cc) * 32;
+          asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                       ::"l"(reinterpret_cast<uint64_t>(&tmDQ)), "r"(x), "r"(y), "r"(smem_u32(wstage + cc * S_::DQ_BOX_BYTES))
+                       : "memory");
+        }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        // the staging bytes are the next iteration's P / dS tiles: wait until the copy engine has read them
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (probe) { const uint64_t now = globaltimer_ns(); t_b2 += now - t_mark; }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
@@ -657,7 +680,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     if (probe) {
       volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(p.status);
       w[8] = static_cast<unsigned>(w_sdp); w[9] = static_cast<unsigned>(t_a); w[10] = static_cast<unsigned>(w_dq);
-      w[11] = static_cast<unsigned>(t_b);
+      w[11] = static_cast<unsigned>(t_b); w[12] = static_cast<unsigned>(t_b1); w[13] = static_cast<unsigned>(t_b2);
     }
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     // dK (column half 0) and dV (half 1) of this KV tile: every MMA has completed (last dq_full seen)
@@ -696,7 +719,8 @@ __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_
 }
 
 template <int HD>
-static int fa_bwd_launch(const CUtensorMap& tq, const CUtensorMap& td, const FaBwdParams& p, int device, cudaStream_t s) {
+static int fa_bwd_launch(const CUtensorMap& tq, const CUtensorMap& td, const CUtensorMap& tdq, const FaBwdParams& p,
+                         int device, cudaStream_t s) {
   using S_ = FaBwdSmem<HD>;
   static bool configured[64] = {false};
   auto kern = fa_bwd_kernel<HD>;
@@ -705,7 +729,7 @@ static int fa_bwd_launch(const CUtensorMap& tq, const CUtensorMap& td, const FaB
     configured[device & 63] = true;
   }
   dim3 grid(p.G, p.B, p.S / 128);   // z (slowest) = KV tile: all CTAs with the most iterations are scheduled first
-  kern<<<grid, FA_BWD_THREADS, S_::TOTAL, s>>>(tq, td, p);
+  kern<<<grid, FA_BWD_THREADS, S_::TOTAL, s>>>(tq, td, tdq, p);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }
@@ -728,9 +752,10 @@ extern "C" int axb_flash_attn_bwd(const void* qkv, const void* out, const void* 
   fa_delta_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out),
                                          delta, B, S, H, D);
   AXB_CUDA(cudaGetLastError());
-  CUtensorMap tq, td;
+  CUtensorMap tq, td, tdq;
   if (make_tmap_2d_16bit(&tq, qkv, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(G) * (qpk + 2) * D, 128, 0)) return -1;
   if (make_tmap_2d_16bit(&td, d_out, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(H) * D, 128, 0)) return -1;
+  if (make_tmap_2d_f32(&tdq, dq_acc, static_cast<uint64_t>(B) * S, static_cast<uint64_t>(H) * D, 32)) return -1;
   FaBwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
   p.B = B; p.S = S; p.G = G; p.qpk = qpk; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
@@ -738,6 +763,6 @@ extern "C" int axb_flash_attn_bwd(const void* qkv, const void* out, const void* 
   if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
   p.status = st; p.timeout_ns = wait_timeout_ns();
   { const char* dbg = getenv("AXB_FA_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
-  if (D == 128) return fa_bwd_launch<128>(tq, td, p, device, s);
-  return fa_bwd_launch<64>(tq, td, p, device, s);
+  if (D == 128) return fa_bwd_launch<128>(tq, td, tdq, p, device, s);
+  return fa_bwd_launch<64>(tq, td, tdq, p, device, s);
 }

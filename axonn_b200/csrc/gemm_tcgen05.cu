@@ -1085,6 +1085,26 @@ int make_tmap_2d_16bit(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
   return 0;
 }
 
+// Row-major fp32 [rows, cols] with 32 x `box_rows` boxes (128-byte rows, 128-byte swizzle): destination of
+// bulk tensor reductions.
+int make_tmap_2d_f32(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { set_error("cuTensorMapEncodeTiled entry point not available"); return -1; }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (cols * 4) % 16 != 0) {
+    set_error("TMA tensor must be 16-byte aligned with a row pitch that is a multiple of 16 bytes");
+    return -1;
+  }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {cols * 4};
+  cuuint32_t box[2] = {32, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (fp32) failed with CUresult %d", (int)r); return -1; }
+  return 0;
+}
+
 int sm_count(int device) {
   static int cached[64] = {0};
   if (device < 0 || device >= 64) return 148;

@@ -109,12 +109,13 @@ def bench_attention(small=False):
         if int(os.environ.get("AXB_FA_DEBUG", "0")) & 4:
             from axonn_b200.ops import _lib
 
-            w = {i: _lib.lib().axb_debug_word(0, i, 1) for i in (2, 3, 4, 7, 8, 9, 10, 11)}
+            w = {i: _lib.lib().axb_debug_word(0, i, 1) for i in (2, 3, 4, 7, 8, 9, 10, 11, 12, 13)}
             n = max(1, w[7])
             print("bwd CTA (0,0,0), us per iteration: MMA warp waits: Q/dO %.2f, S columns free %.2f, P/dS %.2f | "
-                  "softmax warp: wait S/dP %.2f, P/dS math %.2f, wait dQ %.2f, dQ reduction %.2f (%d iterations)" % (
+                  "softmax warp: wait S/dP %.2f, P/dS math %.2f, wait dQ %.2f, dQ reduction %.2f (TMEM -> smem done at %.2f, "
+                  "bulk reduce issued at %.2f) (%d iterations)" % (
                       w[2] / n / 1e3, w[3] / n / 1e3, w[4] / n / 1e3, w[8] / n / 1e3, w[9] / n / 1e3,
-                      w[10] / n / 1e3, w[11] / n / 1e3, n), flush=True)
+                      w[10] / n / 1e3, w[11] / n / 1e3, w[12] / n / 1e3, w[13] / n / 1e3, n), flush=True)
         print(json.dumps(dict(B=B, S=S, heads=G * qpk, kv_heads=G, D=D, ms=round(t_ours, 4),
                               tflops=round(fl / t_ours / 1e9, 1), cudnn_ms=round(t_lib, 4),
                               cudnn_tflops=round(fl / t_lib / 1e9, 1), bwd_ms=round(t_bwd, 4),
