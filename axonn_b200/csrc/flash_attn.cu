@@ -594,16 +594,6 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       if (!mbar_wait(sdp_full, ph, abort_flag, timeout)) { ok = false; break; }
       if (probe) { const uint64_t now = globaltimer_ns(); w_sdp += now - t_mark; t_mark = now; }
       tcgen05_fence_after();
-      if (it > 0) {
-        // the P / dS tiles still hold the previous iteration's dQ staging boxes until the copy engine has read
-        // them: every warp waits for its own reductions' reads and counts itself, all wait for the eight counts
-        if (lane == 0) {
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          __threadfence_block();
-          atomicAdd(const_cast<int*>(reads_done), 1);
-        }
-        if (!wait_partner(reads_done, 8 * it, abort_flag, timeout)) { ok = false; break; }
-      }
       const bool diag = (i == jt);
 #pragma unroll 1
       for (int c = 2 * half; c < 2 * half + 2; ++c) {
@@ -626,6 +616,17 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
           pp[k] = *reinterpret_cast<const uint32_t*>(&hp);
           dd[k] = *reinterpret_cast<const uint32_t*>(&hd);
         }
+        if (it > 0 && c == 2 * half) {
+          // the P / dS tiles still hold the previous iteration's dQ staging boxes until the copy engine has read
+          // them: every warp waits for its own reductions' reads and counts itself, all wait for the eight
+          // counts - here, after the first chunk's arithmetic, so that the wait is usually over already
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __threadfence_block();
+            atomicAdd(const_cast<int*>(reads_done), 1);
+          }
+          if (!wait_partner(reads_done, 8 * it, abort_flag, timeout)) ok = false;
+        }
         const int blk = (c >> 1) * 16384;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -634,6 +635,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
           *reinterpret_cast<uint4*>(ds_row + blk + chunk * 16) = make_uint4(dd[4 * t], dd[4 * t + 1], dd[4 * t + 2], dd[4 * t + 3]);
         }
       }
+      if (!ok) break;
       tcgen05_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
