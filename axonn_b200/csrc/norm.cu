@@ -449,10 +449,10 @@ gelu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __r
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   if (c < N) {
     const int stride = gridDim.y * 8;
-    for (int r = blockIdx.y * 8 + w; r < rows; r += 2 * stride) {
-      float fx[2][8], fd[2][8];
+    for (int r = blockIdx.y * 8 + w; r < rows; r += 4 * stride) {
+      float fx[4][8], fd[4][8];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < 4; ++u) {
         const int rr = r + u * stride;
         if (rr < rows) {
           Vec8<T>::load(x + static_cast<size_t>(rr) * N + c, fx[u]);
@@ -460,7 +460,7 @@ gelu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __r
         }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < 4; ++u) {
         const int rr = r + u * stride;
         if (rr >= rows) continue;
         float o[8];

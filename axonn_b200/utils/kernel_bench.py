@@ -231,6 +231,9 @@ def bench_memory_bound(rows=16384, H=2048):
     yh = ops.gelu(h)
     t, _ = time_cuda(lambda: torch.autograd.grad(yh, h, dh, retain_graph=True), flush=flush)
     report("gelu bwd", t, 3 * 4 * nb)
+    with torch.no_grad():
+        t, _ = time_cuda(lambda: ops.gelu_backward_colsum(dh, h.detach()), flush=flush)
+    report("gelu bwd + column sums (bias gradient)", t, 3 * 4 * nb)
     return out
 
 
