@@ -15,12 +15,16 @@ This is the counterpart of the process-group construction in the reference's
 """
 
 import os
+import weakref
 from typing import Dict, Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
+CANARY_BYTES = 256
+CANARY_VALUE = 0xA5
 _buffers: Dict[Tuple[str, str], "SymmBuffer"] = {}
+_all_buffers = []   # weak references to every live SymmBuffer, for verify_canaries()
 _disabled_reason: Optional[str] = None
 
 
@@ -51,8 +55,12 @@ class SymmBuffer:
         self.rank = dist.get_rank(group)
         self.nbytes = int(nbytes)
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.local = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=dev)
-        self.handle = symm_mem.rendezvous(self.local, group=group)
+        # CANARY_BYTES guard bytes follow the usable range; kernels never address them, so a changed guard
+        # byte means that a kernel (of this rank or of a peer) wrote past the end of the buffer
+        self._full = symm_mem.empty(self.nbytes + CANARY_BYTES, dtype=torch.uint8, device=dev)
+        self._full[self.nbytes:].fill_(CANARY_VALUE)
+        self.local = self._full[:self.nbytes]
+        self.handle = symm_mem.rendezvous(self._full, group=group)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.signal_ptrs = [int(p) for p in self.handle.signal_pad_ptrs]
         self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
@@ -60,6 +68,7 @@ class SymmBuffer:
         self.signal_table = torch.tensor(self.signal_ptrs, dtype=torch.int64, device=dev)
         self.epoch = 0
         self.tag = tag
+        _all_buffers.append(weakref.ref(self))
 
     def view(self, dtype, numel, offset_bytes=0):
         es = torch.empty((), dtype=dtype).element_size()
@@ -71,6 +80,10 @@ class SymmBuffer:
 
     def barrier(self):
         self.handle.barrier()
+
+    def canary_intact(self) -> bool:
+        """True when the guard bytes behind the buffer still hold their pattern (synchronises the device)."""
+        return bool((self._full[self.nbytes:] == CANARY_VALUE).all().item())
 
 
 def get_buffer(group, nbytes: int, tag: str) -> SymmBuffer:
@@ -84,3 +97,23 @@ def get_buffer(group, nbytes: int, tag: str) -> SymmBuffer:
         buf = SymmBuffer(group, size, tag)
         _buffers[key] = buf
     return buf
+
+
+def debug_bounds_enabled() -> bool:
+    return os.environ.get("AXONN_DEBUG_BOUNDS", "0") not in ("", "0")
+
+
+def verify_canaries():
+    """Check the guard bytes of every live symmetric buffer; raises ``RuntimeError`` naming the buffer whose
+    guard was overwritten.  Meant to run once per step under ``AXONN_DEBUG_BOUNDS=1`` (it synchronises)."""
+    live = []
+    for ref in _all_buffers:
+        buf = ref()
+        if buf is None:
+            continue
+        live.append(ref)
+        if not buf.canary_intact():
+            raise RuntimeError(f"symmetric buffer '{buf.tag}' ({buf.nbytes} bytes, group rank {buf.rank}): guard bytes "
+                               f"behind the buffer were overwritten - a kernel wrote out of bounds")
+    _all_buffers[:] = live
+    return len(live)

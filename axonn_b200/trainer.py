@@ -20,6 +20,7 @@ import torch.distributed as dist
 from . import axonn as ax
 from . import ops
 from .ops import _lib
+from .parallel import symm
 from .intra_layer import (clip_grad_norm_, no_grad_sync, optimize_communication,
                           overlap_all_gathers_for_checkpointed_forward, sync_gradients)
 
@@ -105,6 +106,8 @@ class Trainer:
         loss = self.train_step_device(self._to_device(inputs), self._to_device(targets))
         value = float(loss.item())
         _lib.check_status()   # a bounded device-side wait that gave up surfaces here, after the sync above
+        if symm.debug_bounds_enabled():
+            symm.verify_canaries()
         return value
 
 

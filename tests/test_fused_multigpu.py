@@ -41,6 +41,9 @@ def _gemm_ar_case(rank, world):
             other = out.clone()
             dist.broadcast(other, src=0)
             assert torch.equal(other, out), "ranks disagree bitwise"
+    # guard bytes behind every symmetric buffer are untouched: nothing wrote past an inbox or a flag array
+    from axonn_b200.parallel import symm
+    assert symm.verify_canaries() >= 1
     # fused bias + GELU after the reduction
     M, N, K = 768, 512, 256
     a = torch.randn(M, K, device=dev).bfloat16()
