@@ -438,7 +438,7 @@ colsum_partial_kernel(const T* __restrict__ x, float* __restrict__ part, int row
 // dx = dy * gelu'(x) together with the column sums of dx (the bias gradient of the layer that produced x):
 // same thread layout as colsum_partial_kernel, one extra load and one store per element.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 6)
 gelu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx,
                        float* __restrict__ part, int rows, int N) {
   __shared__ float red[8][32][9];
@@ -448,26 +448,16 @@ gelu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __r
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   if (c < N) {
+    // one row per iteration and few registers: the arithmetic of one warp hides behind the loads of the many
+    // other resident warps (48 per SM) instead of behind a deep per-thread batch
     const int stride = gridDim.y * 8;
-    for (int r = blockIdx.y * 8 + w; r < rows; r += 4 * stride) {
-      float fx[4][8], fd[4][8];
+    for (int r = blockIdx.y * 8 + w; r < rows; r += stride) {
+      float fx[8], fd[8], o[8];
+      Vec8<T>::load(x + static_cast<size_t>(r) * N + c, fx);
+      Vec8<T>::load(dy + static_cast<size_t>(r) * N + c, fd);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int rr = r + u * stride;
-        if (rr < rows) {
-          Vec8<T>::load(x + static_cast<size_t>(rr) * N + c, fx[u]);
-          Vec8<T>::load(dy + static_cast<size_t>(rr) * N + c, fd[u]);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int rr = r + u * stride;
-        if (rr >= rows) continue;
-        float o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { o[i] = fd[u][i] * gelu_tanh_grad(fx[u][i]); acc[i] += o[i]; }
-        Vec8<T>::store(dx + static_cast<size_t>(rr) * N + c, o);
-      }
+      for (int i = 0; i < 8; ++i) { o[i] = fd[i] * gelu_tanh_grad(fx[i]); acc[i] += o[i]; }
+      Vec8<T>::store(dx + static_cast<size_t>(r) * N + c, o);
     }
   }
 #pragma unroll
@@ -585,7 +575,7 @@ extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, co
 
 extern "C" int axb_colsum_splits(int device, int rows, int N) {
   const int col_blocks = (N / 8 + 31) / 32;
-  int splits = (4 * axb::sm_count(device) + col_blocks - 1) / col_blocks;
+  int splits = (8 * axb::sm_count(device) + col_blocks - 1) / col_blocks;
   const int max_splits = (rows + 31) / 32;       // at least four rows per thread
   if (splits > max_splits) splits = max_splits;
   return splits < 1 ? 1 : splits;

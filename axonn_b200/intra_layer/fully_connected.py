@@ -158,9 +158,10 @@ class AsyncLinear(Function):
         go2 = grad_output.reshape(-1, grad_output.shape[-1])
         bias_sum = None
         if pre_act is not None:
-            # (ops.gelu_backward_colsum does both in one pass but measured slower than the two kernels:
-            # 0.286 ms against 0.136 + 0.05 ms on [16384, 8192])
-            go2 = ops.gelu_backward(go2, pre_act)
+            if ctx.has_bias and ctx.needs_input_grad[2]:
+                go2, bias_sum = ops.gelu_backward_colsum(go2, pre_act)   # bias gradient in the same pass
+            else:
+                go2 = ops.gelu_backward(go2, pre_act)
         x2 = input_.reshape(-1, input_.shape[-1])
         overlap_rs = oc.OVERLAP_REDUCE_SCATTER
         overlap_ar = oc.OVERLAP_ALL_REDUCE
