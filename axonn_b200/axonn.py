@@ -94,7 +94,8 @@ def create_dataloader(
     """Per-rank loader: data is split over ``G_data x G_intra_d`` replicas
     (depth ranks see different samples, like FSDP); the batch size is the
     per-replica batch when pipelining and the microbatch otherwise
-    (reference ``axonn/axonn.py:70-121``)."""
+    (reference ``axonn/axonn.py:70-121``).  The ``DistributedSampler`` shuffles
+    per epoch by default, as upstream; pass ``shuffle=False`` for a fixed order."""
     assert is_initialized, "call init() first"
     replicas = config.G_data * config.G_intra_d
     if global_batch_size % (config.G_data * micro_batch_size) != 0:
@@ -107,7 +108,7 @@ def create_dataloader(
         dataset,
         num_replicas=replicas,
         rank=config.G_intra_d * config.data_parallel_rank + config.intra_layer_depth_parallel_rank,
-        shuffle=kwargs.pop("shuffle", False),
+        shuffle=kwargs.pop("shuffle", True),   # the sampler's own default, as in the reference
     )
     bs = config.batch_size_per_gpu if config.G_inter > 1 else micro_batch_size
     kwargs.setdefault("pin_memory", torch.cuda.is_available())

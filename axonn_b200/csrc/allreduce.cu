@@ -43,7 +43,7 @@ __device__ __forceinline__ bool comm_wait_all(const CommCtx& c, int* sh_ok) {
       while (static_cast<int>(c_ld_acquire(c.wait_local + j) - c.epoch) < 0) {
         if (globaltimer_ns() - t0 > c.timeout_ns) {
           ok = 0;
-          *reinterpret_cast<volatile unsigned int*>(c.status) = 0x301u;
+          report_status(c.status, 0x301u);   // the first cause stays in the status word
           break;
         }
       }
@@ -53,15 +53,22 @@ __device__ __forceinline__ bool comm_wait_all(const CommCtx& c, int* sh_ok) {
   __syncthreads();
   return *sh_ok != 0;
 }
-__device__ __forceinline__ void comm_signal_when_last(const CommCtx& c) {
+// Every CTA passes here exactly once per launch, also one whose wait ran out (`ok` false): the CTA counter
+// returns to zero for the next call either way, and the completion flag is only published by a launch
+// all of whose CTAs succeeded (peers of a failed launch run into their own deadline instead of reading
+// an incomplete result).  c.counter + 1 collects the number of failed CTAs of the launch.
+__device__ __forceinline__ void comm_signal_when_last(const CommCtx& c, bool ok = true) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (!ok) atomicAdd(c.counter + 1, 1u);
     __threadfence_system();
     if (atomicAdd(c.counter, 1u) == gridDim.x - 1) {
+      const unsigned int failed = atomicExch(c.counter + 1, 0u);
       *c.counter = 0;
       __threadfence_system();
-      for (int j = 0; j < c.n; ++j)
-        if (j != c.rank) c_st_release(c.signal_peer[j] + c.rank, c.epoch);
+      if (failed == 0)
+        for (int j = 0; j < c.n; ++j)
+          if (j != c.rank) c_st_release(c.signal_peer[j] + c.rank, c.epoch);
     }
   }
 }
@@ -84,7 +91,10 @@ __global__ void __launch_bounds__(256)
 bucket_copy_kernel(const long long* __restrict__ table, int ntensors, long long total_chunks, T* bucket, CommCtx c,
                    int wait_first, int signal_last) {
   __shared__ int sh_ok;
-  if (wait_first && c.n > 1 && !comm_wait_all(c, &sh_ok)) return;
+  if (wait_first && c.n > 1 && !comm_wait_all(c, &sh_ok)) {
+    if (signal_last) comm_signal_when_last(c, false);
+    return;
+  }
   for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
     const int t = pk_find(table, ntensors, chunk);
     const long long* row = table + (size_t)t * 5;
@@ -131,7 +141,7 @@ template <typename T>
 __global__ void __launch_bounds__(512)
 allreduce_twoshot_kernel(long long nvec, float scale, CommCtx c) {
   __shared__ int sh_ok;
-  if (!comm_wait_all(c, &sh_ok)) return;
+  if (!comm_wait_all(c, &sh_ok)) { comm_signal_when_last(c, false); return; }
   const long long per = nvec / c.n;
   const long long lo = per * c.rank;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
@@ -174,7 +184,8 @@ extern "C" int axb_bucket_copy(const long long* table, int ntensors, long long t
                                int direction, const AxbCommCtx* ctx, int device, void* stream) {
   CommCtx c;
   if (fill_comm(c, ctx, device)) return -1;
-  const int grid = (int)(total_chunks < 148 * 8 ? (total_chunks < 1 ? 1 : total_chunks) : 148 * 8);
+  const int cap = sm_count(device) * 8;
+  const int grid = (int)(total_chunks < cap ? (total_chunks < 1 ? 1 : total_chunks) : cap);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == 0) {
     if (direction == 0) bucket_copy_kernel<float, true><<<grid, 256, 0, s>>>(table, ntensors, total_chunks, (float*)bucket, c, 0, 1);
@@ -196,7 +207,8 @@ extern "C" int axb_allreduce_twoshot(long long nbytes, int dtype, float scale, c
   const long long nvec = nbytes / 16;
   const long long per = nvec / c.n;
   long long blocks = (per + 511) / 512;
-  const int grid = (int)(blocks < 1 ? 1 : (blocks > 148 * 4 ? 148 * 4 : blocks));
+  const int cap = sm_count(device) * 4;
+  const int grid = (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
   if (dtype == 0) allreduce_twoshot_kernel<float><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, c);
   else allreduce_twoshot_kernel<__nv_bfloat16><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, c);
   AXB_CUDA(cudaGetLastError());

@@ -44,7 +44,9 @@ volatile unsigned int* device_status_word(int device, unsigned int** dev_ptr) {
   return g_status_host[device];
 }
 
-static unsigned long long g_wait_timeout_ns = 2000000000ull;
+// Two minutes: the order of a collective library's watchdog, so that ordinary skew between ranks (a slow
+// data loader, a checkpoint write, a first-call compile) never expires a wait.  Tests shorten it.
+static unsigned long long g_wait_timeout_ns = 120000000000ull;
 unsigned long long wait_timeout_ns() { return g_wait_timeout_ns; }
 
 }  // namespace axb

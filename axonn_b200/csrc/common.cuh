@@ -19,8 +19,19 @@ int check_cuda(cudaError_t e, const char* what);
 // Per-device word that kernels set when a bounded wait expires (0 = clean).
 // Lives in mapped pinned host memory so the host can read it without a sync.
 volatile unsigned int* device_status_word(int device, unsigned int** dev_ptr);
-// Deadline of every device-side wait in nanoseconds (default 2 s; axb_set_wait_timeout_ms changes it).
+// Deadline of every device-side wait in nanoseconds (default 120 s; axb_set_wait_timeout_ms changes it).
 unsigned long long wait_timeout_ns();
+// Number of SMs of `device` (cached); sm_count_current() asks for the calling thread's current device.
+int sm_count(int device);
+int sm_count_current();
+
+// Ablation switches of the kernels (timing experiments) exist only in builds with -DAXB_ABLATION; in the
+// shipped library AXB_DBG is the constant 0, so the branches and the probe words vanish at compile time.
+#ifdef AXB_ABLATION
+#define AXB_DBG(p, bit) (((p).debug & (bit)) != 0)
+#else
+#define AXB_DBG(p, bit) (false)
+#endif
 
 #define AXB_CUDA(call)                                   \
   do {                                                   \

@@ -103,7 +103,8 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
 
 static inline int ew_grid(size_t work, int threads) {
   size_t g = (work + threads - 1) / threads;
-  return (int)(g > 148 * 16 ? 148 * 16 : (g == 0 ? 1 : g));
+  const size_t cap = static_cast<size_t>(sm_count_current()) * 16;
+  return (int)(g > cap ? cap : (g == 0 ? 1 : g));
 }
 
 }  // namespace axb

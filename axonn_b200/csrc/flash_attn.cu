@@ -392,7 +392,7 @@ struct FaBwdParams {
   float scale, scale_log2;
   unsigned int* status;
   unsigned long long timeout_ns;
-  int debug;   // timing experiments only (AXB_FA_DEBUG): 1 no dQ reductions, 2 no exponentials, 4 phase timers, 8 release Q/dO after the dQ MMAs
+  int debug;   // ablation builds only (-DAXB_ABLATION, then read once from AXB_FA_DEBUG; otherwise 0 and every branch on it is compiled out): 1 no dQ reductions, 2 no exponentials, 4 phase timers, 8 release Q/dO after the dQ MMAs
 };
 
 template <int HD>
@@ -519,7 +519,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       const uint32_t k_addr = smem_u32(smem + S_::K_OFF), v_addr = smem_u32(smem + S_::V_OFF);
       const uint32_t q_addr = smem_u32(smem + S_::Q_OFF), do_addr = smem_u32(smem + S_::DO_OFF);
       const uint32_t p_addr = smem_u32(smem + S_::P_OFF), ds_addr = smem_u32(smem + S_::DS_OFF);
-      const bool probe = (p.debug & 4) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+      const bool probe = AXB_DBG(p, 4) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
       uint64_t w_qdo = 0, w_sfree = 0, w_pds = 0, t_mark = probe ? globaltimer_ns() : 0;
       for (int it = 0; it < n_iter && ok; ++it) {
         const uint32_t ph = it & 1;
@@ -555,14 +555,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
           umma_f16(tm_dk, umma_smem_desc(ds_addr + kk * 2048, 16384, 1024), umma_smem_desc(q_addr + kk * 2048, 16384, 1024),
                    idesc_t, (it | kk) != 0);
         }
-        if (!(p.debug & 8)) umma_commit(qdo_empty);   // Q and dO are free once dV / dK are done: the next loads overlap dQ
+        if (!AXB_DBG(p, 8)) umma_commit(qdo_empty);   // Q and dO are free once dV / dK are done: the next loads overlap dQ
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // reduction over the 128 KV rows
           umma_f16(tm_s, umma_smem_desc(ds_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
                    umma_smem_desc(k_addr + kk * 2048, 16384, 1024), idesc_q, kk != 0);
         }
         umma_commit(dq_full);
-        if (p.debug & 8) umma_commit(qdo_empty);
+        if AXB_DBG(p, 8) umma_commit(qdo_empty);
       }
       if (probe) {
         volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(p.status);
@@ -581,7 +581,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
     uint8_t* p_row = smem + S_::P_OFF + (r >> 3) * 1024 + (r & 7) * 128;
     uint8_t* ds_row = smem + S_::DS_OFF + (r >> 3) * 1024 + (r & 7) * 128;
     bool ok = true;
-    const bool probe = (p.debug & 4) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
+    const bool probe = AXB_DBG(p, 4) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
     uint64_t w_sdp = 0, t_a = 0, w_dq = 0, t_b = 0, t_b1 = 0, t_b2 = 0, t_mark = 0;
     for (int it = 0; it < n_iter; ++it) {
       const uint32_t ph = it & 1;
@@ -604,8 +604,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
         uint32_t pp[16], dd[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
-          float p0 = (p.debug & 2) ? __uint_as_float(sv[2 * k]) : exp2f(__uint_as_float(sv[2 * k]) * p.scale_log2 - lse2);
-          float p1 = (p.debug & 2) ? __uint_as_float(sv[2 * k + 1]) : exp2f(__uint_as_float(sv[2 * k + 1]) * p.scale_log2 - lse2);
+          float p0 = AXB_DBG(p, 2) ? __uint_as_float(sv[2 * k]) : exp2f(__uint_as_float(sv[2 * k]) * p.scale_log2 - lse2);
+          float p1 = AXB_DBG(p, 2) ? __uint_as_float(sv[2 * k + 1]) : exp2f(__uint_as_float(sv[2 * k + 1]) * p.scale_log2 - lse2);
           if (diag) {   // key position (column) beyond the query position (row) is masked
             if (c * 32 + 2 * k > r) p0 = 0.f;
             if (c * 32 + 2 * k + 1 > r) p1 = 0.f;
@@ -663,7 +663,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__
       if (probe) { const uint64_t now = globaltimer_ns(); t_b1 += now - t_mark; }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && !(p.debug & 1)) {
+      if (lane == 0 && !AXB_DBG(p, 1)) {
         const int y = b * p.S + i * 128 + q4 * 32;
 #pragma unroll
         for (int cc = 0; cc < NBOX; ++cc) {
@@ -750,7 +750,8 @@ extern "C" int axb_flash_attn_bwd(const void* qkv, const void* out, const void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int H = G * qpk;
   const long long rows = static_cast<long long>(B) * S * H;
-  const int blocks = static_cast<int>(rows / 8 < 148 * 16 ? (rows / 8 < 1 ? 1 : rows / 8) : 148 * 16);
+  const long long cap = static_cast<long long>(sm_count(device)) * 16;
+  const int blocks = static_cast<int>(rows / 8 < cap ? (rows / 8 < 1 ? 1 : rows / 8) : cap);
   fa_delta_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out),
                                          delta, B, S, H, D);
   AXB_CUDA(cudaGetLastError());
@@ -764,7 +765,10 @@ extern "C" int axb_flash_attn_bwd(const void* qkv, const void* out, const void* 
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
   p.status = st; p.timeout_ns = wait_timeout_ns();
-  { const char* dbg = getenv("AXB_FA_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
+  p.debug = 0;
+#ifdef AXB_ABLATION
+  { static int dbg = -1; if (dbg < 0) { const char* e = getenv("AXB_FA_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
+#endif
   if (D == 128) return fa_bwd_launch<128>(tq, td, tdq, p, device, s);
   return fa_bwd_launch<64>(tq, td, tdq, p, device, s);
 }

@@ -63,7 +63,7 @@ struct GemmParams {
   int tn_offset;  // rotation of the N-tile order (all-gather mode: tiles of the local shard first)
   int kb_offset;  // rotation of the K-block order (all-gather mode, B rows = K: local shard first)
   int gemm_ctas;  // number of CTAs computing tiles; the remaining CTAs of the grid reduce over peer memory
-  int debug;      // timing experiments only (AXB_AR_DEBUG): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores, 128 register-path reducer instead of the shared-memory ring
+  int debug;      // ablation builds only (-DAXB_ABLATION, then read once from AXB_AR_DEBUG; otherwise 0 and every branch on it is compiled out): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores, 128 register-path reducer instead of the shared-memory ring
 };
 
 template <int BN>
@@ -297,7 +297,7 @@ __device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, i
         report_status(p.status, 0x121u);
         return;
       }
-      if (!(p.debug & 4)) __threadfence_system();   // acquire side of the flags, once per tile
+      if (!AXB_DBG(p, 4)) __threadfence_system();   // acquire side of the flags, once per tile
       if (ring != nullptr) {
         // two-rank ring mode: bring the tile's inbox slots (own partial and the peer's, 16 KB each per warp-row)
         // into shared memory with bulk copies, one ring group per warp-row, as soon as the group is free
@@ -348,7 +348,7 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
   const int tid = threadIdx.x - 192;          // 0 .. REDUCER_THREADS-1
   bool ok = true;
   int t = -1;
-  const bool probe = (p.debug & 64) && blockIdx.x == 0 && tid == 0;
+  const bool probe = AXB_DBG(p, 64) && blockIdx.x == 0 && tid == 0;
   uint64_t ns_wait = 0, ns_work = 0, ns_mark = probe ? globaltimer_ns() : 0;
   for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
     ++t;
@@ -373,7 +373,7 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
     asm volatile("bar.sync 3, %0;" ::"n"(REDUCER_THREADS) : "memory");
     if (*abort_flag) { ok = false; break; }
     if (probe) { const uint64_t now = globaltimer_ns(); ns_wait += now - ns_mark; ns_mark = now; }
-    if (p.debug & 8) continue;
+    if AXB_DBG(p, 8) continue;
     const uint4* inbox = reinterpret_cast<const uint4*>(p.ar.inbox_local) + static_cast<size_t>(tile) * TVEC;
     // A unit is one output row segment of 32 columns (4 vectors of one lane of one chunk): the thread that
     // reduces it writes 64 contiguous bytes of C, so every 32-byte sector of C is written in one piece.
@@ -466,7 +466,7 @@ __device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int
       const int g = consumed & 1;
       if (!mbar_wait(&ring_full[g], (consumed >> 1) & 1, abort_flag, p.timeout_ns)) { ok = false; break; }
       ++consumed;
-      if (!(p.debug & 8)) {
+      if (!AXB_DBG(p, 8)) {
         const size_t row = static_cast<size_t>(tm) * BM + q * 32 + ln;
         const uint4* s0 = reinterpret_cast<const uint4*>(ring + (g * 2) * SLOT);
         const uint4* s1 = reinterpret_cast<const uint4*>(ring + (g * 2 + 1) * SLOT);
@@ -520,7 +520,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint64_t timeout = p.timeout_ns;
   const int gemm_ctas = p.gemm_ctas;   // == gridDim.x: every CTA computes tiles (and reduces them in comm mode)
   // two ranks, 128x256 tiles: the reducer stages inbox slots in shared memory behind a 3-stage operand ring
-  const bool ring_mode = BN == 256 && p.ar.n == 2 && !(p.debug & 128);
+  const bool ring_mode = BN == 256 && p.ar.n == 2 && !AXB_DBG(p, 128);
   const int nstages = ring_mode ? S::RING_STAGES : S::STAGES;
 
   if (threadIdx.x == 0) {
@@ -680,7 +680,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         if (!good) break;
-        if (!(p.debug & 1)) __threadfence_system();
+        if (!AXB_DBG(p, 1)) __threadfence_system();
         for (int qq = 0; qq < 4; ++qq) {
           const int own = (p.ar.mode == 1) ? (tm * BM + qq * 32) / p.ar.rows_per_shard : -1;
           for (int j = 0; j < p.ar.n; ++j) {
@@ -813,10 +813,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         for (int j = 0; j < p.ar.n; ++j) {
           if (p.ar.mode == 1 && j != owner) continue;
-          if ((p.debug & 2) && j != p.ar.rank) continue;
-          if (p.debug & 16) continue;
+          if (AXB_DBG(p, 2) && j != p.ar.rank) continue;
+          if AXB_DBG(p, 16) continue;
           uint4* dst = reinterpret_cast<uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + slot_vec + (c * 4) * 32;
-          if ((p.debug & 32) && j == p.ar.rank) {
+          if (AXB_DBG(p, 32) && j == p.ar.rank) {
             uint64_t pol;
             asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
 #pragma unroll
@@ -1116,6 +1116,12 @@ int sm_count(int device) {
   return cached[device];
 }
 
+int sm_count_current() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  return sm_count(dev);
+}
+
 template <int BN, int A_MN, int B_MN>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int device, cudaStream_t stream) {
   using S = GemmSmem<BN>;
@@ -1211,7 +1217,10 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
     p.ar.n = 1;
   }
   p.tn_offset = 0; p.kb_offset = 0;
-  { const char* dbg = getenv("AXB_AR_DEBUG"); p.debug = dbg ? atoi(dbg) : 0; }
+  p.debug = 0;
+#ifdef AXB_ABLATION
+  { static int dbg = -1; if (dbg < 0) { const char* e = getenv("AXB_AR_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
+#endif
   if (ag && ag->n > 1) {
     p.ag = *ag;
     {

@@ -111,7 +111,8 @@ using namespace axb;
 extern "C" int axb_ce_fwd(const void* logits, const long long* targets, float* stats, int rows, int V, int vocab_start,
                           void* stream) {
   if (V % 8) { set_error("cross entropy: vocab shard %d must be a multiple of 8", V); return -1; }
-  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  const int cap = sm_count_current() * 8;
+  const int grid = rows < cap ? rows : cap;
   ce_fwd_kernel<<<grid, CE_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, targets, stats, rows, V,
                                                              vocab_start);
   AXB_CUDA(cudaGetLastError());
@@ -120,7 +121,8 @@ extern "C" int axb_ce_fwd(const void* logits, const long long* targets, float* s
 extern "C" int axb_ce_bwd(void* logits, const long long* targets, const float* lse, const float* scale, int rows, int V,
                           int vocab_start, long long ignore_index, void* stream) {
   if (V % 8) { set_error("cross entropy: vocab shard %d must be a multiple of 8", V); return -1; }
-  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  const int cap = sm_count_current() * 8;
+  const int grid = rows < cap ? rows : cap;
   ce_bwd_kernel<<<grid, CE_THREADS, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, targets, lse, scale, rows, V,
                                                              vocab_start, ignore_index);
   AXB_CUDA(cudaGetLastError());

@@ -49,7 +49,7 @@ __device__ __forceinline__ bool moe_wait_all(const MoeCtx& c, int* sh_ok) {
     for (int j = 0; j < c.n && ok; ++j) {
       if (j == c.rank) continue;
       while (static_cast<int>(moe_ld_acquire(c.wait_local + j) - c.wait_value) < 0) {
-        if (globaltimer_ns() - t0 > c.timeout_ns) { ok = 0; *reinterpret_cast<volatile unsigned int*>(c.status) = 0x201u; break; }
+        if (globaltimer_ns() - t0 > c.timeout_ns) { ok = 0; report_status(c.status, 0x201u); break; }
       }
     }
     *sh_ok = ok;
@@ -58,15 +58,21 @@ __device__ __forceinline__ bool moe_wait_all(const MoeCtx& c, int* sh_ok) {
   return *sh_ok != 0;
 }
 
-__device__ __forceinline__ void moe_signal_when_last(const MoeCtx& c) {
+// Every CTA passes here once per launch, also after a wait that ran out (`ok` false): the CTA counter is
+// back at zero for the next call either way; the completion flag is published only when no CTA failed
+// (c.counter + 1 counts the failed ones).
+__device__ __forceinline__ void moe_signal_when_last(const MoeCtx& c, bool ok = true) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (!ok) atomicAdd(c.counter + 1, 1u);
     __threadfence_system();
     if (atomicAdd(c.counter, 1u) == gridDim.x - 1) {
+      const unsigned int failed = atomicExch(c.counter + 1, 0u);
       *c.counter = 0;
       __threadfence_system();
-      for (int j = 0; j < c.n; ++j)
-        if (j != c.rank) moe_st_release(c.signal_peer[j] + c.rank, c.epoch);
+      if (failed == 0)
+        for (int j = 0; j < c.n; ++j)
+          if (j != c.rank) moe_st_release(c.signal_peer[j] + c.rank, c.epoch);
     }
   }
 }
@@ -78,7 +84,7 @@ moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, int x_by_token, con
                         const unsigned char* __restrict__ keep, const long long* __restrict__ counts, int T, int k,
                         int E, int C, int H, MoeCtx c) {
   __shared__ int sh_ok;
-  if (!moe_wait_all(c, &sh_ok)) return;
+  if (!moe_wait_all(c, &sh_ok)) { moe_signal_when_last(c, false); return; }
   const int vec_per_row = H / 8;
   const long long n_assign = static_cast<long long>(T) * k;
   const long long n_slots = static_cast<long long>(E) * C;
@@ -114,7 +120,7 @@ __global__ void __launch_bounds__(256)
 moe_gather_rows_kernel(__nv_bfloat16* __restrict__ out, const long long* __restrict__ dest,
                        const unsigned char* __restrict__ keep, int T, int k, int C, int H, MoeCtx c) {
   __shared__ int sh_ok;
-  if (!moe_wait_all(c, &sh_ok)) return;
+  if (!moe_wait_all(c, &sh_ok)) { moe_signal_when_last(c, false); return; }
   const int vec_per_row = H / 8;
   const long long n_assign = static_cast<long long>(T) * k;
   for (long long item = blockIdx.x; item < n_assign; item += gridDim.x) {
@@ -171,7 +177,8 @@ extern "C" int axb_moe_dispatch(const void* x, int x_by_token, const long long* 
   MoeCtx c;
   if (fill_ctx(c, ctx, device)) return -1;
   const long long items = static_cast<long long>(T) * k + static_cast<long long>(E) * C;
-  const int grid = static_cast<int>(items < 148 * 8 ? (items < 1 ? 1 : items) : 148 * 8);
+  const long long cap = static_cast<long long>(sm_count(device)) * 8;
+  const int grid = static_cast<int>(items < cap ? (items < 1 ? 1 : items) : cap);
   moe_scatter_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, x_by_token, dest, keep,
                                                                  counts, T, k, E, C, H, c);
   AXB_CUDA(cudaGetLastError());
@@ -184,7 +191,8 @@ extern "C" int axb_moe_gather(void* out, const long long* dest, const unsigned c
   MoeCtx c;
   if (fill_ctx(c, ctx, device)) return -1;
   const long long items = static_cast<long long>(T) * k;
-  const int grid = static_cast<int>(items < 148 * 8 ? (items < 1 ? 1 : items) : 148 * 8);
+  const long long cap = static_cast<long long>(sm_count(device)) * 8;
+  const int grid = static_cast<int>(items < cap ? (items < 1 ? 1 : items) : cap);
   moe_gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)out, dest, keep, T, k, C, H, c);
   AXB_CUDA(cudaGetLastError());
   return 0;

@@ -106,11 +106,14 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2;
   const float* grad_scale;       // device scalar multiplied into every gradient (may be null)
   const float* found_inf;        // device scalar; non-zero => skip the whole step (may be null)
+  const unsigned int* status;    // device status word; non-zero (a bounded wait of an earlier kernel expired:
+                                 // gradients may be incomplete) => skip the whole step (may be null)
 };
 
 __global__ void __launch_bounds__(MT_THREADS)
 multi_adamw_kernel(const long long* __restrict__ table, int n, long long total_chunks, AdamArgs a) {
   if (a.found_inf && *a.found_inf != 0.f) return;
+  if (a.status && *reinterpret_cast<const volatile unsigned int*>(a.status) != 0u) return;
   const float gs = a.grad_scale ? *a.grad_scale : 1.f;
   const float decay = 1.f - a.lr * a.weight_decay;
   const float step = a.lr / a.bias_c1;
@@ -201,7 +204,10 @@ multi_adamw_kernel(const long long* __restrict__ table, int n, long long total_c
 }
 
 int sm_count(int device);
-static inline int mt_grid(long long chunks) { return (int)(chunks < 148 * 8 ? (chunks < 1 ? 1 : chunks) : 148 * 8); }
+static inline int mt_grid(long long chunks) {
+  const long long cap = static_cast<long long>(sm_count_current()) * 8;
+  return (int)(chunks < cap ? (chunks < 1 ? 1 : chunks) : cap);
+}
 
 }  // namespace axb
 
@@ -220,7 +226,12 @@ extern "C" int axb_multi_scale(const long long* table, int n, long long total_ch
 extern "C" int axb_multi_adamw(const long long* table, int n, long long total_chunks, float lr, float beta1, float beta2,
                                float eps, float weight_decay, float bias_c1, float bias_c2, const float* grad_scale,
                                const float* found_inf, void* stream) {
-  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale, found_inf};
+  // The step is also skipped when a kernel that ran before it on this device reported an expired wait:
+  // its output (activations or gradients) is incomplete, and the host learns of it at its next check_status.
+  int dev = 0;
+  unsigned int* status = nullptr;
+  if (cudaGetDevice(&dev) == cudaSuccess) device_status_word(dev, &status);
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale, found_inf, status};
   multi_adamw_kernel<<<mt_grid(total_chunks), MT_THREADS, 0, (cudaStream_t)stream>>>(table, n, total_chunks, a);
   AXB_CUDA(cudaGetLastError());
   return 0;

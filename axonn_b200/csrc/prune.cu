@@ -10,6 +10,8 @@
 // same rule as thresholding with the k-th value of a sort.
 //
 // Scratch: 32768 + 65536 + 8 32-bit words, supplied by the caller.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace axb {
@@ -18,9 +20,11 @@ constexpr int PR_BINS1 = 32768;
 constexpr int PR_BINS2 = 65536;
 constexpr int PR_THREADS = 1024;
 constexpr int PR_WORK_WORDS = PR_BINS1 + PR_BINS2 + 8;
+// dtype codes are the library-wide ones of axonn_b200.h: 0 bf16, 1 fp16, 2 fp32
+constexpr int PR_F32 = 2;
 
 __device__ __forceinline__ uint32_t mag_bits(const void* g, long long i, int dtype) {
-  if (dtype == 0) return reinterpret_cast<const uint32_t*>(g)[i] & 0x7FFFFFFFu;
+  if (dtype == PR_F32) return reinterpret_cast<const uint32_t*>(g)[i] & 0x7FFFFFFFu;
   return (static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(g)[i]) & 0x7FFFu) << 16;
 }
 
@@ -30,7 +34,7 @@ prune_hist1_kernel(const void* __restrict__ g, long long n, int dtype, unsigned 
   extern __shared__ unsigned int sh[];
   for (int i = threadIdx.x; i < PR_BINS1; i += blockDim.x) sh[i] = 0;
   __syncthreads();
-  if (dtype != 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+  if (dtype != PR_F32 && (reinterpret_cast<uintptr_t>(g) & 15) == 0) {
     const long long nv = n / 8;
     const uint4* q = reinterpret_cast<const uint4*>(g);
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
@@ -100,8 +104,8 @@ __global__ void prune_hist2_kernel(const void* __restrict__ g, long long n, cons
 // thr = 31-bit magnitude threshold: keep |g| bits >= thr
 __global__ void prune_mask_kernel(void* __restrict__ g, long long n, int dtype, const long long* __restrict__ meta1,
                                   const long long* __restrict__ meta2) {
-  const uint32_t thr = ((uint32_t)meta1[0] << 16) | (dtype == 0 ? (uint32_t)meta2[0] : 0u);
-  if (dtype != 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+  const uint32_t thr = ((uint32_t)meta1[0] << 16) | (dtype == PR_F32 ? (uint32_t)meta2[0] : 0u);
+  if (dtype != PR_F32 && (reinterpret_cast<uintptr_t>(g) & 15) == 0) {
     const long long nv = n / 8;
     uint4* q = reinterpret_cast<uint4*>(g);
     const uint32_t t16 = thr >> 16;
@@ -120,7 +124,7 @@ __global__ void prune_mask_kernel(void* __restrict__ g, long long n, int dtype, 
   } else {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
       if (mag_bits(g, i, dtype) < thr) {
-        if (dtype == 0) reinterpret_cast<uint32_t*>(g)[i] = 0; else reinterpret_cast<uint16_t*>(g)[i] = 0;
+        if (dtype == PR_F32) reinterpret_cast<uint32_t*>(g)[i] = 0; else reinterpret_cast<uint16_t*>(g)[i] = 0;
       }
     }
   }
@@ -131,7 +135,7 @@ int sm_count(int device);
 // Shared by the allocating and the static-scratch entry points.
 int prune_topk_launch(void* g, long long n, int dtype, long long k, unsigned int* work, int device, cudaStream_t s) {
   if (n <= 0) return 0;
-  if (k <= 0) { AXB_CUDA(cudaMemsetAsync(g, 0, (size_t)n * (dtype == 0 ? 4 : 2), s)); return 0; }
+  if (k <= 0) { AXB_CUDA(cudaMemsetAsync(g, 0, (size_t)n * (dtype == PR_F32 ? 4 : 2), s)); return 0; }
   if (k >= n) return 0;
   unsigned int* hist1 = work;
   unsigned int* hist2 = work + PR_BINS1;
@@ -147,7 +151,7 @@ int prune_topk_launch(void* g, long long n, int dtype, long long k, unsigned int
   AXB_CUDA(cudaGetLastError());
   prune_select_kernel<PR_BINS1><<<1, PR_THREADS, 0, s>>>(hist1, nullptr, k, meta);
   AXB_CUDA(cudaGetLastError());
-  if (dtype == 0) {
+  if (dtype == PR_F32) {
     prune_hist2_kernel<<<sms * 4, 512, 0, s>>>(g, n, meta, hist2);
     AXB_CUDA(cudaGetLastError());
     prune_select_kernel<PR_BINS2><<<1, PR_THREADS, 0, s>>>(hist2, meta + 1, 0, meta + 2);
@@ -162,10 +166,11 @@ int prune_topk_launch(void* g, long long n, int dtype, long long k, unsigned int
 
 extern "C" int axb_prune_workspace_words(void) { return axb::PR_WORK_WORDS; }
 
-// g: gradient tensor (dtype 0 fp32, 1 bf16, 2 fp16), modified in place; keeps the k largest |g|.
+// g: gradient tensor (dtype 0 bf16, 1 fp16, 2 fp32: the library-wide codes), modified in place; keeps the k largest |g|.
 // work: device scratch of axb_prune_workspace_words() 32-bit words (8-byte aligned).
 extern "C" int axb_prune_topk(void* g, long long n, int dtype, long long k, void* work, int device, void* stream) {
   if (!work) { axb::set_error("prune: workspace is null"); return -1; }
+  if (dtype < 0 || dtype > 2) { axb::set_error("prune: bad dtype %d (0 bf16, 1 fp16, 2 fp32)", dtype); return -1; }
   return axb::prune_topk_launch(g, n, dtype, k, static_cast<unsigned int*>(work), device, (cudaStream_t)stream);
 }
 
@@ -190,15 +195,16 @@ constexpr long long PR_STATIC_MAX_NUMEL = 2147483647LL;
 // handle for the runtime, not an address a kernel can use, so the address is looked up once per
 // device with cudaGetSymbolAddress while that device is current.
 static unsigned int* g_prune_static_ptr[64] = {nullptr};
+static std::mutex g_prune_static_mu;   // first-use lookup may race between host threads
 }  // namespace axb
 
-// Keep the k largest-magnitude entries of g (dtype 0 fp32, 1 bf16, 2 fp16), zero the rest, in place,
+// Keep the k largest-magnitude entries of g (dtype 0 bf16, 1 fp16, 2 fp32), zero the rest, in place,
 // like axb_prune_topk, but with no workspace argument and without allocating anything: no cudaMalloc,
 // no cudaFree, no allocating library call.
 //
-// * The first call on a device looks up the scratch array's device address (the device must be the
-//   current one, as it is for the launch itself).  Make that first call before starting any stream
-//   capture on the device.
+// * `device` must be the calling thread's current device on every call (checked; the launches and the
+//   clearing of the scratch go to the current device).  The first call on a device also looks up the
+//   scratch array's device address: make that first call before starting any stream capture on the device.
 // * n must not exceed 2,147,483,647 elements; larger tensors are rejected with an error.
 // * All calls on a device share one scratch array.  It is cleared at the start of each call, so
 //   nothing needs to be reset between calls, but two calls whose kernels may overlap on the GPU
@@ -211,13 +217,14 @@ extern "C" int axb_prune_topk_static(void* g, long long n, int dtype, long long 
   }
   if (device < 0 || device >= 64) { set_error("axb_prune_topk_static: bad device index %d", device); return -1; }
   if (dtype < 0 || dtype > 2) { set_error("axb_prune_topk_static: bad dtype %d", dtype); return -1; }
+  int current = -1;
+  AXB_CUDA(cudaGetDevice(&current));
+  if (current != device) {
+    set_error("axb_prune_topk_static: device %d must be the current device (current is %d)", device, current);
+    return -1;
+  }
+  std::lock_guard<std::mutex> lock(g_prune_static_mu);
   if (g_prune_static_ptr[device] == nullptr) {
-    int current = -1;
-    AXB_CUDA(cudaGetDevice(&current));
-    if (current != device) {
-      set_error("axb_prune_topk_static: device %d must be current on first use (current is %d)", device, current);
-      return -1;
-    }
     unsigned int* p = nullptr;
     AXB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_prune_static_scratch));
     if (p == nullptr) { set_error("axb_prune_topk_static: scratch symbol has no device address"); return -1; }

@@ -268,7 +268,9 @@ class AxoNN_Inter_Layer_Engine:
             self._clear_transit_tensors(clear_all=True)
 
         if eval_mode:
-            return float(loss_sum.item()) / n
+            value = float(loss_sum.item()) / n
+            self._check_device_status()
+            return value
         if post_bw_hook is not None:
             post_bw_hook(self.model)
         sync_gradients(self.model, mean=True, expert_mode=True)
@@ -277,7 +279,17 @@ class AxoNN_Inter_Layer_Engine:
                 optimizer.step()
         else:
             optimizer.step()
-        return float(loss_sum.item()) / n
+        value = float(loss_sum.item()) / n   # host synchronisation: the step's kernels have finished
+        self._check_device_status()
+        return value
+
+    def _check_device_status(self):
+        """Raise if a kernel of this step reported an expired device-side wait (read after the loss readback,
+        which already synchronised the host with the device)."""
+        if self.device.type == "cuda":
+            from .ops import _lib
+
+            _lib.check_status(self.device.index)
 
     # ------------------------------------------------------------------ fp16 loss scaling
     def _sync_scale(self, local_overflow: torch.Tensor) -> bool:

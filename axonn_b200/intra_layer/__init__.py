@@ -123,7 +123,9 @@ def sync_gradients(model, gradient_attr_name="grad", mean=False, vectorize=False
     group for all; ``mean`` divides by the two group sizes.
     expert_mode=False ("easy"): TP weights over data; TP biases over data and
     depth; every other parameter over the whole world; ``mean`` divides by the
-    world size (each rank saw a different batch shard).
+    world size (each rank saw a different batch shard).  Expert-parallel
+    parameters (``is_expert_parallel``) are summed over the tensor-parallel grid
+    only and get the same 1/world scale.
     Reference: ``axonn/intra_layer/__init__.py:114-173``."""
     if NO_GRADIENT_SYNC:
         return
@@ -132,9 +134,13 @@ def sync_gradients(model, gradient_attr_name="grad", mean=False, vectorize=False
         sync_gradients_expert_mode_data_parallel(model, gradient_attr_name, mean, vectorize)
         return
     ch = ax.comm_handle
-    weights, biases, others = [], [], []
+    weights, biases, others, experts = [], [], [], []
     for p, g in _grads(model, gradient_attr_name):
-        if getattr(p, "is_tensor_parallel", False):
+        if getattr(p, "is_expert_parallel", False):
+            # a different expert on every data-parallel rank: summed over the replicas inside the
+            # tensor-parallel grid only, never over the data group (that would mix unrelated experts)
+            experts.append(g)
+        elif getattr(p, "is_tensor_parallel", False):
             if not hasattr(p, "needs_depth_parallel_gradient_sync"):
                 raise ValueError("tensor-parallel parameter without needs_depth_parallel_gradient_sync")
             (biases if p.needs_depth_parallel_gradient_sync else weights).append(g)
@@ -145,3 +151,4 @@ def sync_gradients(model, gradient_attr_name="grad", mean=False, vectorize=False
     _all_reduce_many(biases, ch.data_parallel_group, None, vectorize)
     _all_reduce_many(biases, ch.depth_intra_layer_parallel_group, scale, vectorize)
     _all_reduce_many(others, dist.group.WORLD, scale, vectorize)
+    _all_reduce_many(experts, ch.intra_layer_group, scale, vectorize)

@@ -107,7 +107,9 @@ class AsyncLinear(Function):
         elif b is not None:
             epi = ops.EPI_BIAS
         prefetched = id(w_shard) in oc.weights_cache
-        if (depth_n > 1 and not prefetched and (inner_n == 1 or fused.usable(forward_all_reduce_group, x2))
+        out_l, in_l = local_weight_shape
+        ar_ok = inner_n > 1 and fused.usable(forward_all_reduce_group, x2, N=out_l, K=in_l)
+        if (depth_n > 1 and not prefetched and (inner_n == 1 or ar_ok)
                 and fused.all_gather_usable(depth_parallel_group, x2, w_shard, local_weight_shape, 0)):
             # one kernel: pull the depth shards of W over NVLink while computing, multiply, (all-reduce), epilogue
             if activation == "gelu":
@@ -121,7 +123,7 @@ class AsyncLinear(Function):
             w = _gathered_weight(w_shard, depth_parallel_group, local_weight_shape, cache)
             if w.dtype != compute_dtype:
                 w = w.to(compute_dtype)
-            if inner_n > 1 and fused.usable(forward_all_reduce_group, x2):
+            if ar_ok:
                 # GEMM whose epilogue all-reduces the output tiles over NVLink peer memory,
                 # then applies bias / GELU to the reduced values
                 if activation == "gelu":
@@ -171,8 +173,8 @@ class AsyncLinear(Function):
         handle = None
 
         def wgrad():
-            if depth_n > 1 and fused.reduce_scatter_usable(ctx.depth_parallel_group, go2, ctx.shape[0]) \
-                    and go2.dtype == w_shard.dtype:
+            if depth_n > 1 and go2.dtype == w_shard.dtype and \
+                    fused.reduce_scatter_usable(ctx.depth_parallel_group, go2, x2, ctx.shape[0]):
                 # weight-gradient GEMM whose epilogue reduce-scatters the row blocks (= depth shards of the
                 # flattened weight) over NVLink peer memory
                 return fused.gemm_reduce_scatter(2, go2, x2, ctx.depth_parallel_group,
@@ -195,13 +197,15 @@ class AsyncLinear(Function):
         if outer_n > 1 or not overlap_rs:
             # dgrad first so that its all-reduce hides under the wgrad GEMM
             if ctx.needs_input_grad[0]:
+                ar_ok = outer_n > 1 and fused.usable(ctx.backward_all_reduce_group, go2, N=ctx.shape[1],
+                                                     K=ctx.shape[0])
                 if (depth_n > 1 and id(w_shard) not in oc.weights_cache
-                        and (outer_n == 1 or fused.usable(ctx.backward_all_reduce_group, go2))
+                        and (outer_n == 1 or ar_ok)
                         and fused.all_gather_usable(ctx.depth_parallel_group, go2, w_shard, ctx.shape, 1)):
                     grad_input, _ = fused.all_gather_gemm(
                         1, go2.contiguous(), w_shard, ctx.depth_parallel_group, ctx.shape,
                         ar_group=ctx.backward_all_reduce_group if outer_n > 1 else None)
-                elif outer_n > 1 and fused.usable(ctx.backward_all_reduce_group, go2):
+                elif ar_ok:
                     w = _gathered_weight(w_shard, ctx.depth_parallel_group, ctx.shape, cache=False)
                     if w.dtype != ctx.compute_dtype:
                         w = w.to(ctx.compute_dtype)

@@ -64,7 +64,14 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2.0, error_if_nonfinite=Fals
     dev = pieces[0].device
     pieces = torch.stack([p.to(dev) for p in pieces])
     total_norm = pieces.max() if norm_type == inf else pieces.sum() ** (1.0 / norm_type)
-    if error_if_nonfinite and not torch.isfinite(total_norm):
+    if error_if_nonfinite and total_norm.is_cuda:
+        finite = bool(torch.isfinite(total_norm))   # host synchronisation: every kernel before it has finished
+        from ..ops import _lib
+
+        _lib.check_status(total_norm.device.index)   # an expired device-side wait surfaces here, not silently
+    else:
+        finite = (not error_if_nonfinite) or bool(torch.isfinite(total_norm))
+    if not finite:
         raise RuntimeError(f"The total norm of order {norm_type} for gradients is non-finite, "
                            "so it cannot be clipped.")
     clip = torch.clamp(max_norm / (total_norm + 1e-6), max=1.0)

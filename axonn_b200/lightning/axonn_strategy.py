@@ -134,6 +134,15 @@ class AxonnStrategyCore:
     def clip_parameters(self, parameters, max_norm, norm_type=2.0, error_if_nonfinite=True):
         return clip_grad_norm_(parameters, max_norm, norm_type, error_if_nonfinite)
 
+    def check_device_status(self):
+        """Raise ``AxonnCommTimeout`` if a fused kernel reported an expired device-side wait since the last
+        check.  Call it where the training loop already synchronises with the device (after reading the
+        loss); ``clip_parameters(..., error_if_nonfinite=True)`` does it as part of its own readback."""
+        if torch.cuda.is_available():
+            from ..ops import _lib
+
+            _lib.check_status()
+
     def no_backward_sync(self, module=None, enabled: bool = True):
         return self._backward_sync_control.no_backward_sync(module, enabled)
 

@@ -52,7 +52,7 @@ def lib():
 
 def set_wait_timeout_ms(ms: int):
     """Deadline of every device-side wait (mbarrier, peer flag).  A kernel whose wait runs out returns and
-    reports through the status word (``check_status``).  Default 2000 ms; ``AXONN_COMM_TIMEOUT_MS`` sets it
+    reports through the status word (``check_status``).  Default 120000 ms; ``AXONN_COMM_TIMEOUT_MS`` sets it
     at load time."""
     lib().axb_set_wait_timeout_ms(ctypes.c_uint(int(ms)))
 

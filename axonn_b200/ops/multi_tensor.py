@@ -1,7 +1,7 @@
 """Multi-tensor utilities: squared L2 norm, in-place scale, bucketed all-reduce.
 
 GPU paths use one launch over a table of tensor pointers
-(``csrc/multi_tensor.cu``); they replace the per-tensor ``torch.norm`` stacks
+(``csrc/optim.cu``); they replace the per-tensor ``torch.norm`` stacks
 and ``mul_`` loops of the reference's ``gradient_normalization.py:22-25,88-93``
 and the per-tensor all-reduces of ``intra_layer/__init__.py:93-111,154-173``.
 """
@@ -36,13 +36,32 @@ class _PtrTable:
         self.keep = tensors
 
 
+# Tables of recently used tensor lists, keyed by (pointer, numel, dtype) of every tensor: gradient lists
+# repeat from step to step (the caching allocator hands the same blocks back), so the per-step utilities
+# neither allocate pinned memory nor copy a table to the device after the first few steps.
+_table_cache = {}
+_TABLE_CACHE_MAX = 16
+
+
+def _cached_table(tensors):
+    key = tuple((t.data_ptr(), t.numel(), t.dtype) for t in tensors)
+    tab = _table_cache.get(key)
+    if tab is None:
+        if len(_table_cache) >= _TABLE_CACHE_MAX:
+            _table_cache.pop(next(iter(_table_cache)))
+        tab = _PtrTable(tensors)
+        tab.keep = None   # the cache must not keep gradient tensors alive
+        _table_cache[key] = tab
+    return tab
+
+
 def multi_tensor_l2norm_sq(tensors):
     """sum_i ||t_i||_2^2 as a 0-d fp32 tensor on the tensors' device."""
     tensors = [t for t in tensors if t.numel() > 0]
     if not tensors:
         return torch.zeros((), dtype=torch.float32)
     if tensors[0].is_cuda:
-        tab = _PtrTable(tensors)
+        tab = _cached_table(tensors)
         out = torch.zeros((), dtype=torch.float32, device=tensors[0].device)
         st = _lib.lib().axb_multi_l2norm_sq(_lib.ptr(tab.dev), ctypes.c_int(tab.n),
                                             ctypes.c_longlong(tab.total_chunks), _lib.ptr(out), _lib.stream_ptr())
@@ -58,9 +77,9 @@ def multi_tensor_scale_(tensors, scale):
     if not tensors:
         return
     if tensors[0].is_cuda:
-        tab = _PtrTable(tensors)
+        tab = _cached_table(tensors)
         if not torch.is_tensor(scale):
-            scale = torch.tensor(float(scale), dtype=torch.float32, device=tensors[0].device)
+            scale = torch.full((), float(scale), dtype=torch.float32, device=tensors[0].device)   # no host sync
         else:
             scale = scale.to(device=tensors[0].device, dtype=torch.float32)
         st = _lib.lib().axb_multi_scale(_lib.ptr(tab.dev), ctypes.c_int(tab.n),

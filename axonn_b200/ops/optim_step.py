@@ -49,6 +49,8 @@ def adamw_reference_(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step, grad
 
 
 _prune_ws = {}
+# dtype codes of the C interface (csrc/axonn_b200.h)
+_LIB_DTYPE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
 def prune_topk_(grad, keep_fraction):
@@ -65,9 +67,8 @@ def prune_topk_(grad, keep_fraction):
         if ws is None:
             ws = torch.empty(L.axb_prune_workspace_words(), dtype=torch.int32, device=dev)
             _prune_ws[dev] = ws
-        st = L.axb_prune_topk(_lib.ptr(grad), ctypes.c_longlong(n), ctypes.c_int(
-            {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[grad.dtype]), ctypes.c_longlong(k),
-            _lib.ptr(ws), ctypes.c_int(dev.index), _lib.stream_ptr())
+        st = L.axb_prune_topk(_lib.ptr(grad), ctypes.c_longlong(n), ctypes.c_int(_LIB_DTYPE[grad.dtype]),
+                              ctypes.c_longlong(k), _lib.ptr(ws), ctypes.c_int(dev.index), _lib.stream_ptr())
         _lib.check(st, "axb_prune_topk")
         _lib.add_launches(2)
         return grad

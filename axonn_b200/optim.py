@@ -41,6 +41,26 @@ class FusedAdamW(torch.optim.Optimizer):
             st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
         return st
 
+    def load_state_dict(self, state_dict):
+        """``torch.optim.Optimizer.load_state_dict`` casts every floating-point state tensor to the dtype of
+        its parameter, which would turn the fp32 master weights and moments of bf16 parameters into bf16.
+        The fp32 values are restored from the incoming state dict afterwards, and the cached pointer
+        tables (which still name the old state tensors) are dropped."""
+        super().load_state_dict(state_dict)
+        saved = state_dict["state"]
+        ids = [i for g in state_dict["param_groups"] for i in g["params"]]
+        params = [p for g in self.param_groups for p in g["params"]]
+        for i, p in zip(ids, params):
+            src = saved.get(i)
+            if src is None:
+                continue
+            st = self.state[p]
+            for key in ("master", "exp_avg", "exp_avg_sq"):
+                v = src.get(key)
+                if torch.is_tensor(v):
+                    st[key] = v.detach().to(device=p.device, dtype=torch.float32).clone()
+        self._tables.clear()
+
     @torch.no_grad()
     def step(self, closure=None, grad_attr="grad"):
         loss = closure() if closure is not None else None

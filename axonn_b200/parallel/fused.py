@@ -110,13 +110,77 @@ def reset():
     _channels.clear()
     _grad_channels.clear()
     _ag_channels.clear()
+    _group_ok.clear()
 
 
-def usable(group, tensor) -> bool:
+_group_ok = {}
+
+
+def _peer_capable(group) -> bool:
+    """True when every rank of ``group`` sits on the same host, can address every other rank's GPU and a
+    small symmetric allocation works.  Decided once per group, collectively (all ranks of the group reach
+    their first fused call at the same layer), and the verdict is agreed on with a MIN all-reduce so that no
+    rank takes the fused path alone.  A group that spans hosts or lacks peer access keeps using
+    ``torch.distributed``."""
+    key = id(group)
+    ok = _group_ok.get(key)
+    if ok is not None:
+        return ok
+    import socket
+
+    n = dist.get_world_size(group)
+    ok, reason = True, ""
+    try:
+        me = (socket.gethostname(), torch.cuda.current_device())
+        everyone = [None] * n
+        dist.all_gather_object(everyone, me, group=group)
+        if len({h for h, _ in everyone}) != 1:
+            ok, reason = False, "the group's ranks are on different hosts"
+        else:
+            devs = [d for _, d in everyone]
+            if len(set(devs)) != n:
+                ok, reason = False, "several ranks of the group share one GPU"
+            else:
+                for d in devs:
+                    if d != me[1] and not torch.cuda.can_device_access_peer(me[1], d):
+                        ok, reason = False, f"GPU {me[1]} cannot address GPU {d}"
+    except Exception as e:  # noqa: BLE001
+        ok, reason = False, f"peer discovery failed: {e}"
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    ok = bool(flag.item())
+    if ok:
+        try:
+            symm.SymmBuffer(group, 1 << 16, "probe")
+        except Exception as e:  # noqa: BLE001
+            ok, reason = False, f"symmetric allocation failed: {e}"
+        flag.fill_(1 if ok else 0)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        ok = bool(flag.item())
+    if not ok:
+        symm.disable(reason or "a peer rank could not use symmetric memory")
+    _group_ok[key] = ok
+    return ok
+
+
+def group_usable(group, tensor) -> bool:
+    """The peer-memory kernels can serve ``group`` for tensors on ``tensor``'s device."""
     if not (tensor.is_cuda and symm.enabled()):
         return False
     n = dist.get_world_size(group)
-    return 2 <= n <= 8
+    return 2 <= n <= 8 and _peer_capable(group)
+
+
+def usable(group, tensor, N=None, K=None, M=None) -> bool:
+    """The fused GEMM kernels apply: peer-capable group, bf16/fp16 operands and, when given, dimensions
+    that the tensor-core kernel accepts (N and K multiples of 8; M too for the transposed-A layout).
+    Anything else (fp32 layers, odd widths) takes the ``matmul`` + ``torch.distributed`` path."""
+    if tensor.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    for d in (N, K, M):
+        if d is not None and d % 8:
+            return False
+    return group_usable(group, tensor)
 
 
 def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, aux=None, out_dtype=None):
@@ -204,9 +268,11 @@ def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None,
     return out
 
 
-def reduce_scatter_usable(group, tensor, rows) -> bool:
+def reduce_scatter_usable(group, a, b, rows) -> bool:
+    """``a [K, rows]`` and ``b [K, N]`` of the transposed-A product whose row blocks are scattered."""
     n = dist.get_world_size(group)
-    return usable(group, tensor) and rows % n == 0 and (rows // n) % 32 == 0
+    return (a.dtype == b.dtype and rows % n == 0 and (rows // n) % 32 == 0
+            and usable(group, a, N=b.shape[1], K=a.shape[0], M=rows))
 
 
 def gemm_reduce_scatter(layout, a, b, group, out_dtype=None, out=None, accumulate=False):
@@ -319,7 +385,7 @@ _ag_channels = {}
 
 
 def all_gather_usable(group, x, w_shard, local_shape, layout) -> bool:
-    if not usable(group, x) or w_shard.dtype != x.dtype or x.dtype not in (torch.bfloat16, torch.float16):
+    if w_shard.dtype != x.dtype or not usable(group, x, N=local_shape[0], K=local_shape[1]):
         return False
     n = dist.get_world_size(group)
     rows = local_shape[0]
@@ -424,7 +490,7 @@ def _grad_table(ch, grads):
 def try_all_reduce_scale_(grads, group, scale) -> bool:
     """Sum ``grads`` over ``group`` and multiply by ``scale`` with the peer-memory kernels
     (pack -> two-shot reduce with fused scale -> unpack).  Returns False when not applicable."""
-    if not grads or not usable(group, grads[0]):
+    if not grads or not group_usable(group, grads[0]):
         return False
     dtype = grads[0].dtype
     if dtype not in (torch.float32, torch.bfloat16) or any(g.dtype != dtype or not g.is_contiguous() for g in grads):

@@ -4,6 +4,8 @@ import sys
 import pytest
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+# device-side waits give up after 5 s in tests (the library default is two minutes)
+os.environ.setdefault("AXONN_COMM_TIMEOUT_MS", "5000")
 
 
 def pytest_configure(config):

@@ -77,7 +77,7 @@ def _gemm_rs_case(rank, world):
             g = torch.Generator(device=dev).manual_seed(31 * rank + M + rep)
             a = (torch.randn(K, M, device=dev, generator=g) * 0.5).bfloat16()   # dY  [tokens, out]
             b = (torch.randn(K, N, device=dev, generator=g) * 0.5).bfloat16()   # X   [tokens, in]
-            assert fused.reduce_scatter_usable(group, a, M)
+            assert fused.reduce_scatter_usable(group, a, b, M)
             shard = fused.gemm_reduce_scatter(2, a, b, group)
             full = (a.float().t() @ b.float()).bfloat16().float()
             dist.all_reduce(full)

@@ -69,3 +69,32 @@ def test_router_capacity_and_aux_loss():
         u[i, i] = 10.0
     _, _, _, _, aux_u = route_top_k(u, 1, capacity=8)
     assert abs(float(aux_u) - 1.0) < 0.05
+
+
+def _moe_easy_sync(rank, world):
+    """Easy-mode ``sync_gradients`` with expert parallelism over the data group: every rank's expert
+    gradients keep their own values (scaled by 1/world), the replicated router's are summed."""
+    from axonn_b200 import axonn as ax
+    from axonn_b200.intra_layer import sync_gradients
+    from axonn_b200.parallel.moe import ExpertParallelMoE
+
+    ax.init(G_inter=1, G_data=world)
+    torch.manual_seed(5)
+    layer = ExpertParallelMoE(hidden=32, ffn=64, n_experts=4, top_k=2, capacity_factor=4.0, dtype=torch.float32)
+    g = torch.Generator().manual_seed(20 + rank)
+    x = torch.randn(2, 8, 32, generator=g, requires_grad=True)
+    layer(x).sum().backward()
+    w1_before = layer.w1.grad.clone()
+    router_before = layer.router.grad.clone()
+    sync_gradients(layer, mean=True, expert_mode=False)
+    import torch.distributed as dist
+
+    rsum = router_before.clone()
+    dist.all_reduce(rsum)
+    return (torch.allclose(layer.w1.grad, w1_before / world, atol=1e-6),
+            torch.allclose(layer.router.grad, rsum / world, atol=1e-6))
+
+
+def test_easy_mode_sync_leaves_expert_gradients_unmixed():
+    for ok_expert, ok_router in run_distributed(_moe_easy_sync, 2):
+        assert ok_expert and ok_router

@@ -32,3 +32,39 @@ def test_symm_canary_registry_is_empty_without_buffers():
 
     assert symm.verify_canaries() >= 0
     assert symm.debug_bounds_enabled() in (True, False)
+
+
+def test_fused_adamw_state_dict_roundtrip_keeps_fp32_state_for_bf16_parameters():
+    """Saving and reloading the optimizer in the middle of a run with bf16 parameters: master weights and
+    moments stay fp32 and the next step is bit-identical to the uninterrupted run."""
+    from axonn_b200.optim import FusedAdamW
+
+    def make():
+        torch.manual_seed(3)
+        ps = [torch.nn.Parameter(torch.randn(33, 7).bfloat16()), torch.nn.Parameter(torch.randn(5).bfloat16())]
+        return ps, FusedAdamW(ps, lr=1e-2, weight_decay=0.1)
+
+    def grads(ps, seed):
+        g = torch.Generator().manual_seed(seed)
+        for p in ps:
+            p.grad = torch.randn(p.shape, generator=g).bfloat16()
+
+    ps_a, opt_a = make()
+    ps_b, opt_b = make()
+    for seed in (1, 2):
+        grads(ps_a, seed); opt_a.step()
+        grads(ps_b, seed); opt_b.step()
+    # interrupted run: new optimizer object over the same parameter values, state loaded from a state dict
+    ps_c = [torch.nn.Parameter(p.detach().clone()) for p in ps_b]
+    opt_c = FusedAdamW(ps_c, lr=1e-2, weight_decay=0.1)
+    sd = opt_b.state_dict()
+    opt_c.load_state_dict(sd)
+    for p in ps_c:
+        st = opt_c.state[p]
+        assert st["master"].dtype == torch.float32 and st["exp_avg"].dtype == torch.float32
+        assert st["exp_avg_sq"].dtype == torch.float32
+    grads(ps_a, 9); opt_a.step()
+    grads(ps_c, 9); opt_c.step()
+    for a, c in zip(ps_a, ps_c):
+        assert torch.equal(a, c)
+        assert torch.equal(opt_a.state[a]["master"], opt_c.state[c]["master"])

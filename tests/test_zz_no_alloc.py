@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _call_static(lib, g, k):
-    code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[g.dtype]
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[g.dtype]   # codes of csrc/axonn_b200.h
     return lib.axb_prune_topk_static(ctypes.c_void_p(g.data_ptr()), ctypes.c_longlong(g.numel()), ctypes.c_int(code),
                                      ctypes.c_longlong(k), ctypes.c_int(g.device.index),
                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
@@ -47,7 +47,40 @@ def test_static_entry_point_rejects_oversized_request():
 
     lib = _lib.lib()
     g = torch.zeros(8, device="cuda:0")
-    st = lib.axb_prune_topk_static(ctypes.c_void_p(g.data_ptr()), ctypes.c_longlong(2 ** 31), ctypes.c_int(0),
+    st = lib.axb_prune_topk_static(ctypes.c_void_p(g.data_ptr()), ctypes.c_longlong(2 ** 31), ctypes.c_int(2),
                                    ctypes.c_longlong(1), ctypes.c_int(0),
                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert st != 0 and b"exceed" in lib.axb_last_error()
+
+
+def test_static_entry_point_stays_inside_a_bf16_tensor():
+    """A bf16 tensor passed with the header's code for bf16 (0) is pruned as 2-byte elements: the guard
+    elements placed directly behind it keep their values."""
+    from axonn_b200 import ops
+    from axonn_b200.ops import _lib
+
+    lib = _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(1)
+    n, guard = 262_144 + 24, 4096
+    whole = torch.randn(n + guard, device=dev).to(torch.bfloat16)
+    whole[n:] = 7.0
+    g = whole[:n]
+    want = ops.prune_topk_(g.clone(), 0.25)
+    assert _call_static(lib, g, max(1, int(round(n * 0.25)))) == 0, lib.axb_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(g, want)
+    assert bool((whole[n:] == 7.0).all()), "the entry point wrote behind the tensor"
+
+
+def test_static_entry_point_requires_the_current_device():
+    from axonn_b200.ops import _lib
+
+    lib = _lib.lib()
+    g = torch.zeros(64, device="cuda:0")
+    torch.cuda.set_device(0)
+    st = lib.axb_prune_topk_static(ctypes.c_void_p(g.data_ptr()), ctypes.c_longlong(64), ctypes.c_int(2),
+                                   ctypes.c_longlong(8), ctypes.c_int(1),
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st != 0 and b"current device" in lib.axb_last_error()
