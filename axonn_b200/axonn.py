@@ -72,6 +72,10 @@ def init(
     from .parallel import moe_kernels as _mk
 
     _mk.reset()
+    if comm_handle.use_cuda and G_intra_r * G_intra_c > 1:
+        # row / column tensor parallelism all-reduces activations inside the GEMM kernels: their outputs live in
+        # a peer-mapped arena so that the owner of a tile can store the finished values on every rank
+        _symm.create_output_arena()
 
 
 def finalize() -> None:

@@ -50,16 +50,31 @@ typedef struct AxbArCtx {
   unsigned int* counter;      /* local CTA completion counter (zero between calls) */
   unsigned long long inbox_vecs_per_src; /* 16-byte words per source in an inbox */
   unsigned long long flags_per_src;      /* flags per source */
-  int mode;                   /* 0: all-reduce of C; 1: reduce-scatter of C by row blocks */
+  int mode;                   /* 0: one-shot all-reduce of C (every rank receives and sums every partial);
+                                 1: reduce-scatter of C by row blocks;
+                                 2: two-shot all-reduce: every 32-row unit (tile, warp) has one owner rank,
+                                    (tile * 4 + warp) % n, which receives the partials, sums them and stores the
+                                    finished values into C on every rank.  C (and aux) must then lie in a range
+                                    that all ranks of the group have mapped ("arena"); each rank announces the
+                                    offsets of its C and aux in that range through the mailbox, and the kernel
+                                    returns only after every peer has finished writing into this rank's C. */
   int rows_per_shard;         /* mode 1: rows of C owned by each rank (multiple of 32) */
   int comm_ctas;              /* reserved, must be 0 */
-  int pad_;
+  int loopback;               /* mode 2 on one GPU with aliased peer pointers (tests, profiling): owned units are
+                                 stored for both source slots, so that the kernel only waits on its own flags */
+  unsigned long long c_off;   /* mode 2: byte offset of C inside this rank's arena */
+  unsigned long long aux_off; /* mode 2: byte offset of aux inside this rank's arena (unused when aux is null) */
+  void* arena_peer[8];        /* mode 2: base of rank j's arena as mapped in this process */
+  unsigned int* mail_local;   /* mode 2: [source] records of 8 words {c_off lo, hi, aux_off lo, hi, epoch, -, -, -} */
+  unsigned int* mail_peer[8];
 } AxbArCtx;
 
 /* Peer-memory context of the fused all-gather -> GEMM: B's row blocks ("shards", one per rank) are pulled
- * from the owners' outboxes into a local staging copy of B by the first `n_copy` CTAs while the other tiles
- * compute.  `wait_local[j]` reaches `epoch` when rank j has published its shard; `shard_ready[z]` is a local
- * counter that reaches `ready_target` when all copy CTAs have landed shard z. */
+ * from the owners' outboxes into a local staging copy of B while the tiles that need only shards already
+ * present are computed.  Every CTA of the GEMM brings in its slice of every shard: one thread per CTA runs
+ * bulk copies peer outbox -> shared memory -> staging, two 8 KB buffers in flight.  `wait_local[j]` reaches
+ * `epoch` when rank j has published its shard; `shard_ready[z]` is a local counter that reaches the number
+ * of CTAs when shard z is complete (`n_copy` and `ready_target` are set by the launcher). */
 typedef struct AxbAgCtx {
   int n, rank;
   unsigned int epoch;

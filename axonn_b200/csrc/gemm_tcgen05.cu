@@ -66,6 +66,12 @@ struct GemmParams {
   int debug;      // ablation builds only (-DAXB_ABLATION, then read once from AXB_AR_DEBUG; otherwise 0 and every branch on it is compiled out): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores, 128 register-path reducer instead of the shared-memory ring
 };
 
+// Time that the fused kernels spent stalled on peers since the last reset, in units of ns / 1024: every CTA of a
+// communicating launch adds (its wait for weight shards + the tail after its last tile's epilogue, in which only
+// the reduction of peer data and the end-of-call handshake remain) * 1024 / number of CTAs, i.e. each launch
+// contributes the mean over its CTAs.  Read by axb_comm_stall_ms.
+static __device__ unsigned long long g_comm_stall;
+
 template <int BN>
 struct GemmSmem {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -78,10 +84,16 @@ struct GemmSmem {
   static constexpr int RING_SLOT_BYTES = 32 * BN * 2;          // one (tile, warp) slot of one rank
   static constexpr int RING_OFFSET = RING_STAGES * STAGE_BYTES;
   static constexpr int RING_BYTES = (BN == 256) ? 4 * RING_SLOT_BYTES : 0;
-  static constexpr int BAR_OFFSET = (STAGES * STAGE_BYTES > RING_OFFSET + RING_BYTES) ? STAGES * STAGE_BYTES
-                                                                                      : RING_OFFSET + RING_BYTES;
-  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], ring_full[2], ring_empty[2], tmem ptr, flags
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 8) * 8 + 16 + 1024 /* alignment slack */;
+  // All-gather mode: two 8 KB bounce buffers through which one thread per CTA moves its slice of the peers'
+  // weight shards (bulk copy peer memory -> shared memory -> local staging).
+  static constexpr int PULL_BUF_BYTES = 8192;
+  static constexpr int PULL_OFFSET = (STAGES * STAGE_BYTES > RING_OFFSET + RING_BYTES) ? STAGES * STAGE_BYTES
+                                                                                       : RING_OFFSET + RING_BYTES;
+  static constexpr int BAR_OFFSET = PULL_OFFSET + 2 * PULL_BUF_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], ring_full[2], ring_empty[2], pull[2], tmem ptr,
+  // flags, peer output pointers (two-shot all-reduce: C and aux of every rank, 16 x 8 bytes)
+  // + two 8-byte words of stall accounting
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 10) * 8 + 16 + 128 + 16 + 1024 /* alignment slack */;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group, int& tm, int& tn) {
@@ -224,8 +236,35 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
   }
 }
 
-// Finish 8 consecutive reduced values of one output row: bias / GELU / store.
-__device__ __forceinline__ void comm_finish8(const GemmParams& p, float* v, size_t row, int col) {
+// Rank that reduces the 32-row unit (tile, warp-row q): -1 = every rank (one-shot all-reduce), the owner of
+// the rows (reduce-scatter), or round-robin over the units (two-shot all-reduce).
+__device__ __forceinline__ int unit_owner(const GemmParams& p, int tile, int tm, int q) {
+  if (p.ar.mode == 1) return (tm * BM + q * 32) / p.ar.rows_per_shard;
+  if (p.ar.mode == 2) return (tile * 4 + q) % p.ar.n;
+  return -1;
+}
+__device__ __forceinline__ unsigned unit_mask(const GemmParams& p, int tile, int tm) {
+  unsigned mine = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int o = unit_owner(p, tile, tm, q);
+    if (o < 0 || o == p.ar.rank) mine |= 1u << q;
+  }
+  return mine;
+}
+
+__device__ __forceinline__ uint4 pack8(const float* v, int dtype) {
+  uint4 o;
+  o.x = pack2(v[0], v[1], dtype); o.y = pack2(v[2], v[3], dtype);
+  o.z = pack2(v[4], v[5], dtype); o.w = pack2(v[6], v[7], dtype);
+  return o;
+}
+
+// Finish 8 consecutive reduced values of one output row: bias / GELU / store.  Two-shot all-reduce
+// (`peer_out` non-null: C pointers of all ranks at [0..8), aux pointers at [8..16), null for this rank): the
+// finished values also go to the same position of C (and aux) on every peer with 16-byte stores over NVLink.
+__device__ __forceinline__ void comm_finish8(const GemmParams& p, float* v, size_t row, int col,
+                                             const unsigned long long* peer_out = nullptr) {
   if (p.epilogue == 1 || p.epilogue == 2) {
 #pragma unroll
     for (int e = 0; e < 8; ++e)
@@ -233,12 +272,25 @@ __device__ __forceinline__ void comm_finish8(const GemmParams& p, float* v, size
                                 : __half2float(reinterpret_cast<const __half*>(p.bias)[col + e]);
   }
   const size_t out_row = (p.ar.mode == 1) ? row - static_cast<size_t>(p.ar.rank) * p.ar.rows_per_shard : row;
+  const size_t off = out_row * p.N + col;
   if (p.epilogue >= 2) {
-    if (p.aux != nullptr) store_vec8(p.aux, p.out_dtype, out_row * p.N + col, v, false);
+    if (p.aux != nullptr) {
+      store_vec8(p.aux, p.out_dtype, off, v, false);
+      if (peer_out != nullptr) {   // 16-bit outputs only (checked by the launcher)
+        const uint4 o = pack8(v, p.out_dtype);
+        for (int j = 0; j < p.ar.n; ++j)
+          if (peer_out[8 + j]) *(reinterpret_cast<uint4*>(peer_out[8 + j]) + (off >> 3)) = o;
+      }
+    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
   }
-  store_vec8(p.C, p.out_dtype, out_row * p.N + col, v, p.accumulate != 0);
+  store_vec8(p.C, p.out_dtype, off, v, p.accumulate != 0);
+  if (peer_out != nullptr) {
+    const uint4 o = pack8(v, p.out_dtype);
+    for (int j = 0; j < p.ar.n; ++j)
+      if (peer_out[j]) *(reinterpret_cast<uint4*>(peer_out[j]) + (off >> 3)) = o;
+  }
 }
 
 __device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) {
@@ -263,17 +315,32 @@ __device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) 
 // fence overlap the reduction of the previous tile instead of preceding each one.
 template <int BN>
 __device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
-                                               volatile unsigned int* ready_tiles, uint8_t* ring = nullptr,
-                                               uint64_t* ring_full = nullptr, uint64_t* ring_empty = nullptr) {
+                                               volatile unsigned int* ready_tiles, unsigned long long* peer_out,
+                                               uint8_t* ring = nullptr, uint64_t* ring_full = nullptr,
+                                               uint64_t* ring_empty = nullptr) {
   constexpr int WVEC = (BN / 32) * 4 * 32;    // 16-byte words per (tile, warp) slot
   constexpr int SLOT = WVEC * 16;
   int issued = 0;                             // ring mode: units handed to the reducer warps so far
   int t = 0;
+  if (p.ar.mode == 2) {
+    // Two-shot all-reduce: learn where every peer keeps its C (and aux) inside its arena.  Each rank wrote the
+    // offsets of this call into its peers' mailboxes when its kernel started; the pointers are left in shared
+    // memory for the reducer warps, which see them through the ready signal of the first tile.
+    for (int j = 0; j < p.ar.n; ++j) {
+      peer_out[j] = 0ull; peer_out[8 + j] = 0ull;
+      if (j == p.ar.rank) continue;
+      const unsigned int* rec = p.ar.mail_local + j * 8;
+      if (!wait_flag_ge(rec + 4, p.ar.epoch, abort_flag, p.timeout_ns)) { report_status(p.status, 0x124u); return; }
+      const unsigned long long c_off = (static_cast<unsigned long long>(__ldcv(rec + 1)) << 32) | __ldcv(rec + 0);
+      const unsigned long long a_off = (static_cast<unsigned long long>(__ldcv(rec + 3)) << 32) | __ldcv(rec + 2);
+      peer_out[j] = reinterpret_cast<unsigned long long>(p.ar.arena_peer[j]) + c_off;
+      if (p.aux != nullptr) peer_out[8 + j] = reinterpret_cast<unsigned long long>(p.ar.arena_peer[j]) + a_off;
+    }
+    __threadfence_block();
+  }
   for (int tile = blockIdx.x; tile < num_tiles; tile += p.gemm_ctas, ++t) {
     int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
-    unsigned mine = 0;
-    for (int q = 0; q < 4; ++q)
-      if (p.ar.mode == 0 || (tm * BM + q * 32) / p.ar.rows_per_shard == p.ar.rank) mine |= 1u << q;
+    const unsigned mine = unit_mask(p, tile, tm);
     if (mine != 0) {
       // the four (tile, warp) flags of a rank are one aligned 16-byte word
       uint64_t t0 = 0;
@@ -338,7 +405,7 @@ __device__ __forceinline__ void pin(uint4& v) { asm volatile("" : "+r"(v.x), "+r
 
 template <int BN, int NR>
 __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
-                                              volatile unsigned int* ready_tiles) {
+                                              volatile unsigned int* ready_tiles, const unsigned long long* peer_out) {
   constexpr int CH = BN / 32;                 // 32-column chunks per tile row
   constexpr int WVEC = CH * 4 * 32;           // 16-byte words per (tile, warp) slot
   constexpr int TVEC = 4 * WVEC;
@@ -353,9 +420,7 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
   for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
     ++t;
     int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
-    unsigned mine = 0;
-    for (int q = 0; q < 4; ++q)
-      if (p.ar.mode == 0 || (tm * BM + q * 32) / p.ar.rows_per_shard == p.ar.rank) mine |= 1u << q;
+    const unsigned mine = unit_mask(p, tile, tm);
     if (mine == 0) continue;
     if (tid == 0) {
       // the watcher warp has seen (and acquired) the flags of all ranks for tiles [0, *ready_tiles)
@@ -400,7 +465,8 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
             const bool live = j < p.ar.n && u < UNITS && (mine & (1u << q));
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              if (live) in[jj][k][i] = ld_cg_ordered(src + q * WVEC + (c * 4 + i) * 32 + ln);
+              // words of a slot are stored lane-permuted (see the epilogue): word w of row ln sits at w*32 + (ln ^ w)
+              if (live) in[jj][k][i] = ld_cg_ordered(src + q * WVEC + (c * 4 + i) * 32 + (ln ^ ((c * 4 + i) & 31)));
               else in[jj][k][i] = make_uint4(0u, 0u, 0u, 0u);
             }
           }
@@ -430,7 +496,7 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
         for (int i = 0; i < 4; ++i) {
           const int col = tn * BN + c * 32 + i * 8;
           if (col >= p.N) continue;
-          comm_finish8(p, acc[k][i], row, col);
+          comm_finish8(p, acc[k][i], row, col, p.ar.mode == 2 ? peer_out : nullptr);
         }
       }
     }
@@ -447,44 +513,52 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
 // One (tile, warp-row q) unit = two 16 KB slots (own partial and the peer's), each contiguous in the inbox.  The
 // watcher thread copies them into a two-group ring behind the operand stages with bulk copies as soon as the
 // tile's flags are up (32 - 64 KB in flight per SM without holding registers); the eight reducer warps wait for
-// a group, read their 16-byte words from shared memory (warp = 32-column chunk, lane = row), sum them in rank
-// order, apply bias / GELU, store 64 contiguous bytes of C per thread and hand the group back.
+// a group and read it row-wise: each of the eight warps takes four of the unit's 32 rows, a lane the 16-byte
+// word `lane` of the row (the slot's words are stored lane-permuted, word w of row r at w*32 + (r ^ w), so these
+// reads hit distinct banks), sums the two ranks in rank order, applies bias / GELU and stores 16 bytes: one warp
+// instruction writes 512 contiguous bytes of a row of C - locally and, in the two-shot all-reduce, over NVLink
+// into the peer's C as well - then the group is handed back.
 template <int BN>
 __device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
-                                             uint8_t* ring, uint64_t* ring_full, uint64_t* ring_empty) {
+                                             uint8_t* ring, uint64_t* ring_full, uint64_t* ring_empty,
+                                             const unsigned long long* peer_out) {
   constexpr int CH = BN / 32;
   constexpr int WVEC = CH * 4 * 32;           // 16-byte words per slot
   constexpr int SLOT = WVEC * 16;
+  static_assert(CH * 4 == 32, "row-wise ring reducer: one 16-byte word of a row per lane");
   const int tid = threadIdx.x - 192;
-  const int wr = tid >> 5, ln = tid & 31;     // wr: 32-column chunk of the tile, ln: row inside the warp-row
+  const int wr = tid >> 5, ln = tid & 31;     // wr: rows 4*wr .. 4*wr+3 of the unit, ln: 16-byte word of the row
+  const unsigned long long* peers = p.ar.mode == 2 ? peer_out : nullptr;
   bool ok = true;
   int consumed = 0;                           // ring group = consumed & 1, phase = (consumed >> 1) & 1
   for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
     int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+    const unsigned mine = unit_mask(p, tile, tm);
     for (int q = 0; q < 4; ++q) {
-      if (p.ar.mode != 0 && (tm * BM + q * 32) / p.ar.rows_per_shard != p.ar.rank) continue;
+      if (!(mine & (1u << q))) continue;
       const int g = consumed & 1;
       if (!mbar_wait(&ring_full[g], (consumed >> 1) & 1, abort_flag, p.timeout_ns)) { ok = false; break; }
       ++consumed;
       if (!AXB_DBG(p, 8)) {
-        const size_t row = static_cast<size_t>(tm) * BM + q * 32 + ln;
         const uint4* s0 = reinterpret_cast<const uint4*>(ring + (g * 2) * SLOT);
         const uint4* s1 = reinterpret_cast<const uint4*>(ring + (g * 2 + 1) * SLOT);
+        const int col = tn * BN + ln * 8;
         uint4 a[4], b[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { a[i] = s0[(wr * 4 + i) * 32 + ln]; b[i] = s1[(wr * 4 + i) * 32 + ln]; }
-        if (row < static_cast<size_t>(p.M)) {
+        for (int k = 0; k < 4; ++k) {
+          const int r = wr * 4 + k;
+          a[k] = s0[ln * 32 + (r ^ ln)]; b[k] = s1[ln * 32 + (r ^ ln)];
+        }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int col = tn * BN + wr * 32 + i * 8;
-            if (col >= p.N) continue;
-            float acc[8];
+        for (int k = 0; k < 4; ++k) {
+          const size_t row = static_cast<size_t>(tm) * BM + q * 32 + wr * 4 + k;
+          if (row >= static_cast<size_t>(p.M) || col >= p.N) continue;
+          float acc[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-            acc_vec8(acc, a[i], p.in_dtype);     // rank order: identical bits on both ranks
-            acc_vec8(acc, b[i], p.in_dtype);
-            comm_finish8(p, acc, row, col);
-          }
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+          acc_vec8(acc, a[k], p.in_dtype);     // rank order: identical bits on both ranks
+          acc_vec8(acc, b[k], p.in_dtype);
+          comm_finish8(p, acc, row, col, peers);
         }
       }
       __syncwarp();
@@ -492,6 +566,73 @@ __device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int
     }
   }
   if (!ok && tid == 0) report_status(p.status, 0x122u);
+}
+
+// ---- all-gather puller (one thread per CTA): brings this CTA's slice of every shard of B - own shard first,
+// then the peers' in ring order - from the owners' outboxes into the local staging copy of B.  The bytes never
+// pass through registers: a bulk copy lands 8 KB of the (peer-mapped) outbox in shared memory, a second bulk copy
+// writes them to staging, two buffers alternate so that two remote reads are in flight per SM all the time
+// (148 SMs x 16 KB per NVLink round trip).  When the CTA's slice of a shard is complete it adds one to the
+// shard's arrival counter; the TMA producers of all CTAs wait for the counter to reach the number of CTAs
+// before they read tiles of that shard.
+template <int BN>
+__device__ __forceinline__ void ag_puller(const GemmParams& p, uint8_t* buf, uint64_t* pull_bar,
+                                          volatile int* abort_flag) {
+  constexpr uint32_t CHB = GemmSmem<BN>::PULL_BUF_BYTES;
+  const unsigned long long total = p.ag.shard_bytes;
+  unsigned long long per = (total + gridDim.x - 1) / gridDim.x;
+  per = (per + 15ull) & ~15ull;                              // bulk copies move multiples of 16 bytes
+  const unsigned long long lo = per * blockIdx.x < total ? per * blockIdx.x : total;
+  const unsigned long long hi = lo + per < total ? lo + per : total;
+  const uint32_t nch = static_cast<uint32_t>((hi - lo + CHB - 1) / CHB);
+  uint32_t loads = 0, waited = 0;   // bulk loads issued / awaited so far: buffer = index & 1, phase = (index >> 1) & 1
+  bool ok = true;
+  for (int s = 0; s < p.ag.n && ok; ++s) {
+    const int z = (p.ag.rank + s) % p.ag.n;
+    if (z != p.ag.rank && !wait_flag_ge(p.ag.wait_local + z, p.ag.epoch, abort_flag, p.timeout_ns)) { ok = false; break; }
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag.outbox_peer[z]);
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag.staging) + static_cast<unsigned long long>(z) * total;
+    auto chunk_bytes = [&](uint32_t k) {
+      const unsigned long long off = lo + static_cast<unsigned long long>(k) * CHB;
+      return static_cast<uint32_t>(hi - off < CHB ? hi - off : CHB);
+    };
+    auto issue_load = [&](uint32_t k) {
+      const uint32_t b = loads & 1u, bytes = chunk_bytes(k);
+      mbar_expect_tx(&pull_bar[b], bytes);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(buf + b * CHB)), "l"(src + lo + static_cast<unsigned long long>(k) * CHB), "r"(bytes),
+                     "r"(smem_u32(&pull_bar[b])) : "memory");
+      ++loads;
+    };
+    if (nch > 0) issue_load(0);
+    for (uint32_t k = 0; k < nch; ++k) {
+      if (k + 1 < nch) {
+        // the other buffer was last read by the store of chunk k-1: that read must be over before it is refilled
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        issue_load(k + 1);
+      }
+      const uint32_t b = waited & 1u;
+      if (!mbar_wait(&pull_bar[b], (waited >> 1) & 1u, abort_flag, p.timeout_ns)) { ok = false; break; }
+      ++waited;
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                   ::"l"(dst + lo + static_cast<unsigned long long>(k) * CHB), "r"(smem_u32(buf + b * CHB)), "r"(chunk_bytes(k))
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store of this slice has been written
+    if (!ok) break;
+    asm volatile("fence.proxy.async;" ::: "memory");            // bulk-copy writes -> visible to the TMA reads of all CTAs
+    __threadfence();
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag.shard_ready + z) : "memory");
+  }
+  if (!ok) {
+    // loads still in flight must land before the CTA's shared memory goes away (bounded)
+    for (; waited < loads; ++waited) {
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(&pull_bar[waited & 1u], (waited >> 1) & 1u) && globaltimer_ns() - t0 < 2000000ull) {}
+    }
+    report_status(p.status, 0x110u);
+  }
 }
 
 template <int BN, int A_MN, int B_MN>
@@ -507,10 +648,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* ring_full = tmem_empty + 2;
   uint64_t* ring_empty = ring_full + 2;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(ring_empty + 2);
+  uint64_t* pull_bar = ring_empty + 2;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(pull_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
   volatile unsigned int* parts_done = reinterpret_cast<volatile unsigned int*>(tmem_ptr_smem + 2);
   volatile unsigned int* ready_tiles = reinterpret_cast<volatile unsigned int*>(tmem_ptr_smem + 3);
+  unsigned long long* peer_out = reinterpret_cast<unsigned long long*>(tmem_ptr_smem + 4);   // [16], 8-byte aligned
+  unsigned long long* stall_words = peer_out + 16;   // [0] time the last epilogue warp finished, [1] ns the producer waited for shards
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -527,9 +671,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
     for (int b = 0; b < 2; ++b) { mbar_init(&ring_full[b], 1); mbar_init(&ring_empty[b], REDUCER_THREADS / 32); }
+    for (int b = 0; b < 2; ++b) mbar_init(&pull_bar[b], 1);
     *abort_flag = 0;
     *parts_done = 0;
     *ready_tiles = 0;
+    stall_words[0] = 0ull; stall_words[1] = 0ull;
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
@@ -547,6 +693,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!wait_flag_ge(p.ar.done_local + j, p.ar.epoch - 2u, abort_flag, timeout)) {
         report_status(p.status, 0x108u);
         break;
+      }
+    }
+    if (p.ar.mode == 2 && blockIdx.x == 0) {
+      // two-shot all-reduce: tell every peer where this rank's C and aux of this call lie inside its arena
+      for (int j = 0; j < p.ar.n; ++j) {
+        if (j == p.ar.rank) continue;
+        unsigned int* rec = p.ar.mail_peer[j] + p.ar.rank * 8;
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(rec + 0), "r"(static_cast<unsigned>(p.ar.c_off)) : "memory");
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(rec + 1), "r"(static_cast<unsigned>(p.ar.c_off >> 32)) : "memory");
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(rec + 2), "r"(static_cast<unsigned>(p.ar.aux_off)) : "memory");
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(rec + 3), "r"(static_cast<unsigned>(p.ar.aux_off >> 32)) : "memory");
+        st_release_sys(rec + 4, p.ar.epoch);
       }
     }
   }
@@ -571,6 +729,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int shard = brow / p.ag.rows_per_shard;
             if (!(ag_ready_mask & (1u << shard))) {
               uint64_t t0 = 0;
+              const uint64_t t_wait = globaltimer_ns();
               for (uint32_t it = 0;; ++it) {
                 unsigned int v;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ag.shard_ready + shard) : "memory");
@@ -584,6 +743,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               if (!ok) break;
               asm volatile("fence.proxy.async;" ::: "memory");
               ag_ready_mask |= 1u << shard;
+              stall_words[1] += globaltimer_ns() - t_wait;
             }
           }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, timeout)) { ok = false; break; }
@@ -666,7 +826,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // One thread waits until the four epilogue warps have stored a tile's partial (shared counter), runs
     // the single system-scope fence the tile needs and raises its flags on the reducing ranks, so that the
     // fence latency is off the epilogue's path.
-    if (p.ar.n > 1 && lane == 0) {
+    // (lane 16 of the same warp is the all-gather puller; the two run as independent threads)
+    if (p.ag.n > 1 && lane == 16) {
+      ag_puller<BN>(p, smem + S::PULL_OFFSET, pull_bar, abort_flag);
+    } else if (p.ar.n > 1 && lane == 0) {
       int t = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gemm_ctas, ++t) {
         int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
@@ -682,9 +845,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!good) break;
         if (!AXB_DBG(p, 1)) __threadfence_system();
         for (int qq = 0; qq < 4; ++qq) {
-          const int own = (p.ar.mode == 1) ? (tm * BM + qq * 32) / p.ar.rows_per_shard : -1;
+          const int own = unit_owner(p, tile, tm, qq);
           for (int j = 0; j < p.ar.n; ++j) {
-            if (p.ar.mode == 1 && j != own) continue;
+            if (own >= 0 && j != own && !(p.ar.loopback && own == p.ar.rank)) continue;
             unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
                               static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + qq;
             asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar.epoch) : "memory");
@@ -694,52 +857,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == WATCHER_WARP) {
     if (p.ar.n > 1 && lane == 0) {
-      if (ring_mode) watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles, smem + S::RING_OFFSET, ring_full, ring_empty);
-      else watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles);
+      if (ring_mode) watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles, peer_out, smem + S::RING_OFFSET, ring_full, ring_empty);
+      else watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
     }
   } else if (warp >= 6) {
     bool done = false;
     if constexpr (BN == 256) {
       if (ring_mode) {
-        reducer_ring<BN>(p, group, num_tiles, abort_flag, smem + S::RING_OFFSET, ring_full, ring_empty);
+        reducer_ring<BN>(p, group, num_tiles, abort_flag, smem + S::RING_OFFSET, ring_full, ring_empty, peer_out);
         done = true;
       }
     }
     if (done) {
-    } else if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag, ready_tiles);
-    else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4>(p, group, num_tiles, abort_flag, ready_tiles);
-    else if (p.ar.n > 4) reducer_warps<BN, 8>(p, group, num_tiles, abort_flag, ready_tiles);
+    } else if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
+    else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
+    else if (p.ar.n > 4) reducer_warps<BN, 8>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     bool ok = true;
     int t = 0;
-    if (p.ag.n > 1 && static_cast<int>(blockIdx.x) < p.ag.n_copy) {
-      // ---- all-gather stage: pull this CTA's slice of every shard of B (own shard first) from the owners'
-      // outboxes over NVLink into the local staging copy of B, then count the slice as arrived.
-      const int tid = threadIdx.x - 64;  // 0..127
-      const size_t vecs = p.ag.shard_bytes / 16;
-      const size_t per = (vecs + p.ag.n_copy - 1) / p.ag.n_copy;
-      const size_t lo = per * blockIdx.x, hi = (lo + per < vecs) ? lo + per : vecs;
-      for (int s = 0; s < p.ag.n && ok; ++s) {
-        const int z = (p.ag.rank + s) % p.ag.n;
-        if (z != p.ag.rank) {
-          if (tid == 0) ok = wait_flag_ge(p.ag.wait_local + z, p.ag.epoch, abort_flag, timeout);
-          ok = __syncthreads_or_named(ok);
-          if (!ok) break;
-        }
-        const uint4* src = reinterpret_cast<const uint4*>(p.ag.outbox_peer[z]);
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.ag.staging) + static_cast<size_t>(z) * p.ag.shard_bytes);
-        for (size_t i = lo + tid; i < hi; i += 128) dst[i] = src[i];
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (tid == 0) {
-          asm volatile("fence.proxy.async;" ::: "memory");
-          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag.shard_ready + z) : "memory");
-        }
-      }
-      if (!ok && lane == 0) report_status(p.status, 0x110u);
-    }
     // Finish one tile: values v (one row, 32 columns) -> bias / GELU -> C.
     auto finish_chunk = [&](float (&v)[32], size_t out_row, int col, bool store_ok) {
       if (p.epilogue == 1 || p.epilogue == 2) {
@@ -794,9 +931,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // for the peers, plain stores for this rank - then the flagger raises the (tile, warp) flags; the reducer warps of the
       // reducing ranks sum the inbox slots locally.  Slot layout of a (tile, warp): [chunk][vec 0..3][lane]
       // 16-byte words, so every store instruction of a warp covers 512 contiguous bytes.
-      const int owner = (p.ar.mode == 1) ? (tm * BM + q * 32) / p.ar.rows_per_shard : -1;
+      // Words are lane-permuted inside their 512 bytes (word w of row `lane` at w*32 + (lane ^ w)): a store
+      // instruction still covers the same 512 contiguous bytes, and the reducer warps can read a slot row by
+      // row from shared memory without bank conflicts.
+      const int owner = unit_owner(p, tile, tm, q);
+      const bool own_unit = owner < 0 || owner == p.ar.rank;
       const size_t slot_vec = static_cast<size_t>(p.ar.rank) * p.ar.inbox_vecs_per_src +
-                              (static_cast<size_t>(tile) * 4 + q) * (BN / 32) * 4 * 32 + lane;
+                              (static_cast<size_t>(tile) * 4 + q) * (BN / 32) * 4 * 32;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         if (tn * BN + c * 32 >= p.N) break;
@@ -812,21 +953,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           w[i].w = pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]), p.in_dtype);
         }
         for (int j = 0; j < p.ar.n; ++j) {
-          if (p.ar.mode == 1 && j != owner) continue;
+          // one-shot: every rank gets the partial; otherwise only the unit's owner (in the one-GPU emulation
+          // an owned unit is also stored for the other source slot, which stands in for the peer's partial)
+          if (owner >= 0 && j != owner && !(p.ar.loopback && own_unit)) continue;
           if (AXB_DBG(p, 2) && j != p.ar.rank) continue;
           if AXB_DBG(p, 16) continue;
-          uint4* dst = reinterpret_cast<uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + slot_vec + (c * 4) * 32;
-          if (AXB_DBG(p, 32) && j == p.ar.rank) {
-            uint64_t pol;
-            asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+          uint4* dst = reinterpret_cast<uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + slot_vec;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(dst + i * 32), "r"(w[i].x),
-                           "r"(w[i].y), "r"(w[i].z), "r"(w[i].w), "l"(pol) : "memory");
-            continue;
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i * 32] = w[i];
+          for (int i = 0; i < 4; ++i) dst[(c * 4 + i) * 32 + (lane ^ ((c * 4 + i) & 31))] = w[i];
         }
       }
       tcgen05_fence_before();
@@ -839,6 +973,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     if (!ok && lane == 0) report_status(p.status, 0x104u);
+    if (lane == 0 && (p.ar.n > 1 || p.ag.n > 1)) atomicMax(stall_words, static_cast<unsigned long long>(globaltimer_ns()));
   }
 
   tcgen05_fence_before();
@@ -854,13 +989,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   }
   if (p.ar.n > 1 && threadIdx.x == 0) {
-    __threadfence();
+    // the CTA's stores into the peers' inboxes (and, in the two-shot all-reduce, into their C) are ordered
+    // before the CTA counter at system scope; the last CTA then tells the peers that this rank is done
+    if (p.ar.mode == 2) __threadfence_system(); else __threadfence();
     if (atomicAdd(p.ar.counter, 1u) == gridDim.x - 1) {
       *p.ar.counter = 0;
       __threadfence_system();
       for (int j = 0; j < p.ar.n; ++j)
         if (j != p.ar.rank) st_release_sys(p.ar.done_peer[j] + p.ar.rank, p.ar.epoch);
+      if (p.ar.mode == 2) {
+        // two-shot all-reduce: the rows of C that the peers own are written by their reducer warps; C is
+        // complete on this rank once every peer has reported the end of its call (bounded wait)
+        for (int j = 0; j < p.ar.n; ++j) {
+          if (j == p.ar.rank) continue;
+          if (!wait_flag_ge(p.ar.done_local + j, p.ar.epoch, abort_flag, timeout)) { report_status(p.status, 0x109u); break; }
+        }
+      }
     }
+  }
+  if ((p.ar.n > 1 || p.ag.n > 1) && threadIdx.x == 0) {
+    unsigned long long stall = stall_words[1];
+    if (p.ar.n > 1 && stall_words[0] != 0ull) stall += globaltimer_ns() - stall_words[0];
+    atomicAdd(&g_comm_stall, stall * 1024ull / gridDim.x);
   }
 }
 
@@ -1137,7 +1287,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
   const int sms = sm_count(device);
   // every CTA must be resident at once (reducer warps wait for partials of the same launch): grid <= #SMs
   p.gemm_ctas = tiles < sms ? tiles : sms;
-  if (p.ag.n > 1 && p.ag.n_copy > p.gemm_ctas) { p.ag.n_copy = p.gemm_ctas; p.ag.ready_target = p.ag.n_copy; }
+  if (p.ag.n > 1) { p.ag.n_copy = p.gemm_ctas; p.ag.ready_target = static_cast<unsigned int>(p.gemm_ctas); }   // every CTA pulls a slice
   const int grid = p.gemm_ctas;
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
   AXB_CUDA(cudaGetLastError());
@@ -1223,14 +1373,7 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
 #endif
   if (ag && ag->n > 1) {
     p.ag = *ag;
-    {
-      // every copy CTA must be resident: never more of them than CTAs in the grid
-      const long long tiles = static_cast<long long>(tiles_m) * ((N + BN - 1) / BN);
-      const long long grid = tiles < sm_count(device) ? tiles : sm_count(device);
-      if (p.ag.n_copy > grid) p.ag.n_copy = static_cast<int>(grid);
-      p.ag.ready_target = static_cast<unsigned int>(p.ag.n_copy);
-      AXB_CUDA(cudaMemsetAsync(p.ag.shard_ready, 0, 8 * sizeof(unsigned int), static_cast<cudaStream_t>(stream)));
-    }
+    AXB_CUDA(cudaMemsetAsync(p.ag.shard_ready, 0, 8 * sizeof(unsigned int), static_cast<cudaStream_t>(stream)));
     if (layout == 0) {
       if (ag->rows_per_shard % BN != 0 || static_cast<long long>(ag->rows_per_shard) * ag->n != N) {
         set_error("axb_ag_gemm: shard rows (%d) must be a multiple of the tile width %d and n*rows == N", ag->rows_per_shard, BN);
@@ -1271,6 +1414,20 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
 #undef AXB_DISPATCH
 }
 
+// Milliseconds the fused GEMM kernels spent stalled on peers since the last reset (sum over launches of the mean
+// over each launch's CTAs).  Synchronises the device; `device` must be current.  A diagnostic for reporting exposed
+// communication, not for use inside a timed region.
+extern "C" double axb_comm_stall_ms(int device, int reset) {
+  (void)device;
+  unsigned long long v = 0;
+  if (cudaMemcpyFromSymbol(&v, axb::g_comm_stall, sizeof(v)) != cudaSuccess) return -1.0;
+  if (reset) {
+    const unsigned long long z = 0;
+    cudaMemcpyToSymbol(axb::g_comm_stall, &z, sizeof(z));
+  }
+  return static_cast<double>(v) / 1024.0 / 1e6;
+}
+
 extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,
                         int K, int in_dtype, int out_dtype, int epilogue, int accumulate, int device, void* stream) {
   return gemm_common(layout, A, B, C, bias, aux, M, N, K, in_dtype, out_dtype, epilogue, accumulate, device, stream,
@@ -1287,7 +1444,7 @@ extern "C" int axb_ag_gemm(int layout, const void* A, void* C, const void* bias,
                            int in_dtype, int out_dtype, int epilogue, int device, void* stream, const AxbAgCtx* ag,
                            const AxbArCtx* ar) {
   if (!ag || ag->n < 2 || ag->n > 8) { axb::set_error("axb_ag_gemm: group size must be 2..8"); return -1; }
-  if (ag->n_copy < 1 || ag->shard_bytes % 16) { axb::set_error("axb_ag_gemm: bad copy configuration"); return -1; }
+  if (ag->shard_bytes % 16) { axb::set_error("axb_ag_gemm: shard size must be a multiple of 16 bytes"); return -1; }
   return gemm_common(layout, A, ag->staging, C, bias, aux, M, N, K, in_dtype, out_dtype, epilogue, 0, device, stream,
                      (ar && ar->n > 1) ? ar : nullptr, ag);
 }
@@ -1312,6 +1469,7 @@ extern "C" int axb_gemm_ar(int layout, const void* A, const void* B, void* C, co
                            const AxbArCtx* ar) {
   if (!ar || ar->n < 2 || ar->n > 8) { axb::set_error("axb_gemm_ar: group size must be 2..8"); return -1; }
   if (ar->bn != 128 && ar->bn != 256) { axb::set_error("axb_gemm_ar: bn must be 128 or 256"); return -1; }
-  if (ar->mode != 0) { axb::set_error("axb_gemm_ar: context is not in all-reduce mode"); return -1; }
+  if (ar->mode != 0 && ar->mode != 2) { axb::set_error("axb_gemm_ar: context is not in all-reduce mode"); return -1; }
+  if (ar->mode == 2 && out_dtype == 2) { axb::set_error("axb_gemm_ar: the two-shot all-reduce stores 16-bit outputs only"); return -1; }
   return gemm_common(layout, A, B, C, bias, aux, M, N, K, in_dtype, out_dtype, epilogue, 0, device, stream, ar);
 }

@@ -112,11 +112,12 @@ class AsyncLinear(Function):
         if (depth_n > 1 and not prefetched and (inner_n == 1 or ar_ok)
                 and fused.all_gather_usable(depth_parallel_group, x2, w_shard, local_weight_shape, 0)):
             # one kernel: pull the depth shards of W over NVLink while computing, multiply, (all-reduce), epilogue
+            res = fused.all_gather_gemm(0, x2, w_shard, depth_parallel_group, local_weight_shape,
+                                        ar_group=forward_all_reduce_group if inner_n > 1 else None,
+                                        bias=b, epilogue=epi, want_aux=activation == "gelu")
+            out, w = res[0], res[1]
             if activation == "gelu":
-                pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype, device=x2.device)
-            out, w = fused.all_gather_gemm(0, x2, w_shard, depth_parallel_group, local_weight_shape,
-                                           ar_group=forward_all_reduce_group if inner_n > 1 else None,
-                                           bias=b, epilogue=epi, aux=pre_act)
+                pre_act = res[2]
             if cache:
                 oc.weights_cache[id(w_shard)] = [w_shard, w.reshape(-1), None]
         else:
@@ -127,9 +128,10 @@ class AsyncLinear(Function):
                 # GEMM whose epilogue all-reduces the output tiles over NVLink peer memory,
                 # then applies bias / GELU to the reduced values
                 if activation == "gelu":
-                    pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype,
-                                          device=x2.device)
-                out = fused.gemm_all_reduce(0, x2, w, forward_all_reduce_group, bias=b, epilogue=epi, aux=pre_act)
+                    out, pre_act = fused.gemm_all_reduce(0, x2, w, forward_all_reduce_group, bias=b, epilogue=epi,
+                                                         want_aux=True)
+                else:
+                    out = fused.gemm_all_reduce(0, x2, w, forward_all_reduce_group, bias=b, epilogue=epi)
             elif inner_n == 1 and x2.is_cuda and epi != ops.EPI_NONE:
                 if activation == "gelu":
                     pre_act = torch.empty((x2.shape[0], local_weight_shape[0]), dtype=compute_dtype,

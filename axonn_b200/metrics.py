@@ -92,3 +92,112 @@ class StepMeter:
         if reset:
             self.records = []
         return out
+
+
+# ----------------------------------------------------------------------------- exposed communication
+# Kernel names that only move data between ranks (a collective library's kernels and this package's
+# stand-alone peer-memory kernels).  Fused compute+collective kernels are compute kernels here; the time
+# they spend waiting on peers is counted inside the kernels (``fused_comm_stall_ms``).
+COMM_KERNEL_PATTERNS = ("nccl", "allreduce_twoshot", "grad_allreduce", "bucket_copy", "moe_scatter_rows", "moe_gather_rows",
+                        "moe_signal", "moe_wait", "a2a_v", "embedding_p2p", "symm_all_gather", "symm_reduce_scatter")
+
+
+def is_comm_kernel(name: str) -> bool:
+    low = name.lower()
+    return any(p in low for p in COMM_KERNEL_PATTERNS)
+
+
+def _union(intervals):
+    """Merge [(start, end), ...] into disjoint sorted intervals."""
+    out = []
+    for s, e in sorted(intervals):
+        if e <= s:
+            continue
+        if out and s <= out[-1][1]:
+            if e > out[-1][1]:
+                out[-1][1] = e
+        else:
+            out.append([s, e])
+    return out
+
+
+def _length(intervals):
+    return sum(e - s for s, e in intervals)
+
+
+def _subtract(a, b):
+    """Parts of the disjoint sorted intervals ``a`` not covered by the disjoint sorted intervals ``b``."""
+    out, j = [], 0
+    for s, e in a:
+        cur = s
+        while j < len(b) and b[j][1] <= cur:
+            j += 1
+        k = j
+        while k < len(b) and b[k][0] < e:
+            if b[k][0] > cur:
+                out.append([cur, min(b[k][0], e)])
+            cur = max(cur, b[k][1])
+            if cur >= e:
+                break
+            k += 1
+        if cur < e:
+            out.append([cur, e])
+    return out
+
+
+def exposed_comm_from_intervals(kernels):
+    """``kernels``: iterable of (name, start, end) device intervals of one rank (any unit).  Returns
+    (exposed, comm_total, compute_total): the time during which a communication kernel runs and no compute
+    kernel does (union of the communication intervals minus the union of the compute intervals), the union
+    of the communication intervals and the union of the compute intervals.  This is the part of the
+    communication that the step pays for; the reference's exposed points are its blocking forward
+    all-reduce (``axonn/intra_layer/fully_connected.py:119``) and the device-wide synchronisation that ends
+    every overlap window (``axonn/intra_layer/overlap_communication.py:27-30``)."""
+    comm, comp = [], []
+    for name, s, e in kernels:
+        (comm if is_comm_kernel(name) else comp).append((s, e))
+    comm_u, comp_u = _union(comm), _union(comp)
+    return _length(_subtract(comm_u, comp_u)), _length(comm_u), _length(comp_u)
+
+
+def profile_exposed_comm(step_fn):
+    """Run ``step_fn()`` once under the PyTorch profiler (device activities only) and account its kernels.
+    Returns a dict with ``exposed_comm_ms`` (communication kernels not covered by compute kernels),
+    ``comm_kernel_ms``, ``compute_kernel_ms`` and, for this package's fused kernels,
+    ``fused_comm_stall_ms``: the mean per-CTA time that the fused GEMM kernels of the step spent waiting
+    for peers (weight shards not yet arrived + the tail after the CTA's last tile in which only the
+    reduction of peer data remained), measured inside the kernels with the global timer."""
+    from torch.profiler import ProfilerActivity, profile
+
+    stall0 = fused_comm_stall(reset=True)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step_fn()
+        torch.cuda.synchronize()
+    kernels = []
+    for ev in prof.events():
+        if getattr(ev, "device_type", None) is not None and "cuda" in str(ev.device_type).lower():
+            tr = ev.time_range
+            kernels.append((ev.name, float(tr.start), float(tr.end)))
+    exposed, comm, comp = exposed_comm_from_intervals(kernels)
+    stall = fused_comm_stall(reset=True)
+    del stall0
+    return {"exposed_comm_ms": exposed / 1e3, "comm_kernel_ms": comm / 1e3, "compute_kernel_ms": comp / 1e3,
+            "fused_comm_stall_ms": stall, "kernels": len(kernels)}
+
+
+def fused_comm_stall(reset=True) -> float:
+    """Milliseconds that the fused GEMM kernels launched since the last reset spent stalled on peers, as the
+    sum over kernels of the mean over each kernel's CTAs (the CTAs of a kernel stall concurrently).  Zero when
+    the native library is absent or no GPU is present."""
+    try:
+        import ctypes
+
+        from .ops import _lib
+
+        if not (_lib.available() and torch.cuda.is_available()):
+            return 0.0
+        L = _lib.lib()
+        L.axb_comm_stall_ms.restype = ctypes.c_double
+        return float(L.axb_comm_stall_ms(ctypes.c_int(torch.cuda.current_device()), ctypes.c_int(1 if reset else 0)))
+    except Exception:  # noqa: BLE001
+        return 0.0

@@ -34,15 +34,23 @@ class AxbArCtx(ctypes.Structure):
         ("counter", ctypes.c_void_p),
         ("inbox_vecs_per_src", ctypes.c_ulonglong), ("flags_per_src", ctypes.c_ulonglong),
         ("mode", ctypes.c_int), ("rows_per_shard", ctypes.c_int),
-        ("comm_ctas", ctypes.c_int), ("pad_", ctypes.c_int),
+        ("comm_ctas", ctypes.c_int), ("loopback", ctypes.c_int),
+        ("c_off", ctypes.c_ulonglong), ("aux_off", ctypes.c_ulonglong),
+        ("arena_peer", ctypes.c_void_p * 8),
+        ("mail_local", ctypes.c_void_p), ("mail_peer", ctypes.c_void_p * 8),
     ]
+
+
+MODE_ONE_SHOT, MODE_REDUCE_SCATTER, MODE_TWO_SHOT = 0, 1, 2
+_MAIL_OFF = 512   # mailbox of the two-shot all-reduce inside the control block: n records of 32 bytes
 
 
 class _ArChannel:
     """Symmetric buffers and call counter of the fused all-reduce for one group.
 
     Layout of the symmetric allocation (same on every rank):
-      [0, 4096)        control: done[n] (u32) at 0, CTA counter (u32) at 256
+      [0, 4096)        control: done[n] (u32) at 0, CTA counter (u32) at 256, mailbox (n records of 8 u32:
+                       offsets of a peer's C and aux in its output arena + epoch) at 512
       flags[parity]    n * flags_per_src u32   (indexed [source rank][tile * 4 + warp])
       inbox[parity]    n * inbox_vecs_per_src 16-byte words, indexed [source rank][tile][warp]: bf16 partial
                        tiles pushed by every rank's GEMM epilogue (the own ones stored locally)
@@ -56,6 +64,7 @@ class _ArChannel:
         self.flags_per_src = 0
         self.inbox_vecs_per_src = 0
         self.buf = None
+        self.arena_bases = None
 
     def _layout(self):
         fbytes = self.n * self.flags_per_src * 4
@@ -100,6 +109,10 @@ class _ArChannel:
         c.flags_per_src = self.flags_per_src
         c.mode, c.rows_per_shard = mode, rows_per_shard
         c.comm_ctas = 0
+        c.loopback = 0
+        c.mail_local = me + _MAIL_OFF
+        for j in range(self.n):
+            c.mail_peer[j] = base[j] + _MAIL_OFF
         return c
 
 
@@ -183,11 +196,39 @@ def usable(group, tensor, N=None, K=None, M=None) -> bool:
     return group_usable(group, tensor)
 
 
-def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, aux=None, out_dtype=None):
+def _ar_outputs(ch, ctx, shape, dtype, device, want_aux):
+    """Allocate C (and aux) of a fused all-reduce and complete ``ctx``: from the peer-mapped output arena
+    with the two-shot protocol when the arena exists and the output is 16-bit, from ordinary memory with the
+    one-shot protocol otherwise."""
+    arena = symm.output_arena()
+    if arena is not None and dtype in (torch.bfloat16, torch.float16):
+        out = arena.empty(shape, dtype)
+        aux = arena.empty(shape, dtype) if want_aux else None
+        ctx.mode = MODE_TWO_SHOT
+        ctx.c_off = arena.offset(out)
+        ctx.aux_off = arena.offset(aux) if aux is not None else 0
+        if ch.arena_bases is None:
+            ch.arena_bases = arena.peer_bases(ch.group)
+        for j, ptr in enumerate(ch.arena_bases):
+            ctx.arena_peer[j] = ptr
+    else:
+        out = torch.empty(shape, dtype=dtype, device=device)
+        aux = torch.empty(shape, dtype=dtype, device=device) if want_aux else None
+    return out, aux
+
+
+def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, want_aux=False, out_dtype=None):
     """``all_reduce(op(a) @ op(b))`` over ``group`` (+bias, +GELU) in one kernel.
 
     layout 0: a[M,K] b[N,K] -> a b^T; layout 1: a[M,K] b[K,N] -> a b.  Every
-    rank of the group must call this with the same shapes, in the same order."""
+    rank of the group must call this with the same shapes, in the same order.
+    Returns the product, or ``(product, pre_activation)`` with ``want_aux`` (GELU epilogues).
+
+    With a peer-mapped output arena (``symm.output_arena()``) the all-reduce is two-shot: every 32-row unit of
+    a tile has one owner that receives the partials, sums them and stores the finished rows on every rank.
+    For two ranks that is the NVLink volume of the one-shot form with half the stores, half the reduction
+    work and 40 % less DRAM traffic per rank; for n ranks each element crosses NVLink 2 (n-1)/n times per rank
+    instead of n-1.  Without the arena every rank receives and sums every partial (one-shot)."""
     M, K = a.shape
     N = b.shape[0] if layout == 0 else b.shape[1]
     a = a if a.is_contiguous() else a.contiguous()
@@ -200,19 +241,19 @@ def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, aux=None,
     tiles = tiles_m * ((N + bn - 1) // bn)
     ch.ensure(tiles, bn)
     ctx = ch.context(bn)
-    out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+    out, aux = _ar_outputs(ch, ctx, (M, N), out_dtype or a.dtype, a.device, want_aux)
     st = _lib.lib().axb_gemm_ar(
         ctypes.c_int(layout), _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux),
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]),
         ctypes.c_int(epilogue), ctypes.c_int(a.device.index), _lib.stream_ptr(), ctypes.byref(ctx))
     _lib.check(st, "axb_gemm_ar")
-    return out
+    return (out, aux) if want_aux else out
 
 
 _loopback = {}
 
 
-def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None, silent_peer=False):
+def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None, silent_peer=False, two_shot=False):
     """Single-GPU emulation of a two-rank ``gemm_all_reduce`` (layout 0): the "peer" inbox, flags and done
     words are aliased onto this GPU's own slots of source rank 1, so one launch pushes its partial twice,
     reduces both copies and returns ``2 * (a @ b.T)`` (+bias, +GELU).  The kernel only ever waits on flags
@@ -222,7 +263,12 @@ def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None,
 
     ``silent_peer=True`` emulates a peer that never delivers: the flags of source rank 1 are redirected to a
     scratch area that nothing reads, so the kernel's wait for them runs into its deadline, the kernel returns
-    and the status word reports it (``ops._lib.check_status``); the context stays usable."""
+    and the status word reports it (``ops._lib.check_status``); the context stays usable.
+
+    ``two_shot=True`` runs the two-shot protocol as rank 0 of 2: the units this rank owns (32-row groups with
+    an even index) are stored for both source slots, reduced and written to the result and to a second buffer
+    that stands in for the peer's ``C``; units owned by the "peer" are only pushed.  Returns ``(out, peer_out)``:
+    both hold ``2 * (a @ b.T)`` in the owned rows, the other rows are never written."""
     M, K = a.shape
     N = b.shape[0]
     dev = a.device
@@ -260,12 +306,21 @@ def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None,
     c.inbox_vecs_per_src, c.flags_per_src = vecs_per_src, flags_per_src
     c.mode, c.rows_per_shard, c.comm_ctas = 0, 0, 0
     out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=dev)
+    peer_out = None
+    if two_shot:
+        peer_out = torch.empty_like(out)
+        c.mode, c.loopback = MODE_TWO_SHOT, 1
+        c.c_off, c.aux_off = 0, 0
+        c.arena_peer[0], c.arena_peer[1] = out.data_ptr(), peer_out.data_ptr()
+        c.mail_local = me + _MAIL_OFF
+        c.mail_peer[0] = me + _MAIL_OFF
+        c.mail_peer[1] = me + _MAIL_OFF + 32     # the "peer's" record of source 0 == own record of source 1
     rc = _lib.lib().axb_gemm_ar(
         ctypes.c_int(0), _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(None),
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]),
         ctypes.c_int(epilogue), ctypes.c_int(dev.index), _lib.stream_ptr(), ctypes.byref(c))
     _lib.check(rc, "axb_gemm_ar")
-    return out
+    return (out, peer_out) if two_shot else out
 
 
 def reduce_scatter_usable(group, a, b, rows) -> bool:
@@ -398,11 +453,12 @@ def all_gather_usable(group, x, w_shard, local_shape, layout) -> bool:
 
 
 def all_gather_gemm(layout, a, w_shard, depth_group, local_shape, ar_group=None, bias=None, epilogue=EPI_NONE,
-                    aux=None):
+                    want_aux=False):
     """``op(a) @ op(W)`` where ``W [out_l, in_l]`` is the row-wise concatenation of the depth group's flat
     shards: the gather runs inside the GEMM kernel.  layout 0: ``a[M,in_l] @ W.T``; layout 1:
     ``a[M,out_l] @ W``.  With ``ar_group`` the product is additionally all-reduced in the epilogue.
-    Returns ``(product, W)`` — ``W`` is the gathered weight left behind by the kernel."""
+    Returns ``(product, W)`` — ``W`` is the gathered weight left behind by the kernel — or
+    ``(product, W, pre_activation)`` with ``want_aux`` (GELU epilogues)."""
     out_l, in_l = local_shape
     M = a.shape[0]
     N, K = (out_l, in_l) if layout == 0 else (in_l, out_l)
@@ -413,7 +469,7 @@ def all_gather_gemm(layout, a, w_shard, depth_group, local_shape, ar_group=None,
         ch = _ag_channels[id(depth_group)] = _AgChannel(depth_group, nbytes)
     e, parity, nbytes = ch.publish(w_shard.detach())
     staging = torch.empty((out_l, in_l), dtype=w_shard.dtype, device=a.device)
-    ag = ch.context(e, parity, nbytes, staging, out_l // ch.n, n_copy=16)
+    ag = ch.context(e, parity, nbytes, staging, out_l // ch.n, n_copy=0)   # the launcher sets the CTA count
     ar_ref = None
     if ar_group is not None and dist.get_world_size(ar_group) > 1:
         arch = _channels.get(id(ar_group))
@@ -422,14 +478,18 @@ def all_gather_gemm(layout, a, w_shard, depth_group, local_shape, ar_group=None,
         tiles_m = (M + _BM - 1) // _BM
         bn = 128 if (layout == 0 and (out_l // ch.n) % 256) else (256 if tiles_m * ((N + 255) // 256) >= 148 else 128)
         arch.ensure(tiles_m * ((N + bn - 1) // bn), bn)
-        ar_ref = ctypes.byref(arch.context(bn))
-    out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+        ar_ctx = arch.context(bn)
+        out, aux_t = _ar_outputs(arch, ar_ctx, (M, N), a.dtype, a.device, want_aux)
+        ar_ref = ctypes.byref(ar_ctx)
+    else:
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+        aux_t = torch.empty((M, N), dtype=a.dtype, device=a.device) if want_aux else None
     st = _lib.lib().axb_ag_gemm(
-        ctypes.c_int(layout), _lib.ptr(a), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux), ctypes.c_int(M),
+        ctypes.c_int(layout), _lib.ptr(a), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux_t), ctypes.c_int(M),
         ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]),
         ctypes.c_int(epilogue), ctypes.c_int(a.device.index), _lib.stream_ptr(), ctypes.byref(ag), ar_ref)
     _lib.check(st, "axb_ag_gemm")
-    return out, staging
+    return (out, staging, aux_t) if want_aux else (out, staging)
 
 
 class AxbCommCtx(ctypes.Structure):

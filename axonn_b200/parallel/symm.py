@@ -30,6 +30,7 @@ _disabled_reason: Optional[str] = None
 
 def reset():
     _buffers.clear()
+    # the output arena survives a re-initialisation of the grid: it is a property of the process (world group)
 
 
 def enabled() -> bool:
@@ -97,6 +98,121 @@ def get_buffer(group, nbytes: int, tag: str) -> SymmBuffer:
         buf = SymmBuffer(group, size, tag)
         _buffers[key] = buf
     return buf
+
+
+class OutputArena:
+    """A peer-mapped address range from which the outputs of the two-shot fused all-reduce are allocated.
+
+    The two-shot all-reduce epilogue of the fused GEMM writes finished values into ``C`` on every rank, so
+    ``C`` must be memory that the peers have mapped.  One symmetric allocation of ``nbytes`` is made per
+    process (rendezvous over the world group, which therefore has to sit on one NVLink domain); a
+    ``torch.cuda.MemPool`` whose segment allocator carves that range (``csrc/arena.cu``) lets PyTorch's
+    caching allocator place ordinary tensors in it: ``arena.empty(shape, dtype)`` returns a tensor that lives
+    as long as anything references it, like any other.  Ranks need not allocate at equal offsets: every call
+    of the kernel announces its own offset to its peers through a mailbox in peer memory."""
+
+    def __init__(self, nbytes: int):
+        import ctypes
+
+        from ..ops import _lib
+
+        self.group = dist.group.WORLD
+        old = os.environ.get("TORCH_SYMM_MEM_DISABLE_MULTICAST")
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"   # plain peer stores only: no multicast binding needed
+        try:
+            self.buf = SymmBuffer(self.group, int(nbytes), "output_arena")
+        finally:
+            if old is None:
+                os.environ.pop("TORCH_SYMM_MEM_DISABLE_MULTICAST", None)
+            else:
+                os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = old
+        self.device = self.buf.local.device
+        self.base = self.buf.peer_ptrs[self.buf.rank]
+        self.nbytes = self.buf.nbytes
+        self.peer_base = list(self.buf.peer_ptrs)            # indexed by world rank
+        L = _lib.lib()
+        L.axb_arena_stat.restype = ctypes.c_ulonglong
+        rc = L.axb_arena_register(ctypes.c_int(self.device.index), ctypes.c_void_p(self.base),
+                                  ctypes.c_ulonglong(self.nbytes))
+        if rc != 0:
+            raise RuntimeError("axb_arena_register failed")
+        self._allocator = torch.cuda.memory.CUDAPluggableAllocator(_lib.LIB_PATH, "axb_arena_malloc", "axb_arena_free")
+        self.pool = torch.cuda.MemPool(self._allocator.allocator())
+
+    def empty(self, shape, dtype):
+        try:
+            with torch.cuda.use_mem_pool(self.pool, device=self.device):
+                return torch.empty(shape, dtype=dtype, device=self.device)
+        except torch.OutOfMemoryError as e:
+            raise RuntimeError(
+                f"the peer-mapped output arena ({self.nbytes / 2**30:.1f} GiB, {self.stat(0) / 2**30:.1f} GiB handed to "
+                f"the caching allocator) cannot hold another {tuple(shape)} {dtype} tensor; raise "
+                f"AXONN_SYMM_ARENA_GB, or set AXONN_TWO_SHOT=0 to keep all-reduce outputs in ordinary memory") from e
+
+    def offset(self, t) -> int:
+        off = t.data_ptr() - self.base
+        if not (0 <= off and off + t.numel() * t.element_size() <= self.nbytes):
+            raise RuntimeError("tensor does not lie in the output arena")
+        return off
+
+    def peer_bases(self, group):
+        """Arena base addresses of the ranks of ``group`` (in group order) as mapped in this process."""
+        return [self.peer_base[r] for r in dist.get_process_group_ranks(group)]
+
+    def stat(self, what: int) -> int:
+        from ..ops import _lib
+        import ctypes
+
+        return int(_lib.lib().axb_arena_stat(ctypes.c_int(self.device.index), ctypes.c_int(what)))
+
+
+_arena: Optional[OutputArena] = None
+_arena_tried = False
+
+
+def output_arena() -> Optional[OutputArena]:
+    return _arena
+
+
+def create_output_arena(nbytes: Optional[int] = None) -> Optional[OutputArena]:
+    """Create the process-wide output arena (collective over the world group; ``axonn.init`` calls it when the
+    grid has row or column tensor parallelism).  Size: ``nbytes``, else ``AXONN_SYMM_ARENA_GB``, else 40 % of
+    the device's memory.  Returns None - and the fused all-reduce stays one-shot, with outputs in ordinary
+    memory - when ``AXONN_TWO_SHOT=0``, when the world does not share one peer-memory domain, or when the
+    allocation fails on any rank."""
+    global _arena, _arena_tried
+    if _arena is not None or _arena_tried:
+        return _arena
+    _arena_tried = True
+    if not enabled() or os.environ.get("AXONN_TWO_SHOT", "1") == "0":
+        return None
+    world = dist.get_world_size()
+    if world < 2 or world > 8:
+        return None
+    from . import fused
+
+    if not fused._peer_capable(dist.group.WORLD):
+        return None
+    if nbytes is None:
+        gb = os.environ.get("AXONN_SYMM_ARENA_GB")
+        total = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+        nbytes = int(float(gb) * 2**30) if gb else int(total * 0.4)
+    nbytes = (int(nbytes) + (1 << 21) - 1) // (1 << 21) * (1 << 21)
+    ok, arena = True, None
+    try:
+        arena = OutputArena(nbytes)
+    except Exception as e:  # noqa: BLE001
+        ok = False
+        reason = str(e)
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if not bool(flag.item()):
+        if dist.get_rank() == 0:
+            print(f"axonn_b200: output arena unavailable ({reason if not ok else 'a peer failed'}); "
+                  f"fused all-reduce stays one-shot", flush=True)
+        return None
+    _arena = arena
+    return _arena
 
 
 def debug_bounds_enabled() -> bool:

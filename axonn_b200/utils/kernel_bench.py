@@ -104,18 +104,6 @@ def bench_attention(small=False):
         g_ref = torch.randn_like(o_ref)
         t_lib_bwd, _ = time_cuda(lambda: torch.autograd.grad(o_ref, (qr, kr, vr), g_ref, retain_graph=True),
                                  iters=3 if small else 10)
-        import os
-
-        if int(os.environ.get("AXB_FA_DEBUG", "0")) & 4:
-            from axonn_b200.ops import _lib
-
-            w = {i: _lib.lib().axb_debug_word(0, i, 1) for i in (2, 3, 4, 7, 8, 9, 10, 11, 12, 13)}
-            n = max(1, w[7])
-            print("bwd CTA (0,0,0), us per iteration: MMA warp waits: Q/dO %.2f, S columns free %.2f, P/dS %.2f | "
-                  "softmax warp: wait S/dP %.2f, P/dS math %.2f, wait dQ %.2f, dQ reduction %.2f (TMEM -> smem done at %.2f, "
-                  "bulk reduce issued at %.2f) (%d iterations)" % (
-                      w[2] / n / 1e3, w[3] / n / 1e3, w[4] / n / 1e3, w[8] / n / 1e3, w[9] / n / 1e3,
-                      w[10] / n / 1e3, w[11] / n / 1e3, w[12] / n / 1e3, w[13] / n / 1e3, n), flush=True)
         print(json.dumps(dict(B=B, S=S, heads=G * qpk, kv_heads=G, D=D, ms=round(t_ours, 4),
                               tflops=round(fl / t_ours / 1e9, 1), cudnn_ms=round(t_lib, 4),
                               cudnn_tflops=round(fl / t_lib / 1e9, 1), bwd_ms=round(t_bwd, 4),
@@ -133,23 +121,43 @@ FUSED_SHAPES = [
 ]
 
 
-def bench_fused(iters=8):
+def _timed_group(fn, iters, dev):
+    """ms per call: CUDA events around ``iters`` back-to-back calls after 3 warm-up calls, max over ranks."""
+    import torch.distributed as dist
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def bench_fused(iters=8, two_shot=True):
     """Fused GEMM+all-reduce vs GEMM followed by an NCCL all-reduce, on the ranks of the default group.
-    Roofline: max(FLOPs / measured bf16 peak, bytes over NVLink / 770 GB/s), bytes = M*N*2 per direction."""
+    ``two_shot``: outputs in the peer-mapped arena, every 32-row unit reduced by one owner (the default of the
+    layers); otherwise the one-shot form.  Roofline: max(FLOPs / measured bf16 peak, bytes leaving a rank over
+    NVLink / 770 GB/s); bytes = M*N*2 * (n-1) one-shot, M*N*2 * 2(n-1)/n two-shot."""
     import torch.distributed as dist
 
     from axonn_b200 import ops
     from axonn_b200.metrics import measured_peaks
-    from axonn_b200.parallel import fused
+    from axonn_b200.parallel import fused, symm
 
     rank, world = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", torch.cuda.current_device())
     peak, _, kind = measured_peaks()
     group = dist.group.WORLD
-    import os
-
-    shapes = FUSED_SHAPES[:1] if os.environ.get("AXB_AR_DEBUG") else FUSED_SHAPES
-    for M, N, K, label in shapes:
+    if two_shot:
+        assert symm.create_output_arena(4 << 30) is not None, "no output arena"
+    for M, N, K, label in FUSED_SHAPES:
         a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
 
@@ -166,23 +174,13 @@ def bench_fused(iters=8):
 
         res = {}
         for name, fn in (("fused", run_fused), ("gemm+nccl", run_unfused), ("gemm", run_gemm_only)):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            dist.barrier()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            for _ in range(iters):
-                fn()
-            e.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            res[name] = float(t.item())
-        flops, nbytes = 2.0 * M * N * K, 2.0 * M * N * (world - 1)
+            res[name] = _timed_group(fn, iters, dev)
+        flops = 2.0 * M * N * K
+        nbytes = 2.0 * M * N * (2.0 * (world - 1) / world if two_shot else (world - 1))
         roof_ms = max(flops / (peak * 1e12), nbytes / 770e9) * 1e3
         if rank == 0:
-            print(json.dumps(dict(label=label, M=M, N=N, K=K, ranks=world, fused_ms=round(res["fused"], 4),
+            print(json.dumps(dict(label=label, protocol="two-shot" if two_shot else "one-shot", M=M, N=N, K=K,
+                                  ranks=world, fused_ms=round(res["fused"], 4),
                                   gemm_nccl_ms=round(res["gemm+nccl"], 4), gemm_ms=round(res["gemm"], 4),
                                   roofline_ms=round(roof_ms, 4), fraction=round(roof_ms / res["fused"], 3),
                                   nvlink_gbs=round(nbytes / res["fused"] / 1e6, 1), peak=f"{peak} TFLOP/s {kind}")),
@@ -251,16 +249,148 @@ def bench_fused_loopback(M=16384, N=4096, K=1024, iters=3):
     t_gemm, _ = time_cuda(lambda: ops.matmul_nt(a, b), iters=iters, flush=flush)
     ref = 2.0 * (a.float() @ b.float().t())
     err = float((fused.gemm_all_reduce_loopback(a, b).float() - ref).abs().max() / ref.abs().max())
-    import os
-
-    if int(os.environ.get("AXB_AR_DEBUG", "0")) & 64:
-        from axonn_b200.ops import _lib
-
-        w = {i: _lib.lib().axb_debug_word(0, i, 1) for i in (2, 3, 7)}
-        print("reducer of CTA 0, last call: wait %.2f us/tile, work %.2f us/tile, %d tiles" % (
-            w[2] / max(1, w[7]) / 1e3, w[3] / max(1, w[7]) / 1e3, w[7]), flush=True)
+    t_two, _ = time_cuda(lambda: fused.gemm_all_reduce_loopback(a, b, two_shot=True), iters=iters, flush=flush)
     print(json.dumps(dict(label="fused GEMM+AR, two ranks emulated on one GPU", M=M, N=N, K=K,
-                          loopback_ms=round(t_loop, 4), gemm_ms=round(t_gemm, 4), rel_err=round(err, 5))), flush=True)
+                          loopback_ms=round(t_loop, 4), two_shot_loopback_ms=round(t_two, 4),
+                          gemm_ms=round(t_gemm, 4), rel_err=round(err, 5))), flush=True)
+
+
+AG_SHAPES = [
+    # (tokens, out_l, in_l, label): weight [out_l, in_l] sharded by rows over the ranks of the group
+    (16384, 28672, 4096, "Llama-8B gate|up fwd"),
+    (16384, 4096, 14336, "Llama-8B down fwd"),
+    (16384, 6144, 4096, "Llama-8B qkv fwd"),
+    (16384, 8192, 2048, "GPT-1.3B fc1 fwd"),
+]
+
+
+def bench_ag(iters=6):
+    """Fused all-gather -> GEMM (weight shards pulled over NVLink inside the GEMM kernel) against an NCCL
+    all-gather followed by the plain GEMM, and the plain GEMM alone, on the ranks of the default group.
+    Forward (A W^T) and input-gradient (A W) products.  Roofline: max(FLOPs / measured bf16 peak, bytes a rank
+    pulls over NVLink / 770 GB/s)."""
+    import torch.distributed as dist
+
+    from axonn_b200 import ops
+    from axonn_b200.metrics import measured_peaks
+    from axonn_b200.parallel import fused
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peak, _, kind = measured_peaks()
+    group = dist.group.WORLD
+    for T, out_l, in_l, label in AG_SHAPES:
+        if (out_l // world) % 128 or out_l % world:
+            continue
+        shard = (torch.randn(out_l // world, in_l, device=dev) * 0.05).bfloat16().reshape(-1)
+        full = torch.empty(out_l * in_l, device=dev, dtype=torch.bfloat16)
+        for layout, tag in ((0, "fwd  x W^T"), (1, "dgrad g W")):
+            a = torch.randn(T, in_l if layout == 0 else out_l, device=dev, dtype=torch.bfloat16)
+
+            def run_fused():
+                return fused.all_gather_gemm(layout, a, shard, group, (out_l, in_l))[0]
+
+            def run_unfused():
+                dist.all_gather_into_tensor(full, shard, group=group)
+                w = full.view(out_l, in_l)
+                return ops.matmul_nt(a, w) if layout == 0 else ops.matmul_nn(a, w)
+
+            def run_gemm_only():
+                w = full.view(out_l, in_l)
+                return ops.matmul_nt(a, w) if layout == 0 else ops.matmul_nn(a, w)
+
+            res = {n_: _timed_group(f, iters, dev) for n_, f in (("fused", run_fused), ("nccl+gemm", run_unfused),
+                                                                  ("gemm", run_gemm_only))}
+            flops = 2.0 * T * out_l * in_l
+            nbytes = 2.0 * out_l * in_l * (world - 1) / world
+            roof_ms = max(flops / (peak * 1e12), nbytes / 770e9) * 1e3
+            if rank == 0:
+                print(json.dumps(dict(label=f"{label} ({tag})", tokens=T, out_l=out_l, in_l=in_l, ranks=world,
+                                      fused_ms=round(res["fused"], 4), nccl_gemm_ms=round(res["nccl+gemm"], 4),
+                                      gemm_ms=round(res["gemm"], 4), roofline_ms=round(roof_ms, 4),
+                                      fraction=round(roof_ms / res["fused"], 3), peak=f"{peak} TFLOP/s {kind}")),
+                      flush=True)
+            del a
+        del shard, full
+
+
+def bench_rs(iters=6):
+    """Fused weight-gradient GEMM -> reduce-scatter against GEMM + NCCL reduce_scatter_tensor."""
+    import torch.distributed as dist
+
+    from axonn_b200 import ops
+    from axonn_b200.metrics import measured_peaks
+    from axonn_b200.parallel import fused
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peak, _, kind = measured_peaks()
+    group = dist.group.WORLD
+    for T, out_l, in_l, label in [(16384, 14336, 4096, "Llama-8B gate wgrad"), (16384, 4096, 4096, "Llama-8B o wgrad"),
+                                  (16384, 8192, 2048, "GPT-1.3B fc1 wgrad")]:
+        if out_l % world or (out_l // world) % 32:
+            continue
+        dy = torch.randn(T, out_l, device=dev, dtype=torch.bfloat16)
+        x = torch.randn(T, in_l, device=dev, dtype=torch.bfloat16)
+        shard = torch.empty(out_l // world, in_l, device=dev, dtype=torch.bfloat16)
+
+        def run_fused():
+            return fused.gemm_reduce_scatter(2, dy, x, group)
+
+        def run_unfused():
+            gw = ops.matmul_tn(dy, x)
+            dist.reduce_scatter_tensor(shard, gw, group=group)
+            return shard
+
+        def run_gemm_only():
+            return ops.matmul_tn(dy, x)
+
+        res = {n_: _timed_group(f, iters, dev) for n_, f in (("fused", run_fused), ("gemm+nccl", run_unfused),
+                                                              ("gemm", run_gemm_only))}
+        flops = 2.0 * T * out_l * in_l
+        nbytes = 2.0 * out_l * in_l * (world - 1) / world
+        roof_ms = max(flops / (peak * 1e12), nbytes / 770e9) * 1e3
+        if rank == 0:
+            print(json.dumps(dict(label=label, tokens=T, out_l=out_l, in_l=in_l, ranks=world,
+                                  fused_ms=round(res["fused"], 4), gemm_nccl_ms=round(res["gemm+nccl"], 4),
+                                  gemm_ms=round(res["gemm"], 4), roofline_ms=round(roof_ms, 4),
+                                  fraction=round(roof_ms / res["fused"], 3), peak=f"{peak} TFLOP/s {kind}")),
+                  flush=True)
+        del dy, x, shard
+
+
+def bench_grad_ar(iters=6):
+    """Peer-memory gradient all-reduce (+scale) of a list of tensors against flatten + NCCL all-reduce + scale +
+    unflatten.  Roofline: 2 (n-1)/n of the bytes over NVLink at 770 GB/s per direction."""
+    import torch.distributed as dist
+
+    from axonn_b200 import ops
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    group = dist.group.WORLD
+    for dtype in (torch.bfloat16, torch.float32):
+        grads = [torch.randn(n, device=dev).to(dtype) for n in [4096 * 4096] * 24 + [4096] * 48 + [50304 * 512]]
+        nbytes = sum(g.numel() * g.element_size() for g in grads)
+
+        def run_ours():
+            ops.all_reduce_bucketed_(grads, group, scale=1.0 / world)
+
+        def run_nccl():
+            flat = torch._utils._flatten_dense_tensors(grads)
+            dist.all_reduce(flat, group=group)
+            flat.mul_(1.0 / world)
+            for old, new in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+                old.copy_(new)
+
+        res = {n_: _timed_group(f, iters, dev) for n_, f in (("ours", run_ours), ("nccl", run_nccl))}
+        roof_ms = 2.0 * (world - 1) / world * nbytes / 770e9 * 1e3
+        if rank == 0:
+            print(json.dumps(dict(label="gradient all-reduce + scale", dtype=str(dtype), mbytes=round(nbytes / 2**20, 1),
+                                  tensors=len(grads), ranks=world, ours_ms=round(res["ours"], 4),
+                                  nccl_flat_ms=round(res["nccl"], 4), roofline_ms=round(roof_ms, 4),
+                                  fraction=round(roof_ms / res["ours"], 3))), flush=True)
+        del grads
 
 
 if __name__ == "__main__":
@@ -278,7 +408,7 @@ if __name__ == "__main__":
         bench_memory_bound()
     elif what == "fused_loopback":
         bench_fused_loopback()
-    elif what == "fused":
+    elif what in ("fused", "fused_one_shot", "ag", "rs", "grad_ar"):
         import os
 
         import torch.distributed as dist
@@ -286,7 +416,17 @@ if __name__ == "__main__":
         local = int(os.environ.get("LOCAL_RANK", 0))
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        bench_fused()
+        if what == "fused":
+            bench_fused(two_shot=True)
+        elif what == "fused_one_shot":
+            os.environ["AXONN_TWO_SHOT"] = "0"
+            bench_fused(two_shot=False)
+        elif what == "ag":
+            bench_ag()
+        elif what == "rs":
+            bench_rs()
+        else:
+            bench_grad_ar()
         dist.destroy_process_group()
     else:
         raise SystemExit(f"unknown benchmark {what}")

@@ -11,14 +11,19 @@ from _dist import run_distributed
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def _gemm_ar_case(rank, world):
+def _gemm_ar_case(rank, world, two_shot):
     import torch.distributed as dist
 
     from axonn_b200.ops import _lib
-    from axonn_b200.parallel import fused
+    from axonn_b200.parallel import fused, symm
 
     dev = torch.device("cuda", rank)
     group = dist.group.WORLD
+    if two_shot:
+        # outputs in a peer-mapped arena: every 32-row unit is reduced by one owner and stored on all ranks
+        assert symm.create_output_arena(1 << 30) is not None
+    else:
+        os.environ["AXONN_TWO_SHOT"] = "0"
     results = []
     for layout, (M, N, K) in [(0, (512, 512, 256)), (0, (1000, 1288, 520)), (1, (2048, 1024, 512)),
                               (0, (4096, 4096, 1024)), (1, (640, 264, 136))]:
@@ -50,9 +55,8 @@ def _gemm_ar_case(rank, world):
     b = torch.randn(N, K, device=dev).bfloat16()
     bias = torch.randn(N, device=dev).bfloat16()
     dist.broadcast(bias, src=0)
-    aux = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
     from axonn_b200 import ops
-    out = fused.gemm_all_reduce(0, a, b, group, bias=bias, epilogue=ops.EPI_BIAS_GELU, aux=aux)
+    out, aux = fused.gemm_all_reduce(0, a, b, group, bias=bias, epilogue=ops.EPI_BIAS_GELU, want_aux=True)
     ref = (a.float() @ b.float().t()).bfloat16().float()
     dist.all_reduce(ref)
     z = ref + bias.float()
@@ -72,7 +76,7 @@ def _gemm_rs_case(rank, world):
     dev = torch.device("cuda", rank)
     group = dist.group.WORLD
     out = []
-    for (M, N, K) in [(512, 256, 1024), (2048, 1024, 4096), (4096, 2048, 512), (192, 136, 264)]:
+    for (M, N, K) in [(512, 256, 1024), (2048, 1024, 4096), (4096, 2048, 512), (96 * world, 136, 264)]:
         for rep in range(2):
             g = torch.Generator(device=dev).manual_seed(31 * rank + M + rep)
             a = (torch.randn(K, M, device=dev, generator=g) * 0.5).bfloat16()   # dY  [tokens, out]
@@ -96,9 +100,12 @@ def _gemm_rs_case(rank, world):
     return out
 
 
-def test_gemm_reduce_scatter_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gemm_reduce_scatter(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    for per_rank in run_distributed(_gemm_rs_case, 2, backend="nccl", timeout=300):
+    for per_rank in run_distributed(_gemm_rs_case, world, backend="nccl", timeout=300):
         for M, N, K, status, err, scale in per_rank:
             assert status == 0
             assert err <= 1.6e-2 * scale + 1e-3, (M, N, K, err, scale)
@@ -133,9 +140,12 @@ def _grad_ar_case(rank, world):
     return out
 
 
-def test_gradient_all_reduce_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gradient_all_reduce(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    for per_rank in run_distributed(_grad_ar_case, 2, backend="nccl", timeout=300):
+    for per_rank in run_distributed(_grad_ar_case, world, backend="nccl", timeout=300):
         for name, status, err, tol, same in per_rank:
             assert status == 0 and err <= tol and same, (name, status, err)
 
@@ -149,8 +159,9 @@ def _ag_gemm_case(rank, world):
     dev = torch.device("cuda", rank)
     group = dist.group.WORLD
     out = []
-    for layout, (M, out_l, in_l) in [(0, (1024, 512, 256)), (0, (4096, 2048, 1024)), (1, (2048, 1024, 512)),
-                                     (1, (512, 256, 136)), (0, (640, 256, 72))]:
+    for layout, (M, out_l, in_l) in [(0, (1024, 256 * world, 256)), (0, (4096, 1024 * world, 1024)),
+                                     (1, (2048, 512 * world, 512)), (1, (512, 128 * world, 136)),
+                                     (0, (640, 128 * world, 72))]:
         for rep in range(3):
             g = torch.Generator(device=dev).manual_seed(1000 + rep + out_l)       # same full weight on all ranks
             W = (torch.randn(out_l, in_l, device=dev, generator=g) * 0.3).bfloat16()
@@ -166,10 +177,10 @@ def _ag_gemm_case(rank, world):
             err = (y.float() - ref).abs().max().item() / ref.abs().max().item()
             out.append((layout, M, out_l, in_l, status, err, bool(torch.equal(Wg, W))))
     # all-gather over one group combined with the all-reduce epilogue over the same ranks
-    W = (torch.randn(512, 256, device=dev, generator=torch.Generator(device=dev).manual_seed(3)) * 0.3).bfloat16()
+    W = (torch.randn(256 * world, 256, device=dev, generator=torch.Generator(device=dev).manual_seed(3)) * 0.3).bfloat16()
     shard = W[rank * 256:(rank + 1) * 256].reshape(-1).clone()
     a = torch.randn(1024, 256, device=dev).bfloat16()
-    y, _ = fused.all_gather_gemm(0, a, shard, group, (512, 256), ar_group=group)
+    y, _ = fused.all_gather_gemm(0, a, shard, group, (256 * world, 256), ar_group=group)
     ref = (a.float() @ W.float().t()).bfloat16().float()
     dist.all_reduce(ref)
     torch.cuda.synchronize()
@@ -178,17 +189,23 @@ def _ag_gemm_case(rank, world):
     return out
 
 
-def test_all_gather_gemm_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_all_gather_gemm(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    for per_rank in run_distributed(_ag_gemm_case, 2, backend="nccl", timeout=300):
+    for per_rank in run_distributed(_ag_gemm_case, world, backend="nccl", timeout=300):
         for layout, M, out_l, in_l, status, err, same in per_rank:
             assert status == 0, (layout, M, out_l, in_l, status)
             assert err < 1.6e-2 and same, (layout, M, out_l, in_l, err, same)
 
 
-def test_gemm_all_reduce_two_gpus():
+@pytest.mark.parametrize("world,two_shot", [(2, False), (2, True), (4, False), (4, True), (8, True)])
+def test_gemm_all_reduce(world, two_shot):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    res = run_distributed(_gemm_ar_case, 2, backend="nccl", timeout=300)
+    res = run_distributed(_gemm_ar_case, world, two_shot, backend="nccl", timeout=300)
     for per_rank in res:
         for r in per_rank[:-1]:
             layout, M, N, K, rep, status, err, scale = r

@@ -145,6 +145,32 @@ def test_fused_all_reduce_loopback(shape):
     assert err < 2e-2, err
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(1024, 512, 256), (8192, 4096, 512), (300, 136, 64)])
+def test_fused_two_shot_all_reduce_loopback(shape):
+    """Two-shot protocol emulated on one GPU as rank 0 of 2: the 32-row units this rank owns (even index) hold
+    2 * A B^T + bias both in the local result and in the buffer that stands in for the peer's C; the kernel's
+    mailbox, owner-only pushes, row-wise reducer and end-of-call wait all run."""
+    from axonn_b200.ops import _lib
+    from axonn_b200.parallel import fused
+
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = 2.0 * (a.float() @ b.float().t()) + bias.float()
+    for _ in range(3):
+        out, peer = fused.gemm_all_reduce_loopback(a, b, bias=bias, epilogue=1, two_shot=True)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    rows = torch.arange(M, device="cuda")
+    owned = ((rows // 32) % 2) == 0
+    scale = ref.abs().max()
+    assert (out.float()[owned] - ref[owned]).abs().max() < 2e-2 * scale
+    assert torch.equal(out[owned], peer[owned])
+
+
 def test_silent_peer_times_out_and_context_survives():
     """A peer that never raises its flags: the bounded wait of the fused kernel runs out, the kernel returns,
     the status word names the reason, and the next (healthy) call on the same buffers is correct."""
