@@ -160,7 +160,7 @@ def exposed_comm_from_intervals(kernels):
     return _length(_subtract(comm_u, comp_u)), _length(comm_u), _length(comp_u)
 
 
-def profile_exposed_comm(step_fn):
+def profile_exposed_comm(step_fn, fused_stall=True):
     """Run ``step_fn()`` once under the PyTorch profiler (device activities only) and account its kernels.
     Returns a dict with ``exposed_comm_ms`` (communication kernels not covered by compute kernels),
     ``comm_kernel_ms``, ``compute_kernel_ms`` and, for this package's fused kernels,
@@ -169,7 +169,8 @@ def profile_exposed_comm(step_fn):
     reduction of peer data remained), measured inside the kernels with the global timer."""
     from torch.profiler import ProfilerActivity, profile
 
-    stall0 = fused_comm_stall(reset=True)
+    if fused_stall:
+        fused_comm_stall(reset=True)
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         step_fn()
         torch.cuda.synchronize()
@@ -179,8 +180,7 @@ def profile_exposed_comm(step_fn):
             tr = ev.time_range
             kernels.append((ev.name, float(tr.start), float(tr.end)))
     exposed, comm, comp = exposed_comm_from_intervals(kernels)
-    stall = fused_comm_stall(reset=True)
-    del stall0
+    stall = fused_comm_stall(reset=True) if fused_stall else 0.0
     return {"exposed_comm_ms": exposed / 1e3, "comm_kernel_ms": comm / 1e3, "compute_kernel_ms": comp / 1e3,
             "fused_comm_stall_ms": stall, "kernels": len(kernels)}
 

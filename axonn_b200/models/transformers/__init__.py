@@ -1,16 +1,19 @@
 """Hugging Face Transformers integration.
 
 The reference patches ``__init__`` of specific attention / MLP classes of OPT,
-Llama, Mistral and Mixtral (``axonn/models/transformers/modify_*.py``), which
-ties it to one Transformers release.  Here the same service is architecture
-agnostic and works with current Transformers:
+Llama, Mistral and Mixtral (``axonn/models/transformers/modify_*.py``).
 
 ``parallelize(model_id_or_config=None)``
-    context manager; every ``torch.nn.Linear`` constructed inside becomes a
-    tensor-parallel ``Linear`` in easy mode (inputs/outputs keep their full
-    feature dimension, the batch is what each rank holds), so any
-    ``AutoModelForCausalLM.from_config`` / ``from_pretrained`` call builds a
-    sharded model without materialising full weights on one rank's GPU.
+    context manager.  For OPT / Llama / Mistral / Mixtral ``ForCausalLM`` the
+    architecture's attention and MLP constructors are patched (``patches.py``):
+    q/k/v and the first MLP projections shard their outputs - and with them
+    the attention heads - over the row group, the closing projections are
+    transposed layers, head counts are divided by ``G_intra_r`` where the
+    forward needs them.  For any other architecture (or no argument) every
+    ``torch.nn.Linear`` constructed inside becomes a tensor-parallel ``Linear``
+    in easy mode (inputs/outputs keep their full feature dimension, the batch
+    is what each rank holds).  Either way ``AutoModelForCausalLM.from_config``
+    builds a sharded model without materialising full weights on one GPU.
 
 ``parallelize_model(model)``
     converts an already constructed model in place, moving the existing
@@ -54,6 +57,15 @@ def parallelize(model_id_or_config=None, strict=False):
     arch = _architecture_of(model_id_or_config)
     if strict and arch not in SUPPORTED_ARCHITECTURES:
         raise ValueError(f"{arch} has not been validated for tensor parallelism")
+    if arch in SUPPORTED_ARCHITECTURES:
+        from . import patches
+
+        undo = patches.apply_patches(arch)
+        try:
+            yield None
+        finally:
+            patches.remove_patches(undo)
+        return
     with auto_parallelize():
         yield None
 

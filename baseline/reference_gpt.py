@@ -19,8 +19,12 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 
-def build(ref_axonn, cfg, device):
-    """Return (model, train_step) where train_step(tokens, targets, n_micro) -> loss tensor."""
+def build(ref_axonn, cfg, device, bf16_params=False):
+    """Return (model, train_step) where train_step(tokens, targets, n_micro) -> loss tensor.
+
+    ``bf16_params=True`` is a diagnostic variant: the whole model is cast to bf16 (no fp32 master weights, no
+    weight cast per GEMM, bf16 depth all-gathers), which is not the mixed-precision recipe the reference's
+    ``AsyncLinear`` is written for but shows how much of a speed difference is recipe and how much kernels."""
     ax = ref_axonn.axonn
     il = ref_axonn.intra_layer
     Linear, Drop = il.Linear, il.Drop
@@ -141,6 +145,8 @@ def build(ref_axonn, cfg, device):
 
     torch.manual_seed(1234)
     model = GPT().to(device)
+    if bf16_params:
+        model = model.to(torch.bfloat16)
     # parameters that are replicated inside the tensor-parallel group are ordinary
     # (non-"tensor parallel") parameters for the reference's sync_gradients
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)

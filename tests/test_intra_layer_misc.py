@@ -138,11 +138,64 @@ def _hf(rank, world):
     with parallelize(cfg, strict=True):
         m2 = transformers.LlamaForCausalLM(cfg).eval()
     assert isinstance(m2.model.layers[0].mlp.down_proj, Linear)
+    attn = m2.model.layers[0].self_attn
+    # row-parallel attention in expert mode: q/k/v hold half of the heads, o_proj reduces over the row group
+    assert attn.q_proj.expert_mode and attn.q_proj.local_out_features == 32 and attn.o_proj.transpose
     m2.load_state_dict(ref.state_dict())
     with torch.no_grad():
-        got2 = m2(half).logits
-    assert torch.allclose(got2, want[rank:rank + 1], atol=2e-4)
+        got2 = m2(ids).logits          # expert mode: the batch is replicated over the row group
+    assert torch.allclose(got2, want, atol=2e-4), (got2 - want).abs().max()
     return True
+
+
+def _hf_arch(rank, world, arch, grid):
+    """OPT / Mistral / Mixtral built inside ``parallelize``: same logits as the sequential model."""
+    transformers = pytest.importorskip("transformers")
+    from axonn_b200 import axonn as ax
+    from axonn_b200.intra_layer import Linear
+    from axonn_b200.models.transformers import parallelize
+
+    r, c = grid
+    ax.init(1, 1, G_intra_r=r, G_intra_c=c)
+    if arch == "opt":
+        cfg = transformers.OPTConfig(hidden_size=64, ffn_dim=128, num_hidden_layers=2, num_attention_heads=4,
+                                     vocab_size=128, max_position_embeddings=64, word_embed_proj_dim=64)
+        cls, name = transformers.OPTForCausalLM, "OPTForCausalLM"
+    elif arch == "mistral":
+        cfg = transformers.MistralConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                         num_attention_heads=4, num_key_value_heads=2, vocab_size=128,
+                                         max_position_embeddings=64, sliding_window=None)
+        cls, name = transformers.MistralForCausalLM, "MistralForCausalLM"
+    else:
+        cfg = transformers.MixtralConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                         num_attention_heads=4, num_key_value_heads=2, vocab_size=128,
+                                         max_position_embeddings=64, num_local_experts=4, num_experts_per_tok=2,
+                                         sliding_window=None)
+        cls, name = transformers.MixtralForCausalLM, "MixtralForCausalLM"
+    cfg.architectures = [name]
+    torch.manual_seed(0)
+    ref = cls(cfg).eval()
+    ids = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = ref(ids).logits
+    with parallelize(cfg, strict=True):
+        m = cls(cfg).eval()
+    n_tp = sum(isinstance(x, Linear) for x in m.modules())
+    assert n_tp >= 2 * 4, n_tp
+    m.load_state_dict(ref.state_dict())
+    expert = c == 1
+    feed = ids if expert else ids[rank:rank + 1]
+    with torch.no_grad():
+        got = m(feed).logits
+    target = want if expert else want[rank:rank + 1]
+    assert torch.allclose(got, target, atol=3e-4), (got - target).abs().max()
+    return True
+
+
+@pytest.mark.parametrize("arch,grid", [("opt", (2, 1)), ("mistral", (2, 1)), ("mixtral", (2, 1)), ("opt", (1, 2))])
+def test_transformers_architecture_patches(arch, grid):
+    pytest.importorskip("transformers")
+    assert all(run_distributed(_hf_arch, 2, arch, grid, timeout=400))
 
 
 def test_transformers_shim_llama():
