@@ -131,6 +131,37 @@ typedef struct AxbCommCtx {
   unsigned int* counter;
 } AxbCommCtx;
 
+/* Peer-memory context of the row all-to-all and embedding kernels (p2p.cu).  `base_peer[j]`: for the row
+ * all-to-all the base of rank j's output arena (the destination tensor of rank j lies at the offset rank j
+ * announces through the mailbox); for the embedding kernels rank j's published table shard / gradient shard.
+ * Mailbox records are 8 words per source rank: {offset lo, offset hi, -, -, epoch, -, -, -}. */
+typedef struct AxbP2pCtx {
+  int n, rank;
+  unsigned int epoch;
+  int pad;
+  void* base_peer[8];
+  unsigned int* mail_local;
+  unsigned int* mail_peer[8];
+  unsigned int* done_local;
+  unsigned int* done_peer[8];
+  unsigned int* counter;       /* two words: CTA counter, failed-CTA counter (zero between calls) */
+  unsigned long long out_off;  /* row all-to-all: byte offset of my output tensor inside my arena */
+} AxbP2pCtx;
+
+/* One row block per destination rank: `rows` rows of `row_bytes` bytes, read from `src` with pitch `src_pitch`
+ * and stored into the destination's output at byte offset `dst_off` with pitch `dst_pitch` (all multiples of 16). */
+typedef struct AxbRowBlock {
+  const void* src;
+  long long src_pitch, dst_off, dst_pitch, rows, row_bytes;
+} AxbRowBlock;
+
+int axb_a2a_rows(const AxbP2pCtx* ctx, const AxbRowBlock* blocks /* [n] */, int device, void* stream);
+int axb_p2p_publish(const AxbP2pCtx* ctx, int device, void* stream);
+int axb_embedding_fetch(const long long* ids, long long n_tokens, void* out, long long row_bytes,
+                        long long rows_per_shard, const AxbP2pCtx* ctx, int device, void* stream);
+int axb_embedding_scatter_add(const long long* ids, long long n_tokens, const void* dy_bf16, int H,
+                              long long rows_per_shard, const AxbP2pCtx* ctx, int device, void* stream);
+
 int axb_bucket_copy(const long long* table, int ntensors, long long total_chunks, void* bucket, int dtype, int direction,
                     const AxbCommCtx* ctx, int device, void* stream);
 int axb_allreduce_twoshot(long long nbytes, int dtype, float scale, const AxbCommCtx* ctx, int device, void* stream);

@@ -62,7 +62,9 @@ struct GemmParams {
   AxbAgCtx ag;  // ag.n <= 1: B is complete; otherwise B's row blocks are gathered from the peers in-kernel
   int tn_offset;  // rotation of the N-tile order (all-gather mode: tiles of the local shard first)
   int kb_offset;  // rotation of the K-block order (all-gather mode, B rows = K: local shard first)
-  int gemm_ctas;  // number of CTAs computing tiles; the remaining CTAs of the grid reduce over peer memory
+  int gemm_ctas;  // number of CTAs in the grid (every CTA computes tiles and, in the fused modes, reduces them)
+  int pair;       // 1: CTA pairs (clusters of two) compute 256 x BN tiles, each CTA owning 128 rows of them
+  int flag_batch; // tiles whose partial-arrival flags share one system-scope fence (fused all-reduce / reduce-scatter)
   int debug;      // ablation builds only (-DAXB_ABLATION, then read once from AXB_AR_DEBUG; otherwise 0 and every branch on it is compiled out): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores, 128 register-path reducer instead of the shared-memory ring
 };
 
@@ -72,15 +74,15 @@ struct GemmParams {
 // contributes the mean over its CTAs.  Read by axb_comm_stall_ms.
 static __device__ unsigned long long g_comm_stall;
 
-template <int BN>
+template <int BN, bool PAIR = false>
 struct GemmSmem {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;   // a CTA of a pair stages its half of the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 256 && !PAIR) ? 4 : 6;
   // Two-rank all-reduce with 128x256 tiles: the operand ring runs with RING_STAGES stages and the space
   // behind them stages the inbox slots that the reducer warps sum (2 groups x 2 ranks x 16 KB, bulk copies).
-  static constexpr int RING_STAGES = 3;
+  static constexpr int RING_STAGES = PAIR ? 4 : 3;
   static constexpr int RING_SLOT_BYTES = 32 * BN * 2;          // one (tile, warp) slot of one rank
   static constexpr int RING_OFFSET = RING_STAGES * STAGE_BYTES;
   static constexpr int RING_BYTES = (BN == 256) ? 4 * RING_SLOT_BYTES : 0;
@@ -104,6 +106,32 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   const int r = tile - g * per_group;
   tm = first_m + r % gsize;
   tn = r / gsize;
+}
+
+// Tile schedule of a CTA.  Single CTAs walk the tile list with stride = grid size; CTA pairs walk the list of
+// 256-row tile pairs with stride = number of pairs and each CTA of a pair takes the 128 rows of its cluster rank.
+// `tile` is the index under which a 128 x BN tile is known to the communication buffers (inbox slots, flags):
+// the same on every rank for the same rows and columns of C.
+struct Sched { int first, total, stride, crank; };
+template <bool PAIR>
+__device__ __forceinline__ Sched make_sched(const GemmParams& p) {
+  Sched s;
+  if (PAIR) {
+    s.crank = static_cast<int>(cluster_cta_rank());
+    s.first = blockIdx.x >> 1; s.stride = gridDim.x >> 1; s.total = ((p.tiles_m + 1) >> 1) * p.tiles_n;
+  } else {
+    s.crank = 0; s.first = blockIdx.x; s.stride = p.gemm_ctas; s.total = p.tiles_m * p.tiles_n;
+  }
+  return s;
+}
+template <bool PAIR>
+__device__ __forceinline__ void sched_tile(const GemmParams& p, const Sched& s, int it, int group, int& tile, int& tm, int& tn) {
+  if (PAIR) {
+    int tm2; tile_coords(it, (p.tiles_m + 1) >> 1, p.tiles_n, 8, tm2, tn);
+    tm = 2 * tm2 + s.crank; tile = it * 2 + s.crank;
+  } else {
+    tile_coords(it, p.tiles_m, p.tiles_n, group, tm, tn); tile = it;
+  }
 }
 
 template <typename T>
@@ -313,8 +341,8 @@ __device__ __forceinline__ void acc_vec8(float* acc, const uint4& u, int dtype) 
 // (bounded) until the (tile, warp) flags of all ranks are up, performs the acquire fence once per tile and
 // publishes the count of ready tiles in shared memory, so that polling global memory and the system-scope
 // fence overlap the reduction of the previous tile instead of preceding each one.
-template <int BN>
-__device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
+template <int BN, bool PAIR>
+__device__ __forceinline__ void watcher_thread(const GemmParams& p, const Sched& sc, int group, volatile int* abort_flag,
                                                volatile unsigned int* ready_tiles, unsigned long long* peer_out,
                                                uint8_t* ring = nullptr, uint64_t* ring_full = nullptr,
                                                uint64_t* ring_empty = nullptr) {
@@ -338,8 +366,8 @@ __device__ __forceinline__ void watcher_thread(const GemmParams& p, int group, i
     }
     __threadfence_block();
   }
-  for (int tile = blockIdx.x; tile < num_tiles; tile += p.gemm_ctas, ++t) {
-    int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+  for (int it_ = sc.first; it_ < sc.total; it_ += sc.stride, ++t) {
+    int tile, tm, tn; sched_tile<PAIR>(p, sc, it_, group, tile, tm, tn);
     const unsigned mine = unit_mask(p, tile, tm);
     if (mine != 0) {
       // the four (tile, warp) flags of a rank are one aligned 16-byte word
@@ -403,8 +431,8 @@ __device__ __forceinline__ uint4 ld_cg_ordered(const uint4* ptr) {
 // keeps a loaded word from being consumed before every load that precedes this statement was issued
 __device__ __forceinline__ void pin(uint4& v) { asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)); }
 
-template <int BN, int NR>
-__device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
+template <int BN, int NR, bool PAIR>
+__device__ __forceinline__ void reducer_warps(const GemmParams& p, const Sched& sc, int group, volatile int* abort_flag,
                                               volatile unsigned int* ready_tiles, const unsigned long long* peer_out) {
   constexpr int CH = BN / 32;                 // 32-column chunks per tile row
   constexpr int WVEC = CH * 4 * 32;           // 16-byte words per (tile, warp) slot
@@ -417,9 +445,9 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
   int t = -1;
   const bool probe = AXB_DBG(p, 64) && blockIdx.x == 0 && tid == 0;
   uint64_t ns_wait = 0, ns_work = 0, ns_mark = probe ? globaltimer_ns() : 0;
-  for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
+  for (int it_ = sc.first; it_ < sc.total && ok; it_ += sc.stride) {
     ++t;
-    int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+    int tile, tm, tn; sched_tile<PAIR>(p, sc, it_, group, tile, tm, tn);
     const unsigned mine = unit_mask(p, tile, tm);
     if (mine == 0) continue;
     if (tid == 0) {
@@ -518,8 +546,8 @@ __device__ __forceinline__ void reducer_warps(const GemmParams& p, int group, in
 // reads hit distinct banks), sums the two ranks in rank order, applies bias / GELU and stores 16 bytes: one warp
 // instruction writes 512 contiguous bytes of a row of C - locally and, in the two-shot all-reduce, over NVLink
 // into the peer's C as well - then the group is handed back.
-template <int BN>
-__device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int num_tiles, volatile int* abort_flag,
+template <int BN, bool PAIR>
+__device__ __forceinline__ void reducer_ring(const GemmParams& p, const Sched& sc, int group, volatile int* abort_flag,
                                              uint8_t* ring, uint64_t* ring_full, uint64_t* ring_empty,
                                              const unsigned long long* peer_out) {
   constexpr int CH = BN / 32;
@@ -531,8 +559,8 @@ __device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int
   const unsigned long long* peers = p.ar.mode == 2 ? peer_out : nullptr;
   bool ok = true;
   int consumed = 0;                           // ring group = consumed & 1, phase = (consumed >> 1) & 1
-  for (int tile = blockIdx.x; tile < num_tiles && ok; tile += p.gemm_ctas) {
-    int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+  for (int it_ = sc.first; it_ < sc.total && ok; it_ += sc.stride) {
+    int tile, tm, tn; sched_tile<PAIR>(p, sc, it_, group, tile, tm, tn);
     const unsigned mine = unit_mask(p, tile, tm);
     for (int q = 0; q < 4; ++q) {
       if (!(mine & (1u << q))) continue;
@@ -578,7 +606,7 @@ __device__ __forceinline__ void reducer_ring(const GemmParams& p, int group, int
 template <int BN>
 __device__ __forceinline__ void ag_puller(const GemmParams& p, uint8_t* buf, uint64_t* pull_bar,
                                           volatile int* abort_flag) {
-  constexpr uint32_t CHB = GemmSmem<BN>::PULL_BUF_BYTES;
+  constexpr uint32_t CHB = GemmSmem<BN, false>::PULL_BUF_BYTES;
   const unsigned long long total = p.ag.shard_bytes;
   unsigned long long per = (total + gridDim.x - 1) / gridDim.x;
   per = (per + 15ull) & ~15ull;                              // bulk copies move multiples of 16 bytes
@@ -635,11 +663,15 @@ __device__ __forceinline__ void ag_puller(const GemmParams& p, uint8_t* buf, uin
   }
 }
 
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
-  using S = GemmSmem<BN>;
+  // PAIR: launched as clusters of two CTAs (tcgen05.mma.cta_group::2): the pair computes a 256 x BN tile, each
+  // CTA stages its own 128 rows of A and its half of the B tile (no multicast loads), the even CTA issues the
+  // MMAs for both, and each CTA's epilogue, flagger, watcher and reducer warps handle the 128 rows held in its
+  // own TMEM exactly like a single CTA handles a 128 x BN tile.
+  using S = GemmSmem<BN, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
@@ -659,17 +691,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int num_tiles = p.tiles_m * p.tiles_n;
   const int group = (BN == 256) ? 16 : 8;
   const uint64_t timeout = p.timeout_ns;
-  const int gemm_ctas = p.gemm_ctas;   // == gridDim.x: every CTA computes tiles (and reduces them in comm mode)
-  // two ranks, 128x256 tiles: the reducer stages inbox slots in shared memory behind a 3-stage operand ring
+  const Sched sc = make_sched<PAIR>(p);
+  const int crank = sc.crank;           // rank inside the CTA pair (0 without pairs)
+  // two ranks, 128x256 tiles: the reducer stages inbox slots in shared memory behind a shortened operand ring
   const bool ring_mode = BN == 256 && p.ar.n == 2 && !AXB_DBG(p, 128);
   const int nstages = ring_mode ? S::RING_STAGES : S::STAGES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], PAIR ? 8 : 4); }
     for (int b = 0; b < 2; ++b) { mbar_init(&ring_full[b], 1); mbar_init(&ring_empty[b], REDUCER_THREADS / 32); }
     for (int b = 0; b < 2; ++b) mbar_init(&pull_bar[b], 1);
     *abort_flag = 0;
@@ -679,9 +711,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
-  if (warp == 1) { tmem_alloc(tmem_ptr_smem, 2 * BN); tmem_relinquish(); }
+  if (warp == 1) {
+    if (PAIR) { tmem_alloc_pair(tmem_ptr_smem, 2 * BN); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_ptr_smem, 2 * BN); tmem_relinquish(); }
+  }
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) { __syncwarp(); cluster_sync_all(); }   // both CTAs' barriers exist before any remote arrival or TMA signal
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -717,10 +753,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t armed_mask = 0, armed_parity = 0;
       uint32_t ag_ready_mask = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas) {
-        int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+      for (int it_ = sc.first; it_ < sc.total && ok; it_ += sc.stride) {
+        int tile, tm, tn; sched_tile<PAIR>(p, sc, it_, group, tile, tm, tn);
         tn += p.tn_offset; if (tn >= p.tiles_n) tn -= p.tiles_n;
-        const int m0 = tm * BM, n0 = tn * BN;
+        const int m0 = tm * BM, n0 = tn * BN + (PAIR ? crank * (BN / 2) : 0);   // a pair's CTA loads its half of the B tile
         for (int kbi = 0; kbi < num_kb; ++kbi) {
           int kb = kbi + p.kb_offset; if (kb >= num_kb) kb -= num_kb;
           if (p.ag.n > 1) {
@@ -749,21 +785,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, timeout)) { ok = false; break; }
           uint8_t* sA = smem + stage * S::STAGE_BYTES;
           uint8_t* sB = sA + S::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
-          armed_mask |= 1u << stage;
-          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
           const int k0 = kb * BK;
-          if (A_MN == 0) {
-            tma_load_2d(sA, &tmA, &full_bar[stage], k0, m0);
-          } else {
+          if (PAIR) {
+            // the leader's barrier counts the bytes of both CTAs' loads of this stage
+            if (crank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+            if (A_MN == 0) {
+              tma_load_2d_pair(sA, &tmA, &full_bar[stage], k0, m0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * j, k0);
-          }
-          if (B_MN == 0) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], k0, n0);
-          } else {
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sA + j * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * j, k0);
+            }
+            if (B_MN == 0) {
+              tma_load_2d_pair(sB, &tmB, &full_bar[stage], k0, n0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0);
+              for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0);
+            }
+          } else {
+            mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+            armed_mask |= 1u << stage;
+            armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+            if (A_MN == 0) {
+              tma_load_2d(sA, &tmA, &full_bar[stage], k0, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * j, k0);
+            }
+            if (B_MN == 0) {
+              tma_load_2d(sB, &tmB, &full_bar[stage], k0, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0);
+            }
           }
           if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
@@ -782,8 +835,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      const uint32_t idesc = umma_idesc(p.in_dtype == 0 ? 1 : 0, A_MN, B_MN, BM, BN);
+    if ((!PAIR || crank == 0) && elect_one()) {   // in a pair the even CTA issues for both
+      const uint32_t idesc = umma_idesc(p.in_dtype == 0 ? 1 : 0, A_MN, B_MN, PAIR ? 2 * BM : BM, BN);
       // K-major: 8-row groups 1024 B apart, K step = 32 B inside the swizzle row.
       // MN-major: 64-wide MN chunks BK*128 B apart (leading), 8-K-row groups
       // 1024 B apart (stride), K step = 16 rows * 128 B.
@@ -792,7 +845,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++t) {
+      for (int it_ = sc.first; it_ < sc.total && ok; it_ += sc.stride, ++t) {
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
         if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, timeout)) { ok = false; break; }
@@ -807,12 +860,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adesc = umma_smem_desc(a_addr + k * a_kstep, a_lbo, a_sbo);
             const uint64_t bdesc = umma_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);
+          if (PAIR) umma_commit_pair(&empty_bar[stage]);   // frees the stage in both CTAs
+          else umma_commit(&empty_bar[stage]);
           if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&tmem_full[buf]);
+        if (ok) { if (PAIR) umma_commit_pair(&tmem_full[buf]); else umma_commit(&tmem_full[buf]); }
       }
       if (!ok) {
         // MMAs issued before the abort may still be running: give them time before TMEM is released
@@ -830,12 +885,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (p.ag.n > 1 && lane == 16) {
       ag_puller<BN>(p, smem + S::PULL_OFFSET, pull_bar, abort_flag);
     } else if (p.ar.n > 1 && lane == 0) {
-      int t = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gemm_ctas, ++t) {
-        int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+      // The system-scope fence is the expensive part (it waits for every store the SM has in flight over
+      // NVLink), so the flags of `flag_batch` consecutive tiles share one fence; the last tiles of the CTA
+      // are published one by one so that the peers' reducers do not wait at the end of the kernel.
+      const int my_tiles = sc.first < sc.total ? (sc.total - sc.first + sc.stride - 1) / sc.stride : 0;
+      int batch = p.flag_batch < 1 ? 1 : p.flag_batch;
+      int t = 0, published = 0;
+      bool good = true;
+      while (published < my_tiles && good) {
+        const int upto = (my_tiles - published <= batch) ? published + 1 : published + batch;   // tiles [published, upto)
         uint64_t t0 = 0;
-        bool good = true;
-        for (uint32_t it = 0; static_cast<int>(*parts_done - 4u * (t + 1)) < 0; ++it) {
+        for (uint32_t it = 0; static_cast<int>(*parts_done - 4u * upto) < 0; ++it) {
           if ((it & 0xff) == 0xff) {
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
@@ -844,34 +904,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (!good) break;
         if (!AXB_DBG(p, 1)) __threadfence_system();
-        for (int qq = 0; qq < 4; ++qq) {
-          const int own = unit_owner(p, tile, tm, qq);
-          for (int j = 0; j < p.ar.n; ++j) {
-            if (own >= 0 && j != own && !(p.ar.loopback && own == p.ar.rank)) continue;
-            unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
-                              static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + qq;
-            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar.epoch) : "memory");
+        for (t = published; t < upto; ++t) {
+          int tile, tm, tn; sched_tile<PAIR>(p, sc, sc.first + t * sc.stride, group, tile, tm, tn);
+          for (int qq = 0; qq < 4; ++qq) {
+            const int own = unit_owner(p, tile, tm, qq);
+            for (int j = 0; j < p.ar.n; ++j) {
+              if (own >= 0 && j != own && !(p.ar.loopback && own == p.ar.rank)) continue;
+              unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
+                                static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + qq;
+              asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar.epoch) : "memory");
+            }
           }
         }
+        published = upto;
       }
     }
   } else if (warp == WATCHER_WARP) {
     if (p.ar.n > 1 && lane == 0) {
-      if (ring_mode) watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles, peer_out, smem + S::RING_OFFSET, ring_full, ring_empty);
-      else watcher_thread<BN>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
+      if (ring_mode) watcher_thread<BN, PAIR>(p, sc, group, abort_flag, ready_tiles, peer_out, smem + S::RING_OFFSET, ring_full, ring_empty);
+      else watcher_thread<BN, PAIR>(p, sc, group, abort_flag, ready_tiles, peer_out);
     }
   } else if (warp >= 6) {
     bool done = false;
     if constexpr (BN == 256) {
       if (ring_mode) {
-        reducer_ring<BN>(p, group, num_tiles, abort_flag, smem + S::RING_OFFSET, ring_full, ring_empty, peer_out);
+        reducer_ring<BN, PAIR>(p, sc, group, abort_flag, smem + S::RING_OFFSET, ring_full, ring_empty, peer_out);
         done = true;
       }
     }
     if (done) {
-    } else if (p.ar.n == 2) reducer_warps<BN, 2>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
-    else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
-    else if (p.ar.n > 4) reducer_warps<BN, 8>(p, group, num_tiles, abort_flag, ready_tiles, peer_out);
+    } else if (p.ar.n == 2) reducer_warps<BN, 2, PAIR>(p, sc, group, abort_flag, ready_tiles, peer_out);
+    else if (p.ar.n > 2 && p.ar.n <= 4) reducer_warps<BN, 4, PAIR>(p, sc, group, abort_flag, ready_tiles, peer_out);
+    else if (p.ar.n > 4) reducer_warps<BN, 8, PAIR>(p, sc, group, abort_flag, ready_tiles, peer_out);
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -898,8 +962,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (store_ok) store_row32(p.C, p.out_dtype, out_row, p.N, col, p.N, v, p.accumulate != 0);
     };
 
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++t) {
-      int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, group, tm, tn);
+    for (int it_ = sc.first; it_ < sc.total && ok; it_ += sc.stride, ++t) {
+      int tile, tm, tn; sched_tile<PAIR>(p, sc, it_, group, tile, tm, tn);
       tn += p.tn_offset; if (tn >= p.tiles_n) tn -= p.tiles_n;
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
@@ -923,7 +987,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        if (lane == 0) { if (PAIR) mbar_arrive_leader(&tmem_empty[buf]); else mbar_arrive(&tmem_empty[buf]); }
         continue;
       }
       // ---- communication mode: the epilogue moves this warp's bf16 partial (32 rows x BN columns) out of
@@ -965,7 +1029,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);   // accumulator is free: the MMA warp runs ahead
+      if (lane == 0) { if (PAIR) mbar_arrive_leader(&tmem_empty[buf]); else mbar_arrive(&tmem_empty[buf]); }   // accumulator is free: the MMA warp runs ahead
       // hand the stored partial to the flagger warp (release at CTA scope on a monotonic counter)
       if (lane == 0) {
         __threadfence_block();
@@ -978,7 +1042,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+  if (PAIR) {
+    // the peer CTA's shared memory and TMEM stay valid until every MMA and remote arrival of the pair is done
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 1) { tcgen05_fence_after(); tmem_dealloc_pair(tmem_base, 2 * BN); }
+  } else if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
   if (p.ag.n > 1 && threadIdx.x == 32) {
     __threadfence();
     if (atomicAdd(p.ag.counter, 1u) == gridDim.x - 1) {
@@ -1272,11 +1341,40 @@ int sm_count_current() {
   return sm_count(dev);
 }
 
+// Communicating GEMM on CTA pairs: the kernel above with PAIR = true, launched as clusters of two.
+template <int A_MN, int B_MN>
+static int launch_comm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int device, cudaStream_t stream) {
+  using S = GemmSmem<256, true>;
+  static bool configured[64] = {false};
+  auto kern = gemm_tcgen05_kernel<256, A_MN, B_MN, true>;
+  if (!configured[device & 63]) {
+    AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured[device & 63] = true;
+  }
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + 255) / 256;
+  p.pair = 1;
+  const int total = ((p.tiles_m + 1) / 2) * p.tiles_n;
+  const int pairs = sm_count(device) / 2;
+  const int grid = 2 * (total < pairs ? total : pairs);
+  p.gemm_ctas = grid;
+  if (p.ag.n > 1) { p.ag.n_copy = grid; p.ag.ready_target = static_cast<unsigned int>(grid); }   // every CTA pulls a slice
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = S::TOTAL; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  AXB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p));
+  return 0;
+}
+
 template <int BN, int A_MN, int B_MN>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int device, cudaStream_t stream) {
   using S = GemmSmem<BN>;
   static bool configured[64] = {false};
-  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, false>;
+  p.pair = 0;
   if (!configured[device & 63]) {
     AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
     configured[device & 63] = true;
@@ -1314,6 +1412,17 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   return 0;
 }
 
+// Tiles per system-scope fence in the fused reductions (AXONN_FLAG_BATCH, default 4, 1..16).
+static int flag_batch_setting() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("AXONN_FLAG_BATCH");
+    int b = e ? atoi(e) : 4;
+    v = b < 1 ? 1 : (b > 16 ? 16 : b);
+  }
+  return v;
+}
+
 // CTA pairs are used for plain GEMMs wide enough to fill the GPU with 256x256 tiles (AXONN_GEMM_2CTA=0 disables).
 static bool pair_mode_enabled() {
   static int v = -1;
@@ -1338,7 +1447,14 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
   const int tiles_m = (M + BM - 1) / BM;
   const bool wide = static_cast<long long>(tiles_m) * ((N + 255) / 256) >= sm_count(device);
   int BN = (ar && ar->n > 1) ? ar->bn : (wide ? 256 : 128);
-  if (ag && ag->n > 1 && layout == 0 && ag->rows_per_shard % BN != 0) BN = 128;
+  const bool comm = (ar && ar->n > 1) || (ag && ag->n > 1);
+  const bool enough_pairs = static_cast<long long>((tiles_m + 1) / 2) * ((N + 255) / 256) >= sm_count(device) / 2;
+  // Communicating GEMMs run on CTA pairs too (same main loop as the plain pair kernel) when the problem fills
+  // the GPU with 256-wide tiles; a gathered B (layout 0) then needs shards that are multiples of the 128 rows
+  // one CTA of a pair loads.
+  const bool comm_pair = comm && BN == 256 && enough_pairs && pair_mode_enabled() &&
+                         !(ag && ag->n > 1 && layout == 0 && ag->rows_per_shard % 128 != 0);
+  if (!comm_pair && ag && ag->n > 1 && layout == 0 && ag->rows_per_shard % BN != 0) BN = 128;
   const int a_mn = (layout == 2) ? 1 : 0;
   const int b_mn = (layout == 0) ? 0 : 1;
 
@@ -1346,10 +1462,8 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
   // K-major operand [R, K]: box 64(K) x tile rows.  MN-major operand [K, R]: box 64(R) x 64(K).
   if (a_mn == 0) { if (make_tmap_2d_16bit(&tmA, A, M, K, BM, in_dtype)) return -1; }
   else           { if (make_tmap_2d_16bit(&tmA, A, K, M, BK, in_dtype)) return -1; }
-  const bool comm = (ar && ar->n > 1) || (ag && ag->n > 1);
-  const bool pair = !comm && BN == 256 && pair_mode_enabled() &&
-                    static_cast<long long>((tiles_m + 1) / 2) * ((N + 255) / 256) >= sm_count(device) / 2;
-  if (b_mn == 0) { if (make_tmap_2d_16bit(&tmB, B, N, K, pair ? BN / 2 : BN, in_dtype)) return -1; }
+  const bool pair = !comm && BN == 256 && pair_mode_enabled() && enough_pairs;
+  if (b_mn == 0) { if (make_tmap_2d_16bit(&tmB, B, N, K, (pair || comm_pair) ? BN / 2 : BN, in_dtype)) return -1; }
   else           { if (make_tmap_2d_16bit(&tmB, B, K, N, BK, in_dtype)) return -1; }
 
   GemmParams p;
@@ -1358,7 +1472,8 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
   p.status = status_dev; p.timeout_ns = wait_timeout_ns();
   if (ar && ar->n > 1) {
     p.ar = *ar;
-    const long long tiles = static_cast<long long>(tiles_m) * ((N + BN - 1) / BN);
+    // CTA pairs index tiles by (pair, CTA of the pair): an odd number of tile rows leaves one unused index per column
+    const long long tiles = static_cast<long long>(comm_pair ? (tiles_m + 1) / 2 * 2 : tiles_m) * ((N + BN - 1) / BN);
     if (tiles * 4 > ar->flags_per_src || tiles * 4 * (BN / 32) * 128 > ar->inbox_vecs_per_src) {
       set_error("axb_gemm_ar: communication buffers too small for %lld tiles", tiles);
       return -1;
@@ -1367,6 +1482,7 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
     p.ar.n = 1;
   }
   p.tn_offset = 0; p.kb_offset = 0;
+  p.flag_batch = flag_batch_setting();
   p.debug = 0;
 #ifdef AXB_ABLATION
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("AXB_AR_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
@@ -1375,8 +1491,8 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
     p.ag = *ag;
     AXB_CUDA(cudaMemsetAsync(p.ag.shard_ready, 0, 8 * sizeof(unsigned int), static_cast<cudaStream_t>(stream)));
     if (layout == 0) {
-      if (ag->rows_per_shard % BN != 0 || static_cast<long long>(ag->rows_per_shard) * ag->n != N) {
-        set_error("axb_ag_gemm: shard rows (%d) must be a multiple of the tile width %d and n*rows == N", ag->rows_per_shard, BN);
+      if (ag->rows_per_shard % (comm_pair ? 128 : BN) != 0 || static_cast<long long>(ag->rows_per_shard) * ag->n != N) {
+        set_error("axb_ag_gemm: shard rows (%d) must be a multiple of %d and n*rows == N", ag->rows_per_shard, comm_pair ? 128 : BN);
         return -1;
       }
       // With the all-reduce epilogue every rank must walk the tiles in the same order (partials are matched
@@ -1396,6 +1512,11 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
     p.ag.n = 1;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (comm_pair) {
+    if (layout == 0) return launch_comm_pair<0, 0>(tmA, tmB, p, device, s);
+    if (layout == 1) return launch_comm_pair<0, 1>(tmA, tmB, p, device, s);
+    return launch_comm_pair<1, 1>(tmA, tmB, p, device, s);
+  }
   if (pair) {
     if (layout == 0) return launch_pair<0, 0>(tmA, tmB, p, device, s);
     if (layout == 1) return launch_pair<0, 1>(tmA, tmB, p, device, s);

@@ -21,7 +21,7 @@ import torch.nn as nn
 
 from .. import axonn as ax
 from .. import ops
-from ..intra_layer import Linear
+from ..intra_layer import Gather, Linear
 from ..utils import divide
 
 
@@ -140,16 +140,33 @@ class TransformerBlock(nn.Module):
 
 
 class ParallelLMHead(nn.Module):
-    """Final projection to a vocabulary split over the row group + parallel cross-entropy."""
+    """Final projection to a vocabulary split over the whole row x column grid + parallel cross-entropy.
+
+    With a column group of one the projection is the ordinary non-transposed layer (vocabulary over the row
+    group).  With ``G_intra_c > 1`` that layer would all-reduce the ``[tokens, vocab / r]`` logits over the
+    column group - by far the largest tensor of the model.  Instead the hidden dimension of the input is
+    all-gathered over the column group (``tokens x hidden``, small) and the vocabulary is split over all
+    ``r * c`` ranks (a per-layer ``tensor_parallel_dims=(r*c, 1, d)``): the logits need no reduction at all,
+    the input gradient is all-reduced over the ``r * c`` ranks, and the gather's backward keeps this rank's
+    hidden chunk of that (already complete) gradient."""
 
     def __init__(self, hidden, vocab, dtype=None):
         super().__init__()
-        _, outer = _groups()
-        self.group = outer if dist.get_world_size(outer) > 1 else None
+        inner, outer = _groups()
+        r, c = dist.get_world_size(outer), dist.get_world_size(inner)
+        self.gather_group = None
+        dims = None
+        if c > 1 and vocab % (r * c) == 0:
+            self.gather_group = inner
+            dims = (r * c, 1, ax.config.G_intra_d)
         self.proj = Linear(hidden, vocab, bias=False, expert_mode=True, dtype=dtype,
-                           init_method=lambda w: nn.init.normal_(w, std=0.02))
+                           init_method=lambda w: nn.init.normal_(w, std=0.02), tensor_parallel_dims=dims)
+        vocab_group = self.proj.outer_group
+        self.group = vocab_group if dist.get_world_size(vocab_group) > 1 else None
 
     def forward(self, x, targets=None):
+        if self.gather_group is not None:
+            x = Gather.apply(x, self.gather_group, -1)
         logits = self.proj(x)
         if targets is None:
             return logits

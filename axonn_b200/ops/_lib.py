@@ -16,7 +16,8 @@ import torch
 _LIB = None
 _LOCK = threading.Lock()
 LIB_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib")
-LIB_PATH = os.path.join(LIB_DIR, "libaxonn_b200.so")
+# AXONN_LIB_PATH selects a library built elsewhere (e.g. an ablation build with -DAXB_ABLATION)
+LIB_PATH = os.environ.get("AXONN_LIB_PATH") or os.path.join(LIB_DIR, "libaxonn_b200.so")
 
 # number of kernels launched through this library since the last reset
 launch_count = 0

@@ -25,6 +25,14 @@ _BM = 128
 _CTRL_BYTES = 4096
 
 
+def _tile_geometry(M, N):
+    """(tile width, number of tile indices) the kernel uses for an M x N product: 256-wide tiles when they
+    fill the GPU, and tile rows rounded up to an even count because CTA pairs index tiles by (pair, CTA)."""
+    tiles_m = (M + _BM - 1) // _BM
+    bn = 256 if tiles_m * ((N + 255) // 256) >= 148 else 128
+    return bn, (tiles_m + 1) // 2 * 2 * ((N + bn - 1) // bn)
+
+
 class AxbArCtx(ctypes.Structure):
     _fields_ = [
         ("n", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint), ("bn", ctypes.c_int),
@@ -124,6 +132,8 @@ def reset():
     _grad_channels.clear()
     _ag_channels.clear()
     _group_ok.clear()
+    _a2a_channels.clear()
+    _emb_channels.clear()
 
 
 _group_ok = {}
@@ -236,9 +246,7 @@ def gemm_all_reduce(layout, a, b, group, bias=None, epilogue=EPI_NONE, want_aux=
     ch = _channels.get(id(group))
     if ch is None:
         ch = _channels[id(group)] = _ArChannel(group)
-    tiles_m = (M + _BM - 1) // _BM
-    bn = 256 if tiles_m * ((N + 255) // 256) >= 148 else 128
-    tiles = tiles_m * ((N + bn - 1) // bn)
+    bn, tiles = _tile_geometry(M, N)
     ch.ensure(tiles, bn)
     ctx = ch.context(bn)
     out, aux = _ar_outputs(ch, ctx, (M, N), out_dtype or a.dtype, a.device, want_aux)
@@ -272,9 +280,7 @@ def gemm_all_reduce_loopback(a, b, bias=None, epilogue=EPI_NONE, out_dtype=None,
     M, K = a.shape
     N = b.shape[0]
     dev = a.device
-    tiles_m = (M + _BM - 1) // _BM
-    bn = 256 if tiles_m * ((N + 255) // 256) >= 148 else 128
-    tiles = tiles_m * ((N + bn - 1) // bn)
+    bn, tiles = _tile_geometry(M, N)
     flags_per_src = (tiles * 4 + 1023) // 1024 * 1024
     vecs_per_src = tiles * 4 * (bn // 32) * 128
     fbytes, ibytes = 2 * flags_per_src * 4, 2 * vecs_per_src * 16
@@ -351,9 +357,7 @@ def gemm_reduce_scatter(layout, a, b, group, out_dtype=None, out=None, accumulat
     if ch is None:
         ch = _channels[id(group)] = _ArChannel(group)
     R = M // ch.n
-    tiles_m = (M + _BM - 1) // _BM
-    bn = 256 if tiles_m * ((N + 255) // 256) >= 148 else 128
-    tiles = tiles_m * ((N + bn - 1) // bn)
+    bn, tiles = _tile_geometry(M, N)
     ch.ensure(tiles, bn)
     ctx = ch.context(bn, mode=1, rows_per_shard=R)
     if out is None:
@@ -475,9 +479,11 @@ def all_gather_gemm(layout, a, w_shard, depth_group, local_shape, ar_group=None,
         arch = _channels.get(id(ar_group))
         if arch is None:
             arch = _channels[id(ar_group)] = _ArChannel(ar_group)
-        tiles_m = (M + _BM - 1) // _BM
-        bn = 128 if (layout == 0 and (out_l // ch.n) % 256) else (256 if tiles_m * ((N + 255) // 256) >= 148 else 128)
-        arch.ensure(tiles_m * ((N + bn - 1) // bn), bn)
+        bn, tiles = _tile_geometry(M, N)
+        if layout == 0 and (out_l // ch.n) % 128:
+            bn = 128
+            tiles = (M + _BM - 1) // _BM * ((N + 127) // 128)
+        arch.ensure(tiles, bn)
         ar_ctx = arch.context(bn)
         out, aux_t = _ar_outputs(arch, ar_ctx, (M, N), a.dtype, a.device, want_aux)
         ar_ref = ctypes.byref(ar_ctx)
@@ -581,3 +587,149 @@ def try_all_reduce_scale_(grads, group, scale) -> bool:
                                  ctypes.c_void_p(bucket), ctypes.c_int(code), ctypes.c_int(1), ctypes.byref(unpack),
                                  ctypes.c_int(dev), _lib.stream_ptr()), "axb_bucket_copy")
     return True
+
+
+# ----------------------------------------------------------------------------- row all-to-all / embedding rows
+class AxbP2pCtx(ctypes.Structure):
+    _fields_ = [("n", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint), ("pad", ctypes.c_int),
+                ("base_peer", ctypes.c_void_p * 8), ("mail_local", ctypes.c_void_p),
+                ("mail_peer", ctypes.c_void_p * 8), ("done_local", ctypes.c_void_p),
+                ("done_peer", ctypes.c_void_p * 8), ("counter", ctypes.c_void_p), ("out_off", ctypes.c_ulonglong)]
+
+
+class AxbRowBlock(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("src_pitch", ctypes.c_longlong), ("dst_off", ctypes.c_longlong),
+                ("dst_pitch", ctypes.c_longlong), ("rows", ctypes.c_longlong), ("row_bytes", ctypes.c_longlong)]
+
+
+class _P2pChannel:
+    """Control words (and optionally a data region) of the row all-to-all / embedding kernels for one group.
+    Layout: mailbox (n records of 32 bytes) at 0, DONE[n] at 512, CTA counters at 1024, data from 4096."""
+
+    _MAIL, _DONE, _COUNTER = 0, 512, 1024
+
+    def __init__(self, group, data_bytes=0, tag="p2p"):
+        self.group, self.n, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.data_bytes = (int(data_bytes) + 255) // 256 * 256
+        torch.cuda.synchronize()
+        self.buf = symm.SymmBuffer(group, _CTRL_BYTES + self.data_bytes, tag)
+        self.buf.local.zero_()
+        torch.cuda.synchronize()
+        self.buf.barrier()
+        dist.barrier(group=group)
+        self.epoch = 0
+
+    def ctx(self, base_peer, out_off=0):
+        self.epoch += 1
+        base = self.buf.peer_ptrs
+        c = AxbP2pCtx()
+        c.n, c.rank, c.epoch = self.n, self.rank, self.epoch
+        for j in range(self.n):
+            c.base_peer[j] = base_peer[j]
+            c.mail_peer[j] = base[j] + self._MAIL
+            c.done_peer[j] = base[j] + self._DONE
+        c.mail_local = base[self.rank] + self._MAIL
+        c.done_local = base[self.rank] + self._DONE
+        c.counter = base[self.rank] + self._COUNTER
+        c.out_off = out_off
+        return c
+
+    def data_ptrs(self):
+        return [p + _CTRL_BYTES for p in self.buf.peer_ptrs]
+
+    def data_view(self, dtype, numel):
+        return self.buf.view(dtype, numel, _CTRL_BYTES)
+
+
+_a2a_channels = {}
+
+
+def a2a_rows_usable(group, tensor) -> bool:
+    return group_usable(group, tensor) and symm.output_arena() is not None
+
+
+def a2a_rows(group, blocks, out_shape, dtype, device):
+    """All-to-all-v of row blocks in one kernel (``csrc/p2p.cu``): ``blocks[j]`` = ``(src_ptr, src_pitch,
+    dst_off, dst_pitch, rows, row_bytes)`` describes what this rank stores into rank ``j``'s output (byte
+    quantities, multiples of 16).  The output tensor of shape ``out_shape`` is allocated from the peer-mapped
+    arena and returned complete (the kernel ends after every peer has finished storing into it)."""
+    arena = symm.output_arena()
+    ch = _a2a_channels.get(id(group))
+    if ch is None:
+        ch = _a2a_channels[id(group)] = _P2pChannel(group, 0, "a2a_rows")
+    out = arena.empty(out_shape, dtype)
+    ctx = ch.ctx(arena.peer_bases(group), arena.offset(out))
+    arr = (AxbRowBlock * ch.n)()
+    for j, (src, sp, doff, dp, rows, rb) in enumerate(blocks):
+        arr[j].src, arr[j].src_pitch, arr[j].dst_off, arr[j].dst_pitch, arr[j].rows, arr[j].row_bytes = \
+            src, sp, doff, dp, rows, rb
+    st = _lib.lib().axb_a2a_rows(ctypes.byref(ctx), arr, ctypes.c_int(device.index), _lib.stream_ptr())
+    _lib.check(st, "axb_a2a_rows")
+    return out
+
+
+class _EmbeddingChannel:
+    """Peer-mapped copies of the depth shards of an embedding table (forward) and fp32 gradient shards
+    (backward) for one depth group."""
+
+    def __init__(self, group, shard_bytes, grad_bytes):
+        self.fwd = _P2pChannel(group, shard_bytes, "embedding_rows")
+        self.bwd = _P2pChannel(group, grad_bytes, "embedding_grad")
+        self.shard_bytes, self.grad_bytes = shard_bytes, grad_bytes
+
+
+_emb_channels = {}
+
+
+def embedding_p2p_usable(group, table_shard, rows_per_shard, row_elems) -> bool:
+    return (table_shard.dtype == torch.bfloat16 and group_usable(group, table_shard)
+            and (row_elems * 2) % 16 == 0 and table_shard.numel() == rows_per_shard * row_elems)
+
+
+def _emb_channel(group, shard):
+    nbytes = shard.numel() * shard.element_size()
+    gbytes = shard.numel() * 4
+    ch = _emb_channels.get(id(group))
+    if ch is None or ch.shard_bytes < nbytes or ch.grad_bytes < gbytes:
+        ch = _emb_channels[id(group)] = _EmbeddingChannel(group, nbytes, gbytes)
+    return ch
+
+
+def embedding_fetch(group, ids, table_shard, rows_per_shard, row_elems):
+    """Rows ``ids`` of a table whose row blocks are sharded over ``group``: every token's row is fetched from
+    the owning rank's published shard over NVLink; the table is never gathered.  ``ids`` int64 ``[T]``;
+    returns bf16 ``[T, row_elems]``."""
+    ch = _emb_channel(group, table_shard).fwd
+    L = _lib.lib()
+    dev = table_shard.device
+    # publish my shard: copy into the peer-mapped buffer, then raise this call's epoch in every peer's mailbox
+    ctx = ch.ctx(ch.data_ptrs())
+    ch.data_view(torch.bfloat16, table_shard.numel()).copy_(table_shard.detach().reshape(-1))
+    _lib.check(L.axb_p2p_publish(ctypes.byref(ctx), ctypes.c_int(dev.index), _lib.stream_ptr()), "axb_p2p_publish")
+    ids = ids.reshape(-1).contiguous()
+    out = torch.empty((ids.numel(), row_elems), dtype=torch.bfloat16, device=dev)
+    st = L.axb_embedding_fetch(_lib.ptr(ids), ctypes.c_longlong(ids.numel()), _lib.ptr(out),
+                               ctypes.c_longlong(row_elems * 2), ctypes.c_longlong(rows_per_shard),
+                               ctypes.byref(ctx), ctypes.c_int(dev.index), _lib.stream_ptr())
+    _lib.check(st, "axb_embedding_fetch")
+    return out
+
+
+def embedding_scatter_add(group, ids, dy, rows_per_shard, row_elems, shard_numel):
+    """Gradient of ``embedding_fetch`` w.r.t. the table: every token's gradient row is added into the owning
+    rank's fp32 gradient shard with remote atomics; returns this rank's summed shard (fp32, flat)."""
+    ch_all = _emb_channels[id(group)]
+    ch = ch_all.bwd
+    L = _lib.lib()
+    dev = dy.device
+    ctx = ch.ctx(ch.data_ptrs())
+    grad = ch.data_view(torch.float32, shard_numel)
+    grad.zero_()
+    _lib.check(L.axb_p2p_publish(ctypes.byref(ctx), ctypes.c_int(dev.index), _lib.stream_ptr()), "axb_p2p_publish")
+    ids = ids.reshape(-1).contiguous()
+    dy = dy.reshape(-1, row_elems).contiguous()
+    st = L.axb_embedding_scatter_add(_lib.ptr(ids), ctypes.c_longlong(ids.numel()), _lib.ptr(dy),
+                                     ctypes.c_int(row_elems), ctypes.c_longlong(rows_per_shard), ctypes.byref(ctx),
+                                     ctypes.c_int(dev.index), _lib.stream_ptr())
+    _lib.check(st, "axb_embedding_scatter_add")
+    return grad.clone()

@@ -59,6 +59,25 @@ def _compile(src, verbose):
     return obj, r.stderr
 
 
+def build_variant(out_path, extra_flags, obj_dir):
+    """Build a variant of the library (extra nvcc flags, e.g. ``-DAXB_ABLATION``) to ``out_path``; select it
+    at run time with ``AXONN_LIB_PATH``.  The default library is not touched."""
+    os.makedirs(obj_dir, exist_ok=True)
+    objs = []
+    for src in sources():
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        r = subprocess.run([_nvcc()] + NVCC_FLAGS + list(extra_flags) + ["-I", CSRC, "-c", src, "-o", obj],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+        objs.append(obj)
+    r = subprocess.run([_nvcc(), "-shared", "-o", out_path] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return out_path
+
+
 def build_library(force=False, verbose=True):
     if not force and up_to_date():
         return LIB_PATH
