@@ -163,6 +163,173 @@ allreduce_twoshot_kernel(long long nvec, float scale, CommCtx c) {
   comm_signal_when_last(c);
 }
 
+
+// ----------------------------------------------------------------------------- one-kernel gradient all-reduce
+// The whole data-parallel gradient all-reduce of a list of tensors in ONE launch, straight from and to the
+// gradient tensors (no pack or unpack pass): the chunk list of the table is cut into n slices, rank k owns slice k.
+//   phase 1  every rank reads its gradients of the slices it does not own and stores them into the owners'
+//            receive slots (posted stores over NVLink);
+//   phase 2  the owner adds its own gradients and the n-1 received partials in rank order (fp32 accumulation,
+//            identical bits on every rank), multiplies by `scale`, writes the result back into its gradient
+//            tensors and stores it into every peer's result area;
+//   phase 3  every rank copies the slices it does not own from its result area into its gradient tensors.
+// Phases are separated by epoch flags in peer memory (PUSHED, REDUCED); the last CTA of a phase publishes
+// them.  All CTAs of the launch must be resident at once (grid <= 2 x #SMs at 512 threads); waits are bounded.
+struct GradArCtx {
+  int n, rank;
+  unsigned int epoch;
+  void* recv_peer[8];        // rank j's receive area: n slots (one per source rank) of slot_bytes
+  void* result_peer[8];      // rank j's result area: one position per chunk of the table
+  unsigned int* pushed_local;    // [n] epoch flags written by peers when their phase 1 is complete
+  unsigned int* pushed_peer[8];
+  unsigned int* reduced_local;   // [n] ... when their phase 2 is complete
+  unsigned int* reduced_peer[8];
+  unsigned int* counters;        // 3 words: CTA counters of phase 1 and 2, failed-CTA count (all zero between calls)
+  unsigned long long slot_bytes;
+  unsigned int* status;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ bool gar_wait_peers(const GradArCtx& c, const unsigned int* flags, int* sh_ok, unsigned int code) {
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const uint64_t t0 = globaltimer_ns();
+    for (int j = 0; j < c.n && ok; ++j) {
+      if (j == c.rank) continue;
+      while (static_cast<int>(c_ld_acquire(flags + j) - c.epoch) < 0) {
+        if (globaltimer_ns() - t0 > c.timeout_ns) { ok = 0; report_status(c.status, code); break; }
+      }
+    }
+    *sh_ok = ok;
+  }
+  __syncthreads();
+  return *sh_ok != 0;
+}
+// The last CTA to pass publishes `epoch` into flag[rank] of every peer - unless a CTA of this launch passed with
+// `ok` false (a wait of an earlier phase ran out; counters[2] counts those): the peers then run into their own
+// deadline instead of consuming an incomplete result.  The counter is back at zero either way.
+__device__ __forceinline__ void gar_phase_done(const GradArCtx& c, unsigned int* counter, unsigned int* const* flag_peer,
+                                               bool ok = true) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!ok) atomicAdd(c.counters + 2, 1u);
+    __threadfence_system();
+    if (atomicAdd(counter, 1u) == gridDim.x - 1) {
+      const unsigned int failed = atomicExch(c.counters + 2, 0u);
+      *counter = 0;
+      __threadfence_system();
+      if (failed == 0)
+        for (int j = 0; j < c.n; ++j)
+          if (j != c.rank) c_st_release(flag_peer[j] + c.rank, c.epoch);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+grad_allreduce_kernel(const long long* __restrict__ table, int ntensors, long long total_chunks, long long chunks_per_slice,
+                      float scale, GradArCtx c) {
+  constexpr int VN = V16<T>::N;                 // elements per 16-byte vector
+  __shared__ int sh_ok;
+  const long long my_lo = chunks_per_slice * c.rank;
+  const long long my_hi = my_lo + chunks_per_slice < total_chunks ? my_lo + chunks_per_slice : total_chunks;
+  // ---- phase 1: my gradients of foreign slices -> the owners' receive slots
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    if (chunk >= my_lo && chunk < my_hi) continue;
+    const int owner = static_cast<int>(chunk / chunks_per_slice);
+    const int t = pk_find(table, ntensors, chunk);
+    const long long* row = table + static_cast<size_t>(t) * 5;
+    const T* tensor = reinterpret_cast<const T*>(row[0]);
+    const long long numel = row[1];
+    const long long begin = (chunk - row[4]) * PK_CHUNK;
+    const long long end = begin + PK_CHUNK < numel ? begin + PK_CHUNK : numel;
+    T* slot = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(c.recv_peer[owner]) + c.rank * c.slot_bytes) +
+              (chunk - owner * chunks_per_slice) * PK_CHUNK;
+    if ((reinterpret_cast<uintptr_t>(tensor) & 15) == 0) {
+      const long long nv = (end - begin) / VN;
+      const uint4* sp = reinterpret_cast<const uint4*>(tensor + begin);
+      uint4* dp = reinterpret_cast<uint4*>(slot);
+      for (long long i = threadIdx.x; i < nv; i += blockDim.x) dp[i] = sp[i];
+      for (long long i = begin + nv * VN + threadIdx.x; i < end; i += blockDim.x) slot[i - begin] = tensor[i];
+    } else {
+      for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) slot[i - begin] = tensor[i];
+    }
+  }
+  gar_phase_done(c, c.counters, c.pushed_peer);
+  // ---- phase 2: reduce my slice, write it back and hand it to every peer
+  bool ok = gar_wait_peers(c, c.pushed_local, &sh_ok, 0x302u);
+  if (ok) {
+    for (long long chunk = my_lo + blockIdx.x; chunk < my_hi; chunk += gridDim.x) {
+      const int t = pk_find(table, ntensors, chunk);
+      const long long* row = table + static_cast<size_t>(t) * 5;
+      T* tensor = reinterpret_cast<T*>(row[0]);
+      const long long numel = row[1];
+      const long long begin = (chunk - row[4]) * PK_CHUNK;
+      const long long end = begin + PK_CHUNK < numel ? begin + PK_CHUNK : numel;
+      const long long in_slot = (chunk - my_lo) * PK_CHUNK;
+      const bool vec = (reinterpret_cast<uintptr_t>(tensor) & 15) == 0;
+      const long long nv = vec ? (end - begin) / VN : 0;
+      for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+        float acc[VN];
+#pragma unroll
+        for (int e = 0; e < VN; ++e) acc[e] = 0.f;
+        for (int j = 0; j < c.n; ++j) {       // rank order: identical bits on every rank
+          uint4 u;
+          if (j == c.rank) u = *(reinterpret_cast<const uint4*>(tensor + begin) + i);
+          else u = *(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(c.recv_peer[c.rank]) +
+                                                     j * c.slot_bytes) + in_slot) + i);
+          float f[VN];
+          V16<T>::unpack(u, f);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) acc[e] += f[e];
+        }
+#pragma unroll
+        for (int e = 0; e < VN; ++e) acc[e] *= scale;
+        const uint4 o = V16<T>::pack(acc);
+        *(reinterpret_cast<uint4*>(tensor + begin) + i) = o;
+        for (int j = 0; j < c.n; ++j)
+          if (j != c.rank) *(reinterpret_cast<uint4*>(reinterpret_cast<T*>(c.result_peer[j]) + chunk * PK_CHUNK) + i) = o;
+      }
+      for (long long i = begin + nv * VN + threadIdx.x; i < end; i += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < c.n; ++j) {
+          const T v = (j == c.rank) ? tensor[i]
+                                    : (reinterpret_cast<const T*>(reinterpret_cast<const uint8_t*>(c.recv_peer[c.rank]) + j * c.slot_bytes) +
+                                       in_slot)[i - begin];
+          acc += static_cast<float>(v);
+        }
+        const T o = static_cast<T>(acc * scale);
+        tensor[i] = o;
+        for (int j = 0; j < c.n; ++j)
+          if (j != c.rank) (reinterpret_cast<T*>(c.result_peer[j]) + chunk * PK_CHUNK)[i - begin] = o;
+      }
+    }
+  }
+  gar_phase_done(c, c.counters + 1, c.reduced_peer, ok);
+  // ---- phase 3: the other slices come out of my result area
+  ok = ok && gar_wait_peers(c, c.reduced_local, &sh_ok, 0x303u);
+  if (!ok) return;
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    if (chunk >= my_lo && chunk < my_hi) continue;
+    const int t = pk_find(table, ntensors, chunk);
+    const long long* row = table + static_cast<size_t>(t) * 5;
+    T* tensor = reinterpret_cast<T*>(row[0]);
+    const long long numel = row[1];
+    const long long begin = (chunk - row[4]) * PK_CHUNK;
+    const long long end = begin + PK_CHUNK < numel ? begin + PK_CHUNK : numel;
+    const T* res = reinterpret_cast<const T*>(c.result_peer[c.rank]) + chunk * PK_CHUNK;
+    if ((reinterpret_cast<uintptr_t>(tensor) & 15) == 0) {
+      const long long nv = (end - begin) / VN;
+      const uint4* sp = reinterpret_cast<const uint4*>(res);
+      uint4* dp = reinterpret_cast<uint4*>(tensor + begin);
+      for (long long i = threadIdx.x; i < nv; i += blockDim.x) dp[i] = sp[i];
+      for (long long i = begin + nv * VN + threadIdx.x; i < end; i += blockDim.x) tensor[i] = res[i - begin];
+    } else {
+      for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) tensor[i] = res[i - begin];
+    }
+  }
+}
+
 }  // namespace axb
 
 using namespace axb;
@@ -211,6 +378,35 @@ extern "C" int axb_allreduce_twoshot(long long nbytes, int dtype, float scale, c
   const int grid = (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
   if (dtype == 0) allreduce_twoshot_kernel<float><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, c);
   else allreduce_twoshot_kernel<__nv_bfloat16><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, c);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Sum the tensors of `table` ({ptr, numel, -, -, chunk prefix} rows, chunks of 32768 elements) over the group,
+// times `scale`, in place, in one kernel (see grad_allreduce_kernel).  `ctx` names the peer-mapped receive and
+// result areas: recv holds n slots of chunks_per_slice * 32768 elements, result total_chunks * 32768 elements.
+extern "C" int axb_grad_allreduce(const long long* table, int ntensors, long long total_chunks, long long chunks_per_slice,
+                                  int dtype, float scale, const AxbGradArCtx* h, int device, void* stream) {
+  if (!h || h->n < 2 || h->n > 8) { set_error("grad all-reduce: group size must be 2..8"); return -1; }
+  if (chunks_per_slice * h->n < total_chunks) { set_error("grad all-reduce: slices do not cover the chunk list"); return -1; }
+  GradArCtx c;
+  c.n = h->n; c.rank = h->rank; c.epoch = h->epoch;
+  for (int j = 0; j < 8; ++j) {
+    c.recv_peer[j] = h->recv_peer[j]; c.result_peer[j] = h->result_peer[j];
+    c.pushed_peer[j] = h->pushed_peer[j]; c.reduced_peer[j] = h->reduced_peer[j];
+  }
+  c.pushed_local = h->pushed_local; c.reduced_local = h->reduced_local; c.counters = h->counters;
+  c.slot_bytes = h->slot_bytes;
+  unsigned int* st = nullptr;
+  if (!device_status_word(device, &st)) { set_error("grad all-reduce: no status word"); return -1; }
+  c.status = st;
+  c.timeout_ns = 2 * axb::wait_timeout_ns();
+  // all CTAs wait on each other's phases: keep the grid within what is resident at once
+  const long long cap = static_cast<long long>(sm_count(device)) * 2;
+  const int grid = static_cast<int>(total_chunks < cap ? (total_chunks < 1 ? 1 : total_chunks) : cap);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0) grad_allreduce_kernel<float><<<grid, 512, 0, s>>>(table, ntensors, total_chunks, chunks_per_slice, scale, c);
+  else grad_allreduce_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(table, ntensors, total_chunks, chunks_per_slice, scale, c);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }

@@ -166,6 +166,24 @@ int axb_bucket_copy(const long long* table, int ntensors, long long total_chunks
                     const AxbCommCtx* ctx, int device, void* stream);
 int axb_allreduce_twoshot(long long nbytes, int dtype, float scale, const AxbCommCtx* ctx, int device, void* stream);
 
+/* Peer-memory context of the one-kernel gradient all-reduce (allreduce.cu::grad_allreduce_kernel). */
+typedef struct AxbGradArCtx {
+  int n, rank;
+  unsigned int epoch;
+  int pad;
+  void* recv_peer[8];            /* rank j's receive area: n slots (one per source rank) of slot_bytes */
+  void* result_peer[8];          /* rank j's result area */
+  unsigned int* pushed_local;    /* [n] epoch flags */
+  unsigned int* pushed_peer[8];
+  unsigned int* reduced_local;
+  unsigned int* reduced_peer[8];
+  unsigned int* counters;        /* 3 words, zero between calls */
+  unsigned long long slot_bytes;
+} AxbGradArCtx;
+/* dtype here: 0 fp32, 1 bf16 (the bucket kernels' own codes) */
+int axb_grad_allreduce(const long long* table, int ntensors, long long total_chunks, long long chunks_per_slice,
+                       int dtype, float scale, const AxbGradArCtx* ctx, int device, void* stream);
+
 /* Top-k gradient pruning for callers that cannot allocate device memory (programs that own the whole GPU
  * through their own pool, or that forbid allocation after start-up).  This entry point has no counterpart
  * in the reference project.  Same result as axb_prune_topk, but the radix-select scratch is a 393,248-byte

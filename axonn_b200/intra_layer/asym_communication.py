@@ -10,9 +10,13 @@ reference's ``axonn/intra_layer/asym_communication.py:16-252``
 
 Differences: row counts are exchanged once per distinct (group, local rows)
 pair and cached on the host, so steady-state steps have no device-to-host
-synchronisation (the reference syncs twice per layer call, ``:16-30``); the
-exchanges are single ``all_to_all_single`` / ``all_gather`` calls on
-contiguous buffers; devices follow the input instead of a literal "cuda".
+synchronisation (the reference syncs twice per layer call, ``:16-30``).  On
+GPUs whose group shares peer memory each exchange is one kernel
+(``csrc/p2p.cu::a2a_rows_kernel``) in which every rank stores its row blocks
+straight into the destination's output tensor over NVLink - the transposition
+is done by the addressing, without the pack / unpack copies around a library
+all-to-all.  Elsewhere (CPU ranks, ``AXONN_BACKEND=nccl``) the exchanges are
+single ``all_to_all_single`` / ``all_gather`` calls on contiguous buffers.
 """
 
 from typing import List
@@ -56,6 +60,15 @@ def gather_batch_sizes(local_batch_size: int, process_group=None, device=None) -
     return everyone
 
 
+def _p2p_ok(tensor, process_group, row_bytes) -> bool:
+    """The peer-memory row all-to-all applies: CUDA tensor, peer-capable group, 16-byte row granularity."""
+    if not tensor.is_cuda or row_bytes % 16 or tensor.data_ptr() % 16:
+        return False
+    from ..parallel import fused
+
+    return fused.a2a_rows_usable(process_group, tensor)
+
+
 def _sizes(rank_local_batch_sizes) -> List[int]:
     if isinstance(rank_local_batch_sizes, torch.Tensor):
         return [int(v) for v in rank_local_batch_sizes.tolist()]
@@ -73,6 +86,18 @@ def _allgatherv(tensor, rank_local_batch_sizes, process_group=None):
     t.start("allgatherv")
     tensor = tensor.contiguous()
     tail = tuple(tensor.shape[1:])
+    row_bytes = tensor.element_size()
+    for t_ in tail:
+        row_bytes *= t_
+    if _p2p_ok(tensor, process_group, row_bytes):
+        from ..parallel import fused
+
+        me = dist.get_rank(process_group)
+        off = sum(sizes[:me]) * row_bytes
+        blocks = [(tensor.data_ptr(), row_bytes, off, row_bytes, tensor.shape[0], row_bytes)] * n
+        out = fused.a2a_rows(process_group, blocks, (sum(sizes),) + tail, tensor.dtype, tensor.device)
+        t.stop("allgatherv")
+        return out
     out = torch.empty((sum(sizes),) + tail, dtype=tensor.dtype, device=tensor.device)
     if len(set(sizes)) == 1:
         dist.all_gather_into_tensor(out, tensor, group=process_group)
@@ -140,6 +165,19 @@ def _gather_batch_scatter_channels(input_, rank_local_batch_sizes, process_group
     m, k = input_.shape[0], input_.shape[-1]
     if k % n != 0:
         raise ValueError(f"feature dim {k} not divisible by group size {n}")
+    es = input_.element_size()
+    if input_.ndim == 2 and _p2p_ok(input_, process_group, (k // n) * es):
+        # rank j receives my columns [j*k/G, (j+1)*k/G) of all my rows, at the rows of my batch offset
+        from ..parallel import fused
+
+        x = input_.contiguous()
+        me, kc = dist.get_rank(process_group), k // n
+        off = sum(sizes[:me]) * kc * es
+        blocks = [(x.data_ptr() + j * kc * es, k * es, off, kc * es, m, kc * es) for j in range(n)]
+        recv = fused.a2a_rows(process_group, blocks, (sum(sizes), kc), x.dtype, x.device)
+        t.stop("alltoallv")
+        t.stop("gather-batch-scatter-channels")
+        return recv
     # [m, G, k/G] -> [G, m, k/G]: chunk j goes to rank j
     send = input_.reshape(m, n, k // n).transpose(0, 1).contiguous()
     recv = torch.empty((sum(sizes), k // n), dtype=input_.dtype, device=input_.device)
@@ -165,6 +203,19 @@ def _gather_channels_scatter_batch(input_, rank_local_batch_sizes, process_group
     input_ = input_.contiguous()
     kc = input_.shape[-1]
     mine = sizes[me]
+    es = input_.element_size()
+    if input_.ndim == 2 and _p2p_ok(input_, process_group, kc * es):
+        # rank j receives my feature chunk of ITS rows, at column block `me` of its [m_j, G * kc] output
+        from ..parallel import fused
+
+        blocks, start = [], 0
+        for j in range(n):
+            blocks.append((input_.data_ptr() + start * kc * es, kc * es, me * kc * es, n * kc * es, sizes[j], kc * es))
+            start += sizes[j]
+        out = fused.a2a_rows(process_group, blocks, (mine, n * kc), input_.dtype, input_.device)
+        t.stop("alltoallv")
+        t.stop("gather-channels-scatter-batch")
+        return out
     recv = torch.empty((n * mine, kc), dtype=input_.dtype, device=input_.device)
     dist.all_to_all_single(
         recv, input_, output_split_sizes=[mine] * n, input_split_sizes=sizes, group=process_group

@@ -5,6 +5,13 @@ table is kept as ``[V, H]`` with ``H`` split over the outer group (inner group
 when ``transpose``), flattened and depth-sharded; the other group must have
 size one.  Forward gathers the table over depth, looks rows up and, in easy
 mode, gathers the hidden dimension back.
+
+On GPUs whose depth group shares peer memory the table is never gathered:
+every token fetches its row from the depth rank that owns it, and the backward
+adds the token gradients into the owners' gradient shards with remote atomics
+(``csrc/p2p.cu``; ``AXONN_EMBEDDING_P2P=0`` keeps the gather).  For a 128256 x
+4096 table that replaces 1 GB of all-gather per forward and a 1 GB
+reduce-scatter per backward by the rows actually used.
 """
 
 import torch
@@ -30,6 +37,32 @@ def extract_local_params_from_full_params(params, hidden_group, depth_group):
 @torch.no_grad()
 def default_init_method(weight, padding_idx=None):
     return torch.nn.init.normal_(weight)
+
+
+class _EmbeddingRowsP2P(torch.autograd.Function):
+    """Row lookup in a depth-sharded ``[V, H_l]`` table without gathering it."""
+
+    @staticmethod
+    def forward(ctx, ids, shard, group, rows_per_shard, row_elems, padding_idx):
+        from ..parallel import fused
+
+        flat = ids.reshape(-1)
+        out = fused.embedding_fetch(group, flat, shard, rows_per_shard, row_elems)
+        ctx.save_for_backward(flat)
+        ctx.group, ctx.rows_per_shard, ctx.row_elems = group, rows_per_shard, row_elems
+        ctx.shard_numel, ctx.shard_dtype, ctx.padding_idx = shard.numel(), shard.dtype, padding_idx
+        return out.reshape(*ids.shape, row_elems)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from ..parallel import fused
+
+        (flat,) = ctx.saved_tensors
+        g = grad_out.reshape(-1, ctx.row_elems).to(torch.bfloat16)
+        if ctx.padding_idx is not None:
+            g = g.masked_fill((flat == ctx.padding_idx)[:, None], 0)
+        gshard = fused.embedding_scatter_add(ctx.group, flat, g, ctx.rows_per_shard, ctx.row_elems, ctx.shard_numel)
+        return None, gshard.to(ctx.shard_dtype), None, None, None, None
 
 
 class Embedding(torch.nn.Module):
@@ -88,7 +121,29 @@ class Embedding(torch.nn.Module):
     def get_output_feature_size(self):
         return self.local_out_features
 
+    def _p2p_rows(self, x):
+        """Peer-memory row fetch applies: depth > 1, whole rows per depth shard, plain lookup semantics."""
+        import os
+
+        if self.depth_group_size == 1 or not x.is_cuda or os.environ.get("AXONN_EMBEDDING_P2P", "1") == "0":
+            return False
+        if self.max_norm is not None or self.scale_grad_by_freq or self.sparse:
+            return False
+        if self.num_embeddings % self.depth_group_size:
+            return False
+        from ..parallel import fused
+
+        return fused.embedding_p2p_usable(self.depth_group, self.weight,
+                                          self.num_embeddings // self.depth_group_size, self.local_out_features)
+
     def forward(self, x):
+        if self._p2p_rows(x):
+            x = _EmbeddingRowsP2P.apply(x, self.weight, self.depth_group,
+                                        self.num_embeddings // self.depth_group_size, self.local_out_features,
+                                        self.padding_idx)
+            if not self.expert_mode:
+                x = Gather.apply(x, self.hidden_group)
+            return x
         weight = ForwardGather_BackwardReduceScatter.apply(self.weight, self.depth_group).reshape(
             self.local_in_features, self.local_out_features)
         x = F.embedding(x, weight, self.padding_idx, self.max_norm, self.norm_type,

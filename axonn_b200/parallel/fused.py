@@ -134,6 +134,7 @@ def reset():
     _group_ok.clear()
     _a2a_channels.clear()
     _emb_channels.clear()
+    _grad_ar_channels.clear()
 
 
 _group_ok = {}
@@ -553,14 +554,110 @@ def _grad_table(ch, grads):
     return tab
 
 
+class AxbGradArCtx(ctypes.Structure):
+    _fields_ = [("n", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint), ("pad", ctypes.c_int),
+                ("recv_peer", ctypes.c_void_p * 8), ("result_peer", ctypes.c_void_p * 8),
+                ("pushed_local", ctypes.c_void_p), ("pushed_peer", ctypes.c_void_p * 8),
+                ("reduced_local", ctypes.c_void_p), ("reduced_peer", ctypes.c_void_p * 8),
+                ("counters", ctypes.c_void_p), ("slot_bytes", ctypes.c_ulonglong)]
+
+
+class _GradArChannel:
+    """Receive and result areas of the one-kernel gradient all-reduce for one group.
+    Control block: PUSHED[n] at 0, REDUCED[n] at 64, counters at 256; then the receive area (n slots of
+    ``slot_bytes``) and the result area (``result_bytes``)."""
+
+    _PUSHED, _REDUCED, _COUNTERS = 0, 64, 256
+
+    def __init__(self, group, slot_bytes, result_bytes):
+        self.group, self.n, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.slot_bytes = (int(slot_bytes) + (1 << 20) - 1) // (1 << 20) * (1 << 20)
+        self.result_bytes = (int(result_bytes) + (1 << 20) - 1) // (1 << 20) * (1 << 20)
+        torch.cuda.synchronize()
+        self.buf = symm.SymmBuffer(group, _CTRL_BYTES + self.n * self.slot_bytes + self.result_bytes, "grad_allreduce")
+        self.buf.local[:_CTRL_BYTES].zero_()
+        torch.cuda.synchronize()
+        self.buf.barrier()
+        dist.barrier(group=group)
+        self.epoch = 0
+        self.tables = {}
+
+    def ctx(self):
+        self.epoch += 1
+        c = AxbGradArCtx()
+        c.n, c.rank, c.epoch = self.n, self.rank, self.epoch
+        base = self.buf.peer_ptrs
+        for j in range(self.n):
+            c.recv_peer[j] = base[j] + _CTRL_BYTES
+            c.result_peer[j] = base[j] + _CTRL_BYTES + self.n * self.slot_bytes
+            c.pushed_peer[j] = base[j] + self._PUSHED
+            c.reduced_peer[j] = base[j] + self._REDUCED
+        c.pushed_local = base[self.rank] + self._PUSHED
+        c.reduced_local = base[self.rank] + self._REDUCED
+        c.counters = base[self.rank] + self._COUNTERS
+        c.slot_bytes = self.slot_bytes
+        return c
+
+
+_grad_ar_channels = {}
+_GRAD_AR_MAX_BYTES = 512 << 20     # tensors of one call; longer lists are processed in several calls
+
+
+def _grad_allreduce_one_kernel(grads, group, scale) -> None:
+    """``csrc/allreduce.cu::grad_allreduce_kernel`` over ``grads`` (same dtype, contiguous)."""
+    dtype = grads[0].dtype
+    es = grads[0].element_size()
+    n = dist.get_world_size(group)
+    chunks = sum((g.numel() + _PK_CHUNK - 1) // _PK_CHUNK for g in grads)
+    cps = (chunks + n - 1) // n
+    slot_bytes, result_bytes = cps * _PK_CHUNK * es, chunks * _PK_CHUNK * es
+    ch = _grad_ar_channels.get(id(group))
+    if ch is None or ch.slot_bytes < slot_bytes or ch.result_bytes < result_bytes:
+        ch = _grad_ar_channels[id(group)] = _GradArChannel(group, max(slot_bytes, 32 << 20),
+                                                             max(result_bytes, n * (32 << 20)))
+    key = tuple((g.data_ptr(), g.numel()) for g in grads)
+    tab = ch.tables.get(key)
+    if tab is None:
+        rows, prefix = [], 0
+        for g in grads:
+            rows.append((g.data_ptr(), g.numel(), 0, 0, prefix))
+            prefix += (g.numel() + _PK_CHUNK - 1) // _PK_CHUNK
+        if len(ch.tables) > 8:
+            ch.tables.clear()
+        tab = ch.tables[key] = torch.tensor(rows, dtype=torch.int64).to(grads[0].device)
+    ctx = ch.ctx()
+    st = _lib.lib().axb_grad_allreduce(
+        _lib.ptr(tab), ctypes.c_int(len(grads)), ctypes.c_longlong(chunks), ctypes.c_longlong(cps),
+        ctypes.c_int(0 if dtype == torch.float32 else 1), ctypes.c_float(1.0 if scale is None else float(scale)),
+        ctypes.byref(ctx), ctypes.c_int(grads[0].device.index), _lib.stream_ptr())
+    _lib.check(st, "axb_grad_allreduce")
+
+
 def try_all_reduce_scale_(grads, group, scale) -> bool:
-    """Sum ``grads`` over ``group`` and multiply by ``scale`` with the peer-memory kernels
-    (pack -> two-shot reduce with fused scale -> unpack).  Returns False when not applicable."""
+    """Sum ``grads`` over ``group`` and multiply by ``scale`` with the peer-memory kernels: by default one
+    kernel that reads and writes the gradient tensors directly (owners of the slices receive the partials,
+    reduce in rank order, scale and hand the result to every peer); ``AXONN_GRAD_AR=bucket`` selects the older
+    pack -> two-shot -> unpack form.  Returns False when not applicable."""
     if not grads or not group_usable(group, grads[0]):
         return False
     dtype = grads[0].dtype
     if dtype not in (torch.float32, torch.bfloat16) or any(g.dtype != dtype or not g.is_contiguous() for g in grads):
         return False
+    import os
+
+    if os.environ.get("AXONN_GRAD_AR", "fused") != "bucket":
+        es = grads[0].element_size()
+        batch, size = [], 0
+        for g in grads:
+            padded = (g.numel() + _PK_CHUNK - 1) // _PK_CHUNK * _PK_CHUNK * es
+            if batch and size + padded > _GRAD_AR_MAX_BYTES:
+                _grad_allreduce_one_kernel(batch, group, scale)
+                batch, size = [], 0
+            batch.append(g)
+            size += padded
+        if batch:
+            _grad_allreduce_one_kernel(batch, group, scale)
+        return True
     es = 4 if dtype == torch.float32 else 2
     total_elems = sum((g.numel() + 7) // 8 * 8 for g in grads)
     n = dist.get_world_size(group)

@@ -38,10 +38,11 @@ class Trainer:
         self.clip_grad = clip_grad
         self.prune_keep_fraction = prune_keep_fraction
         self.overlap = overlap
-        # depth all-gathers: either prefetched one layer ahead on the collective library's stream, or (False)
-        # left to the GEMM kernels that gather their weight shards themselves over peer memory
+        # depth all-gathers: by default the GEMM kernels gather their weight shards themselves over peer memory
+        # while they compute; AXONN_AG_PREFETCH=1 (or prefetch_all_gather=True) prefetches them one layer ahead
+        # with the collective library on a side stream instead (also what CPU ranks do)
         if prefetch_all_gather is None:
-            prefetch_all_gather = os.environ.get("AXONN_AG_PREFETCH", "1") == "1"
+            prefetch_all_gather = os.environ.get("AXONN_AG_PREFETCH", "0") == "1"
         self.prefetch_all_gather = prefetch_all_gather and overlap
         self.loss_fn = loss_fn
         self.expert_mode = expert_mode
