@@ -184,11 +184,70 @@ typedef struct AxbGradArCtx {
 int axb_grad_allreduce(const long long* table, int ntensors, long long total_chunks, long long chunks_per_slice,
                        int dtype, float scale, const AxbGradArCtx* ctx, int device, void* stream);
 
+/* ---- runtime helpers (common.cu) */
+void axb_set_wait_timeout_ms(unsigned int ms);   /* deadline of every device-side wait; default 120000 */
+unsigned int axb_debug_word(int device, int index, int clear);   /* diagnostic words 1..15 next to the status word */
+double axb_comm_stall_ms(int device, int reset); /* time the fused GEMM kernels spent stalled on peers; synchronises */
+
+/* ---- elementwise kernels (elementwise.cu); bf16 tensors, n / F multiples of 8 */
+int axb_gelu_fwd(const void* x, void* y, long long n, void* stream);
+int axb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, void* stream);
+int axb_swiglu_fwd(const void* gate_up, void* out, int T, int F, void* stream);   /* gate|up interleaved in blocks of 8 */
+int axb_swiglu_bwd(const void* dout, const void* gate_up, void* dgate_up, int T, int F, void* stream);
+/* rotary embedding in place on rows of nh heads of D elements; cs: [positions, D/2, 2] cos/sin table */
+int axb_rope(void* x, const float* cs, long long rows, int S, int nh, int D, int pos_div, long long row_stride,
+             int inverse, void* stream);
+
+/* ---- flash attention on the packed projection output [B, S, G, qpk + 2, D] (flash_attn.cu); D 64 or 128, S % 128 == 0 */
+int axb_flash_attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int G, int qpk, int D, float scale,
+                       int device, void* stream);
+int axb_flash_attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta, float* dq_acc,
+                       void* dqkv, int B, int S, int G, int qpk, int D, float scale, int device, void* stream);
+
+/* ---- cross entropy on a vocabulary shard of bf16 logits (loss.cu); backward overwrites the logits with their gradient */
+int axb_ce_fwd(const void* logits, const long long* targets, float* stats, int rows, int V, int vocab_start, void* stream);
+int axb_ce_bwd(void* logits, const long long* targets, const float* lse, const float* scale, int rows, int V,
+               int vocab_start, long long ignore_index, void* stream);
+
+/* ---- LayerNorm / RMSNorm and column sums (norm.cu) */
+int axb_norm_grid(int device, int rows);
+int axb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H, int H_total,
+                 float eps, int rms, int mode, int dtype, int device, void* stream);
+/* dgamma / dbeta are written in `param_dtype`, column sums in `out_dtype` (the dtype codes above) */
+int axb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* stats, void* dx, float* sums,
+                 float* dgamma_part, float* dbeta_part, void* dgamma, void* dbeta, int rows, int H, int H_total, int rms,
+                 int mode, int dtype, int param_dtype, int device, void* stream);
+int axb_colsum_splits(int device, int rows, int N);
+int axb_colsum(const void* x, float* part, void* out, int rows, int N, int dtype, int out_dtype, int device, void* stream);
+int axb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, float* part, void* colsum, int rows, int N, int dtype,
+                        int out_dtype, int device, void* stream);
+
+/* ---- multi-tensor kernels over a device table of tensor pointers (optim.cu) */
+int axb_multi_l2norm_sq(const long long* table, int n, long long total_chunks, float* out, void* stream);
+int axb_multi_scale(const long long* table, int n, long long total_chunks, const float* scale, void* stream);
+int axb_multi_adamw(const long long* table, int n, long long total_chunks, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, float bias_c1, float bias_c2, const float* grad_scale, const float* found_inf,
+                    void* stream);
+
+/* ---- output arena (arena.cu): host-side allocator over a registered peer-mapped range; the malloc / free pair
+ * has the signature of torch's pluggable-allocator hook */
+int axb_arena_register(int device, void* base, unsigned long long nbytes);
+void* axb_arena_malloc(long long size, int device, void* stream);
+void axb_arena_free(void* ptr, long long size, int device, void* stream);
+unsigned long long axb_arena_stat(int device, int what);
+int axb_arena_contains(int device, const void* ptr, unsigned long long nbytes);
+
+/* ---- top-k gradient pruning (prune.cu): keep the k largest |g|, zero the rest, in place.
+ * dtype: the codes above (0 bf16, 1 fp16, 2 fp32).  `work`: device scratch of axb_prune_workspace_words() 32-bit words. */
+int axb_prune_workspace_words(void);
+int axb_prune_topk(void* g, long long n, int dtype, long long k, void* work, int device, void* stream);
+
 /* Top-k gradient pruning for callers that cannot allocate device memory (programs that own the whole GPU
  * through their own pool, or that forbid allocation after start-up).  This entry point has no counterpart
- * in the reference project.  Same result as axb_prune_topk, but the radix-select scratch is a 393,248-byte
- * array inside the library image, held on every GPU that loads the library until the process exits.
- * The first call on a device (with that device current) resolves the array's address: make it before any
+ * in the reference project.  Same result and same dtype codes (0 bf16, 1 fp16, 2 fp32) as axb_prune_topk,
+ * but the radix-select scratch is a 393,248-byte array inside the library image, held on every GPU that
+ * loads the library until the process exits.  `device` must be the calling thread's current device on
+ * every call (checked).  The first call on a device also resolves the array's address: make it before any
  * stream capture.  n is limited to 2,147,483,647 elements.  Calls share the scratch: they must not overlap
  * on the GPU. */
 int axb_prune_topk_static(void* g, long long n, int dtype, long long k, int device, void* stream);

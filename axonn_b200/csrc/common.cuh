@@ -117,6 +117,24 @@ __device__ __forceinline__ void report_status(unsigned int* status, unsigned int
   if (*w == 0u) *w = code;
 }
 
+// Debug builds (-DAXB_DEBUG_BOUNDS, `python axonn_b200/utils/build.py --debug-bounds`): every store that a kernel
+// makes into peer memory or through a computed index is checked against the extent of its target first; a
+// violation is recorded (status code + the offending byte offset in diagnostic words 14 / 15) and the access is
+// skipped instead of being made.  In the shipped library the check is the constant `true`.
+#ifdef AXB_DEBUG_BOUNDS
+__device__ __forceinline__ bool in_range_or_report(unsigned int* status, unsigned long long offset, unsigned long long bytes,
+                                                   unsigned long long extent, unsigned int code) {
+  if (offset + bytes <= extent) return true;
+  report_status(status, code);
+  volatile unsigned int* w = reinterpret_cast<volatile unsigned int*>(status);
+  w[14] = static_cast<unsigned int>(offset); w[15] = static_cast<unsigned int>(offset >> 32);
+  return false;
+}
+#define AXB_IN_RANGE(status, offset, bytes, extent, code) (::axb::in_range_or_report((status), (offset), (bytes), (extent), (code)))
+#else
+#define AXB_IN_RANGE(status, offset, bytes, extent, code) (true)
+#endif
+
 // 2-D tiled TMA load (no multicast) into CTA shared memory.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar,
                                             int32_t c0, int32_t c1) {

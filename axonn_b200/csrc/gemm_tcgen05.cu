@@ -301,6 +301,9 @@ __device__ __forceinline__ void comm_finish8(const GemmParams& p, float* v, size
   }
   const size_t out_row = (p.ar.mode == 1) ? row - static_cast<size_t>(p.ar.rank) * p.ar.rows_per_shard : row;
   const size_t off = out_row * p.N + col;
+  // debug builds: the 8 values must lie inside C (and, on the peers, inside the tensor they announced)
+  if (!AXB_IN_RANGE(p.status, off * 2ull, 16ull,
+                    static_cast<unsigned long long>(p.ar.mode == 1 ? p.ar.rows_per_shard : p.M) * p.N * 2ull, 0x702u)) return;
   if (p.epilogue >= 2) {
     if (p.aux != nullptr) {
       store_vec8(p.aux, p.out_dtype, off, v, false);
@@ -910,6 +913,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int own = unit_owner(p, tile, tm, qq);
             for (int j = 0; j < p.ar.n; ++j) {
               if (own >= 0 && j != own && !(p.ar.loopback && own == p.ar.rank)) continue;
+              if (!AXB_IN_RANGE(p.status, static_cast<unsigned long long>(tile) * 4 + qq, 1ull, p.ar.flags_per_src, 0x703u)) continue;
               unsigned int* f = (j == p.ar.rank ? p.ar.flags_local : p.ar.flags_peer[j]) +
                                 static_cast<size_t>(p.ar.rank) * p.ar.flags_per_src + tile * 4 + qq;
               asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(p.ar.epoch) : "memory");
@@ -1023,6 +1027,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (AXB_DBG(p, 2) && j != p.ar.rank) continue;
           if AXB_DBG(p, 16) continue;
           uint4* dst = reinterpret_cast<uint4*>(j == p.ar.rank ? p.ar.inbox_local : p.ar.inbox_peer[j]) + slot_vec;
+          // debug builds: the slot must lie inside rank j's inbox (n sources x inbox_vecs_per_src 16-byte words)
+          if (!AXB_IN_RANGE(p.status, (slot_vec + (c * 4 + 3) * 32 + 31) * 16ull, 16ull,
+                            p.ar.inbox_vecs_per_src * 16ull * p.ar.n, 0x701u)) continue;
 #pragma unroll
           for (int i = 0; i < 4; ++i) dst[(c * 4 + i) * 32 + (lane ^ ((c * 4 + i) & 31))] = w[i];
         }

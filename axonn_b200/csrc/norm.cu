@@ -363,8 +363,15 @@ norm_bwd_rows_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
 
 // out[c] = sum_b part[b, c]   (optionally two tables at once).  Block = 32 columns x 32 row-groups; every
 // thread keeps four independent loads in flight.
-__global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb, float* __restrict__ oa,
-                                     float* __restrict__ ob, int nblocks, int H) {
+// Results are written in `out_dtype` (0 bf16, 1 fp16, 2 fp32) - the dtype of the parameter whose gradient this is -
+// so that no separate cast kernel follows.
+__device__ __forceinline__ void fold_store(void* o, int out_dtype, int c, float v) {
+  if (out_dtype == 2) reinterpret_cast<float*>(o)[c] = v;
+  else if (out_dtype == 0) reinterpret_cast<__nv_bfloat16*>(o)[c] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(o)[c] = __float2half_rn(v);
+}
+__global__ void fold_partials_kernel(const float* __restrict__ pa, const float* __restrict__ pb, void* __restrict__ oa,
+                                     void* __restrict__ ob, int nblocks, int H, int out_dtype) {
   __shared__ float sa[32][33], sb[32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
@@ -387,8 +394,8 @@ __global__ void fold_partials_kernel(const float* __restrict__ pa, const float* 
     float ta = 0.f, tb = 0.f;
 #pragma unroll
     for (int k = 0; k < 32; ++k) { ta += sa[k][threadIdx.x]; tb += sb[k][threadIdx.x]; }
-    oa[c] = ta;
-    if (pb) ob[c] = tb;
+    fold_store(oa, out_dtype, c, ta);
+    if (pb) fold_store(ob, out_dtype, c, tb);
   }
 }
 
@@ -553,8 +560,8 @@ extern "C" int axb_norm_fwd(const void* x, const void* gamma, const void* beta, 
 
 // dgamma_part / dbeta_part: [grid, H] fp32 scratch (grid from axb_norm_grid); dgamma/dbeta: [H] fp32 outputs.
 extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* stats, void* dx,
-                            float* sums, float* dgamma_part, float* dbeta_part, float* dgamma, float* dbeta, int rows,
-                            int H, int H_total, int rms, int mode, int dtype, int device, void* stream) {
+                            float* sums, float* dgamma_part, float* dbeta_part, void* dgamma, void* dbeta, int rows,
+                            int H, int H_total, int rms, int mode, int dtype, int param_dtype, int device, void* stream) {
   using namespace axb;
   if (H % 8 || H > NORM_THREADS * 8 * NORM_MAX_CHUNKS) { set_error("norm: hidden %d unsupported", H); return -1; }
   if (rows <= 0) return 0;
@@ -567,7 +574,7 @@ extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, co
   if (rc) return rc;
   if (mode != 1 && dgamma_part && dgamma) {
     fold_partials_kernel<<<(H + 31) / 32, dim3(32, 32), 0, s>>>(dgamma_part, rms ? nullptr : dbeta_part, dgamma,
-                                                              rms ? nullptr : dbeta, nblocks, H);
+                                                              rms ? nullptr : dbeta, nblocks, H, param_dtype);
     AXB_CUDA(cudaGetLastError());
   }
   return 0;
@@ -582,7 +589,8 @@ extern "C" int axb_colsum_splits(int device, int rows, int N) {
 }
 
 // out[c] = sum_r x[r, c]; part: [axb_colsum_splits, N] fp32 scratch, out: [N] fp32.  N must be a multiple of 8.
-extern "C" int axb_colsum(const void* x, float* part, float* out, int rows, int N, int dtype, int device, void* stream) {
+extern "C" int axb_colsum(const void* x, float* part, void* out, int rows, int N, int dtype, int out_dtype, int device,
+                          void* stream) {
   using namespace axb;
   if (N % 8 || rows <= 0) { set_error("colsum: N must be a multiple of 8 and rows positive"); return -1; }
   const int splits = axb_colsum_splits(device, rows, N);
@@ -592,14 +600,14 @@ extern "C" int axb_colsum(const void* x, float* part, float* out, int rows, int 
   else if (dtype == 1) colsum_partial_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, part, rows, N);
   else colsum_partial_kernel<float><<<grid, 256, 0, s>>>((const float*)x, part, rows, N);
   AXB_CUDA(cudaGetLastError());
-  fold_partials_kernel<<<(N + 31) / 32, dim3(32, 32), 0, s>>>(part, nullptr, out, nullptr, splits, N);
+  fold_partials_kernel<<<(N + 31) / 32, dim3(32, 32), 0, s>>>(part, nullptr, out, nullptr, splits, N, out_dtype);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }
 
 // dx = dy * gelu'(x) (tanh form) and colsum[c] = sum_r dx[r, c] in one pass.  part: [axb_colsum_splits, N] fp32.
-extern "C" int axb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, float* part, float* colsum, int rows,
-                                   int N, int dtype, int device, void* stream) {
+extern "C" int axb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, float* part, void* colsum, int rows,
+                                   int N, int dtype, int out_dtype, int device, void* stream) {
   using namespace axb;
   if (N % 8 || rows <= 0) { set_error("gelu_bwd_colsum: N must be a multiple of 8 and rows positive"); return -1; }
   if (dtype != 0 && dtype != 1) { set_error("gelu_bwd_colsum: bf16 or fp16 only"); return -1; }
@@ -612,7 +620,7 @@ extern "C" int axb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, floa
   else
     gelu_bwd_colsum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)dy, (const __half*)x, (__half*)dx, part, rows, N);
   AXB_CUDA(cudaGetLastError());
-  fold_partials_kernel<<<(N + 31) / 32, dim3(32, 32), 0, s>>>(part, nullptr, colsum, nullptr, splits, N);
+  fold_partials_kernel<<<(N + 31) / 32, dim3(32, 32), 0, s>>>(part, nullptr, colsum, nullptr, splits, N, out_dtype);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }

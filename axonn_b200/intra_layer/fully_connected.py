@@ -153,7 +153,10 @@ class AsyncLinear(Function):
         ctx.depth_parallel_group = depth_parallel_group
         ctx.shape = local_weight_shape
         ctx.compute_dtype = compute_dtype
-        return out.reshape(*input_.shape[:-1], local_weight_shape[0])
+        # a view created inside a custom Function may not be modified in place later (rotary embeddings are
+        # applied in place to the projection output): return the tensor itself when no reshape is needed
+        target = (*input_.shape[:-1], local_weight_shape[0])
+        return out if tuple(out.shape) == target else out.reshape(target)
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -163,7 +166,7 @@ class AsyncLinear(Function):
         bias_sum = None
         if pre_act is not None:
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                go2, bias_sum = ops.gelu_backward_colsum(go2, pre_act)   # bias gradient in the same pass
+                go2, bias_sum = ops.gelu_backward_colsum(go2, pre_act, out_dtype=ctx.bias_dtype)   # bias gradient in the same pass
             else:
                 go2 = ops.gelu_backward(go2, pre_act)
         x2 = input_.reshape(-1, input_.shape[-1])
@@ -220,7 +223,7 @@ class AsyncLinear(Function):
             if ctx.needs_input_grad[1]:
                 grad_weight = wgrad()
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                grad_bias = (bias_sum if bias_sum is not None else ops.column_sum(go2)).to(ctx.bias_dtype)
+                grad_bias = bias_sum if bias_sum is not None else ops.column_sum(go2, out_dtype=ctx.bias_dtype)
             if handle is not None and overlap_ar:
                 handle.wait()
         else:
@@ -230,7 +233,7 @@ class AsyncLinear(Function):
             if ctx.needs_input_grad[0]:
                 grad_input = dgrad()
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                grad_bias = (bias_sum if bias_sum is not None else ops.column_sum(go2)).to(ctx.bias_dtype)
+                grad_bias = bias_sum if bias_sum is not None else ops.column_sum(go2, out_dtype=ctx.bias_dtype)
         if grad_input is not None:
             grad_input = grad_input.reshape(input_.shape)
         return grad_input, grad_weight, grad_bias, None, None, None, None, None, None

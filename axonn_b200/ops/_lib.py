@@ -16,8 +16,13 @@ import torch
 _LIB = None
 _LOCK = threading.Lock()
 LIB_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib")
-# AXONN_LIB_PATH selects a library built elsewhere (e.g. an ablation build with -DAXB_ABLATION)
-LIB_PATH = os.environ.get("AXONN_LIB_PATH") or os.path.join(LIB_DIR, "libaxonn_b200.so")
+# AXONN_LIB_PATH selects a library built elsewhere (e.g. an ablation build with -DAXB_ABLATION);
+# AXONN_DEBUG_BOUNDS=1 selects the bounds-checking build when it has been built
+# (``python axonn_b200/utils/build.py --debug-bounds``)
+_DEBUG_LIB = os.path.join(LIB_DIR, "libaxonn_b200_debug.so")
+LIB_PATH = os.environ.get("AXONN_LIB_PATH") or (
+    _DEBUG_LIB if os.environ.get("AXONN_DEBUG_BOUNDS", "0") not in ("", "0") and os.path.exists(_DEBUG_LIB)
+    else os.path.join(LIB_DIR, "libaxonn_b200.so"))
 
 # number of kernels launched through this library since the last reset
 launch_count = 0
@@ -100,8 +105,19 @@ _STATUS_NAMES = {
     0x121: "fused reduction: partial tiles of a peer never arrived",
     0x122: "fused reduction (shared-memory ring): inbox slots never arrived",
     0x123: "fused reduction (shared-memory ring): ring group never freed",
+    0x109: "fused all-reduce (two-shot): a peer never finished writing its rows of the result",
+    0x124: "fused all-reduce (two-shot): a peer never announced where its output lies",
     0x201: "expert dispatch / combine: a peer never signalled",
     0x301: "gradient all-reduce: a peer never published its bucket",
+    0x302: "gradient all-reduce: a peer never delivered its partial slices",
+    0x303: "gradient all-reduce: a peer never delivered its reduced slice",
+    0x501: "row all-to-all: a peer never announced its output",
+    0x502: "row all-to-all / embedding rows: a peer never finished",
+    0x503: "embedding row fetch: a peer never published its table shard",
+    0x504: "embedding gradient: a peer never published its gradient shard",
+    0x701: "bounds check (debug build): inbox slot outside the peer's inbox",
+    0x702: "bounds check (debug build): output element outside C",
+    0x703: "bounds check (debug build): flag index outside the flag array",
     0x401: "flash attention forward: producer timed out",
     0x402: "flash attention forward: MMA issuer timed out",
     0x404: "flash attention forward: softmax warps timed out",

@@ -28,9 +28,10 @@ class _GeluFn(torch.autograd.Function):
         return gelu_backward(dy, x)
 
 
-def gelu_backward_colsum(dy, x):
-    """``dx = dy * gelu'(x)`` and ``dx.sum(0)`` (fp32) of 2-D tensors in one pass: the backward of a fused
-    bias + GELU layer needs both, and the column sums come for free while ``dx`` is being written."""
+def gelu_backward_colsum(dy, x, out_dtype=torch.float32):
+    """``dx = dy * gelu'(x)`` and ``dx.sum(0)`` (fp32 accumulation, returned as ``out_dtype``) of 2-D tensors in
+    one pass: the backward of a fused bias + GELU layer needs both, and the column sums come for free while
+    ``dx`` is being written."""
     if (x.is_cuda and x.dim() == 2 and x.shape[1] % 8 == 0 and x.dtype in (torch.bfloat16, torch.float16)
             and dy.dtype == x.dtype and x.shape[0] > 0):
         x, dy = x.contiguous(), dy.contiguous()
@@ -39,16 +40,17 @@ def gelu_backward_colsum(dy, x):
         dev = x.device.index
         splits = L.axb_colsum_splits(ctypes.c_int(dev), ctypes.c_int(rows), ctypes.c_int(n))
         part = torch.empty((splits, n), dtype=torch.float32, device=x.device)
-        colsum = torch.empty(n, dtype=torch.float32, device=x.device)
+        colsum = torch.empty(n, dtype=out_dtype, device=x.device)
         dx = torch.empty_like(x)
         _lib.check(L.axb_gelu_bwd_colsum(_lib.ptr(dy), _lib.ptr(x), _lib.ptr(dx), _lib.ptr(part), _lib.ptr(colsum),
                                          ctypes.c_int(rows), ctypes.c_int(n),
-                                         ctypes.c_int(0 if x.dtype == torch.bfloat16 else 1), ctypes.c_int(dev),
-                                         _lib.stream_ptr()), "axb_gelu_bwd_colsum")
+                                         ctypes.c_int(0 if x.dtype == torch.bfloat16 else 1),
+                                         ctypes.c_int({torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out_dtype]),
+                                         ctypes.c_int(dev), _lib.stream_ptr()), "axb_gelu_bwd_colsum")
         _lib.add_launches(1)
         return dx, colsum
     dx = gelu_backward(dy, x)
-    return dx, dx.sum(0, dtype=torch.float32)
+    return dx, dx.sum(0, dtype=torch.float32).to(out_dtype)
 
 
 def gelu_backward(dy, x):

@@ -109,14 +109,14 @@ class _NormFn(torch.autograd.Function):
         dx = torch.empty_like(x2)
         sums = torch.empty((rows, 2), dtype=torch.float32, device=x2.device) if n > 1 else None
         part = torch.empty((2, grid, H), dtype=torch.float32, device=x2.device)
-        dgb = torch.empty((2, H), dtype=torch.float32, device=x2.device)
+        dgb = torch.empty((2, H), dtype=g.dtype, device=x2.device)   # written in the parameter's dtype: no cast kernel
 
         def call(mode):
             st = L.axb_norm_bwd(_lib.ptr(dy2), _lib.ptr(x2), _lib.ptr(g), _lib.ptr(stats), _lib.ptr(dx),
                                 _lib.ptr(sums), _lib.ptr(part[0]), _lib.ptr(part[1]), _lib.ptr(dgb[0]),
                                 _lib.ptr(dgb[1]), ctypes.c_int(rows), ctypes.c_int(H), ctypes.c_int(H * n),
                                 ctypes.c_int(1 if rms else 0), ctypes.c_int(mode), ctypes.c_int(_DT[x2.dtype]),
-                                ctypes.c_int(dev), _lib.stream_ptr())
+                                ctypes.c_int(_DT[g.dtype]), ctypes.c_int(dev), _lib.stream_ptr())
             _lib.check(st, "axb_norm_bwd")
             if mode != 1:
                 _lib.add_launches(1)
@@ -127,8 +127,8 @@ class _NormFn(torch.autograd.Function):
             call(1)
             dist.all_reduce(sums, group=group)
             call(2)
-        dgamma = dgb[0].to(g.dtype)
-        dbeta = dgb[1].to(g.dtype) if ctx.has_beta else None
+        dgamma = dgb[0]
+        dbeta = dgb[1] if ctx.has_beta else None
         return dx.reshape(ctx.shape), dgamma, dbeta, None, None, None
 
 
@@ -142,20 +142,22 @@ def rms_norm(x, gamma, eps=1e-6, group=None):
     return _NormFn.apply(x, gamma, None, eps, True, group)
 
 
-def column_sum(x):
-    """``x.sum(0)`` of a 2-D tensor in fp32 (bias gradients).  One pass over ``x`` at memory bandwidth on
-    CUDA (partial sums per row split, then a fold); plain PyTorch elsewhere."""
+def column_sum(x, out_dtype=torch.float32):
+    """``x.sum(0)`` of a 2-D tensor, accumulated in fp32 and returned as ``out_dtype`` (bias gradients).  One
+    pass over ``x`` at memory bandwidth on CUDA (partial sums per row split, then a fold that writes the
+    requested dtype); plain PyTorch elsewhere."""
     if not (_lib.use_cuda_kernels(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.is_contiguous()
-            and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and x.shape[0] > 0):
-        return x.sum(0, dtype=torch.float32)
+            and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and x.shape[0] > 0
+            and out_dtype in _DT):
+        return x.sum(0, dtype=torch.float32).to(out_dtype)
     rows, n = x.shape
     L = _lib.lib()
     dev = x.device.index
     splits = L.axb_colsum_splits(ctypes.c_int(dev), ctypes.c_int(rows), ctypes.c_int(n))
     part = torch.empty((splits, n), dtype=torch.float32, device=x.device)
-    out = torch.empty(n, dtype=torch.float32, device=x.device)
-    dt = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[x.dtype]
+    out = torch.empty(n, dtype=out_dtype, device=x.device)
     _lib.check(L.axb_colsum(_lib.ptr(x), _lib.ptr(part), _lib.ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
-                            ctypes.c_int(dt), ctypes.c_int(dev), _lib.stream_ptr()), "axb_colsum")
+                            ctypes.c_int(_DT[x.dtype]), ctypes.c_int(_DT[out_dtype]), ctypes.c_int(dev),
+                            _lib.stream_ptr()), "axb_colsum")
     _lib.add_launches(1)
     return out

@@ -98,5 +98,19 @@ def build_library(force=False, verbose=True):
     return LIB_PATH
 
 
+DEBUG_LIB_PATH = os.path.join(LIB_DIR, "libaxonn_b200_debug.so")
+
+
+def build_debug_library():
+    """The bounds-checking build (``-DAXB_DEBUG_BOUNDS``): kernels verify computed offsets into peer memory
+    before every store and record violations in the device status word instead of making the access.  Loaded
+    instead of the normal library when ``AXONN_DEBUG_BOUNDS=1`` and the file exists."""
+    os.makedirs(LIB_DIR, exist_ok=True)
+    return build_variant(DEBUG_LIB_PATH, ["-DAXB_DEBUG_BOUNDS"], os.path.join(LIB_DIR, "obj_debug"))
+
+
 if __name__ == "__main__":
-    build_library(force="--force" in sys.argv)
+    if "--debug-bounds" in sys.argv:
+        print(build_debug_library())
+    else:
+        build_library(force="--force" in sys.argv)
