@@ -76,6 +76,12 @@ def init(
         # row / column tensor parallelism all-reduces activations inside the GEMM kernels: their outputs live in
         # a peer-mapped arena so that the owner of a tile can store the finished values on every rank
         _symm.create_output_arena()
+    elif comm_handle.use_cuda and G_intra_d * G_data > 1:
+        # depth / data parallelism only: a small arena serves the stand-alone peer-memory collectives
+        # (all-gather, reduce-scatter, row all-to-all of tensors that do not go through a fused GEMM)
+        import os
+
+        _symm.create_output_arena(None if os.environ.get("AXONN_SYMM_ARENA_GB") else 2 << 30)
 
 
 def finalize() -> None:

@@ -164,6 +164,60 @@ allreduce_twoshot_kernel(long long nvec, float scale, CommCtx c) {
 }
 
 
+// ----------------------------------------------------------------------------- in-switch (NVLS) all-reduce of the bucket
+// Same contract as allreduce_twoshot_kernel, but the reduction happens inside the NVSwitch: rank k owns slice k of
+// the bucket, loads the SUM of that slice over all ranks with one multimem.ld_reduce per 16 bytes (fp32 accumulation
+// in the switch for bf16), scales it and broadcasts it to every rank's bucket with multimem.st.  `mc` is the
+// multicast address of the bucket (the symmetric allocation is bound to an NVLink multicast object).  Per rank
+// and direction only 1/n of the bucket crosses the link twice, independent of n.
+template <typename T> struct MultiMem;
+template <> struct MultiMem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* mc, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct MultiMem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* mc, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_nvls_kernel(long long nvec, float scale, uint8_t* mc, CommCtx c) {
+  __shared__ int sh_ok;
+  if (!comm_wait_all(c, &sh_ok)) { comm_signal_when_last(c, false); return; }
+  const long long per = nvec / c.n;
+  const long long lo = per * c.rank;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
+    uint8_t* addr = mc + (lo + i) * 16;
+    uint4 u = MultiMem<T>::ld_reduce(addr);
+    if (scale != 1.f) {
+      float f[V16<T>::N];
+      V16<T>::unpack(u, f);
+#pragma unroll
+      for (int e = 0; e < V16<T>::N; ++e) f[e] *= scale;
+      u = V16<T>::pack(f);
+    }
+    MultiMem<T>::st(addr, u);
+  }
+  comm_signal_when_last(c);
+}
+
 // ----------------------------------------------------------------------------- one-kernel gradient all-reduce
 // The whole data-parallel gradient all-reduce of a list of tensors in ONE launch, straight from and to the
 // gradient tensors (no pack or unpack pass): the chunk list of the table is cut into n slices, rank k owns slice k.
@@ -407,6 +461,25 @@ extern "C" int axb_grad_allreduce(const long long* table, int ntensors, long lon
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == 0) grad_allreduce_kernel<float><<<grid, 512, 0, s>>>(table, ntensors, total_chunks, chunks_per_slice, scale, c);
   else grad_allreduce_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(table, ntensors, total_chunks, chunks_per_slice, scale, c);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// In-place all-reduce of every rank's bucket through the NVSwitch (multimem); `mc_bucket` is the multicast
+// address of the bucket.  Same flags as axb_allreduce_twoshot.
+extern "C" int axb_allreduce_nvls(long long nbytes, int dtype, float scale, void* mc_bucket, const AxbCommCtx* ctx,
+                                  int device, void* stream) {
+  CommCtx c;
+  if (fill_comm(c, ctx, device)) return -1;
+  if (!mc_bucket) { set_error("allreduce (NVLS): no multicast address"); return -1; }
+  if (nbytes % (16 * c.n)) { set_error("allreduce: bucket bytes must be a multiple of 16 * group size"); return -1; }
+  const long long nvec = nbytes / 16;
+  const long long per = nvec / c.n;
+  long long blocks = (per + 511) / 512;
+  const int cap = sm_count(device) * 2;
+  const int grid = (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+  if (dtype == 0) allreduce_nvls_kernel<float><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, (uint8_t*)mc_bucket, c);
+  else allreduce_nvls_kernel<__nv_bfloat16><<<grid, 512, 0, (cudaStream_t)stream>>>(nvec, scale, (uint8_t*)mc_bucket, c);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }

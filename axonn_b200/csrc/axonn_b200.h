@@ -165,6 +165,9 @@ int axb_embedding_scatter_add(const long long* ids, long long n_tokens, const vo
 int axb_bucket_copy(const long long* table, int ntensors, long long total_chunks, void* bucket, int dtype, int direction,
                     const AxbCommCtx* ctx, int device, void* stream);
 int axb_allreduce_twoshot(long long nbytes, int dtype, float scale, const AxbCommCtx* ctx, int device, void* stream);
+/* the same reduction inside the NVSwitch (multimem.ld_reduce / multimem.st on the bucket's multicast address) */
+int axb_allreduce_nvls(long long nbytes, int dtype, float scale, void* mc_bucket, const AxbCommCtx* ctx, int device,
+                       void* stream);
 
 /* Peer-memory context of the one-kernel gradient all-reduce (allreduce.cu::grad_allreduce_kernel). */
 typedef struct AxbGradArCtx {

@@ -40,10 +40,39 @@ def _drop(input_, dim, process_group=None):
     return torch.narrow(input_, dim, me * chunk, chunk)
 
 
+def _p2p_rows_ok(tensor, process_group, row_bytes, out_bytes) -> bool:
+    """The peer-memory row kernel can serve this exchange: CUDA, peer-capable group, 16-byte rows, and an output
+    that is small against the output arena (a rule every rank evaluates identically, so all ranks of the group
+    take the same path)."""
+    if not tensor.is_cuda or row_bytes % 16 or tensor.data_ptr() % 16:
+        return False
+    from ..parallel import fused, symm
+
+    arena = symm.output_arena()
+    return arena is not None and out_bytes * 16 <= arena.nbytes and fused.a2a_rows_usable(process_group, tensor)
+
+
 def _gather_raw(input_, dim, process_group):
     n = _size(process_group)
     input_ = input_.contiguous()
     dim = dim % input_.ndim
+    # Peer-memory all-gather: every rank stores its block straight into its place in every rank's output
+    # (rows = the dimensions before `dim`, one row = this rank's extent of `dim` and everything behind it), so
+    # a gather along an inner dimension needs no concatenation copy afterwards.
+    rows = 1
+    for d_ in input_.shape[:dim]:
+        rows *= d_
+    row_bytes = input_.element_size()
+    for d_ in input_.shape[dim:]:
+        row_bytes *= d_
+    if input_.numel() > 0 and _p2p_rows_ok(input_, process_group, row_bytes, n * rows * row_bytes):
+        from ..parallel import fused
+
+        me = dist.get_rank(process_group)
+        shape = list(input_.shape)
+        shape[dim] *= n
+        blocks = [(input_.data_ptr(), row_bytes, me * row_bytes, n * row_bytes, rows, row_bytes)] * n
+        return fused.a2a_rows(process_group, blocks, tuple(shape), input_.dtype, input_.device)
     flat = torch.empty((n * input_.shape[0],) + tuple(input_.shape[1:]), dtype=input_.dtype,
                        device=input_.device)
     dist.all_gather_into_tensor(flat, input_, group=process_group)
@@ -87,6 +116,17 @@ def _reduce_scatter(input_, dim, process_group=None, overlap_comm=False):
     input_ = input_.contiguous()
     shape = list(input_.shape)
     shape[0] //= n
+    shard_bytes = input_.numel() // n * input_.element_size()
+    if input_.numel() > 0 and _p2p_rows_ok(input_, process_group, shard_bytes, n * shard_bytes):
+        # Peer-memory reduce-scatter: chunk j of every rank is stored into slot [source rank] of rank j's
+        # receive tensor in one kernel, then summed locally in rank order (fp32 accumulation)
+        from ..parallel import fused
+
+        me = dist.get_rank(process_group)
+        blocks = [(input_.data_ptr() + j * shard_bytes, shard_bytes, me * shard_bytes, shard_bytes, 1, shard_bytes)
+                  for j in range(n)]
+        parts = fused.a2a_rows(process_group, blocks, (n,) + tuple(shape), input_.dtype, input_.device)
+        return parts.sum(0, dtype=torch.float32).to(input_.dtype) if input_.dtype != torch.float32 else parts.sum(0)
     output = torch.empty(shape, dtype=input_.dtype, device=input_.device)
     h = dist.reduce_scatter_tensor(output, input_, group=process_group, async_op=overlap_comm)
     if overlap_comm:

@@ -637,7 +637,9 @@ def try_all_reduce_scale_(grads, group, scale) -> bool:
     """Sum ``grads`` over ``group`` and multiply by ``scale`` with the peer-memory kernels: by default one
     kernel that reads and writes the gradient tensors directly (owners of the slices receive the partials,
     reduce in rank order, scale and hand the result to every peer); ``AXONN_GRAD_AR=bucket`` selects the older
-    pack -> two-shot -> unpack form.  Returns False when not applicable."""
+    pack -> two-shot -> unpack form and ``AXONN_GRAD_AR=nvls`` the same with the reduction done inside the
+    NVSwitch (``multimem.ld_reduce`` / ``multimem.st``; needs a multicast-bound symmetric allocation, i.e. NVLS
+    not disabled for symmetric memory).  Returns False when not applicable."""
     if not grads or not group_usable(group, grads[0]):
         return False
     dtype = grads[0].dtype
@@ -645,7 +647,8 @@ def try_all_reduce_scale_(grads, group, scale) -> bool:
         return False
     import os
 
-    if os.environ.get("AXONN_GRAD_AR", "fused") != "bucket":
+    mode = os.environ.get("AXONN_GRAD_AR", "fused")
+    if mode not in ("bucket", "nvls"):
         es = grads[0].element_size()
         batch, size = [], 0
         for g in grads:
@@ -676,9 +679,16 @@ def try_all_reduce_scale_(grads, group, scale) -> bool:
                                  ctypes.c_void_p(bucket), ctypes.c_int(code), ctypes.c_int(0), ctypes.byref(pack),
                                  ctypes.c_int(dev), _lib.stream_ptr()), "axb_bucket_copy")
     red = ch.ctx(ch._READY, ch._DONE)       # waits READY, publishes DONE
-    _lib.check(L.axb_allreduce_twoshot(ctypes.c_longlong(nbytes), ctypes.c_int(code),
-                                       ctypes.c_float(1.0 if scale is None else float(scale)), ctypes.byref(red),
-                                       ctypes.c_int(dev), _lib.stream_ptr()), "axb_allreduce_twoshot")
+    if mode == "nvls" and ch.buf.multicast_ptr:
+        # reduction inside the NVSwitch: multimem.ld_reduce / multimem.st on the bucket's multicast address
+        _lib.check(L.axb_allreduce_nvls(ctypes.c_longlong(nbytes), ctypes.c_int(code),
+                                        ctypes.c_float(1.0 if scale is None else float(scale)),
+                                        ctypes.c_void_p(ch.buf.multicast_ptr + _CTRL_BYTES), ctypes.byref(red),
+                                        ctypes.c_int(dev), _lib.stream_ptr()), "axb_allreduce_nvls")
+    else:
+        _lib.check(L.axb_allreduce_twoshot(ctypes.c_longlong(nbytes), ctypes.c_int(code),
+                                           ctypes.c_float(1.0 if scale is None else float(scale)), ctypes.byref(red),
+                                           ctypes.c_int(dev), _lib.stream_ptr()), "axb_allreduce_twoshot")
     unpack = ch.ctx(ch._DONE, ch._READY)    # waits DONE
     _lib.check(L.axb_bucket_copy(_lib.ptr(tab), ctypes.c_int(ntens), ctypes.c_longlong(chunks),
                                  ctypes.c_void_p(bucket), ctypes.c_int(code), ctypes.c_int(1), ctypes.byref(unpack),

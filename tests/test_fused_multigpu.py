@@ -46,6 +46,9 @@ def _gemm_ar_case(rank, world, two_shot):
             other = out.clone()
             dist.broadcast(other, src=0)
             assert torch.equal(other, out), "ranks disagree bitwise"
+            # the reduction order is fixed (rank order): the same inputs give the same bits on every run
+            again = fused.gemm_all_reduce(layout, a, b, group)
+            assert torch.equal(again, out), "results differ from run to run"
     # guard bytes behind every symmetric buffer are untouched: nothing wrote past an inbox or a flag array
     from axonn_b200.parallel import symm
     assert symm.verify_canaries() >= 1
@@ -111,12 +114,15 @@ def test_gemm_reduce_scatter(world):
             assert err <= 1.6e-2 * scale + 1e-3, (M, N, K, err, scale)
 
 
-def _grad_ar_case(rank, world):
+def _grad_ar_case(rank, world, mode):
     import torch.distributed as dist
 
     from axonn_b200 import ops
     from axonn_b200.ops import _lib
 
+    # "fused": one kernel straight from / to the gradient tensors; "bucket": pack -> two-shot -> unpack;
+    # "nvls": the bucket form with the reduction inside the NVSwitch (falls back to two-shot without multicast)
+    os.environ["AXONN_GRAD_AR"] = mode
     dev = torch.device("cuda", rank)
     out = []
     for dtype in (torch.bfloat16, torch.float32):
@@ -140,12 +146,12 @@ def _grad_ar_case(rank, world):
     return out
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_gradient_all_reduce(world):
+@pytest.mark.parametrize("world,mode", [(2, "fused"), (2, "bucket"), (2, "nvls"), (4, "fused"), (8, "fused"), (8, "nvls")])
+def test_gradient_all_reduce(world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    for per_rank in run_distributed(_grad_ar_case, world, backend="nccl", timeout=300):
+    for per_rank in run_distributed(_grad_ar_case, world, mode, backend="nccl", timeout=300):
         for name, status, err, tol, same in per_rank:
             assert status == 0 and err <= tol and same, (name, status, err)
 
