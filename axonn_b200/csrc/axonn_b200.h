@@ -118,6 +118,8 @@ int axb_moe_dispatch(const void* x, int x_by_token, const long long* dest, const
 int axb_moe_gather(void* out, const long long* dest, const unsigned char* keep, int T, int k, int C, int H,
                    const AxbMoeCtx* ctx, int device, void* stream);
 int axb_moe_signal(const AxbMoeCtx* ctx, int device, void* stream);
+/* wait for the flags of ctx, copy src into this rank's peer-readable dst, publish ctx->epoch: one launch */
+int axb_copy_publish(const void* src, void* dst, long long nbytes, const AxbMoeCtx* ctx, int device, void* stream);
 int axb_moe_wait(const AxbMoeCtx* ctx, int device, void* stream);
 
 /* Peer-memory context of the gradient all-reduce kernels (see AxbMoeCtx for the flag conventions). */
@@ -220,6 +222,13 @@ int axb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, fl
 int axb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* stats, void* dx, float* sums,
                  float* dgamma_part, float* dbeta_part, void* dgamma, void* dbeta, int rows, int H, int H_total, int rms,
                  int mode, int dtype, int param_dtype, int device, void* stream);
+/* the residual add fused into the norm: y = norm(x + delta), hout = x + delta; dx = norm_backward(dy) + dres */
+int axb_add_norm_fwd(const void* x, const void* delta, void* hout, const void* gamma, const void* beta, void* y,
+                     float* stats, int rows, int H, int H_total, float eps, int rms, int mode, int dtype, int device,
+                     void* stream);
+int axb_add_norm_bwd(const void* dy, const void* dres, const void* x, const void* gamma, const float* stats, void* dx,
+                     float* sums, float* dgamma_part, float* dbeta_part, void* dgamma, void* dbeta, int rows, int H,
+                     int H_total, int rms, int mode, int dtype, int param_dtype, int device, void* stream);
 int axb_colsum_splits(int device, int rows, int N);
 int axb_colsum(const void* x, float* part, void* out, int rows, int N, int dtype, int out_dtype, int device, void* stream);
 int axb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, float* part, void* colsum, int rows, int N, int dtype,

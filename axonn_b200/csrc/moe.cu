@@ -139,6 +139,19 @@ moe_gather_rows_kernel(__nv_bfloat16* __restrict__ out, const long long* __restr
   moe_signal_when_last(c);
 }
 
+// Copy `nvec` 16-byte words into a peer-readable buffer once every peer has released it (flags >= wait_value),
+// then publish `epoch` to every peer: the publication step of the fused all-gather (a rank's weight shard goes
+// into its outbox) as one launch instead of wait + copy + signal.
+__global__ void __launch_bounds__(256)
+copy_publish_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long nvec, MoeCtx c) {
+  __shared__ int sh_ok;
+  if (!moe_wait_all(c, &sh_ok)) { moe_signal_when_last(c, false); return; }
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+  moe_signal_when_last(c);
+}
+
 // One thread: publish `value` into flag[my rank] of every peer (after all prior work of the stream).
 __global__ void moe_signal_kernel(MoeCtx c) {
   __threadfence_system();
@@ -194,6 +207,25 @@ extern "C" int axb_moe_gather(void* out, const long long* dest, const unsigned c
   const long long cap = static_cast<long long>(sm_count(device)) * 8;
   const int grid = static_cast<int>(items < cap ? (items < 1 ? 1 : items) : cap);
   moe_gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)out, dest, keep, T, k, C, H, c);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// dst (this rank's peer-readable buffer) <- src, nbytes a multiple of 16, gated by the flags of `ctx` and followed
+// by the publication of ctx->epoch to every peer.
+extern "C" int axb_copy_publish(const void* src, void* dst, long long nbytes, const AxbMoeCtx* ctx, int device,
+                                void* stream) {
+  MoeCtx c;
+  if (fill_ctx(c, ctx, device)) return -1;
+  if (nbytes % 16 || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) {
+    set_error("axb_copy_publish: buffers must be 16-byte aligned and sized");
+    return -1;
+  }
+  const long long nvec = nbytes / 16;
+  const long long want = (nvec + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count(device)) * 2;
+  const int grid = static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+  copy_publish_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), nvec, c);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }

@@ -60,6 +60,19 @@ template <> struct Vec8<float> {
   }
 };
 
+// f = T(f + d): the residual sum, rounded to the storage type exactly like a separate elementwise add would.
+template <typename T> __device__ __forceinline__ float round_as(float v);
+template <> __device__ __forceinline__ float round_as<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+template <> __device__ __forceinline__ float round_as<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <> __device__ __forceinline__ float round_as<float>(float v) { return v; }
+template <typename T>
+__device__ __forceinline__ void add_rounded(float (&f)[8], const T* delta) {
+  float d[8];
+  Vec8<T>::load(delta, d);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = round_as<T>(f[i] + d[i]);
+}
+
 // Sum two values over the block; result broadcast to all threads.
 __device__ __forceinline__ void block_sum2(float& a, float& b, float* red /* [2*32] */) {
 #pragma unroll
@@ -78,7 +91,10 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float* red /* [2*
 template <typename T, bool RMS>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-                T* __restrict__ y, float* __restrict__ stats, int rows, int H, int H_total, float eps, int mode) {
+                T* __restrict__ y, float* __restrict__ stats, int rows, int H, int H_total, float eps, int mode,
+                const T* __restrict__ delta, T* __restrict__ hout) {
+  // delta != null (modes 0 and 1): the row that is normalised is h = x + delta, which is also written to hout
+  // (the residual stream after the add); every thread re-reads only the chunks of hout that it wrote itself.
   __shared__ float red[64];
   const int nchunk = H / 8;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -88,6 +104,10 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
       float s1 = 0.f, s2 = 0.f;
       for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
         float f[8]; Vec8<T>::load(xr + c * 8, f);
+        if (delta) {
+          add_rounded<T>(f, delta + static_cast<size_t>(row) * H + c * 8);
+          Vec8<T>::store(hout + static_cast<size_t>(row) * H + c * 8, f);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s1 += f[i]; s2 += f[i] * f[i]; }
       }
@@ -102,6 +122,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     } else {
       mean = stats[2 * row]; rstd = stats[2 * row + 1];
     }
+    if (delta) xr = hout + static_cast<size_t>(row) * H;
     T* yr = y + static_cast<size_t>(row) * H;
     for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
       float f[8], g[8], b[8];
@@ -125,7 +146,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                 const float* __restrict__ stats, T* __restrict__ dx, float* __restrict__ sums,
                 float* __restrict__ dgamma_part, float* __restrict__ dbeta_part, int rows, int H, int H_total,
-                int mode) {
+                int mode, const T* __restrict__ dres) {
+  // dres != null: gradient that reaches the normalised row through the residual path; it is added to dx
   __shared__ float red[64];
   const int nchunk = H / 8;
   float ag[CH][8], ab[CH][8];
@@ -170,6 +192,12 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
           float xh = (f[i] - mean) * rstd;
           o[i] = rstd * (g[i] * d[i] - m1 - xh * m2);
           ag[k][i] += d[i] * xh; ab[k][i] += d[i];
+        }
+        if (dres) {
+          float r8[8];
+          Vec8<T>::load(dres + static_cast<size_t>(row) * H + c * 8, r8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += r8[i];
         }
         Vec8<T>::store(dxr + c * 8, o);
       }
@@ -220,7 +248,8 @@ __device__ __forceinline__ void block_sum_n(float (&v)[NV], float* red /* [2][NV
 template <typename T, bool RMS, int CH, int R>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-                     T* __restrict__ y, float* __restrict__ stats, int rows, int H, float eps) {
+                     T* __restrict__ y, float* __restrict__ stats, int rows, int H, float eps,
+                     const T* __restrict__ delta, T* __restrict__ hout) {
   __shared__ float red[2 * 2 * R * 8];
   const int nchunk = H / 8;
   float g[CH][8], b[CH][8];
@@ -244,8 +273,13 @@ norm_fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const
 #pragma unroll
       for (int k = 0; k < CH; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
-        if (row0 + r < rows && c < nchunk) Vec8<T>::load(x + static_cast<size_t>(row0 + r) * H + c * 8, f[r][k]);
-        else {
+        if (row0 + r < rows && c < nchunk) {
+          Vec8<T>::load(x + static_cast<size_t>(row0 + r) * H + c * 8, f[r][k]);
+          if (delta) {
+            add_rounded<T>(f[r][k], delta + static_cast<size_t>(row0 + r) * H + c * 8);
+            Vec8<T>::store(hout + static_cast<size_t>(row0 + r) * H + c * 8, f[r][k]);
+          }
+        } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[r][k][i] = 0.f;
         }
@@ -282,7 +316,7 @@ template <typename T, bool RMS, int CH, int R>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_rows_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                      const float* __restrict__ stats, T* __restrict__ dx, float* __restrict__ dgamma_part,
-                     float* __restrict__ dbeta_part, int rows, int H) {
+                     float* __restrict__ dbeta_part, int rows, int H, const T* __restrict__ dres) {
   __shared__ float red[2 * 2 * R * 8];
   const int nchunk = H / 8;
   float g[CH][8], ag[CH][8], ab[CH][8];
@@ -340,6 +374,12 @@ norm_bwd_rows_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
         float o[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = rstd[r] * (g[k][i] * d[r][k][i] - m1 - xh[r][k][i] * m2);
+        if (dres) {
+          float r8[8];
+          Vec8<T>::load(dres + static_cast<size_t>(row0 + r) * H + c * 8, r8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += r8[i];
+        }
         Vec8<T>::store(dx + static_cast<size_t>(row0 + r) * H + c * 8, o);
       }
     }
@@ -482,13 +522,13 @@ int sm_count(int device);
 
 template <typename T>
 static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
-                      int H_total, float eps, int rms, int mode, int grid, cudaStream_t s) {
+                      int H_total, float eps, int rms, int mode, int grid, cudaStream_t s, const void* delta, void* hout) {
   const int threads = (H / 8 <= 128) ? 128 : NORM_THREADS;  // no idle threads for narrow (sharded) rows
   if (mode == 0 && H == H_total && H / 8 <= 2 * NORM_THREADS && H / 8 > 128) {
     const int ch = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
 #define AXB_NORM_FWD_ROWS(RMS_, CH_, R_)                                                                         \
   norm_fwd_rows_kernel<T, RMS_, CH_, R_><<<min(grid, (rows + R_ - 1) / R_), NORM_THREADS, 0, s>>>(              \
-      (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, stats, rows, H, eps)
+      (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, stats, rows, H, eps, (const T*)delta, (T*)hout)
     if (rms) { if (ch == 1) AXB_NORM_FWD_ROWS(true, 1, 4); else AXB_NORM_FWD_ROWS(true, 2, 2); }
     else { if (ch == 1) AXB_NORM_FWD_ROWS(false, 1, 4); else AXB_NORM_FWD_ROWS(false, 2, 2); }
 #undef AXB_NORM_FWD_ROWS
@@ -497,10 +537,10 @@ static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* 
   }
   if (rms)
     norm_fwd_kernel<T, true><<<grid, threads, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
-                                                     stats, rows, H, H_total, eps, mode);
+                                                     stats, rows, H, H_total, eps, mode, (const T*)delta, (T*)hout);
   else
     norm_fwd_kernel<T, false><<<grid, threads, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y,
-                                                      stats, rows, H, H_total, eps, mode);
+                                                      stats, rows, H, H_total, eps, mode, (const T*)delta, (T*)hout);
   AXB_CUDA(cudaGetLastError());
   return 0;
 }
@@ -508,7 +548,7 @@ static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* 
 template <typename T>
 static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const float* stats, void* dx, float* sums,
                       float* dgp, float* dbp, int rows, int H, int H_total, int rms, int mode, int grid,
-                      cudaStream_t s, int* blocks_launched) {
+                      cudaStream_t s, int* blocks_launched, const void* dres) {
   *blocks_launched = grid;
   const int nchunk = H / 8;
   const int threads = (nchunk <= 128) ? 128 : NORM_THREADS;
@@ -517,7 +557,7 @@ static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const fl
 #define AXB_NORM_BWD_ROWS(RMS_, CH_, R_)                                                                       \
   *blocks_launched = min(grid, (rows + R_ - 1) / R_);                                                          \
   norm_bwd_rows_kernel<T, RMS_, CH_, R_><<<*blocks_launched, NORM_THREADS, 0, s>>>(                            \
-      (const T*)dy, (const T*)x, (const T*)gamma, stats, (T*)dx, dgp, dbp, rows, H)
+      (const T*)dy, (const T*)x, (const T*)gamma, stats, (T*)dx, dgp, dbp, rows, H, (const T*)dres)
     if (rms) { if (ch == 1) { AXB_NORM_BWD_ROWS(true, 1, 2); } else { AXB_NORM_BWD_ROWS(true, 2, 1); } }
     else { if (ch == 1) { AXB_NORM_BWD_ROWS(false, 1, 2); } else { AXB_NORM_BWD_ROWS(false, 2, 1); } }
 #undef AXB_NORM_BWD_ROWS
@@ -526,7 +566,7 @@ static int norm_bwd_t(const void* dy, const void* x, const void* gamma, const fl
   }
 #define AXB_NORM_BWD(RMS_, CH_)                                                                              \
   norm_bwd_kernel<T, RMS_, CH_><<<grid, threads, 0, s>>>((const T*)dy, (const T*)x, (const T*)gamma, stats, \
-                                                              (T*)dx, sums, dgp, dbp, rows, H, H_total, mode)
+                                                              (T*)dx, sums, dgp, dbp, rows, H, H_total, mode, (const T*)dres)
   if (rms) {
     if (ch <= 1) AXB_NORM_BWD(true, 1); else if (ch <= 2) AXB_NORM_BWD(true, 2);
     else if (ch <= 4) AXB_NORM_BWD(true, 4); else AXB_NORM_BWD(true, 8);
@@ -546,31 +586,53 @@ extern "C" int axb_norm_grid(int device, int rows) {
   return rows < g ? rows : g;
 }
 
-extern "C" int axb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
-                            int H_total, float eps, int rms, int mode, int dtype, int device, void* stream) {
+// y = norm(x + delta) and hout = x + delta when delta is non-null (the residual add fused into the norm; not in
+// mode 2, which applies given statistics to a row that has already been summed); y = norm(x) otherwise.
+extern "C" int axb_add_norm_fwd(const void* x, const void* delta, void* hout, const void* gamma, const void* beta,
+                                void* y, float* stats, int rows, int H, int H_total, float eps, int rms, int mode,
+                                int dtype, int device, void* stream) {
   using namespace axb;
   if (H % 8 || H > NORM_THREADS * 8 * NORM_MAX_CHUNKS) { set_error("norm: hidden %d unsupported", H); return -1; }
+  if (delta && (mode == 2 || !hout)) { set_error("norm: the fused residual add needs an output for x + delta and mode 0 or 1"); return -1; }
   if (rows <= 0) return 0;
   const int grid = axb_norm_grid(device, rows);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == 0) return norm_fwd_t<__nv_bfloat16>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s);
-  if (dtype == 1) return norm_fwd_t<__half>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s);
-  return norm_fwd_t<float>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s);
+  if (dtype == 0) return norm_fwd_t<__nv_bfloat16>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s, delta, hout);
+  if (dtype == 1) return norm_fwd_t<__half>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s, delta, hout);
+  return norm_fwd_t<float>(x, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, grid, s, delta, hout);
+}
+
+extern "C" int axb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
+                            int H_total, float eps, int rms, int mode, int dtype, int device, void* stream) {
+  return axb_add_norm_fwd(x, nullptr, nullptr, gamma, beta, y, stats, rows, H, H_total, eps, rms, mode, dtype, device, stream);
 }
 
 // dgamma_part / dbeta_part: [grid, H] fp32 scratch (grid from axb_norm_grid); dgamma/dbeta: [H] fp32 outputs.
+extern "C" int axb_add_norm_bwd(const void* dy, const void* dres, const void* x, const void* gamma, const float* stats,
+                                void* dx, float* sums, float* dgamma_part, float* dbeta_part, void* dgamma, void* dbeta,
+                                int rows, int H, int H_total, int rms, int mode, int dtype, int param_dtype, int device,
+                                void* stream);
 extern "C" int axb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* stats, void* dx,
                             float* sums, float* dgamma_part, float* dbeta_part, void* dgamma, void* dbeta, int rows,
                             int H, int H_total, int rms, int mode, int dtype, int param_dtype, int device, void* stream) {
+  return axb_add_norm_bwd(dy, nullptr, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, dgamma, dbeta, rows, H, H_total,
+                          rms, mode, dtype, param_dtype, device, stream);
+}
+
+// dx = norm_backward(dy) + dres (dres, optional: the gradient arriving through the residual path of a fused add + norm)
+extern "C" int axb_add_norm_bwd(const void* dy, const void* dres, const void* x, const void* gamma, const float* stats,
+                                void* dx, float* sums, float* dgamma_part, float* dbeta_part, void* dgamma, void* dbeta,
+                                int rows, int H, int H_total, int rms, int mode, int dtype, int param_dtype, int device,
+                                void* stream) {
   using namespace axb;
   if (H % 8 || H > NORM_THREADS * 8 * NORM_MAX_CHUNKS) { set_error("norm: hidden %d unsupported", H); return -1; }
   if (rows <= 0) return 0;
   const int grid = axb_norm_grid(device, rows);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int rc, nblocks = grid;
-  if (dtype == 0) rc = norm_bwd_t<__nv_bfloat16>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks);
-  else if (dtype == 1) rc = norm_bwd_t<__half>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks);
-  else rc = norm_bwd_t<float>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks);
+  if (dtype == 0) rc = norm_bwd_t<__nv_bfloat16>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks, dres);
+  else if (dtype == 1) rc = norm_bwd_t<__half>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks, dres);
+  else rc = norm_bwd_t<float>(dy, x, gamma, stats, dx, sums, dgamma_part, dbeta_part, rows, H, H_total, rms, mode, grid, s, &nblocks, dres);
   if (rc) return rc;
   if (mode != 1 && dgamma_part && dgamma) {
     fold_partials_kernel<<<(H + 31) / 32, dim3(32, 32), 0, s>>>(dgamma_part, rms ? nullptr : dbeta_part, dgamma,

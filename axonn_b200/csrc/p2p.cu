@@ -122,11 +122,23 @@ a2a_rows_kernel(RowBlocks blocks, P2pCtx c) {
     const int j = (c.rank + s) % c.n;
     const RowBlock& b = blocks.b[j];
     uint8_t* dst = reinterpret_cast<uint8_t*>(sh_out[j]) + b.dst_off;
+    // work unit = one 2 KB piece of one row (four 16-byte words per lane in flight), so that the parallelism
+    // does not depend on the shape: a single row of 100 MB spreads over the whole grid like 100k short rows do
     const long long vecs = b.row_bytes >> 4;
-    for (long long row = me; row < b.rows; row += warps) {
-      const uint4* sp = reinterpret_cast<const uint4*>(b.src + row * b.src_pitch);
-      uint4* dp = reinterpret_cast<uint4*>(dst + row * b.dst_pitch);
-      for (long long v = lane; v < vecs; v += 32) dp[v] = sp[v];
+    const long long pieces = (vecs + 127) >> 7;
+    const long long units = b.rows * pieces;
+    for (long long u = me; u < units; u += warps) {
+      const long long row = u / pieces, v0 = (u - row * pieces) << 7;
+      const uint4* sp = reinterpret_cast<const uint4*>(b.src + row * b.src_pitch) + v0;
+      uint4* dp = reinterpret_cast<uint4*>(dst + row * b.dst_pitch) + v0;
+      const long long left = vecs - v0;
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (lane + k * 32 < left) r[k] = sp[lane + k * 32];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (lane + k * 32 < left) dp[lane + k * 32] = r[k];
     }
   }
   p2p_finish(c, true);
@@ -241,7 +253,7 @@ extern "C" int axb_a2a_rows(const AxbP2pCtx* ctx, const AxbRowBlock* blocks, int
         set_error("axb_a2a_rows: rows, pitches and offsets must be multiples of 16 bytes");
         return -1;
       }
-      rows_total += b.rows;
+      rows_total += b.rows * ((b.row_bytes + 2047) / 2048);   // 2 KB work units
     } else {
       b = RowBlock{nullptr, 0, 0, 0, 0, 0};
     }

@@ -58,6 +58,13 @@ class TPNorm(nn.Module):
             return ops.rms_norm(x, self.weight, self.eps, self.group)
         return ops.layer_norm(x, self.weight, self.bias, self.eps, self.group)
 
+    def add_norm(self, x, delta):
+        """``h = x + delta`` and ``norm(h)`` in one kernel (the residual add fused into the normalisation);
+        returns ``(h, norm(h))``."""
+        if self.rms:
+            return ops.add_rms_norm(x, delta, self.weight, self.eps, self.group)
+        return ops.add_layer_norm(x, delta, self.weight, self.bias, self.eps, self.group)
+
 
 class ParallelAttention(nn.Module):
     """Causal self-attention; KV groups (a KV head with its query heads) are split
@@ -134,9 +141,22 @@ class TransformerBlock(nn.Module):
     def _make_mlp(self, hidden, ffn, activation, bias, dtype, out_std):
         return ParallelMLP(hidden, ffn, activation, bias, dtype, out_init_std=out_std)
 
+    def forward_deferred(self, x, delta=None):
+        """The block with its residual adds fused into the normalisation kernels.  ``delta`` is the output of
+        the previous block's MLP that has not been added to the residual stream ``x`` yet; returns
+        ``(residual stream, this block's MLP output)`` - the caller (the next block, or the model's final norm)
+        performs the last add inside its own norm kernel."""
+        if delta is None:
+            y = self.norm1(x)
+        else:
+            x, y = self.norm1.add_norm(x, delta)
+        a = self.attn(y)
+        x, y = self.norm2.add_norm(x, a)
+        return x, self.mlp(y)
+
     def forward(self, x):
-        x = x + self.attn(self.norm1(x))
-        return x + self.mlp(self.norm2(x))
+        x, m = self.forward_deferred(x)
+        return x + m
 
 
 class ParallelLMHead(nn.Module):

@@ -61,12 +61,16 @@ class Llama(nn.Module):
 
     def forward(self, tokens, targets=None):
         x = self.tok_emb(tokens)
+        delta = None   # MLP output of the previous block, added to x inside the next norm kernel
         for blk in self.blocks:
             if self.cfg.activation_checkpointing and self.training:
+                if delta is not None:
+                    x, delta = x + delta, None
                 x = checkpoint(blk, x, use_reentrant=False)
             else:
-                x = blk(x)
-        return self.head(self.norm_f(x), targets)
+                x, delta = blk.forward_deferred(x, delta)
+        y = self.norm_f(x) if delta is None else self.norm_f.add_norm(x, delta)[1]
+        return self.head(y, targets)
 
     def num_parameters(self):
         return count_parameters(self)

@@ -80,12 +80,16 @@ class Mixtral(nn.Module):
 
     def forward(self, tokens, targets=None):
         x = self.tok_emb(tokens)
+        delta = None   # expert-layer output of the previous block, added to x inside the next norm kernel
         for blk in self.blocks:
             if self.cfg.activation_checkpointing and self.training:
+                if delta is not None:
+                    x, delta = x + delta, None
                 x = checkpoint(blk, x, use_reentrant=False)
             else:
-                x = blk(x)
-        out = self.head(self.norm_f(x), targets)
+                x, delta = blk.forward_deferred(x, delta)
+        y = self.norm_f(x) if delta is None else self.norm_f.add_norm(x, delta)[1]
+        out = self.head(y, targets)
         if targets is None:
             return out
         aux = sum(b.mlp.last_aux_loss for b in self.blocks) / len(self.blocks)

@@ -23,6 +23,6 @@ from .multi_tensor import (  # noqa: F401
     multi_tensor_l2norm_sq,
     multi_tensor_scale_,
 )
-from .norm import column_sum, layer_norm, rms_norm  # noqa: F401
+from .norm import add_layer_norm, add_rms_norm, column_sum, layer_norm, rms_norm  # noqa: F401
 from .optim_step import AdamTable, adamw_reference_, multi_tensor_adamw, prune_topk_  # noqa: F401
 from .rope import apply_rope, rope_table  # noqa: F401

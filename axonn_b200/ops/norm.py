@@ -132,6 +132,117 @@ class _NormFn(torch.autograd.Function):
         return dx.reshape(ctx.shape), dgamma, dbeta, None, None, None
 
 
+class _AddNormFn(torch.autograd.Function):
+    """``h = x + delta``; ``y = norm(h)``; returns ``(h, y)``.  On CUDA the add is done inside the norm kernel
+    (one read of ``x`` and ``delta``, one write of ``h`` and ``y``) and the backward adds the gradient of the
+    residual path to the norm's input gradient inside the backward kernel; elsewhere it is the two plain steps."""
+
+    @staticmethod
+    def forward(ctx, x, delta, gamma, beta, eps, rms, group):
+        shape = x.shape
+        H = shape[-1]
+        n = _group_size(group)
+        ctx.rms, ctx.group, ctx.n, ctx.shape, ctx.has_beta = rms, group, n, shape, beta is not None
+        x2 = x.reshape(-1, H).contiguous()
+        d2 = delta.reshape(-1, H).contiguous()
+        rows = x2.shape[0]
+        if not x2.is_cuda:
+            h = x2 + d2
+            y, mean, rstd = _torch_norm_fwd(h, gamma, beta, eps, rms, group)
+            ctx.save_for_backward(h, gamma, mean, rstd)
+            return h.reshape(shape), y.reshape(shape)
+        L = _lib.lib()
+        dev = x2.device.index
+        h = torch.empty_like(x2)
+        y = torch.empty_like(x2)
+        stats = torch.empty((rows, 2), dtype=torch.float32, device=x2.device)
+        g = gamma.to(x2.dtype) if gamma.dtype != x2.dtype else gamma
+        b = None if beta is None else (beta.to(x2.dtype) if beta.dtype != x2.dtype else beta)
+
+        def call(mode, src, dl):
+            st = L.axb_add_norm_fwd(_lib.ptr(src), _lib.ptr(dl), _lib.ptr(h if dl is not None else None), _lib.ptr(g),
+                                    _lib.ptr(b), _lib.ptr(y), _lib.ptr(stats), ctypes.c_int(rows), ctypes.c_int(H),
+                                    ctypes.c_int(H * n), ctypes.c_float(eps), ctypes.c_int(1 if rms else 0),
+                                    ctypes.c_int(mode), ctypes.c_int(_DT[x2.dtype]), ctypes.c_int(dev), _lib.stream_ptr())
+            _lib.check(st, "axb_add_norm_fwd")
+
+        if n == 1:
+            call(0, x2, d2)
+        else:
+            call(1, x2, d2)                      # writes h and the partial row sums
+            dist.all_reduce(stats, group=group)
+            Ht = float(H * n)
+            mean = stats[:, 0] / Ht if not rms else torch.zeros_like(stats[:, 0])
+            var = stats[:, 1] / Ht - mean * mean
+            stats = torch.stack([mean, torch.rsqrt(var.clamp_min(0) + eps)], 1).contiguous()
+            call(2, h, None)
+        ctx.save_for_backward(h, g, stats)
+        return h.reshape(shape), y.reshape(shape)
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        rms, group, n = ctx.rms, ctx.group, ctx.n
+        H = ctx.shape[-1]
+        dy2 = dy.reshape(-1, H).contiguous()
+        dh2 = None if dh is None else dh.reshape(-1, H).contiguous()
+        if not dy2.is_cuda:
+            x2, gamma, mean, rstd = ctx.saved_tensors
+            xh = (x2.float() - mean) * rstd
+            gd = dy2.float() * gamma.float()
+            s1 = torch.zeros_like(mean) if rms else gd.sum(-1, keepdim=True)
+            s2 = (gd * xh).sum(-1, keepdim=True)
+            if n > 1:
+                st = torch.cat([s1, s2], -1)
+                dist.all_reduce(st, group=group)
+                s1, s2 = st[..., :1], st[..., 1:]
+            Ht = H * n
+            dx = rstd * (gd - s1 / Ht - xh * s2 / Ht)
+            if dh2 is not None:
+                dx = dx + dh2.float()
+            dgamma = (dy2.float() * xh).sum(0).to(gamma.dtype)
+            dbeta = dy2.float().sum(0).to(gamma.dtype) if ctx.has_beta else None
+            dx = dx.to(dy.dtype).reshape(ctx.shape)
+            return dx, dx, dgamma, dbeta, None, None, None
+        x2, g, stats = ctx.saved_tensors
+        rows = x2.shape[0]
+        L = _lib.lib()
+        dev = x2.device.index
+        grid = L.axb_norm_grid(ctypes.c_int(dev), ctypes.c_int(rows))
+        dx = torch.empty_like(x2)
+        sums = torch.empty((rows, 2), dtype=torch.float32, device=x2.device) if n > 1 else None
+        part = torch.empty((2, grid, H), dtype=torch.float32, device=x2.device)
+        dgb = torch.empty((2, H), dtype=g.dtype, device=x2.device)
+
+        def call(mode):
+            st = L.axb_add_norm_bwd(_lib.ptr(dy2), _lib.ptr(dh2), _lib.ptr(x2), _lib.ptr(g), _lib.ptr(stats), _lib.ptr(dx),
+                                    _lib.ptr(sums), _lib.ptr(part[0]), _lib.ptr(part[1]), _lib.ptr(dgb[0]),
+                                    _lib.ptr(dgb[1]), ctypes.c_int(rows), ctypes.c_int(H), ctypes.c_int(H * n),
+                                    ctypes.c_int(1 if rms else 0), ctypes.c_int(mode), ctypes.c_int(_DT[x2.dtype]),
+                                    ctypes.c_int(_DT[g.dtype]), ctypes.c_int(dev), _lib.stream_ptr())
+            _lib.check(st, "axb_add_norm_bwd")
+            if mode != 1:
+                _lib.add_launches(1)
+
+        if n == 1:
+            call(0)
+        else:
+            call(1)
+            dist.all_reduce(sums, group=group)
+            call(2)
+        dx = dx.reshape(ctx.shape)
+        return dx, dx, dgb[0], (dgb[1] if ctx.has_beta else None), None, None, None
+
+
+def add_layer_norm(x, delta, gamma, beta, eps=1e-5, group=None):
+    """``h = x + delta; y = LayerNorm(h)`` in one kernel; returns ``(h, y)``."""
+    return _AddNormFn.apply(x, delta, gamma, beta, eps, False, group)
+
+
+def add_rms_norm(x, delta, gamma, eps=1e-6, group=None):
+    """``h = x + delta; y = RMSNorm(h)`` in one kernel; returns ``(h, y)``."""
+    return _AddNormFn.apply(x, delta, gamma, None, eps, True, group)
+
+
 def layer_norm(x, gamma, beta, eps=1e-5, group=None):
     """LayerNorm over the last dimension; with ``group`` the last dimension is one
     shard of a hidden dimension split over that process group."""

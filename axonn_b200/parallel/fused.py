@@ -416,12 +416,13 @@ class _AgChannel:
         for j in range(self.n):
             c.buf_peer[j] = base[j]
             c.signal_peer[j] = base[j] + self._READY
-        # the outbox of this parity was last read by the peers in call e-2
-        _lib.check(L.axb_moe_wait(ctypes.byref(c), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_wait")
+        # one launch: wait until the peers are done with this parity's outbox (they read it in call e-2), copy the
+        # shard into it, raise READY on every peer
         nbytes = shard.numel() * shard.element_size()
         off = _CTRL_BYTES + parity * self.capacity
-        self.buf.local[off:off + nbytes].view(shard.dtype).copy_(shard.reshape(-1))
-        _lib.check(L.axb_moe_signal(ctypes.byref(c), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_signal")
+        shard = shard.contiguous()
+        _lib.check(L.axb_copy_publish(_lib.ptr(shard), ctypes.c_void_p(base[self.rank] + off), ctypes.c_longlong(nbytes),
+                                      ctypes.byref(c), ctypes.c_int(dev), _lib.stream_ptr()), "axb_copy_publish")
         return e, parity, nbytes
 
     def context(self, e, parity, nbytes, staging, rows_per_shard, n_copy):

@@ -255,6 +255,20 @@ def bench_fused_loopback(M=16384, N=4096, K=1024, iters=3):
                           gemm_ms=round(t_gemm, 4), rel_err=round(err, 5))), flush=True)
 
 
+def bench_fused_loopback_two_shot(M=16384, N=4096, K=1024, iters=3):
+    """Only the two-shot kernel of the one-GPU emulation (3 warm-up + 3 timed launches of one kernel): the
+    case that is captured with ncu (``-k regex:gemm_tcgen05 -s 3 -c 1``)."""
+    from axonn_b200.parallel import fused
+
+    dev = torch.device("cuda", 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    t_two, _ = time_cuda(lambda: fused.gemm_all_reduce_loopback(a, b, two_shot=True), iters=iters, flush=flush)
+    print(json.dumps(dict(label="fused GEMM+AR two-shot, rank 0 of 2 emulated on one GPU", M=M, N=N, K=K,
+                          two_shot_loopback_ms=round(t_two, 4))), flush=True)
+
+
 AG_SHAPES = [
     # (tokens, out_l, in_l, label): weight [out_l, in_l] sharded by rows over the ranks of the group
     (16384, 28672, 4096, "Llama-8B gate|up fwd"),
@@ -408,6 +422,8 @@ if __name__ == "__main__":
         bench_memory_bound()
     elif what == "fused_loopback":
         bench_fused_loopback()
+    elif what == "fused_loopback_two_shot":
+        bench_fused_loopback_two_shot()
     elif what in ("fused", "fused_one_shot", "ag", "rs", "grad_ar"):
         import os
 

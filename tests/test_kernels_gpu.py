@@ -40,6 +40,39 @@ def test_norm_fwd_bwd(rms, shape):
         _close(b.grad, br.grad, 2e-2, 5e-2)
 
 
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("shape", [(300, 2048), (64, 4096), (130, 1024), (17, 8192)])
+def test_add_norm_fused_residual(rms, shape):
+    """h = x + delta and norm(h) in one kernel, backward with the residual-path gradient added in the kernel:
+    against the two plain steps evaluated in fp32."""
+    from axonn_b200 import ops
+
+    rows, H = shape
+    torch.manual_seed(5)
+    x = torch.randn(rows, H, device=DEV).bfloat16().requires_grad_(True)
+    dl = torch.randn(rows, H, device=DEV).bfloat16().requires_grad_(True)
+    g = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True)
+    b = (0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True)
+    dy = torch.randn(rows, H, device=DEV).bfloat16()
+    dh = torch.randn(rows, H, device=DEV).bfloat16()
+    h, y = ops.add_rms_norm(x, dl, g, 1e-5) if rms else ops.add_layer_norm(x, dl, g, b, 1e-5)
+    torch.autograd.backward([h, y], [dh, dy])
+    assert torch.equal(h, (x.detach() + dl.detach()))          # the same rounding as a separate add
+    xr, dr, gr, br = (t.detach().float().requires_grad_(True) for t in (x, dl, g, b))
+    hr = (xr + dr) + ((xr + dr).bfloat16().float() - (xr + dr)).detach()   # value rounded like the kernel, gradient of the sum
+    if rms:
+        yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * gr
+    else:
+        yr = F.layer_norm(hr, (H,), gr, br, 1e-5)
+    torch.autograd.backward([hr, yr], [dh.float(), dy.float()])
+    _close(y, yr, 1e-2)
+    _close(x.grad, xr.grad, 2e-2)
+    assert torch.equal(x.grad, dl.grad)
+    _close(g.grad, gr.grad, 2e-2, 5e-2)
+    if not rms:
+        _close(b.grad, br.grad, 2e-2, 5e-2)
+
+
 def test_gelu_swiglu():
     from axonn_b200 import ops
     from axonn_b200.ops.activation import _split_gu
