@@ -25,6 +25,14 @@ unsigned int axb_device_status(int device, int clear);
  * epilogue: 0 none, 1 +bias[N], 2 +bias then GELU(tanh), 3 GELU; with GELU the
  * pre-activation is also written to `aux` when it is non-null.
  * accumulate != 0: C += result.  Dimensions must be multiples of 8. */
+/* nb problems of one shape in one launch: problem e starts e * {a,b,c}_batch_rows rows below problem 0 in the
+   stacked 2-D operands; layouts 1 and 2 need K % 64 == 0.  With seg_counts the masked dimension (M; K in layout 2)
+   is nseg segments of seg_rows rows whose first seg_counts[e][s] rows hold data (the rest are zero): tiles or K
+   blocks without data are skipped, skipped tiles are stored as zeros */
+int axb_gemm_batched(int layout, const void* A, const void* B, void* C, int nb, int M, int N, int K,
+                     int a_batch_rows, int b_batch_rows, int c_batch_rows, int in_dtype, int out_dtype,
+                     int accumulate, const int* seg_counts /* device int32 [nb, nseg] or NULL */, int seg_rows,
+                     int nseg, int device, void* stream);
 int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias, void* aux,
              int M, int N, int K, int in_dtype, int out_dtype, int epilogue, int accumulate,
              int device, void* stream);
@@ -110,6 +118,7 @@ typedef struct AxbMoeCtx {
   unsigned int wait_value;
   unsigned int* signal_peer[8];
   unsigned int* counter;
+  int* cnt_peer[8];   /* dispatch only, may be NULL: rank j's table [n_local][n] of rows that every source sent per expert */
 } AxbMoeCtx;
 
 int axb_moe_dispatch(const void* x, int x_by_token, const long long* dest, const unsigned char* keep,

@@ -348,6 +348,306 @@ static int fa_launch(const CUtensorMap& tm, const FaParams& p, int device, cudaS
   return 0;
 }
 
+
+// -----------------------------------------------------------------------------------------------------
+// Forward, two query tiles per CTA ("ping-pong").  One CTA handles the adjacent 128-row query tiles
+// A = 2u and B = 2u + 1 of one (batch, head); they share every K_j / V_j tile that the TMA warp loads.
+//
+//   warp 0      TMA: Q_A, Q_B once; K_j and V_j into separate 2-stage rings
+//   warp 1      MMA: S_X = Q_X K_j^T into the 128 score columns of tile X, then O_X += P_X V_j with the
+//               A operand P_X read from tensor memory (bf16, in the first 64 of the score columns, written
+//               there by the softmax threads) and O_X accumulating in tensor memory over all KV tiles
+//   warps 2-3   idle: they complete the first warpgroup, which hands most of its registers to the others
+//   warps 4-7   softmax of tile A, one thread per query row (TMEM lane): one read of the 128 scores, row
+//   warps 8-11  maximum, exponentials, row sum, P back into tensor memory.  (8-11: the same for tile B.)
+//
+// While the threads of one tile work on their scores, the tensor core runs the other tile's two MMAs, so
+// neither side waits for the other in steady state.  The running maximum of a row is only raised when the
+// tile's maximum exceeds it by more than 2^8 (the probabilities then stay below 256, exact in the final
+// normalisation because the row sum uses the same reference); only then the row's O accumulator is rescaled
+// in tensor memory, by the softmax thread itself, between the completion of the previous PV MMA (implied by
+// the score barrier, which is committed after it) and the release of P.
+template <int HD>
+struct Fa2Smem {
+  static constexpr int TILE = 128 * HD * 2;
+  static constexpr int Q_OFF = 0;                  // Q_A, Q_B
+  static constexpr int K_OFF = 2 * TILE;           // 2 stages
+  static constexpr int V_OFF = 4 * TILE;           // 2 stages
+  static constexpr int BAR_OFF = 6 * TILE;
+  static constexpr int NBARS = 1 + 2 + 2 + 2 + 2 + 2 + 2 + 2;
+  static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16 + 1024;
+};
+
+constexpr int FA2_THREADS = 384;
+
+template <int HD>
+__global__ void __launch_bounds__(FA2_THREADS, 1)
+fa_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams p) {
+  using S_ = Fa2Smem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S_::BAR_OFF);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 3;
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 7;
+  uint64_t* s_full = bars + 9;     // per query tile
+  uint64_t* p_full = bars + 11;    // per query tile
+  uint64_t* o_done = bars + 13;    // per query tile
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + S_::NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int npairs = p.S / (2 * FA_BQ);
+  const int u = npairs - 1 - static_cast<int>(blockIdx.z);   // heaviest pairs first, over the whole grid
+  const int head = blockIdx.x;
+  const int b = blockIdx.y;
+  const int g = head / p.qpk, jq = head % p.qpk;
+  const int n_a = 2 * u + 1, n_b = 2 * u + 2;                // causal: KV tiles 0..qt of each query tile
+  const int row0 = b * p.S + 2 * u * FA_BQ;
+  const int col_q = (g * (p.qpk + 2) + jq) * HD;
+  const int col_k = (g * (p.qpk + 2) + p.qpk) * HD;
+  const int col_v = col_k + HD;
+  const uint64_t timeout = p.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_done[i], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) tma_prefetch_desc(&tmQKV);
+  if (warp == 1) { tmem_alloc(tmem_ptr_smem, 512); tmem_relinquish(); }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  // columns: scores of A [0,128), of B [128,256) (P_X = the first 64 of them), O_A [256,256+HD), O_B [384,384+HD)
+  // the register budget of a role must be set inside its branch: after a join the compiler assumes the smaller one
+  if (warp < 4) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+   if (warp == 0) {
+    if (elect_one()) {
+      bool ok = true;
+      mbar_expect_tx(q_full, 2 * S_::TILE);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_2d(smem + S_::Q_OFF + x * S_::TILE + c * 16384, &tmQKV, q_full, col_q + 64 * c, row0 + x * FA_BQ);
+      for (int j = 0; j < n_b && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int krow = b * p.S + j * FA_BKV;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], S_::TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_2d(smem + S_::K_OFF + st * S_::TILE + c * 16384, &tmQKV, &k_full[st], col_k + 64 * c, krow);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+        mbar_expect_tx(&v_full[st], S_::TILE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_2d(smem + S_::V_OFF + st * S_::TILE + c * 16384, &tmQKV, &v_full[st], col_v + 64 * c, krow);
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();     // give in-flight copies time to land before the CTA exits
+        while (globaltimer_ns() - t0 < 200000ull) {}
+        report_status(p.status, 0x405u);
+      }
+    }
+   } else if (warp == 1) {
+    if (elect_one()) {
+      bool ok = true;
+      const uint32_t idesc_s = umma_idesc(1, 0, 0, 128, 128);
+      const uint32_t idesc_o = umma_idesc(1, 0, 1, 128, HD);
+      // descriptors of a k-step = the tile's descriptor + a constant in the (16-byte unit) address field
+      auto issue_s = [&](int x, int j) {
+        const uint64_t qd = umma_smem_desc(smem_u32(smem + S_::Q_OFF + x * S_::TILE), 16, 1024);
+        const uint64_t kd = umma_smem_desc(smem_u32(smem + S_::K_OFF + (j & 1) * S_::TILE), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
+          umma_f16(tmem_base + x * 128, qd + off, kd + off, idesc_s, kk != 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int x, int j) {
+        // V: MN-major, 64-wide column chunks 16 KB apart (leading), 8-row groups 1 KB apart (stride)
+        const uint64_t vd = umma_smem_desc(smem_u32(smem + S_::V_OFF + (j & 1) * S_::TILE), 16384, 1024);
+#pragma unroll
+        for (int kk = 0; kk < FA_BKV / 16; ++kk)
+          umma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8, vd + ((kk * 2048) >> 4), idesc_o,
+                      (j | kk) != 0 ? 1u : 0u);
+      };
+      ok = mbar_wait(q_full, 0, abort_flag, timeout) && mbar_wait(&k_full[0], 0, abort_flag, timeout);
+      if (ok) {
+        tcgen05_fence_after();
+        issue_s(0, 0); umma_commit(&s_full[0]);
+        issue_s(1, 0); umma_commit(&s_full[1]);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_b && ok; ++j) {
+        const uint32_t kv_ph = (j >> 1) & 1, nx_ph = ((j + 1) >> 1) & 1;
+#pragma unroll 1
+        for (int x = 0; x < 2; ++x) {
+          const int n_x = x ? n_b : n_a;
+          if (j >= n_x) continue;
+          if (!mbar_wait(&p_full[x], j & 1, abort_flag, timeout) || !mbar_wait(&v_full[j & 1], kv_ph, abort_flag, timeout)) {
+            ok = false; break;
+          }
+          tcgen05_fence_after();
+          issue_pv(x, j);
+          if (x == 1) umma_commit(&v_empty[j & 1]);
+          if (j + 1 < n_x) {
+            if (!mbar_wait(&k_full[(j + 1) & 1], nx_ph, abort_flag, timeout)) { ok = false; break; }
+            tcgen05_fence_after();
+            issue_s(x, j + 1);
+            umma_commit(&s_full[x]);
+            if (x == 1) umma_commit(&k_empty[(j + 1) & 1]);
+          } else {
+            umma_commit(&o_done[x]);
+          }
+        }
+      }
+      if (!ok) report_status(p.status, 0x406u);
+    }
+   }
+  } else {
+    // ------------------------------------------------------------------ softmax of query tile x
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int x = (warp - 4) >> 2;
+    const int q4 = warp & 3;                         // the TMEM lane quarter this warp may access
+    const int r = q4 * 32 + lane;                    // query row inside the tile
+    const int n_x = x ? n_b : n_a;
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_base + x * 128;
+    const uint32_t o_addr = tmem_base + lane_base + 256 + x * 128;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_x; ++j) {
+      if (!mbar_wait(&s_full[x], j & 1, abort_flag, timeout)) { ok = false; break; }
+      tcgen05_fence_after();
+      uint32_t sv[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+      tmem_ld_wait();
+      const bool diag = (j == n_x - 1);
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      if (!diag) {
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sv[i])); mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          if (i > r) sv[i] = 0xff800000u;             // -inf: exp2 gives exactly 0
+          mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+        }
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;   // the scale is positive
+      const float m_new = (mx - m > 8.f) ? mx : m;   // first tile: m = -inf, always raised
+      const float alpha = exp2f(m - m_new);          // 1 when the reference stays
+      if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
+        // PV of tile j-1 has completed (the score barrier was committed after it): rescale O in place
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(o_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32(o_addr + c * 32, v);
+        }
+      }
+      l *= alpha;
+      m = m_new;
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i]), p.scale_log2, -m));
+          const float e1 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 1]), p.scale_log2, -m));
+          const float e2 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 2]), p.scale_log2, -m));
+          const float e3 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 3]), p.scale_log2, -m));
+          s0 += e0; s1 += e1; s2 += e2; s3 += e3;
+          const __nv_bfloat162 h0 = __floats2bfloat162_rn(e0, e1), h1 = __floats2bfloat162_rn(e2, e3);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&h0);
+          packed[i + 1] = *reinterpret_cast<const uint32_t*>(&h1);
+        }
+        tmem_st_32x32(s_addr + c * 32, packed);
+      }
+      l += (s0 + s1) + (s2 + s3);
+      tmem_st_wait();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[x]);
+    }
+    if (ok && mbar_wait(&o_done[x], 0, abort_flag, timeout)) {
+      tcgen05_fence_after();
+      const float inv_l = 1.f / l;
+      const size_t heads = static_cast<size_t>(p.G) * p.qpk;
+      const size_t qrow = static_cast<size_t>(b) * p.S + (2 * u + x) * FA_BQ + r;
+      __nv_bfloat16* dst = p.out + (qrow * heads + head) * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(o_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int e = t * 8 + i * 2;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[e]) * inv_l, __uint_as_float(v[e + 1]) * inv_l);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      p.lse[(static_cast<size_t>(b) * heads + head) * p.S + (2 * u + x) * FA_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
+    } else {
+      ok = false;
+    }
+    if (!ok && lane == 0) report_status(p.status, 0x407u);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tcgen05_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+template <int HD>
+static int fa_launch_pingpong(const CUtensorMap& tm, const FaParams& p, int device, cudaStream_t s) {
+  using S_ = Fa2Smem<HD>;
+  static bool configured[64] = {false};
+  auto kern = fa_fwd_pingpong_kernel<HD>;
+  if (!configured[device & 63]) {
+    AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_::TOTAL));
+    configured[device & 63] = true;
+  }
+  dim3 grid(p.G * p.qpk, p.B, p.S / (2 * FA_BQ));   // z (slowest) = pair of query tiles, heaviest first
+  kern<<<grid, FA2_THREADS, S_::TOTAL, s>>>(tm, p);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// AXONN_FA_FWD=single keeps the one-tile-per-CTA forward for every shape (A/B runs); read once.
+static bool fa_pingpong_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("AXONN_FA_FWD");
+    return !(e && e[0] == 's');
+  }();
+  return on;
+}
+
 }  // namespace axb
 
 // qkv: [B, S, G, qpk + 2, D] bf16 contiguous; out: [B, S, G*qpk, D] bf16; lse: [B, G*qpk, S] fp32.
@@ -365,6 +665,10 @@ extern "C" int axb_flash_attn_fwd(const void* qkv, void* out, float* lse, int B,
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
   p.status = st; p.timeout_ns = wait_timeout_ns();
+  if (S % 256 == 0 && fa_pingpong_enabled()) {
+    if (D == 128) return fa_launch_pingpong<128>(tm, p, device, static_cast<cudaStream_t>(stream));
+    return fa_launch_pingpong<64>(tm, p, device, static_cast<cudaStream_t>(stream));
+  }
   if (D == 128) return fa_launch<128>(tm, p, device, static_cast<cudaStream_t>(stream));
   return fa_launch<64>(tm, p, device, static_cast<cudaStream_t>(stream));
 }

@@ -65,6 +65,15 @@ struct GemmParams {
   int gemm_ctas;  // number of CTAs in the grid (every CTA computes tiles and, in the fused modes, reduces them)
   int pair;       // 1: CTA pairs (clusters of two) compute 256 x BN tiles, each CTA owning 128 rows of them
   int flag_batch; // tiles whose partial-arrival flags share one system-scope fence (fused all-reduce / reduce-scatter)
+  // Batched mode of the plain CTA-pair kernel: nb independent M x N x K problems of one shape in one launch.
+  // Problem e reads and writes its operands e * {a,b,c}_batch_rows rows further down the (stacked) 2-D arrays.
+  int nb, a_batch_rows, b_batch_rows, c_batch_rows;
+  // Row mask of the batched mode (capacity buffers of a mixture-of-experts layer): the masked dimension of
+  // problem e (mask_mode 1: the M rows; 2: the K rows of layout 2) consists of nseg segments of seg_rows rows of
+  // which only the first seg_counts[e * nseg + s] hold data, the rest being zero.  Tiles (mode 1) or K blocks
+  // (mode 2) without a data row are not computed; a skipped tile is stored as zeros.
+  const int* seg_counts;
+  int seg_rows, nseg, mask_mode;
   int debug;      // ablation builds only (-DAXB_ABLATION, then read once from AXB_AR_DEBUG; otherwise 0 and every branch on it is compiled out): 1 no flagger fence, 2 no peer stores, 4 no reducer fence, 8 no reduction, 16 no partial stores, 128 register-path reducer instead of the shared-memory ring
 };
 
@@ -97,6 +106,16 @@ struct GemmSmem {
   // + two 8-byte words of stall accounting
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 10) * 8 + 16 + 128 + 16 + 1024 /* alignment slack */;
 };
+
+// Does any of the rows [r0, r0 + len) of problem e hold data (see GemmParams::seg_counts)?
+__device__ __forceinline__ bool rows_hold_data(const int* __restrict__ seg_counts, int seg_rows, int nseg, int e, int r0,
+                                               int len) {
+  const int* cnt = seg_counts + e * nseg;
+  const int r1 = min(r0 + len, nseg * seg_rows);
+  for (int s = r0 / seg_rows; s < nseg && s * seg_rows < r1; ++s)
+    if (max(r0, s * seg_rows) < s * seg_rows + __ldg(cnt + s)) return true;
+  return false;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group, int& tm, int& tn) {
   const int per_group = group * tiles_n;
@@ -1109,6 +1128,14 @@ struct PairSmem {
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024 /* alignment slack */;
 };
 
+// Masked batched mode: is the 256-row tile pair tm2 of problem e computed at all?  (mode 1: one of its rows holds
+// data; mode 2: one of the problem's K blocks does.)  All three roles of the kernel ask the same question.
+__device__ __forceinline__ bool pair_tile_computed(const GemmParams& p, int e, int tm2, int num_kb) {
+  if (p.mask_mode == 1) return rows_hold_data(p.seg_counts, p.seg_rows, p.nseg, e, tm2 * 2 * BM, 2 * BM);
+  if (p.mask_mode == 2) return rows_hold_data(p.seg_counts, p.seg_rows, p.nseg, e, 0, num_kb * BK);
+  return true;
+}
+
 template <int A_MN, int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -1131,7 +1158,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_pairs = gridDim.x >> 1;
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles_m2 = (p.tiles_m + 1) >> 1;         // 256-row tile rows
-  const int total = tiles_m2 * p.tiles_n;
+  const int per_batch = tiles_m2 * p.tiles_n;
+  const int total = per_batch * p.nb;
   const uint64_t timeout = p.timeout_ns;
 
   if (threadIdx.x == 0) {
@@ -1155,10 +1183,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int it = pair_id; it < total && ok; it += num_pairs) {
-        int tm2, tn; tile_coords(it, tiles_m2, p.tiles_n, 8, tm2, tn);
+        const int e = it / per_batch;
+        int tm2, tn; tile_coords(it - e * per_batch, tiles_m2, p.tiles_n, 8, tm2, tn);
         const int m0 = (2 * tm2 + static_cast<int>(rank)) * BM;
         const int n0 = tn * BN + static_cast<int>(rank) * (BN / 2);   // this CTA's half of the B tile
+        // row coordinate of problem e in the stacked operands (rows = M or N for a K-major operand, K otherwise)
+        const int a_r = e * p.a_batch_rows, b_r = e * p.b_batch_rows;
+        if (p.mask_mode == 1 && !rows_hold_data(p.seg_counts, p.seg_rows, p.nseg, e, tm2 * 2 * BM, 2 * BM)) continue;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (p.mask_mode == 2 && !rows_hold_data(p.seg_counts, p.seg_rows, p.nseg, e, kb * BK, BK)) continue;
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, timeout)) { ok = false; break; }
           uint8_t* sA = smem + stage * S::STAGE_BYTES;
           uint8_t* sB = sA + S::A_BYTES;
@@ -1166,16 +1199,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
           const int k0 = kb * BK;
           if (A_MN == 0) {
-            tma_load_2d_pair(sA, &tmA, &full_bar[stage], k0, m0);
+            tma_load_2d_pair(sA, &tmA, &full_bar[stage], k0, m0 + a_r);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sA + j * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * j, k0);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sA + j * (BK * 128), &tmA, &full_bar[stage], m0 + 64 * j, k0 + a_r);
           }
           if (B_MN == 0) {
-            tma_load_2d_pair(sB, &tmB, &full_bar[stage], k0, n0);
+            tma_load_2d_pair(sB, &tmB, &full_bar[stage], k0, n0 + b_r);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0);
+            for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sB + j * (BK * 128), &tmB, &full_bar[stage], n0 + 64 * j, k0 + b_r);
           }
           if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
         }
@@ -1191,13 +1224,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int it = pair_id; it < total && ok; it += num_pairs, ++t) {
+      for (int it = pair_id; it < total && ok; it += num_pairs) {
+        const int e = it / per_batch;
+        if (p.mask_mode != 0) {
+          int tm2, tn; tile_coords(it - e * per_batch, tiles_m2, p.tiles_n, 8, tm2, tn);
+          if (!pair_tile_computed(p, e, tm2, num_kb)) continue;      // no accumulator buffer is used for it
+        }
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
+        ++t;
         if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, timeout)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
+        bool first = true;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (p.mask_mode == 2 && !rows_hold_data(p.seg_counts, p.seg_rows, p.nseg, e, kb * BK, BK)) continue;
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, timeout)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * S::STAGE_BYTES);
@@ -1206,8 +1247,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adesc = umma_smem_desc(a_addr + k * a_kstep, a_lbo, a_sbo);
             const uint64_t bdesc = umma_smem_desc(b_addr + k * b_kstep, b_lbo, b_sbo);
-            umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_pair(d_tmem, adesc, bdesc, idesc, (first && k == 0) ? 0u : 1u);
           }
+          first = false;
           umma_commit_pair(&empty_bar[stage]);      // frees this stage in both CTAs
           if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
         }
@@ -1224,15 +1266,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;
     bool ok = true;
     int t = 0;
-    for (int it = pair_id; it < total && ok; it += num_pairs, ++t) {
-      int tm2, tn; tile_coords(it, tiles_m2, p.tiles_n, 8, tm2, tn);
+    for (int it = pair_id; it < total && ok; it += num_pairs) {
+      const int e = it / per_batch;
+      int tm2, tn; tile_coords(it - e * per_batch, tiles_m2, p.tiles_n, 8, tm2, tn);
       const int tm = 2 * tm2 + static_cast<int>(rank);
+      const size_t local_row = static_cast<size_t>(tm) * BM + q * 32 + lane;
+      const bool row_ok = local_row < static_cast<size_t>(p.M);     // rows past M belong to the next problem
+      const size_t row = local_row + static_cast<size_t>(e) * p.c_batch_rows;
+      if (p.mask_mode != 0 && !pair_tile_computed(p, e, tm2, num_kb)) {
+        // a tile without data: zeros (nothing to add when accumulating), no accumulator buffer involved
+        if (row_ok && !p.accumulate) {
+          float z[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) z[i] = 0.f;
+          for (int c = 0; c < BN / 32 && tn * BN + c * 32 < p.N; ++c)
+            store_row32(p.C, p.out_dtype, row, p.N, tn * BN + c * 32, p.N, z, false);
+        }
+        continue;
+      }
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
+      ++t;
       if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, timeout)) { ok = false; break; }
       tcgen05_fence_after();
-      const size_t row = static_cast<size_t>(tm) * BM + q * 32 + lane;
-      const bool row_ok = row < static_cast<size_t>(p.M);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -1410,7 +1466,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   }
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + PAIR_BN - 1) / PAIR_BN;
-  const int total = ((p.tiles_m + 1) / 2) * p.tiles_n;
+  const int total = ((p.tiles_m + 1) / 2) * p.tiles_n * p.nb;
   const int pairs = sm_count(device) / 2;
   const int grid = 2 * (total < pairs ? total : pairs);
   p.gemm_ctas = grid;
@@ -1489,6 +1545,8 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
     p.ar.n = 1;
   }
   p.tn_offset = 0; p.kb_offset = 0;
+  p.nb = 1; p.a_batch_rows = p.b_batch_rows = p.c_batch_rows = 0;
+  p.seg_counts = nullptr; p.seg_rows = 0; p.nseg = 0; p.mask_mode = 0;
   p.flag_batch = flag_batch_setting();
   p.debug = 0;
 #ifdef AXB_ABLATION
@@ -1554,6 +1612,62 @@ extern "C" double axb_comm_stall_ms(int device, int reset) {
     cudaMemcpyToSymbol(axb::g_comm_stall, &z, sizeof(z));
   }
   return static_cast<double>(v) / 1024.0 / 1e6;
+}
+
+// nb problems of one shape in one launch of the CTA-pair kernel (the expert GEMMs of a mixture-of-experts layer):
+// A, B and C are 2-D arrays in which problem e starts e * {a,b,c}_batch_rows rows below problem 0.  Layouts as in
+// axb_gemm.  Tiles may run past a problem's M and N (those rows and columns are not stored), but an operand whose
+// rows are the reduction dimension (B in layout 1, A and B in layout 2) needs K to be a multiple of 64 so that no
+// K block reads the next problem's rows.
+//
+// seg_counts (device, int32 [nb, nseg]; nullptr = no mask): the M rows (layouts 0 and 1) or the K rows (layout 2)
+// of every problem are nseg segments of seg_rows rows, of which only the first seg_counts[e][s] hold data and the
+// others are zero.  Tiles (K blocks in layout 2) without a data row are skipped; a skipped tile is stored as zeros.
+extern "C" int axb_gemm_batched(int layout, const void* A, const void* B, void* C, int nb, int M, int N, int K,
+                                int a_batch_rows, int b_batch_rows, int c_batch_rows, int in_dtype, int out_dtype,
+                                int accumulate, const int* seg_counts, int seg_rows, int nseg, int device,
+                                void* stream) {
+  using namespace axb;
+  if (nb <= 0 || M <= 0 || N <= 0 || K <= 0) { set_error("axb_gemm_batched: empty problem"); return -1; }
+  if (layout < 0 || layout > 2) { set_error("axb_gemm_batched: bad layout %d", layout); return -1; }
+  if (in_dtype != 0 && in_dtype != 1) { set_error("axb_gemm_batched: operands must be bf16 or fp16"); return -1; }
+  if ((N % 8) || (K % 8) || (layout == 2 && (M % 8))) { set_error("axb_gemm_batched: dims must be multiples of 8"); return -1; }
+  if (layout != 0 && K % BK) { set_error("axb_gemm_batched: K must be a multiple of %d in layouts 1 and 2", BK); return -1; }
+  const int a_mn = (layout == 2) ? 1 : 0, b_mn = (layout == 0) ? 0 : 1;
+  const int a_rows = a_mn ? K : M, b_rows = b_mn ? K : N;
+  if (a_batch_rows < a_rows || b_batch_rows < b_rows || c_batch_rows < M) {
+    set_error("axb_gemm_batched: problems overlap (batch strides %d %d %d)", a_batch_rows, b_batch_rows, c_batch_rows);
+    return -1;
+  }
+  unsigned int* status_dev = nullptr;
+  if (!device_status_word(device, &status_dev)) { set_error("axb_gemm_batched: no status word"); return -1; }
+  CUtensorMap tmA, tmB;
+  const uint64_t a_total = static_cast<uint64_t>(a_batch_rows) * (nb - 1) + a_rows;
+  const uint64_t b_total = static_cast<uint64_t>(b_batch_rows) * (nb - 1) + b_rows;
+  if (a_total > 0x7fffffffull || b_total > 0x7fffffffull) { set_error("axb_gemm_batched: stacked operands too tall"); return -1; }
+  if (a_mn == 0) { if (make_tmap_2d_16bit(&tmA, A, a_total, K, BM, in_dtype)) return -1; }
+  else           { if (make_tmap_2d_16bit(&tmA, A, a_total, M, BK, in_dtype)) return -1; }
+  if (b_mn == 0) { if (make_tmap_2d_16bit(&tmB, B, b_total, K, PAIR_BN / 2, in_dtype)) return -1; }
+  else           { if (make_tmap_2d_16bit(&tmB, B, b_total, N, BK, in_dtype)) return -1; }
+  GemmParams p;
+  p.C = C; p.bias = nullptr; p.aux = nullptr; p.M = M; p.N = N; p.K = K;
+  p.out_dtype = out_dtype; p.in_dtype = in_dtype; p.epilogue = 0; p.accumulate = accumulate;
+  p.status = status_dev; p.timeout_ns = wait_timeout_ns();
+  p.ar.n = 1; p.ag.n = 1; p.tn_offset = 0; p.kb_offset = 0; p.flag_batch = 1; p.debug = 0; p.pair = 1;
+  p.nb = nb; p.a_batch_rows = a_batch_rows; p.b_batch_rows = b_batch_rows; p.c_batch_rows = c_batch_rows;
+  p.seg_counts = nullptr; p.seg_rows = 0; p.nseg = 0; p.mask_mode = 0;
+  if (seg_counts) {
+    const long long masked = (layout == 2) ? K : M;
+    if (seg_rows <= 0 || nseg <= 0 || static_cast<long long>(seg_rows) * nseg != masked) {
+      set_error("axb_gemm_batched: %d segments of %d rows do not cover the masked dimension (%lld)", nseg, seg_rows, masked);
+      return -1;
+    }
+    p.seg_counts = seg_counts; p.seg_rows = seg_rows; p.nseg = nseg; p.mask_mode = (layout == 2) ? 2 : 1;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (layout == 0) return launch_pair<0, 0>(tmA, tmB, p, device, s);
+  if (layout == 1) return launch_pair<0, 1>(tmA, tmB, p, device, s);
+  return launch_pair<1, 1>(tmA, tmB, p, device, s);
 }
 
 extern "C" int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N,

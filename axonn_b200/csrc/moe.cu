@@ -28,6 +28,7 @@ struct MoeCtx {
   unsigned int wait_value;
   unsigned int* signal_peer[8];  // flag array (indexed by my rank) on rank j that this kernel sets when done
   unsigned int* counter;      // local CTA completion counter
+  int* cnt_peer[8];           // dispatch: rank j's table [n_local][n] of the row counts per (expert, source)
   unsigned int* status;
   unsigned long long timeout_ns;
 };
@@ -98,7 +99,7 @@ moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, int x_by_token, con
       const int e = static_cast<int>(d / C), slot = static_cast<int>(d % C);
       const int owner = e / c.n_local, le = e % c.n_local;
       dst = reinterpret_cast<uint4*>(c.buf_peer[owner]) +
-            ((static_cast<size_t>(c.rank) * c.n_local + le) * C + slot) * vec_per_row;
+            ((static_cast<size_t>(le) * c.n + c.rank) * C + slot) * vec_per_row;
       const long long row = x_by_token ? item / k : item;
       src = reinterpret_cast<const uint4*>(x) + static_cast<size_t>(row) * vec_per_row;
     } else {
@@ -107,11 +108,16 @@ moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, int x_by_token, con
       if (slot < counts[e]) continue;
       const int owner = e / c.n_local, le = e % c.n_local;
       dst = reinterpret_cast<uint4*>(c.buf_peer[owner]) +
-            ((static_cast<size_t>(c.rank) * c.n_local + le) * C + slot) * vec_per_row;
+            ((static_cast<size_t>(le) * c.n + c.rank) * C + slot) * vec_per_row;
     }
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x)
       dst[v] = src ? src[v] : make_uint4(0u, 0u, 0u, 0u);
   }
+  // tell every owner how many of the capacity rows it received from this rank hold tokens (its expert GEMMs skip
+  // the tiles without any)
+  if (blockIdx.x == 0 && c.cnt_peer[0] != nullptr)
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+      c.cnt_peer[e / c.n_local][(e % c.n_local) * c.n + c.rank] = static_cast<int>(counts[e]);
   moe_signal_when_last(c);
 }
 
@@ -133,7 +139,7 @@ moe_gather_rows_kernel(__nv_bfloat16* __restrict__ out, const long long* __restr
     const int e = static_cast<int>(d / C), slot = static_cast<int>(d % C);
     const int owner = e / c.n_local, le = e % c.n_local;
     const uint4* src = reinterpret_cast<const uint4*>(c.buf_peer[owner]) +
-                       ((static_cast<size_t>(c.rank) * c.n_local + le) * C + slot) * vec_per_row;
+                       ((static_cast<size_t>(le) * c.n + c.rank) * C + slot) * vec_per_row;
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = src[v];
   }
   moe_signal_when_last(c);
@@ -176,6 +182,7 @@ static int fill_ctx(MoeCtx& c, const AxbMoeCtx* h, int device) {
   c.n = h->n; c.rank = h->rank; c.epoch = h->epoch; c.n_local = h->n_local;
   for (int j = 0; j < 8; ++j) { c.buf_peer[j] = h->buf_peer[j]; c.signal_peer[j] = h->signal_peer[j]; }
   c.wait_local = h->wait_local; c.wait_value = h->wait_value; c.counter = h->counter;
+  for (int j = 0; j < 8; ++j) c.cnt_peer[j] = h->cnt_peer[j];
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("moe: no status word"); return -1; }
   c.status = st;

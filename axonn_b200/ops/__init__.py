@@ -16,7 +16,7 @@ from .gemm import (  # noqa: F401
     matmul_nt,
     matmul_tn,
 )
-from .linear import linear  # noqa: F401
+from .linear import linear, linear_batched  # noqa: F401
 from .loss import cross_entropy  # noqa: F401
 from .multi_tensor import (  # noqa: F401
     all_reduce_bucketed_,

@@ -119,3 +119,62 @@ def matmul_tn(a, b, out_dtype=None, out=None, accumulate=False):
     if out is not None:
         return out.add_(y) if accumulate else out.copy_(y)
     return y
+
+
+def _batched_ok(a, b):
+    return (a.is_cuda and b.is_cuda and a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16)
+            and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0 and b.shape[-2] % 8 == 0
+            and hasattr(_lib.lib(), "axb_gemm_batched"))
+
+
+def _launch_batched(layout, a, b, nb, M, N, K, out, seg=None, seg_rows=0):
+    L = _lib.lib()
+    nseg = 0
+    if seg is not None:
+        assert seg.dtype == torch.int32 and seg.is_cuda and seg.is_contiguous() and seg.shape[0] == nb
+        nseg = seg.shape[1]
+    st = L.axb_gemm_batched(
+        ctypes.c_int(layout), _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), ctypes.c_int(nb), ctypes.c_int(M),
+        ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(a.shape[1]), ctypes.c_int(b.shape[1]), ctypes.c_int(M),
+        ctypes.c_int(_DT[a.dtype]), ctypes.c_int(_DT[out.dtype]), ctypes.c_int(0),
+        _lib.ptr(seg), ctypes.c_int(seg_rows), ctypes.c_int(nseg),
+        ctypes.c_int(a.device.index), _lib.stream_ptr())
+    _lib.check(st, "axb_gemm_batched")
+    return out
+
+
+def bmm_nt(a, b, out_dtype=None, seg=None, seg_rows=0):
+    """``a[E,M,K] @ b[E,N,K].T`` per problem ``E``: one launch of the CTA-pair kernel over all problems' tiles.
+    ``seg`` / ``seg_rows``: row mask over M (see ``ops.linear_batched``)."""
+    E, M, K = a.shape
+    N = b.shape[1]
+    if _batched_ok(a, b):
+        a, b = _rowmajor(a), _rowmajor(b)
+        out = torch.empty((E, M, N), dtype=out_dtype or a.dtype, device=a.device)
+        return _launch_batched(0, a, b, E, M, N, K, out, seg, seg_rows)
+    y = torch.matmul(a, b.transpose(1, 2))
+    return y if out_dtype is None else y.to(out_dtype)
+
+
+def bmm_nn(a, b, out_dtype=None, seg=None, seg_rows=0):
+    """``a[E,M,K] @ b[E,K,N]`` per problem; row mask over M."""
+    E, M, K = a.shape
+    N = b.shape[2]
+    if _batched_ok(a, b) and K % 64 == 0:
+        a, b = _rowmajor(a), _rowmajor(b)
+        out = torch.empty((E, M, N), dtype=out_dtype or a.dtype, device=a.device)
+        return _launch_batched(1, a, b, E, M, N, K, out, seg, seg_rows)
+    y = torch.matmul(a, b)
+    return y if out_dtype is None else y.to(out_dtype)
+
+
+def bmm_tn(a, b, out_dtype=None, seg=None, seg_rows=0):
+    """``a[E,K,M].T @ b[E,K,N]`` per problem (reduction over the rows of both); row mask over K."""
+    E, K, M = a.shape
+    N = b.shape[2]
+    if _batched_ok(a, b) and K % 64 == 0:
+        a, b = _rowmajor(a), _rowmajor(b)
+        out = torch.empty((E, M, N), dtype=out_dtype or a.dtype, device=a.device)
+        return _launch_batched(2, a, b, E, M, N, K, out, seg, seg_rows)
+    y = torch.matmul(a.transpose(1, 2), b)
+    return y if out_dtype is None else y.to(out_dtype)

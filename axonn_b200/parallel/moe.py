@@ -108,13 +108,13 @@ class ExpertParallelMoE(nn.Module):
         c = math.ceil(self.capacity_factor * tokens * self.top_k / self.n_experts)
         return max(8, (c + 7) // 8 * 8)
 
-    def _experts(self, x):
-        """x: [n_local, rows, H] -> [n_local, rows, H]"""
-        outs = []
-        for e in range(self.n_local):
-            h = ops.swiglu(ops.linear(x[e], self.w1[e]))
-            outs.append(ops.linear(h, self.w2[e]))
-        return torch.stack(outs, 0)
+    def _experts(self, x, seg=None, seg_rows=0):
+        """x: [n_local, rows, H] -> [n_local, rows, H].  One launch per GEMM over the tiles of all local experts
+        (capacity buffers make the shapes uniform).  ``seg`` (int32 [n_local, rows / seg_rows]): how many rows of
+        each ``seg_rows``-row capacity segment hold tokens - the others are zero, and the GEMMs skip the tiles
+        (weight gradient: the K blocks) that contain none."""
+        h = ops.swiglu(ops.linear_batched(x, self.w1, seg, seg_rows))
+        return ops.linear_batched(h, self.w2, seg, seg_rows)
 
     def forward(self, x):
         shape = x.shape

@@ -3,9 +3,13 @@ dispatch / combine kernels of ``csrc/moe.cu``.
 
 Each expert-parallel group owns one symmetric allocation per rank:
 
-    control block   FILLED_X[n] FREE_X[n] READY_Y[n] PULLED_Y[n] (u32 epochs), CTA counter
-    X buffer        [source][local expert][capacity][hidden]   tokens arriving for my experts
+    control block   FILLED_X[n] FREE_X[n] READY_Y[n] PULLED_Y[n] (u32 epochs), CTA counter,
+                    COUNTS[local expert][source] (rows of each capacity segment that hold tokens)
+    X buffer        [local expert][source][capacity][hidden]   tokens arriving for my experts
     Y buffer        same shape                                  my experts' outputs, pulled by the sources
+
+The expert-major layout makes the X buffer the stacked operand of the batched expert GEMM as it is, and
+COUNTS lets that GEMM skip the tiles of the capacity padding (``axb_gemm_batched``'s row mask).
 
 ``scatter`` stores rows into the owners' X buffers (FREE_X gates the stores,
 FILLED_X tells the owner they are complete); ``gather`` pulls rows from the
@@ -22,18 +26,21 @@ import torch.distributed as dist
 from ..ops import _lib
 from . import symm
 
-_FILLED_X, _FREE_X, _READY_Y, _PULLED_Y, _COUNTER = 0, 64, 128, 192, 1024
+_FILLED_X, _FREE_X, _READY_Y, _PULLED_Y, _COUNTER, _COUNTS = 0, 64, 128, 192, 1024, 2048
 _CTRL = 4096
 
 
 class AxbMoeCtx(ctypes.Structure):
     _fields_ = [("n", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint), ("n_local", ctypes.c_int),
                 ("buf_peer", ctypes.c_void_p * 8), ("wait_local", ctypes.c_void_p), ("wait_value", ctypes.c_uint),
-                ("signal_peer", ctypes.c_void_p * 8), ("counter", ctypes.c_void_p)]
+                ("signal_peer", ctypes.c_void_p * 8), ("counter", ctypes.c_void_p), ("cnt_peer", ctypes.c_void_p * 8)]
+
+
+DISABLED = False     # benchmarks flip this to time the all_to_all_single path on the same layer
 
 
 def usable(group, x) -> bool:
-    if not (x.is_cuda and symm.enabled() and x.dtype == torch.bfloat16):
+    if DISABLED or not (x.is_cuda and symm.enabled() and x.dtype == torch.bfloat16):
         return False
     n = dist.get_world_size(group)
     if n < 2 or n > 8:
@@ -61,7 +68,10 @@ class _Channel:
 
     def view(self, off):
         return self.buf.local[off:off + self.buf_bytes].view(torch.bfloat16).view(
-            self.n, self.n_local, self.C, self.H)
+            self.n_local, self.n, self.C, self.H)
+
+    def counts_view(self):
+        return self.buf.local[_COUNTS:_COUNTS + self.n_local * self.n * 4].view(torch.int32).view(self.n_local, self.n)
 
     def ctx(self, epoch, buf_off, wait_off, wait_value, signal_off):
         c = AxbMoeCtx()
@@ -77,12 +87,15 @@ class _Channel:
 
     # -- primitives -----------------------------------------------------------------
     def scatter(self, rows, by_token, dest, keep, counts, T, k):
-        """rows -> owners' X buffers; returns my experts' inputs [n_local, n*C, H] (a copy)."""
+        """rows -> owners' X buffers; returns my experts' inputs [n_local, n*C, H] (a copy) and the int32 table
+        [n_local, n] of how many rows of each source's capacity segment hold tokens."""
         L = _lib.lib()
         dev = self.device.index
         self.epoch_x += 1
         e = self.epoch_x
         c = self.ctx(e, self.x_off, _FREE_X, e - 1, _FILLED_X)
+        for j in range(self.n):
+            c.cnt_peer[j] = self.buf.peer_ptrs[j] + _COUNTS
         _lib.check(L.axb_moe_dispatch(_lib.ptr(rows), ctypes.c_int(1 if by_token else 0), _lib.ptr(dest),
                                       _lib.ptr(keep), _lib.ptr(counts), ctypes.c_int(T), ctypes.c_int(k),
                                       ctypes.c_int(self.n * self.n_local), ctypes.c_int(self.C),
@@ -90,9 +103,10 @@ class _Channel:
                    "axb_moe_dispatch")
         w = self.ctx(e, self.x_off, _FILLED_X, e, _FREE_X)
         _lib.check(L.axb_moe_wait(ctypes.byref(w), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_wait")
-        mine = self.view(self.x_off).transpose(0, 1).reshape(self.n_local, self.n * self.C, self.H).clone()
+        mine = self.view(self.x_off).reshape(self.n_local, self.n * self.C, self.H).clone()
+        seg = self.counts_view().clone()
         _lib.check(L.axb_moe_signal(ctypes.byref(w), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_signal")
-        return mine
+        return mine, seg
 
     def gather(self, y_local, dest, keep, T, k):
         """my experts' outputs [n_local, n*C, H] -> Y buffer; returns the rows of my assignments [T*k, H]."""
@@ -102,7 +116,7 @@ class _Channel:
         e = self.epoch_y
         w = self.ctx(e, self.y_off, _PULLED_Y, e - 1, _READY_Y)
         _lib.check(L.axb_moe_wait(ctypes.byref(w), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_wait")
-        self.view(self.y_off).copy_(y_local.reshape(self.n_local, self.n, self.C, self.H).transpose(0, 1))
+        self.view(self.y_off).copy_(y_local.reshape(self.n_local, self.n, self.C, self.H))
         _lib.check(L.axb_moe_signal(ctypes.byref(w), ctypes.c_int(dev), _lib.stream_ptr()), "axb_moe_signal")
         out = torch.empty((T * k, self.H), dtype=torch.bfloat16, device=self.device)
         c = self.ctx(e, self.y_off, _READY_Y, e, _PULLED_Y)
@@ -132,10 +146,12 @@ class _Scatter(torch.autograd.Function):
     def forward(ctx, x2, dest, keep, counts, ch, k):
         ctx.ch, ctx.k, ctx.T = ch, k, x2.shape[0]
         ctx.save_for_backward(dest, keep)
-        return ch.scatter(x2.contiguous(), True, dest, keep, counts, x2.shape[0], k)
+        xin, seg = ch.scatter(x2.contiguous(), True, dest, keep, counts, x2.shape[0], k)
+        ctx.mark_non_differentiable(seg)
+        return xin, seg
 
     @staticmethod
-    def backward(ctx, g):
+    def backward(ctx, g, _seg_grad=None):
         dest, keep = ctx.saved_tensors
         picked = ctx.ch.gather(g.contiguous(), dest, keep, ctx.T, ctx.k)
         return picked.view(ctx.T, ctx.k, -1).sum(1), None, None, None, None, None
@@ -151,7 +167,7 @@ class _Gather(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         dest, keep, counts = ctx.saved_tensors
-        gy = ctx.ch.scatter(g.contiguous(), False, dest, keep, counts, ctx.T, ctx.k)
+        gy, _ = ctx.ch.scatter(g.contiguous(), False, dest, keep, counts, ctx.T, ctx.k)
         return gy, None, None, None, None, None, None
 
 
@@ -164,8 +180,8 @@ def dispatch_experts_combine(layer, x2, dest, keep, gate, capacity):
     keep_u8 = keep.to(torch.uint8).contiguous()
     counts = torch.zeros(E, dtype=torch.int64, device=x2.device)
     counts.index_add_(0, torch.div(dest, capacity, rounding_mode="floor"), keep.to(torch.int64))
-    xin = _Scatter.apply(x2, dest, keep_u8, counts, ch, k)
-    out = layer._experts(xin)
+    xin, seg = _Scatter.apply(x2, dest, keep_u8, counts, ch, k)
+    out = layer._experts(xin, seg, capacity)
     picked = _Gather.apply(out, dest, keep_u8, counts, ch, T, k)
     w = (gate * keep).to(picked.dtype)
     return (picked.view(T, k, H) * w.view(T, k, 1)).sum(1)

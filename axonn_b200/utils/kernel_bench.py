@@ -407,6 +407,59 @@ def bench_grad_ar(iters=6):
         del grads
 
 
+def bench_moe(iters=5, tokens=8192, hidden=4096, ffn=14336, n_experts=8, top_k=2):
+    """Expert-parallel MoE layer (Mixtral-8x7B layer shape: 8192 tokens per GPU, top-2 of 8 experts), forward +
+    backward, on the ranks of the default group: peer-memory dispatch / combine kernels against NCCL
+    ``all_to_all_single``, and the expert GEMMs as one batched launch per GEMM against one launch per expert."""
+    import torch.distributed as dist
+
+    from .. import axonn as ax
+    from .. import ops
+    from ..parallel import moe, moe_kernels
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ax.init(G_inter=1, G_data=world, G_intra_r=1, G_intra_c=1, G_intra_d=1)
+    torch.manual_seed(5)
+    layer = moe.ExpertParallelMoE(hidden, ffn, n_experts, top_k, dtype=torch.bfloat16).to(dev)
+    x = (torch.randn(tokens, hidden, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    g = (torch.randn(tokens, hidden, device=dev) * 0.1).bfloat16()
+
+    def step():
+        layer(x).backward(g)
+        x.grad = None
+        for p in layer.parameters():
+            p.grad = None
+
+    def experts_batched(xin):
+        return ops.linear_batched(ops.swiglu(ops.linear_batched(xin, layer.w1)), layer.w2)
+
+    def experts_loop(xin):
+        return torch.stack([ops.linear(ops.swiglu(ops.linear(xin[e], layer.w1[e])), layer.w2[e])
+                            for e in range(layer.n_local)], 0)
+
+    res = {"label": "MoE layer fwd+bwd", "tokens": tokens, "hidden": hidden, "ffn": ffn, "experts": n_experts,
+           "top_k": top_k, "ranks": world, "local_experts": layer.n_local, "capacity": layer.capacity(tokens)}
+    res["p2p_kernels_ms"] = round(_timed_group(step, iters, dev), 4)
+    moe_kernels.DISABLED = True
+    res["nccl_all_to_all_ms"] = round(_timed_group(step, iters, dev), 4)
+    moe_kernels.DISABLED = False
+    rows = world * layer.capacity(tokens)
+    xin = (torch.randn(layer.n_local, rows, hidden, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    gin = (torch.randn(layer.n_local, rows, hidden, device=dev) * 0.1).bfloat16()
+    for name, fn in (("experts_batched_ms", experts_batched), ("experts_loop_ms", experts_loop)):
+        def run():
+            fn(xin).backward(gin)
+            xin.grad = None
+            for p in layer.parameters():
+                p.grad = None
+        res[name] = round(_timed_group(run, iters, dev), 4)
+    flops = 3 * 2.0 * layer.n_local * rows * hidden * ffn * 3           # fwd + dgrad + wgrad of three projections
+    res["experts_tflops_batched"] = round(flops / res["experts_batched_ms"] / 1e9, 1)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
@@ -424,7 +477,7 @@ if __name__ == "__main__":
         bench_fused_loopback()
     elif what == "fused_loopback_two_shot":
         bench_fused_loopback_two_shot()
-    elif what in ("fused", "fused_one_shot", "ag", "rs", "grad_ar"):
+    elif what in ("fused", "fused_one_shot", "ag", "rs", "grad_ar", "moe"):
         import os
 
         import torch.distributed as dist
@@ -441,6 +494,8 @@ if __name__ == "__main__":
             bench_ag()
         elif what == "rs":
             bench_rs()
+        elif what == "moe":
+            bench_moe()
         else:
             bench_grad_ar()
         dist.destroy_process_group()

@@ -202,3 +202,65 @@ def test_silent_peer_times_out_and_context_survives():
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+
+
+@pytest.mark.parametrize("shape", [(4, 256, 512, 256), (3, 640, 1024, 320), (2, 2560, 2048, 1024), (8, 128, 264, 192)])
+def test_batched_gemm_matches_fp32(shape):
+    """All three layouts of the batched CTA-pair GEMM (one launch over the tiles of E problems) against fp32
+    matmuls; M and N need not be multiples of the tile, so tiles run into the next problem's rows and must not
+    store them."""
+    from axonn_b200.ops import gemm
+    from axonn_b200.ops import _lib
+
+    E, M, N, K = shape
+    torch.manual_seed(21)
+    a = torch.randn(E, M, K, device="cuda:0").bfloat16()
+    b = torch.randn(E, N, K, device="cuda:0").bfloat16()
+    y = gemm.bmm_nt(a, b)
+    ref = torch.matmul(a.float(), b.float().transpose(1, 2))
+    assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    g = torch.randn(E, M, N, device="cuda:0").bfloat16()
+    if N % 64 == 0:
+        gx = gemm.bmm_nn(g, b)                       # [E, M, N] @ [E, N, K]
+        ref = torch.matmul(g.float(), b.float())
+        assert (gx.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    if M % 64 == 0:
+        gw = gemm.bmm_tn(g, a, out_dtype=torch.float32)   # [E, M, N].T @ [E, M, K]
+        ref = torch.matmul(g.float().transpose(1, 2), a.float())
+        assert (gw - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 640, 512, 256), (1, 8, 2560, 1024, 512), (3, 2, 192, 264, 128)])
+def test_batched_gemm_row_mask(shape):
+    """Capacity-padded problems: only the first ``seg[e, s]`` rows of every segment hold data, the rest are zero.
+    With the mask the kernels skip tiles (K blocks for the weight gradient) without data; the results must equal
+    the unmasked products, zeros included."""
+    from axonn_b200.ops import _lib, gemm
+
+    E, nseg, seg_rows, N, K = shape
+    M = nseg * seg_rows
+    torch.manual_seed(22)
+    seg = torch.randint(0, seg_rows + 1, (E, nseg), device="cuda:0", dtype=torch.int32)
+    seg[0, 0] = 0
+    seg[-1, -1] = seg_rows
+    rows = torch.arange(M, device="cuda:0") % seg_rows
+    live = rows[None, :] < seg.long().repeat_interleave(seg_rows, dim=1)          # [E, M]
+    a = torch.randn(E, M, K, device="cuda:0").bfloat16() * live[:, :, None]
+    b = torch.randn(E, N, K, device="cuda:0").bfloat16()
+    y = gemm.bmm_nt(a, b, seg=seg, seg_rows=seg_rows)
+    ref = torch.matmul(a.float(), b.float().transpose(1, 2))
+    assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    assert (y.float()[~live] == 0).all()
+    g = torch.randn(E, M, N, device="cuda:0").bfloat16() * live[:, :, None]
+    if N % 64 == 0:
+        gx = gemm.bmm_nn(g, b, seg=seg, seg_rows=seg_rows)
+        ref = torch.matmul(g.float(), b.float())
+        assert (gx.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    if M % 64 == 0:
+        gw = gemm.bmm_tn(g, a, out_dtype=torch.float32, seg=seg, seg_rows=seg_rows)
+        ref = torch.matmul(g.float().transpose(1, 2), a.float())
+        assert (gw - ref).abs().max().item() <= 2e-2 * max(ref.abs().max().item(), 1.0)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0

@@ -225,6 +225,36 @@ def test_flash_attention_forward(cfg):
     assert (lse - lse_ref).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("D", [128, 64])
+def test_flash_attention_forward_large_scores(D):
+    """Scores whose row maximum keeps growing by far more than 2^8 from one KV tile to the next: the two-tile
+    forward must rescale its tensor-memory accumulator (it only does so past that threshold), and rows whose
+    maximum moves by less must stay exact although their reference maximum is stale."""
+    from axonn_b200.ops import _lib
+    from axonn_b200.ops.attention_cuda import flash_fwd_packed
+
+    B, S, G, qpk = 1, 1024, 2, 2
+    torch.manual_seed(8)
+    qkv = torch.randn(B, S, G, qpk + 2, D, device=DEV)
+    ramp = torch.linspace(0.2, 4.0, S, device=DEV)[None, :, None, None]
+    qkv[:, :, :, qpk] *= ramp                     # later keys score higher and higher
+    qkv[:, :, :, :qpk] *= 2.0
+    qkv = qkv.bfloat16()
+    scale = D ** -0.5
+    out, lse = flash_fwd_packed(qkv, scale)
+    torch.cuda.synchronize()
+    assert _lib.lib().axb_device_status(0, 1) == 0
+    q = qkv[:, :, :, :qpk].reshape(B, S, G * qpk, D).float().transpose(1, 2)
+    k = qkv[:, :, :, qpk].float().transpose(1, 2).repeat_interleave(qpk, dim=1)
+    v = qkv[:, :, :, qpk + 1].float().transpose(1, 2).repeat_interleave(qpk, dim=1)
+    s = (q @ k.transpose(-1, -2)) * scale
+    s = s.masked_fill(~torch.ones(S, S, device=DEV, dtype=torch.bool).tril(), float("-inf"))
+    ref = (s.softmax(-1) @ v).transpose(1, 2)
+    assert torch.isfinite(out.float()).all()
+    _close(out, ref, 2e-2, 2e-2)
+    assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 5e-2
+
+
 @pytest.mark.parametrize("cfg", [(2, 256, 2, 1, 128), (1, 512, 2, 4, 128), (2, 384, 3, 1, 64), (1, 640, 1, 2, 64)])
 def test_flash_attention_backward(cfg):
     from axonn_b200.ops import _lib
