@@ -33,6 +33,7 @@ struct FaParams {
   float scale_log2;
   unsigned int* status;
   unsigned long long timeout_ns;
+  int debug;   // ablation builds only (-DAXB_ABLATION, read once from AXB_FA_DEBUG; otherwise 0 and compiled out): 4 phase timers of the two-tile forward
 };
 
 constexpr int FA_BQ = 128, FA_BKV = 128, FA_THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps
@@ -350,23 +351,27 @@ static int fa_launch(const CUtensorMap& tm, const FaParams& p, int device, cudaS
 
 
 // -----------------------------------------------------------------------------------------------------
-// Forward, two query tiles per CTA ("ping-pong").  One CTA handles the adjacent 128-row query tiles
-// A = 2u and B = 2u + 1 of one (batch, head); they share every K_j / V_j tile that the TMA warp loads.
+// Forward, two query tiles at a time ("ping-pong"), persistent CTAs.  A work item is the pair of adjacent
+// 128-row query tiles A = 2u and B = 2u + 1 of one (batch, head); they share every K_j / V_j tile that the TMA
+// warp loads.  One CTA per SM walks its share of the items (longest first): the loads and the first score MMAs
+// of the next item overlap the previous item's last softmax steps and its output stores.
 //
 //   warp 0      TMA: Q_A, Q_B once; K_j and V_j into separate 2-stage rings
-//   warp 1      MMA: S_X = Q_X K_j^T into the 128 score columns of tile X, then O_X += P_X V_j with the
-//               A operand P_X read from tensor memory (bf16, in the first 64 of the score columns, written
-//               there by the softmax threads) and O_X accumulating in tensor memory over all KV tiles
-//   warps 2-3   idle: they complete the first warpgroup, which hands most of its registers to the others
-//   warps 4-7   softmax of tile A, one thread per query row (TMEM lane): one read of the 128 scores, row
+//   warps 1, 2  MMA of tile A and of tile B: S_X = Q_X K^T for 64 keys into one of the two score buffers of tile X, then O_X += P_X V
+//               with the A operand P_X read from tensor memory (bf16, in the first 32 columns of the score
+//               buffer, written there by the softmax threads) and O_X accumulating in tensor memory
+//   warp 3      idle: it completes the first warpgroup, which hands most of its registers to the others
+//   warps 4-7   softmax of tile A, one thread per query row (TMEM lane): one read of the step's 64 scores, row
 //   warps 8-11  maximum, exponentials, row sum, P back into tensor memory.  (8-11: the same for tile B.)
 //
-// While the threads of one tile work on their scores, the tensor core runs the other tile's two MMAs, so
-// neither side waits for the other in steady state.  The running maximum of a row is only raised when the
-// tile's maximum exceeds it by more than 2^8 (the probabilities then stay below 256, exact in the final
-// normalisation because the row sum uses the same reference); only then the row's O accumulator is rescaled
-// in tensor memory, by the softmax thread itself, between the completion of the previous PV MMA (implied by
-// the score barrier, which is committed after it) and the release of P.
+// The work of a query tile proceeds in steps of 64 key columns, and the 128 score columns of the tile are two
+// 64-column buffers used alternately: while the softmax threads work on step s, the scores of step s + 1 are
+// already complete in the other buffer (S(s + 2) is issued right after the PV MMA of step s, which is the last
+// reader of that buffer), so the threads go from one step to the next without waiting for the tensor core, and
+// the tensor core always has the other tile's and the next step's MMAs queued.  The running maximum of a row is
+// only raised when a step's maximum exceeds it by more than 2^8 (the probabilities then stay below 256, exact
+// in the final normalisation because the row sum uses the same reference); only then the row's O accumulator
+// is rescaled in tensor memory, by the softmax thread itself, after waiting for the previous step's PV MMA.
 template <int HD>
 struct Fa2Smem {
   static constexpr int TILE = 128 * HD * 2;
@@ -374,11 +379,38 @@ struct Fa2Smem {
   static constexpr int K_OFF = 2 * TILE;           // 2 stages
   static constexpr int V_OFF = 4 * TILE;           // 2 stages
   static constexpr int BAR_OFF = 6 * TILE;
-  static constexpr int NBARS = 1 + 2 + 2 + 2 + 2 + 2 + 2 + 2;
+  static constexpr int NBARS = 2 + 8 + 4 + 4 + 2;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16 + 1024;
 };
 
 constexpr int FA2_THREADS = 384;
+#ifndef FA2_POLY_OF_8
+#define FA2_POLY_OF_8 3     // pairs of every 8 whose exponential runs on the FMA pipes instead of the ex2 unit
+#endif
+#ifndef FA2_PACKED
+#define FA2_PACKED 1        // packed fp32x2 arithmetic for the scale-and-subtract and the row sum
+#endif
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Work item `idx` of the persistent grid: pairs of query tiles sorted by decreasing length (pair u has 4u + 3 tile
+// steps), dealt to the CTAs in a snake (0..G-1, G-1..0, ...) so that every CTA gets nearly the same total.
+struct Fa2Item { int u, head, b; };
+__device__ __forceinline__ bool fa2_item(const FaParams& p, int k, Fa2Item& w) {
+  const int G = gridDim.x, c = blockIdx.x;
+  const int heads = p.G * p.qpk, bh = p.B * heads, npairs = p.S / (2 * FA_BQ);
+  const int idx = k * G + ((k & 1) ? G - 1 - c : c);
+  if (idx >= bh * npairs) return false;
+  w.u = npairs - 1 - idx / bh;
+  const int rem = idx % bh;
+  w.head = rem % heads;
+  w.b = rem / heads;
+  return true;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(FA2_THREADS, 1)
@@ -387,36 +419,28 @@ fa_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S_::BAR_OFF);
-  uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 3;
-  uint64_t* v_full = bars + 5;
-  uint64_t* v_empty = bars + 7;
-  uint64_t* s_full = bars + 9;     // per query tile
-  uint64_t* p_full = bars + 11;    // per query tile
-  uint64_t* o_done = bars + 13;    // per query tile
+  uint64_t* q_full = bars;         // one arrival per work item
+  uint64_t* q_empty = bars + 1;    // both Q tiles may be overwritten (the item's last score MMAs are done)
+  uint64_t* k_full = bars + 2;
+  uint64_t* k_empty = bars + 4;
+  uint64_t* v_full = bars + 6;
+  uint64_t* v_empty = bars + 8;
+  uint64_t* s_full = bars + 10;    // [query tile][score buffer]
+  uint64_t* p_full = bars + 14;    // [query tile][score buffer]
+  uint64_t* pv_done = bars + 18;   // per query tile: one phase per step, completed by that step's PV MMA
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + S_::NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int npairs = p.S / (2 * FA_BQ);
-  const int u = npairs - 1 - static_cast<int>(blockIdx.z);   // heaviest pairs first, over the whole grid
-  const int head = blockIdx.x;
-  const int b = blockIdx.y;
-  const int g = head / p.qpk, jq = head % p.qpk;
-  const int n_a = 2 * u + 1, n_b = 2 * u + 2;                // causal: KV tiles 0..qt of each query tile
-  const int row0 = b * p.S + 2 * u * FA_BQ;
-  const int col_q = (g * (p.qpk + 2) + jq) * HD;
-  const int col_k = (g * (p.qpk + 2) + p.qpk) * HD;
-  const int col_v = col_k + HD;
   const uint64_t timeout = p.timeout_ns;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(q_full, 1); mbar_init(q_empty, 2);           // "empty": one release per MMA warp
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_done[i], 1);
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 2); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 2);
+      mbar_init(&pv_done[i], 1);
     }
+    for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -426,33 +450,45 @@ fa_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  // columns: scores of A [0,128), of B [128,256) (P_X = the first 64 of them), O_A [256,256+HD), O_B [384,384+HD)
+  // columns: score buffers of A [0,64) [64,128), of B [128,192) [192,256) (P = the first 32 columns of a
+  // buffer), O_A [256,256+HD), O_B [384,384+HD)
   // the register budget of a role must be set inside its branch: after a join the compiler assumes the smaller one
   if (warp < 4) {
-   asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
    if (warp == 0) {
     if (elect_one()) {
       bool ok = true;
-      mbar_expect_tx(q_full, 2 * S_::TILE);
+      uint32_t kvc = 0;                                     // KV tiles loaded so far: ring stage and phase
+      Fa2Item w;
+      for (int it = 0; ok && fa2_item(p, it, w); ++it) {
+        const int g = w.head / p.qpk, jq = w.head % p.qpk;
+        const int col_q = (g * (p.qpk + 2) + jq) * HD;
+        const int col_k = (g * (p.qpk + 2) + p.qpk) * HD;
+        const int col_v = col_k + HD;
+        const int row0 = w.b * p.S + 2 * w.u * FA_BQ;
+        const int n_b = 2 * w.u + 2;                         // KV tiles of 128 keys
+        if (!mbar_wait(q_empty, (it & 1) ^ 1, abort_flag, timeout)) { ok = false; break; }
+        mbar_expect_tx(q_full, 2 * S_::TILE);
 #pragma unroll
-      for (int x = 0; x < 2; ++x)
+        for (int x = 0; x < 2; ++x)
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_2d(smem + S_::Q_OFF + x * S_::TILE + c * 16384, &tmQKV, q_full, col_q + 64 * c, row0 + x * FA_BQ);
-      for (int j = 0; j < n_b && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int krow = b * p.S + j * FA_BKV;
-        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, timeout)) { ok = false; break; }
-        mbar_expect_tx(&k_full[st], S_::TILE);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_2d(smem + S_::Q_OFF + x * S_::TILE + c * 16384, &tmQKV, q_full, col_q + 64 * c, row0 + x * FA_BQ);
+        for (int j = 0; j < n_b && ok; ++j, ++kvc) {
+          const int st = kvc & 1;
+          const uint32_t ph = (kvc >> 1) & 1;
+          const int krow = w.b * p.S + j * FA_BKV;
+          if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+          mbar_expect_tx(&k_full[st], S_::TILE);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_2d(smem + S_::K_OFF + st * S_::TILE + c * 16384, &tmQKV, &k_full[st], col_k + 64 * c, krow);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, timeout)) { ok = false; break; }
-        mbar_expect_tx(&v_full[st], S_::TILE);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_2d(smem + S_::K_OFF + st * S_::TILE + c * 16384, &tmQKV, &k_full[st], col_k + 64 * c, krow);
+          if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, timeout)) { ok = false; break; }
+          mbar_expect_tx(&v_full[st], S_::TILE);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_2d(smem + S_::V_OFF + st * S_::TILE + c * 16384, &tmQKV, &v_full[st], col_v + 64 * c, krow);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_2d(smem + S_::V_OFF + st * S_::TILE + c * 16384, &tmQKV, &v_full[st], col_v + 64 * c, krow);
+        }
       }
       if (!ok) {
         const uint64_t t0 = globaltimer_ns();     // give in-flight copies time to land before the CTA exits
@@ -460,142 +496,215 @@ fa_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams
         report_status(p.status, 0x405u);
       }
     }
-   } else if (warp == 1) {
+   } else if (warp <= 2) {
+    // ------------------------------------------------------------------ MMA issue: warp 1 for tile A, warp 2 for B
+    // (one thread cannot issue both tiles' 24 instructions per step as fast as the tensor core retires them)
     if (elect_one()) {
       bool ok = true;
-      const uint32_t idesc_s = umma_idesc(1, 0, 0, 128, 128);
+      const int x = warp - 1;
+      const uint32_t idesc_s = umma_idesc(1, 0, 0, 128, 64);
       const uint32_t idesc_o = umma_idesc(1, 0, 1, 128, HD);
+      const uint32_t s_tmem = tmem_base + x * 128, o_tmem = tmem_base + 256 + x * 128;
+      const uint64_t qd = umma_smem_desc(smem_u32(smem + S_::Q_OFF + x * S_::TILE), 16, 1024);
       // descriptors of a k-step = the tile's descriptor + a constant in the (16-byte unit) address field
-      auto issue_s = [&](int x, int j) {
-        const uint64_t qd = umma_smem_desc(smem_u32(smem + S_::Q_OFF + x * S_::TILE), 16, 1024);
-        const uint64_t kd = umma_smem_desc(smem_u32(smem + S_::K_OFF + (j & 1) * S_::TILE), 16, 1024);
+      // scores of step s (keys [64 s, 64 s + 64)): rows (s & 1) * 64 .. of K tile kv, into score buffer s & 1
+      auto issue_s = [&](uint32_t kv, int sb) {
+        const uint64_t kd = umma_smem_desc(smem_u32(smem + S_::K_OFF + (kv & 1) * S_::TILE) + sb * 8192, 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint64_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
-          umma_f16(tmem_base + x * 128, qd + off, kd + off, idesc_s, kk != 0 ? 1u : 0u);
+          umma_f16(s_tmem + sb * 64, qd + off, kd + off, idesc_s, kk != 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int x, int j) {
+      auto issue_pv = [&](uint32_t kv, int sb, bool first) {
         // V: MN-major, 64-wide column chunks 16 KB apart (leading), 8-row groups 1 KB apart (stride)
-        const uint64_t vd = umma_smem_desc(smem_u32(smem + S_::V_OFF + (j & 1) * S_::TILE), 16384, 1024);
+        const uint64_t vd = umma_smem_desc(smem_u32(smem + S_::V_OFF + (kv & 1) * S_::TILE) + sb * 8192, 16384, 1024);
 #pragma unroll
-        for (int kk = 0; kk < FA_BKV / 16; ++kk)
-          umma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8, vd + ((kk * 2048) >> 4), idesc_o,
-                      (j | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16_ts(o_tmem, s_tmem + sb * 64 + kk * 8, vd + ((kk * 2048) >> 4), idesc_o, (first && kk == 0) ? 0u : 1u);
       };
-      ok = mbar_wait(q_full, 0, abort_flag, timeout) && mbar_wait(&k_full[0], 0, abort_flag, timeout);
-      if (ok) {
+      uint32_t kvc = 0;            // KV tiles of earlier items
+      uint32_t tc = 0;             // steps of earlier items and of this one so far (barrier phases)
+      const bool probe = AXB_DBG(p, 4) && blockIdx.x == 0 && x == 0;
+      long long pw_p = 0, pw_kv = 0, p_mark = 0, p_t0 = probe ? clock64() : 0;
+      Fa2Item w;
+      for (int it = 0; ok && fa2_item(p, it, w); ++it) {
+        const int n_b = 4 * w.u + 4, n_x = n_b - 2 + 2 * x;     // steps of 64 keys: causal, tiles 2u and 2u + 1
+        if (!mbar_wait(q_full, it & 1, abort_flag, timeout) ||
+            !mbar_wait(&k_full[kvc & 1], (kvc >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
         tcgen05_fence_after();
-        issue_s(0, 0); umma_commit(&s_full[0]);
-        issue_s(1, 0); umma_commit(&s_full[1]);
-        umma_commit(&k_empty[0]);
-      }
-      for (int j = 0; j < n_b && ok; ++j) {
-        const uint32_t kv_ph = (j >> 1) & 1, nx_ph = ((j + 1) >> 1) & 1;
-#pragma unroll 1
-        for (int x = 0; x < 2; ++x) {
-          const int n_x = x ? n_b : n_a;
-          if (j >= n_x) continue;
-          if (!mbar_wait(&p_full[x], j & 1, abort_flag, timeout) || !mbar_wait(&v_full[j & 1], kv_ph, abort_flag, timeout)) {
-            ok = false; break;
-          }
+        // both score buffers are free: the previous item's PV MMAs, which read P from them, were issued earlier
+#pragma unroll
+        for (int sb = 0; sb < 2; ++sb) { issue_s(kvc, sb); umma_commit(&s_full[x * 2 + sb]); }
+        umma_commit(&k_empty[kvc & 1]);
+        if (n_x == 2) umma_commit(q_empty);                    // a two-step tile has no further score MMAs
+        for (int st = 0; st < n_x && ok; ++st) {
+          const uint32_t kv = kvc + (st >> 1);
+          const int sb = st & 1;
+          if (probe) p_mark = clock64();
+          if (!mbar_wait(&p_full[x * 2 + sb], (tc >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
+          if (probe) { const long long now = clock64(); pw_p += now - p_mark; p_mark = now; }
+          if (!mbar_wait(&v_full[kv & 1], (kv >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
+          if (probe) pw_kv += clock64() - p_mark;
+          ++tc;
           tcgen05_fence_after();
-          issue_pv(x, j);
-          if (x == 1) umma_commit(&v_empty[j & 1]);
-          if (j + 1 < n_x) {
-            if (!mbar_wait(&k_full[(j + 1) & 1], nx_ph, abort_flag, timeout)) { ok = false; break; }
+          issue_pv(kv, sb, st == 0);
+          umma_commit(&pv_done[x]);
+          if (sb == 1) umma_commit(&v_empty[kv & 1]);
+          if (st + 2 < n_x) {
+            const uint32_t kn = kv + 1;                        // step st + 2 reads the next K tile
+            if (probe) p_mark = clock64();
+            if (!mbar_wait(&k_full[kn & 1], (kn >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
+            if (probe) pw_kv += clock64() - p_mark;
             tcgen05_fence_after();
-            issue_s(x, j + 1);
-            umma_commit(&s_full[x]);
-            if (x == 1) umma_commit(&k_empty[(j + 1) & 1]);
-          } else {
-            umma_commit(&o_done[x]);
+            issue_s(kn, sb);
+            umma_commit(&s_full[x * 2 + sb]);
+            if (sb == 1) {
+              umma_commit(&k_empty[kn & 1]);                   // this tile's last read of that K tile
+              if (st + 3 == n_x) umma_commit(q_empty);         // ... and of Q: the item's last score MMAs
+            }
           }
         }
+        if (x == 0 && ok) {
+          // tile A does not read the item's last KV tile, but the ring counts two releases per tile
+          const uint32_t last = kvc + (n_b >> 1) - 1;
+          umma_commit(&k_empty[last & 1]);
+          umma_commit(&v_empty[last & 1]);
+        }
+        kvc += n_b >> 1;
+      }
+      if (probe) {
+        volatile unsigned int* wd = reinterpret_cast<volatile unsigned int*>(p.status);
+        wd[13] = static_cast<unsigned>(pw_p); wd[14] = static_cast<unsigned>(pw_kv);
+        wd[15] = static_cast<unsigned>(clock64() - p_t0);
       }
       if (!ok) report_status(p.status, 0x406u);
     }
    }
   } else {
     // ------------------------------------------------------------------ softmax of query tile x
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int x = (warp - 4) >> 2;
     const int q4 = warp & 3;                         // the TMEM lane quarter this warp may access
     const int r = q4 * 32 + lane;                    // query row inside the tile
-    const int n_x = x ? n_b : n_a;
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_base + x * 128;
     const uint32_t o_addr = tmem_base + lane_base + 256 + x * 128;
-    float m = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_x; ++j) {
-      if (!mbar_wait(&s_full[x], j & 1, abort_flag, timeout)) { ok = false; break; }
-      tcgen05_fence_after();
-      uint32_t sv[128];
+    uint32_t tc = 0;                                 // steps so far (all items): barrier phases
+    const bool probe = AXB_DBG(p, 4) && blockIdx.x == 0 && warp == 4 && lane == 0;
+    long long pw_s = 0, pt_ld = 0, pt_max = 0, pt_exp = 0, pt_epi = 0, p_mark = 0;
+    Fa2Item w;
+    for (int it = 0; ok && fa2_item(p, it, w); ++it) {
+      const int n_x = 4 * w.u + 2 + 2 * x;           // steps of 64 keys; the item's step counts are even, so the
+      float m = -INFINITY, l = 0.f;                  // score buffer of a step is also (tc & 1)
+      for (int st = 0; st < n_x; ++st, ++tc) {
+        const int sb = st & 1;
+        if (probe) p_mark = clock64();
+        if (!mbar_wait(&s_full[x * 2 + sb], (tc >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
+        if (probe) { const long long now = clock64(); pw_s += now - p_mark; p_mark = now; }
+        tcgen05_fence_after();
+        uint32_t sv[64];
+        tmem_ld_32x32(s_addr + sb * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld_32x32(s_addr + sb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        tmem_ld_wait();
+        if (probe) { const long long now = clock64(); pt_ld += now - p_mark; p_mark = now; }
+        // key column 64 st + i is visible to query row 256 u + 128 x + r when it is not to the right of it
+        const int d = 64 * st - 128 * x - 256 * w.u;
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        if (d + 63 > 0) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
-      tmem_ld_wait();
-      const bool diag = (j == n_x - 1);
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-      if (!diag) {
-#pragma unroll
-        for (int i = 0; i < 128; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sv[i])); mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+          for (int i = 0; i < 64; ++i)
+            if (d + i > r) sv[i] = 0xff800000u;         // -inf: exp2 gives exactly 0
         }
-      } else {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          if (i > r) sv[i] = 0xff800000u;             // -inf: exp2 gives exactly 0
-          mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+        for (int i = 0; i < 64; i += 8) {              // three-input maxima, four independent chains
+          mx0 = fmax3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
         }
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;   // the scale is positive
-      const float m_new = (mx - m > 8.f) ? mx : m;   // first tile: m = -inf, always raised
-      const float alpha = exp2f(m - m_new);          // 1 when the reference stays
-      if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
-        // PV of tile j-1 has completed (the score barrier was committed after it): rescale O in place
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;   // the scale is positive
+        const float m_new = (mx - m > 8.f) ? mx : m;   // first step: m = -inf, always raised (key 0 is visible)
+        float alpha = 1.f;                             // stays 1 when no row of the warp raises its reference
+        if (__any_sync(0xffffffffu, m_new != m)) {
+          alpha = exp2f(m - m_new);
+          if (st > 0) {
+            // rescale O in place once the previous step's PV MMA has completed (phase tc - 1 of pv_done)
+            if (!mbar_wait(&pv_done[x], (tc - 1) & 1, abort_flag, timeout)) { ok = false; break; }
+            tcgen05_fence_after();
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(o_addr + c * 32, v);
-          tmem_ld_wait();
+            for (int c = 0; c < HD / 32; ++c) {
+              uint32_t v[32];
+              tmem_ld_32x32(o_addr + c * 32, v);
+              tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(o_addr + c * 32, v);
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              tmem_st_32x32(o_addr + c * 32, v);
+            }
+          }
+          l *= alpha;
+          m = m_new;
         }
-      }
-      l *= alpha;
-      m = m_new;
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+        if (probe) { const long long now = clock64(); pt_max += now - p_mark; p_mark = now; }
+        // Exponentials of the step's 64 scores, two at a time with packed fp32 arithmetic.  The special-function
+        // unit (ex2) is the scarcest resource of this kernel, so FA2_POLY_OF_8 of every 8 pairs are computed on
+        // the FMA pipes instead: 2^x = 2^n * 2^f with n = round(x) (taken from the mantissa of x + 1.5 * 2^23)
+        // and a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding of P; the row sum
+        // uses the same values, so the normalisation stays consistent).
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m, -m);
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
         uint32_t packed[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float e0 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i]), p.scale_log2, -m));
-          const float e1 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 1]), p.scale_log2, -m));
-          const float e2 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 2]), p.scale_log2, -m));
-          const float e3 = exp2f(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 3]), p.scale_log2, -m));
-          s0 += e0; s1 += e1; s2 += e2; s3 += e3;
-          const __nv_bfloat162 h0 = __floats2bfloat162_rn(e0, e1), h1 = __floats2bfloat162_rn(e2, e3);
-          packed[i] = *reinterpret_cast<const uint32_t*>(&h0);
-          packed[i + 1] = *reinterpret_cast<const uint32_t*>(&h1);
+        for (int i = 0; i < 32; ++i) {
+#if FA2_PACKED
+          float2 xx = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), sc2, nm2);
+#else
+          float2 xx = make_float2(fmaf(__uint_as_float(sv[2 * i]), sc2.x, nm2.x), fmaf(__uint_as_float(sv[2 * i + 1]), sc2.x, nm2.x));
+#endif
+          float2 e;
+          if ((i & 7) < FA2_POLY_OF_8) {
+            xx.x = fmaxf(xx.x, -125.f); xx.y = fmaxf(xx.y, -125.f);     // masked scores (-inf) become 2^-125
+            const float2 t = __fadd2_rn(xx, make_float2(12582912.f, 12582912.f));
+            const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+            const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), xx);
+            float2 q = __ffma2_rn(make_float2(0.05517147481441498f, 0.05517147481441498f), f,
+                                  make_float2(0.242610901594162f, 0.242610901594162f));
+            q = __ffma2_rn(q, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+            q = __ffma2_rn(q, f, make_float2(0.9999281167984009f, 0.9999281167984009f));
+            e.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+            e.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+          } else {
+            e.x = exp2f(xx.x); e.y = exp2f(xx.y);
+          }
+#if FA2_PACKED
+          if (i & 1) acc1 = __fadd2_rn(acc1, e); else acc0 = __fadd2_rn(acc0, e);
+#else
+          if (i & 1) { acc1.x += e.x; acc1.y += e.y; } else { acc0.x += e.x; acc0.y += e.y; }
+#endif
+          const __nv_bfloat162 h = __floats2bfloat162_rn(e.x, e.y);
+          packed[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
-        tmem_st_32x32(s_addr + c * 32, packed);
+        tmem_st_32x32(s_addr + sb * 64, packed);
+        l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+        // A parity wait is only meaningful while the barrier is at most one phase ahead of the waiter, so every
+        // phase of pv_done is observed, in order: the previous step's PV MMA here - it has had this whole step to
+        // complete, and this step's cannot be issued before the arrival below.
+        if (st >= 1 && !mbar_wait(&pv_done[x], (tc - 1) & 1, abort_flag, timeout)) { ok = false; break; }
+        tmem_st_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[x * 2 + sb]);
+        if (probe) { const long long now = clock64(); pt_exp += now - p_mark; p_mark = now; }
       }
-      l += (s0 + s1) + (s2 + s3);
-      tmem_st_wait();
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[x]);
-    }
-    if (ok && mbar_wait(&o_done[x], 0, abort_flag, timeout)) {
+      if (probe) p_mark = clock64();
+      // the item's last PV MMA: phase tc - 1 of pv_done (tc - 2 was observed in the last step)
+      if (!ok || !mbar_wait(&pv_done[x], (tc - 1) & 1, abort_flag, timeout)) { ok = false; break; }
       tcgen05_fence_after();
       const float inv_l = 1.f / l;
       const size_t heads = static_cast<size_t>(p.G) * p.qpk;
-      const size_t qrow = static_cast<size_t>(b) * p.S + (2 * u + x) * FA_BQ + r;
-      __nv_bfloat16* dst = p.out + (qrow * heads + head) * HD;
+      const size_t qrow = static_cast<size_t>(w.b) * p.S + (2 * w.u + x) * FA_BQ + r;
+      __nv_bfloat16* dst = p.out + (qrow * heads + w.head) * HD;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t v[32];
@@ -603,19 +712,26 @@ fa_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams
         tmem_ld_wait();
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          uint32_t w[4];
+          uint32_t wv[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int e = t * 8 + i * 2;
             const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[e]) * inv_l, __uint_as_float(v[e + 1]) * inv_l);
-            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            wv[i] = *reinterpret_cast<const uint32_t*>(&h);
           }
-          *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + c * 32 + t * 8) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
         }
       }
-      p.lse[(static_cast<size_t>(b) * heads + head) * p.S + (2 * u + x) * FA_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
-    } else {
-      ok = false;
+      p.lse[(static_cast<size_t>(w.b) * heads + w.head) * p.S + (2 * w.u + x) * FA_BQ + r] = (m + log2f(l)) * 0.6931471805599453f;
+      // the next item's first PV MMA overwrites O: it waits for this thread's next arrival on p_full, which follows
+      // these reads in program order
+      tcgen05_fence_before();
+      if (probe) pt_epi += clock64() - p_mark;
+    }
+    if (probe) {
+      volatile unsigned int* wd = reinterpret_cast<volatile unsigned int*>(p.status);
+      wd[8] = static_cast<unsigned>(pw_s); wd[9] = static_cast<unsigned>(pt_ld); wd[10] = static_cast<unsigned>(pt_max);
+      wd[11] = static_cast<unsigned>(pt_exp); wd[12] = static_cast<unsigned>(pt_epi); wd[7] = tc;
     }
     if (!ok && lane == 0) report_status(p.status, 0x407u);
   }
@@ -633,8 +749,9 @@ static int fa_launch_pingpong(const CUtensorMap& tm, const FaParams& p, int devi
     AXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_::TOTAL));
     configured[device & 63] = true;
   }
-  dim3 grid(p.G * p.qpk, p.B, p.S / (2 * FA_BQ));   // z (slowest) = pair of query tiles, heaviest first
-  kern<<<grid, FA2_THREADS, S_::TOTAL, s>>>(tm, p);
+  const long long items = static_cast<long long>(p.B) * p.G * p.qpk * (p.S / (2 * FA_BQ));
+  const int sms = sm_count(device);
+  kern<<<static_cast<int>(items < sms ? items : sms), FA2_THREADS, S_::TOTAL, s>>>(tm, p);   // persistent CTAs
   AXB_CUDA(cudaGetLastError());
   return 0;
 }
@@ -665,6 +782,10 @@ extern "C" int axb_flash_attn_fwd(const void* qkv, void* out, float* lse, int B,
   unsigned int* st = nullptr;
   if (!device_status_word(device, &st)) { set_error("flash attention: no status word"); return -1; }
   p.status = st; p.timeout_ns = wait_timeout_ns();
+  p.debug = 0;
+#ifdef AXB_ABLATION
+  { static int dbg = -1; if (dbg < 0) { const char* e = getenv("AXB_FA_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
+#endif
   if (S % 256 == 0 && fa_pingpong_enabled()) {
     if (D == 128) return fa_launch_pingpong<128>(tm, p, device, static_cast<cudaStream_t>(stream));
     return fa_launch_pingpong<64>(tm, p, device, static_cast<cudaStream_t>(stream));
