@@ -217,6 +217,10 @@ int axb_flash_attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int
                        int device, void* stream);
 int axb_flash_attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta, float* dq_acc,
                        void* dqkv, int B, int S, int G, int qpk, int D, float scale, int device, void* stream);
+/* two-kernel backward without atomics; which: bit 0 = dQ kernel (query slots of dqkv), bit 1 = dK / dV kernel */
+int axb_flash_attn_bwd_split(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta,
+                             void* dqkv, int B, int S, int G, int qpk, int D, float scale, int which, int device,
+                             void* stream);
 
 /* ---- cross entropy on a vocabulary shard of bf16 logits (loss.cu); backward overwrites the logits with their gradient */
 int axb_ce_fwd(const void* logits, const long long* targets, float* stats, int rows, int V, int vocab_start, void* stream);

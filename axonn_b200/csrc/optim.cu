@@ -4,6 +4,8 @@
 // into fixed-size chunks and a grid-stride loop maps chunk -> (tensor, offset)
 // by binary search in the table's chunk prefix sums, so one launch replaces
 // hundreds of per-parameter launches.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace axb {
@@ -106,8 +108,9 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2;
   const float* grad_scale;       // device scalar multiplied into every gradient (may be null)
   const float* found_inf;        // device scalar; non-zero => skip the whole step (may be null)
-  const unsigned int* status;    // device status word; non-zero (a bounded wait of an earlier kernel expired:
-                                 // gradients may be incomplete) => skip the whole step (may be null)
+  const unsigned int* status;    // copy, in device memory, of the device status word taken just before this launch;
+                                 // non-zero (a bounded wait of an earlier kernel expired: gradients may be
+                                 // incomplete) => skip the whole step (may be null)
 };
 
 __global__ void __launch_bounds__(MT_THREADS)
@@ -203,6 +206,13 @@ multi_adamw_kernel(const long long* __restrict__ table, int n, long long total_c
   }
 }
 
+// The status word itself lives in mapped host memory (the host polls it without synchronising); a read of it
+// costs a PCIe round trip per warp, which serialises to milliseconds when every warp of a large grid does it.
+// One thread copies it into device memory first and the optimizer's blocks read that copy.
+__global__ void status_gate_kernel(const unsigned int* __restrict__ status, unsigned int* __restrict__ gate) {
+  *gate = *reinterpret_cast<const volatile unsigned int*>(status);
+}
+
 int sm_count(int device);
 static inline int mt_grid(long long chunks) {
   const long long cap = static_cast<long long>(sm_count_current()) * 8;
@@ -230,8 +240,22 @@ extern "C" int axb_multi_adamw(const long long* table, int n, long long total_ch
   // its output (activations or gradients) is incomplete, and the host learns of it at its next check_status.
   int dev = 0;
   unsigned int* status = nullptr;
-  if (cudaGetDevice(&dev) == cudaSuccess) device_status_word(dev, &status);
-  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale, found_inf, status};
+  unsigned int* gate = nullptr;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    device_status_word(dev, &status);
+    static unsigned int* gates[64] = {nullptr};
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (status && !gates[dev]) {
+      if (cudaMalloc(&gates[dev], sizeof(unsigned int)) != cudaSuccess) { gates[dev] = nullptr; cudaGetLastError(); }
+    }
+    gate = status ? gates[dev] : nullptr;
+  }
+  if (gate) {
+    status_gate_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(status, gate);
+    AXB_CUDA(cudaGetLastError());
+  }
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale, found_inf, gate};
   multi_adamw_kernel<<<mt_grid(total_chunks), MT_THREADS, 0, (cudaStream_t)stream>>>(table, n, total_chunks, a);
   AXB_CUDA(cudaGetLastError());
   return 0;

@@ -11,6 +11,8 @@ import torch
 
 from . import _lib
 
+_BWD_DEFAULT = "fused"
+
 
 def available():
     return hasattr(_lib.lib(), "axb_flash_attn_fwd") and os.environ.get("AXONN_FLASH", "1") == "1"
@@ -34,15 +36,34 @@ def flash_fwd_packed(qkv, scale):
     return out, lse
 
 
+def _bwd_split(qkv, out, d_out, lse, delta, dqkv, scale, which):
+    B, S, G, n, D = qkv.shape
+    st = _lib.lib().axb_flash_attn_bwd_split(
+        _lib.ptr(qkv), _lib.ptr(out), _lib.ptr(d_out), _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dqkv),
+        ctypes.c_int(B), ctypes.c_int(S), ctypes.c_int(G), ctypes.c_int(n - 2), ctypes.c_int(D),
+        ctypes.c_float(scale), ctypes.c_int(which), ctypes.c_int(qkv.device.index), _lib.stream_ptr())
+    _lib.check(st, "axb_flash_attn_bwd_split")
+    _lib.add_launches(1)
+
+
 def flash_bwd_packed(qkv, out, d_out, lse, scale):
-    """Gradient of the packed QKV tensor for ``flash_fwd_packed``."""
+    """Gradient of the packed QKV tensor for ``flash_fwd_packed``.
+
+    ``AXONN_FA_BWD`` selects the implementation: ``split`` - the two-kernel backward without atomics
+    (``csrc/flash_attn_bwd_split.cu``: one kernel for dQ, one for dK and dV); ``fused`` - the one-kernel form
+    (``csrc/flash_attn.cu``) with its fp32 dQ accumulator; ``split_dq`` / ``split_dkv`` take only dQ or only
+    dK, dV from the two-kernel form (A/B runs)."""
     B, S, G, n, D = qkv.shape
     qpk = n - 2
     H = G * qpk
+    mode = os.environ.get("AXONN_FA_BWD", _BWD_DEFAULT)
     d_out = d_out if d_out.is_contiguous() else d_out.contiguous()
     delta = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
-    dq_acc = torch.zeros((B, S, H, D), dtype=torch.float32, device=qkv.device)
     dqkv = torch.empty_like(qkv)
+    if mode == "split":
+        _bwd_split(qkv, out, d_out, lse, delta, dqkv, scale, 3)
+        return dqkv
+    dq_acc = torch.zeros((B, S, H, D), dtype=torch.float32, device=qkv.device)
     st = _lib.lib().axb_flash_attn_bwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(d_out), _lib.ptr(lse), _lib.ptr(delta),
                                        _lib.ptr(dq_acc), _lib.ptr(dqkv), ctypes.c_int(B), ctypes.c_int(S),
                                        ctypes.c_int(G), ctypes.c_int(qpk), ctypes.c_int(D), ctypes.c_float(scale),
@@ -50,6 +71,10 @@ def flash_bwd_packed(qkv, out, d_out, lse, scale):
     _lib.check(st, "axb_flash_attn_bwd")
     _lib.add_launches(1)
     dqkv[:, :, :, :qpk].copy_(dq_acc.view(B, S, G, qpk, D))
+    if mode == "split_dq":
+        _bwd_split(qkv, out, d_out, lse, delta, dqkv, scale, 1)
+    elif mode == "split_dkv":
+        _bwd_split(qkv, out, d_out, lse, delta, dqkv, scale, 2)
     return dqkv
 
 
