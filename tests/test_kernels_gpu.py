@@ -255,11 +255,17 @@ def test_flash_attention_forward_large_scores(D):
     assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 5e-2
 
 
-@pytest.mark.parametrize("cfg", [(2, 256, 2, 1, 128), (1, 512, 2, 4, 128), (2, 384, 3, 1, 64), (1, 640, 1, 2, 64)])
-def test_flash_attention_backward(cfg):
+@pytest.mark.parametrize("mode", ["fused", "split"])
+@pytest.mark.parametrize("cfg", [(2, 256, 2, 1, 128), (1, 512, 2, 4, 128), (2, 384, 3, 1, 64), (1, 640, 1, 2, 64),
+                                 (1, 1024, 1, 2, 64)])
+def test_flash_attention_backward(cfg, mode, monkeypatch):
+    """Both backward implementations (one kernel with an fp32 dQ accumulator; two kernels without atomics) against
+    autograd through an fp32 reference; the head_dim 64 GQA cases have many short steps per work item, which is
+    where an ordering mistake between the softmax warps of a row shows first."""
     from axonn_b200.ops import _lib
     from axonn_b200.ops.attention_cuda import flash_bwd_packed, flash_fwd_packed
 
+    monkeypatch.setenv("AXONN_FA_BWD", mode)
     B, S, G, qpk, D = cfg
     torch.manual_seed(11)
     qkv = torch.randn(B, S, G, qpk + 2, D, device=DEV).bfloat16()
