@@ -100,7 +100,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* xr = x + static_cast<size_t>(row) * H;
     float mean = 0.f, rstd = 0.f;
-    if (mode != 2) {
+    if (mode != 2 && mode != 3) {
       float s1 = 0.f, s2 = 0.f;
       for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
         float f[8]; Vec8<T>::load(xr + c * 8, f);
@@ -119,10 +119,18 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
       if (RMS) { mean = 0.f; rstd = rsqrtf(s2 / H_total + eps); }
       else { mean = s1 / H_total; rstd = rsqrtf(fmaxf(s2 / H_total - mean * mean, 0.f) + eps); }
       if (threadIdx.x == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
+    } else if (mode == 3) {
+      // stats hold (sum x, sum x^2) over the full hidden dimension (the partial sums of mode 1 after their
+      // all-reduce): finish them here instead of in separate element-wise launches, keep (mean, rstd) for backward
+      const float s1 = stats[2 * row], s2 = stats[2 * row + 1];
+      if (RMS) { mean = 0.f; rstd = rsqrtf(s2 / H_total + eps); }
+      else { mean = s1 / H_total; rstd = rsqrtf(fmaxf(s2 / H_total - mean * mean, 0.f) + eps); }
+      __syncthreads();                               // every thread has read the sums
+      if (threadIdx.x == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
     } else {
       mean = stats[2 * row]; rstd = stats[2 * row + 1];
     }
-    if (delta) xr = hout + static_cast<size_t>(row) * H;
+    if (delta && mode != 3) xr = hout + static_cast<size_t>(row) * H;
     T* yr = y + static_cast<size_t>(row) * H;
     for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
       float f[8], g[8], b[8];

@@ -71,13 +71,9 @@ class _NormFn(torch.autograd.Function):
         if n == 1:
             call(0)
         else:
-            call(1)
+            call(1)                              # partial (sum x, sum x^2) of my slice of the hidden dimension
             dist.all_reduce(stats, group=group)
-            Ht = float(H * n)
-            mean = stats[:, 0] / Ht if not rms else torch.zeros_like(stats[:, 0])
-            var = stats[:, 1] / Ht - mean * mean
-            stats = torch.stack([mean, torch.rsqrt(var.clamp_min(0) + eps)], 1).contiguous()
-            call(2)
+            call(3)                              # finishes (mean, rstd) in place and applies them
         ctx.save_for_backward(x2, g, stats)
         return y.reshape(shape)
 
@@ -171,11 +167,7 @@ class _AddNormFn(torch.autograd.Function):
         else:
             call(1, x2, d2)                      # writes h and the partial row sums
             dist.all_reduce(stats, group=group)
-            Ht = float(H * n)
-            mean = stats[:, 0] / Ht if not rms else torch.zeros_like(stats[:, 0])
-            var = stats[:, 1] / Ht - mean * mean
-            stats = torch.stack([mean, torch.rsqrt(var.clamp_min(0) + eps)], 1).contiguous()
-            call(2, h, None)
+            call(3, h, None)                     # finishes (mean, rstd) in place and applies them
         ctx.save_for_backward(h, g, stats)
         return h.reshape(shape), y.reshape(shape)
 

@@ -41,6 +41,53 @@ def test_norm_fwd_bwd(rms, shape):
 
 
 @pytest.mark.parametrize("rms", [False, True])
+def test_norm_forward_split_hidden_modes(rms):
+    """The three launches of a norm whose hidden dimension is split over ranks, emulated on one GPU: partial row sums
+    per slice (mode 1), their sum (what the all-reduce produces), then the finishing mode (3), which turns the sums
+    into (mean, rstd) in place and applies them to the slice."""
+    import ctypes
+
+    from axonn_b200.ops import _lib
+
+    torch.manual_seed(4)
+    rows, H, n = 257, 2048, 2
+    x = torch.randn(rows, H, device=DEV).bfloat16()
+    g = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+    b = (0.1 * torch.randn(H, device=DEV)).bfloat16()
+    L = _lib.lib()
+    Hl = H // n
+    xs = [x[:, i * Hl:(i + 1) * Hl].contiguous() for i in range(n)]
+    ys = [torch.empty_like(t) for t in xs]
+    stats = [torch.empty(rows, 2, dtype=torch.float32, device=DEV) for _ in range(n)]
+
+    def call(i, mode):
+        gi, bi = g[i * Hl:(i + 1) * Hl].contiguous(), b[i * Hl:(i + 1) * Hl].contiguous()
+        st = L.axb_norm_fwd(_lib.ptr(xs[i]), _lib.ptr(gi), _lib.ptr(None if rms else bi), _lib.ptr(ys[i]),
+                            _lib.ptr(stats[i]), ctypes.c_int(rows), ctypes.c_int(Hl), ctypes.c_int(H),
+                            ctypes.c_float(1e-5), ctypes.c_int(1 if rms else 0), ctypes.c_int(mode), ctypes.c_int(0),
+                            ctypes.c_int(0), _lib.stream_ptr())
+        _lib.check(st, "axb_norm_fwd")
+
+    for i in range(n):
+        call(i, 1)
+    total = stats[0] + stats[1]
+    for i in range(n):
+        stats[i].copy_(total)
+        call(i, 3)
+    y = torch.cat(ys, 1)
+    xr = x.float()
+    if rms:
+        ref = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()
+        mean_ref = torch.zeros(rows, device=DEV)
+    else:
+        ref = F.layer_norm(xr, (H,), g.float(), b.float(), 1e-5)
+        mean_ref = xr.mean(-1)
+    _close(y, ref, 1e-2)
+    assert (stats[0][:, 0] - mean_ref).abs().max().item() < 1e-3        # (mean, rstd) left behind for the backward
+    assert torch.equal(stats[0], stats[1])
+
+
+@pytest.mark.parametrize("rms", [False, True])
 @pytest.mark.parametrize("shape", [(300, 2048), (64, 4096), (130, 1024), (17, 8192)])
 def test_add_norm_fused_residual(rms, shape):
     """h = x + delta and norm(h) in one kernel, backward with the residual-path gradient added in the kernel:
