@@ -33,6 +33,8 @@ int axb_gemm_batched(int layout, const void* A, const void* B, void* C, int nb, 
                      int a_batch_rows, int b_batch_rows, int c_batch_rows, int in_dtype, int out_dtype,
                      int accumulate, const int* seg_counts /* device int32 [nb, nseg] or NULL */, int seg_rows,
                      int nseg, int device, void* stream);
+/* cap on the CTAs of the following GEMM launches (0: one per SM), for GEMMs that share the GPU from two streams */
+void axb_gemm_set_max_ctas(int n);
 int axb_gemm(int layout, const void* A, const void* B, void* C, const void* bias, void* aux,
              int M, int N, int K, int in_dtype, int out_dtype, int epilogue, int accumulate,
              int device, void* stream);

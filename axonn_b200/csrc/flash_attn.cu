@@ -566,9 +566,14 @@ fa_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQKV, const FaParams
           }
         }
         if (x == 0 && ok) {
-          // tile A does not read the item's last KV tile, but the ring counts two releases per tile
+          // Tile A does not read the item's last KV tile, but the ring counts two releases per tile.  The release
+          // may only be given once that tile has been loaded: before that, the stage still belongs to the tile
+          // two steps earlier, and an early arrival would complete that tile's "empty" phase while tile B's warp
+          // is still reading it.
           const uint32_t last = kvc + (n_b >> 1) - 1;
+          if (!mbar_wait(&k_full[last & 1], (last >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
           umma_commit(&k_empty[last & 1]);
+          if (!mbar_wait(&v_full[last & 1], (last >> 1) & 1, abort_flag, timeout)) { ok = false; break; }
           umma_commit(&v_empty[last & 1]);
         }
         kvc += n_b >> 1;

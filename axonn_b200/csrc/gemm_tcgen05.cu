@@ -1405,6 +1405,15 @@ int sm_count_current() {
 }
 
 // Communicating GEMM on CTA pairs: the kernel above with PAIR = true, launched as clusters of two.
+// Upper bound on the CTAs of the next GEMM launches (0 = all SMs): lets two GEMMs that are launched on different
+// streams - a communication-bound fused kernel and a compute-bound one - share the GPU instead of queueing behind
+// each other (a persistent grid of one CTA per SM leaves no room for a second kernel).
+static int g_max_ctas = 0;
+static inline int usable_sms(int device) {
+  const int sms = sm_count(device);
+  return (g_max_ctas >= 2 && g_max_ctas < sms) ? g_max_ctas : sms;
+}
+
 template <int A_MN, int B_MN>
 static int launch_comm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p, int device, cudaStream_t stream) {
   using S = GemmSmem<256, true>;
@@ -1418,7 +1427,7 @@ static int launch_comm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   p.tiles_n = (p.N + 255) / 256;
   p.pair = 1;
   const int total = ((p.tiles_m + 1) / 2) * p.tiles_n;
-  const int pairs = sm_count(device) / 2;
+  const int pairs = usable_sms(device) / 2;
   const int grid = 2 * (total < pairs ? total : pairs);
   p.gemm_ctas = grid;
   if (p.ag.n > 1) { p.ag.n_copy = grid; p.ag.ready_target = static_cast<unsigned int>(grid); }   // every CTA pulls a slice
@@ -1445,7 +1454,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int sms = sm_count(device);
+  const int sms = usable_sms(device);
   // every CTA must be resident at once (reducer warps wait for partials of the same launch): grid <= #SMs
   p.gemm_ctas = tiles < sms ? tiles : sms;
   if (p.ag.n > 1) { p.ag.n_copy = p.gemm_ctas; p.ag.ready_target = static_cast<unsigned int>(p.gemm_ctas); }   // every CTA pulls a slice
@@ -1467,7 +1476,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + PAIR_BN - 1) / PAIR_BN;
   const int total = ((p.tiles_m + 1) / 2) * p.tiles_n * p.nb;
-  const int pairs = sm_count(device) / 2;
+  const int pairs = usable_sms(device) / 2;
   const int grid = 2 * (total < pairs ? total : pairs);
   p.gemm_ctas = grid;
   kern<<<grid, PAIR_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
@@ -1603,6 +1612,8 @@ static int gemm_common(int layout, const void* A, const void* B, void* C, const 
 // Milliseconds the fused GEMM kernels spent stalled on peers since the last reset (sum over launches of the mean
 // over each launch's CTAs).  Synchronises the device; `device` must be current.  A diagnostic for reporting exposed
 // communication, not for use inside a timed region.
+extern "C" void axb_gemm_set_max_ctas(int n) { axb::g_max_ctas = n; }
+
 extern "C" double axb_comm_stall_ms(int device, int reset) {
   (void)device;
   unsigned long long v = 0;

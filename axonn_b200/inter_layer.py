@@ -24,6 +24,7 @@ What is different:
 """
 
 import threading
+import os
 import time
 from dataclasses import dataclass
 from enum import Enum
@@ -100,7 +101,9 @@ class AxoNN_Inter_Layer_Engine:
         self.model, self.criterion = model, loss_fn
         self.computation_dtype = computation_dtype
         self.scaler = LossScaler()
-        self.timeout_s = timeout_s
+        # AXONN_PIPELINE_TIMEOUT_S overrides the deadline after which a stage that hears nothing from its
+        # neighbours raises PipelineTimeout (with the direction it was waiting for)
+        self.timeout_s = float(os.environ.get("AXONN_PIPELINE_TIMEOUT_S", timeout_s))
         self.device = ax.comm_handle.device
         self.input_tensors_cache, self.output_tensors_cache = {}, {}
         self.transit_tensors = []          # (work, tensor) of sends not yet complete

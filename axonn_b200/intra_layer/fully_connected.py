@@ -20,7 +20,9 @@ collective with the GEMM (``axonn_b200.parallel.fused``); on CPU the same
 autograd function runs on ``torch.matmul`` + ``torch.distributed``.
 """
 
+import ctypes
 import math
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -29,6 +31,7 @@ from torch.autograd import Function
 
 from .. import axonn as ax
 from .. import ops
+from ..ops import _lib
 from ..parallel import fused
 from ..utils import divide
 from . import overlap_communication as oc
@@ -77,6 +80,31 @@ def _gathered_weight(weight, depth_group, local_shape, cache):
     """Depth all-gather of the flat shard, shaped ``[out_l, in_l]``."""
     full = _gather(weight, dim=0, process_group=depth_group, cache=cache)
     return full.reshape(local_shape)
+
+
+_side_streams = {}
+_OVERLAP_WGRAD_DEFAULT = "0"
+
+
+def _side_stream(device):
+    st = _side_streams.get(device)
+    if st is None:
+        st = _side_streams[device] = torch.cuda.Stream(device=device)
+    return st
+
+
+def _sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def _wgrad_overlap_ctas() -> int:
+    """CTAs that the communication-bound input-gradient kernel gets when it runs beside the weight-gradient GEMM
+    (``AXONN_OVERLAP_WGRAD``: 0 = off, the two kernels run one after the other; otherwise an even CTA count)."""
+    try:
+        n = int(os.environ.get("AXONN_OVERLAP_WGRAD", _OVERLAP_WGRAD_DEFAULT))
+    except ValueError:
+        return 0
+    return max(0, n) // 2 * 2
 
 
 class AsyncLinear(Function):
@@ -201,9 +229,27 @@ class AsyncLinear(Function):
 
         if outer_n > 1 or not overlap_rs:
             # dgrad first so that its all-reduce hides under the wgrad GEMM
+            side = None
             if ctx.needs_input_grad[0]:
                 ar_ok = outer_n > 1 and fused.usable(ctx.backward_all_reduce_group, go2, N=ctx.shape[1],
                                                      K=ctx.shape[0])
+                split = _wgrad_overlap_ctas() if (ar_ok and go2.is_cuda and ctx.needs_input_grad[1]) else 0
+                if split:
+                    # The fused input-gradient GEMM + all-reduce is bound by NVLink, the weight-gradient GEMM by the
+                    # tensor cores: run them side by side on disjoint sets of SMs (two streams, CTA caps that add up to
+                    # the SM count, so that both persistent grids are resident together).  The streams are joined
+                    # again before this function returns, which keeps every buffer and channel in stream order
+                    # across layers.
+                    main = torch.cuda.current_stream()
+                    side = _side_stream(go2.device)
+                    side.wait_stream(main)
+                    L = _lib.lib()
+                    L.axb_gemm_set_max_ctas(ctypes.c_int(_sm_count(go2.device) - split))
+                    with torch.cuda.stream(side):
+                        grad_weight = wgrad()
+                        if ctx.has_bias and ctx.needs_input_grad[2]:
+                            grad_bias = bias_sum if bias_sum is not None else ops.column_sum(go2, out_dtype=ctx.bias_dtype)
+                    L.axb_gemm_set_max_ctas(ctypes.c_int(split))
                 if (depth_n > 1 and id(w_shard) not in oc.weights_cache
                         and (outer_n == 1 or ar_ok)
                         and fused.all_gather_usable(ctx.depth_parallel_group, go2, w_shard, ctx.shape, 1)):
@@ -220,10 +266,14 @@ class AsyncLinear(Function):
                     if outer_n > 1:
                         handle = dist.all_reduce(grad_input, group=ctx.backward_all_reduce_group,
                                                  async_op=overlap_ar)
-            if ctx.needs_input_grad[1]:
-                grad_weight = wgrad()
-            if ctx.has_bias and ctx.needs_input_grad[2]:
-                grad_bias = bias_sum if bias_sum is not None else ops.column_sum(go2, out_dtype=ctx.bias_dtype)
+            if side is not None:
+                _lib.lib().axb_gemm_set_max_ctas(ctypes.c_int(0))
+                torch.cuda.current_stream().wait_stream(side)
+            else:
+                if ctx.needs_input_grad[1]:
+                    grad_weight = wgrad()
+                if ctx.has_bias and ctx.needs_input_grad[2]:
+                    grad_bias = bias_sum if bias_sum is not None else ops.column_sum(go2, out_dtype=ctx.bias_dtype)
             if handle is not None and overlap_ar:
                 handle.wait()
         else:
