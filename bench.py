@@ -40,6 +40,10 @@ import sys
 import threading
 import time
 
+# more hardware work queues than the default 8, set before the CUDA context exists: a pipeline stage keeps several
+# blocking NCCL point-to-point kernels in flight beside its compute stream (both arms get the same setting)
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
