@@ -252,6 +252,10 @@ int axb_gelu_bwd_colsum(const void* dy, const void* x, void* dx, float* part, vo
 /* ---- multi-tensor kernels over a device table of tensor pointers (optim.cu) */
 int axb_multi_l2norm_sq(const long long* table, int n, long long total_chunks, float* out, void* stream);
 int axb_multi_scale(const long long* table, int n, long long total_chunks, const float* scale, void* stream);
+/* SGD with momentum over a pointer table (rows {param, grad, fp32 momentum buffer, numel, param dtype, grad dtype,
+   chunk prefix, 0}; dtype codes 0 fp32, 1 bf16, 2 fp16) */
+int axb_multi_sgd(const long long* table, int n, long long total_chunks, float lr, float momentum, float weight_decay,
+                  const float* grad_scale, void* stream);
 int axb_multi_adamw(const long long* table, int n, long long total_chunks, float lr, float beta1, float beta2, float eps,
                     float weight_decay, float bias_c1, float bias_c2, const float* grad_scale, const float* found_inf,
                     void* stream);

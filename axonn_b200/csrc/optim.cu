@@ -104,6 +104,34 @@ multi_scale_kernel(const long long* __restrict__ table, int n, long long total_c
   }
 }
 
+// SGD with momentum (torch.optim.SGD semantics without dampening / Nesterov): g' = g * grad_scale + wd * p,
+// buf = mu * buf + g', p -= lr * buf.  Table rows: {param, grad, momentum buffer (fp32), numel, param dtype,
+// grad dtype, chunk prefix, -}.
+__global__ void __launch_bounds__(MT_THREADS)
+multi_sgd_kernel(const long long* __restrict__ table, int n, long long total_chunks, float lr, float momentum,
+                 float weight_decay, const float* __restrict__ grad_scale, const unsigned int* __restrict__ status) {
+  if (status && *reinterpret_cast<const volatile unsigned int*>(status) != 0u) return;
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    const int t = find_tensor(table, 8, 6, n, chunk);
+    const long long* row = table + (size_t)t * 8;
+    void* p = reinterpret_cast<void*>(row[0]);
+    const void* g = reinterpret_cast<const void*>(row[1]);
+    float* buf = reinterpret_cast<float*>(row[2]);
+    const long long numel = row[3];
+    const int pdtype = (int)row[4], gdtype = (int)row[5];
+    const long long begin = (chunk - row[6]) * MT_CHUNK;
+    const long long end = begin + MT_CHUNK < numel ? begin + MT_CHUNK : numel;
+    for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      const float w = load_as_f32(p, i, pdtype);
+      const float gi = load_as_f32(g, i, gdtype) * gs + weight_decay * w;
+      const float b = momentum * buf[i] + gi;
+      buf[i] = b;
+      store_from_f32(p, i, pdtype, w - lr * b);
+    }
+  }
+}
+
 struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2;
   const float* grad_scale;       // device scalar multiplied into every gradient (may be null)
@@ -233,11 +261,9 @@ extern "C" int axb_multi_scale(const long long* table, int n, long long total_ch
   AXB_CUDA(cudaGetLastError());
   return 0;
 }
-extern "C" int axb_multi_adamw(const long long* table, int n, long long total_chunks, float lr, float beta1, float beta2,
-                               float eps, float weight_decay, float bias_c1, float bias_c2, const float* grad_scale,
-                               const float* found_inf, void* stream) {
-  // The step is also skipped when a kernel that ran before it on this device reported an expired wait:
-  // its output (activations or gradients) is incomplete, and the host learns of it at its next check_status.
+// Device-memory copy of the status word of the current device, refreshed on `stream` (see status_gate_kernel);
+// null when the device has no status word.
+static unsigned int* refreshed_status_gate(cudaStream_t stream) {
   int dev = 0;
   unsigned int* status = nullptr;
   unsigned int* gate = nullptr;
@@ -251,10 +277,27 @@ extern "C" int axb_multi_adamw(const long long* table, int n, long long total_ch
     }
     gate = status ? gates[dev] : nullptr;
   }
-  if (gate) {
-    status_gate_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(status, gate);
-    AXB_CUDA(cudaGetLastError());
-  }
+  if (gate) status_gate_kernel<<<1, 1, 0, stream>>>(status, gate);
+  return gate;
+}
+
+extern "C" int axb_multi_sgd(const long long* table, int n, long long total_chunks, float lr, float momentum,
+                             float weight_decay, const float* grad_scale, void* stream) {
+  unsigned int* gate = refreshed_status_gate((cudaStream_t)stream);
+  AXB_CUDA(cudaGetLastError());
+  multi_sgd_kernel<<<mt_grid(total_chunks), MT_THREADS, 0, (cudaStream_t)stream>>>(table, n, total_chunks, lr, momentum,
+                                                                                weight_decay, grad_scale, gate);
+  AXB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int axb_multi_adamw(const long long* table, int n, long long total_chunks, float lr, float beta1, float beta2,
+                               float eps, float weight_decay, float bias_c1, float bias_c2, const float* grad_scale,
+                               const float* found_inf, void* stream) {
+  // The step is also skipped when a kernel that ran before it on this device reported an expired wait:
+  // its output (activations or gradients) is incomplete, and the host learns of it at its next check_status.
+  unsigned int* gate = refreshed_status_gate((cudaStream_t)stream);
+  AXB_CUDA(cudaGetLastError());
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale, found_inf, gate};
   multi_adamw_kernel<<<mt_grid(total_chunks), MT_THREADS, 0, (cudaStream_t)stream>>>(table, n, total_chunks, a);
   AXB_CUDA(cudaGetLastError());

@@ -109,6 +109,30 @@ class AxoNN_Inter_Layer_Engine:
         self.transit_tensors = []          # (work, tensor) of sends not yet complete
         self.requests = {"fw": None, "bw": None}
         self._seq = {"fw": 0, "bw": 0}
+        self._connect_neighbours()
+
+    def _connect_neighbours(self):
+        """Exchange one element with each neighbouring stage in both directions, pair by pair in stage order.
+
+        NCCL sets up the connection of a point-to-point communicator inside the first send / receive call on it,
+        and that call does not return before the peer has made the matching call.  The engine posts its receives
+        for forward and backward messages before it has anything to send, so with more than two stages a middle
+        stage would sit in its first backward receive - whose sender can only answer after getting forward data
+        through this very stage.  Connecting every pair up front, in an order without cycles, removes that wait
+        from the schedule."""
+        G, rank = ax.config.G_inter, self._rank
+        if G <= 1:
+            return
+        token = torch.zeros(1, device=self.device, dtype=torch.float32)
+        for s in range(G - 1):
+            if rank == s:
+                ax.comm_handle.send(token, s + 1, async_op=False)
+                ax.comm_handle.recv(token, s + 1, async_op=False)
+            elif rank == s + 1:
+                ax.comm_handle.recv(token, s, async_op=False)
+                ax.comm_handle.send(token, s, async_op=False)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------------------ helpers
     @property

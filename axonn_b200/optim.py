@@ -14,11 +14,13 @@ memory, streamed through fixed-size GPU staging buckets — on top of the same
 kernel, with the copies double-buffered on a side stream.
 """
 
+import ctypes
 from typing import Iterable, Optional
 
 import torch
 
 from . import ops
+from .ops import _lib, multi_tensor as _mt
 
 
 class FusedAdamW(torch.optim.Optimizer):
@@ -104,6 +106,54 @@ class FusedAdamW(torch.optim.Optimizer):
                                          b1, b2, group["eps"], group["weight_decay"], st["step"], gs)
                     if st["master"] is not None:
                         p.data.copy_(tgt)
+        return loss
+
+
+class FusedSGD(torch.optim.Optimizer):
+    """SGD with momentum and weight decay (``torch.optim.SGD`` semantics without dampening or Nesterov) as one
+    multi-tensor kernel launch per parameter group (``csrc/optim.cu::multi_sgd_kernel``); parameters and gradients
+    may be fp32, bf16 or fp16, the momentum buffers are fp32.  On CPU tensors it falls back to the plain update."""
+
+    def __init__(self, params: Iterable, lr=1e-2, momentum=0.9, weight_decay=0.0):
+        super().__init__(params, dict(lr=lr, momentum=momentum, weight_decay=weight_decay))
+        self._tables = {}
+        self.grad_scale = None
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for gi, group in enumerate(self.param_groups):
+            params = [p for p in group["params"] if p.grad is not None]
+            if not params:
+                continue
+            for p in params:
+                if "momentum_buffer" not in self.state[p]:
+                    self.state[p]["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32)
+            if params[0].is_cuda:
+                grads = [p.grad if p.grad.is_contiguous() else p.grad.contiguous() for p in params]
+                ptrs = tuple(g.data_ptr() for g in grads)
+                tab = self._tables.get(gi)
+                if tab is None or tab[0] != ptrs:
+                    rows, prefix = [], 0
+                    for p, g in zip(params, grads):
+                        assert p.is_contiguous()
+                        rows.append((p.data_ptr(), g.data_ptr(), self.state[p]["momentum_buffer"].data_ptr(), p.numel(),
+                                     _mt._DT_CODE[p.dtype], _mt._DT_CODE[g.dtype], prefix, 0))
+                        prefix += (p.numel() + _mt._CHUNK - 1) // _mt._CHUNK
+                    host = torch.tensor(rows, dtype=torch.int64).pin_memory()
+                    tab = self._tables[gi] = (ptrs, host, host.to(params[0].device, non_blocking=True), len(rows), prefix)
+                st = _lib.lib().axb_multi_sgd(_lib.ptr(tab[2]), ctypes.c_int(tab[3]), ctypes.c_longlong(tab[4]),
+                                              ctypes.c_float(group["lr"]), ctypes.c_float(group["momentum"]),
+                                              ctypes.c_float(group["weight_decay"]), _lib.ptr(self.grad_scale),
+                                              _lib.stream_ptr())
+                _lib.check(st, "axb_multi_sgd")
+                _lib.add_launches(1)
+            else:
+                for p in params:
+                    g = p.grad.float() + group["weight_decay"] * p.float()
+                    buf = self.state[p]["momentum_buffer"]
+                    buf.mul_(group["momentum"]).add_(g)
+                    p.add_(buf.to(p.dtype), alpha=-group["lr"])
         return loss
 
 

@@ -357,7 +357,9 @@ def build_vgg(args, torch, dist, rank, world, dev):
         ax.init(G_inter=G_inter, G_data=G_data)
         torch.manual_seed(1234)
         model = DistributedVGG16(image_size=image, num_classes=classes).to(dev)
-        opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+        from axonn_b200.optim import FusedSGD
+
+        opt = FusedSGD(model.parameters(), lr=0.01, momentum=0.9)      # same update rule as the baseline's torch.optim.SGD
         engine = AxoNN_Inter_Layer_Engine(model, torch.nn.functional.cross_entropy, computation_dtype=torch.bfloat16)
         ax.config.micro_batch_size = micro
         w.launches, w.check = (lambda: _lib.launch_count), _lib.check_status
@@ -386,6 +388,12 @@ BUILDERS = {"gpt1.3b": build_gpt, "llama8b": build_llama, "mixtral": build_mixtr
 
 def main():
     args = parse()
+    dump_after = float(os.environ.get("AXONN_BENCH_DUMP_STACKS_S", "0") or 0)
+    if dump_after > 0:
+        # diagnostic for a run that stops making progress: every thread's Python stack on stderr after that many seconds
+        import faulthandler
+
+        faulthandler.dump_traceback_later(dump_after, exit=False)
     if args.impl == "reference" and args.config in ("gpt1.3b", "llama8b"):
         ref_dir = os.path.join(ROOT, "baseline", "_ref")
         if not os.path.isdir(os.path.join(ref_dir, "axonn", "intra_layer")):

@@ -233,6 +233,27 @@ def test_multi_tensor_norm_and_scale():
         _close(a, b.float() * 0.5, 1e-2, 1e-6)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_sgd_matches_torch_sgd(dtype):
+    from axonn_b200.optim import FusedSGD
+
+    torch.manual_seed(9)
+    shapes = [(1000, 33), (4096,), (257, 129), (70000,)]
+    ours = [torch.nn.Parameter(torch.randn(s, device=DEV).to(dtype)) for s in shapes]
+    ref = [torch.nn.Parameter(p.detach().float().clone()) for p in ours]
+    a = FusedSGD(ours, lr=0.05, momentum=0.9, weight_decay=0.01)
+    b = torch.optim.SGD(ref, lr=0.05, momentum=0.9, weight_decay=0.01)
+    for _ in range(3):
+        for p, q in zip(ours, ref):
+            g = torch.randn_like(q)
+            p.grad = g.to(dtype)
+            q.grad = g.to(dtype).float()
+        a.step()
+        b.step()
+    for p, q in zip(ours, ref):
+        _close(p.detach(), q.detach(), 1e-2 if dtype == torch.bfloat16 else 1e-5, 1e-5)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("n", [4096, 1_000_003, 14336 * 512])
 def test_prune_topk(dtype, n):
