@@ -11,6 +11,8 @@
 //   mode 0  statistics computed locally and applied in one kernel
 //   mode 1  only emit per-row partial sums
 //   mode 2  apply with externally supplied (already reduced) statistics
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace axb {
@@ -320,6 +322,60 @@ norm_fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const
   }
 }
 
+// Forward with one warp per row (hidden = 256 * VPL elements, the whole row in registers): the statistics need only
+// warp shuffles, so there is no block barrier between the load and the store phase and the eight warps of a block
+// run their rows independently - their loads stay in flight continuously.  gamma / beta are re-read per row (they
+// stay in L1).
+template <typename T, bool RMS, int VPL>
+__global__ void __launch_bounds__(256)
+norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                     T* __restrict__ y, float* __restrict__ stats, int rows, int H, float eps,
+                     const T* __restrict__ delta, T* __restrict__ hout) {
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = static_cast<long long>(gridDim.x) * 8;
+  for (long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += nwarps) {
+    const size_t base = static_cast<size_t>(row) * H;
+    float f[VPL][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      Vec8<T>::load(x + base + c, f[k]);
+      if (delta) {
+        add_rounded<T>(f[k], delta + base + c);
+        Vec8<T>::store(hout + base + c, f[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s1 += f[k][i]; s2 += f[k][i] * f[k][i]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    float mean, rstd;
+    if (RMS) { mean = 0.f; rstd = rsqrtf(s2 / H + eps); }
+    else { mean = s1 / H; rstd = rsqrtf(fmaxf(s2 / H - mean * mean, 0.f) + eps); }
+    if (lane == 0) { stats[2 * row] = mean; stats[2 * row + 1] = rstd; }
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int c = (lane + 32 * k) * 8;
+      float g[8], b[8], o[8];
+      Vec8<T>::load(gamma + c, g);
+      if (!RMS && beta) Vec8<T>::load(beta + c, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v = (f[k][i] - mean) * rstd * g[i];
+        if (!RMS && beta) v += b[i];
+        o[i] = v;
+      }
+      Vec8<T>::store(y + base + c, o);
+    }
+  }
+}
+
 template <typename T, bool RMS, int CH, int R>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_rows_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
@@ -528,10 +584,31 @@ gelu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __r
 
 int sm_count(int device);
 
+// The warp-per-row forward serves hidden sizes 1024 / 2048 / 4096; AXONN_NORM_WARP=0 keeps the block-per-rows kernel
+// for them too (read once).
+static bool norm_warp_rows_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("AXONN_NORM_WARP");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 template <typename T>
 static int norm_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* stats, int rows, int H,
                       int H_total, float eps, int rms, int mode, int grid, cudaStream_t s, const void* delta, void* hout) {
   const int threads = (H / 8 <= 128) ? 128 : NORM_THREADS;  // no idle threads for narrow (sharded) rows
+  if (mode == 0 && H == H_total && norm_warp_rows_enabled() && (H == 1024 || H == 2048 || H == 4096)) {
+    const int wgrid = min((rows + 7) / 8, grid * 2);
+#define AXB_NORM_FWD_WARP(RMS_, VPL_)                                                                           \
+  norm_fwd_warp_kernel<T, RMS_, VPL_><<<wgrid, 256, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y, \
+                                                           stats, rows, H, eps, (const T*)delta, (T*)hout)
+    if (rms) { if (H == 1024) AXB_NORM_FWD_WARP(true, 4); else if (H == 2048) AXB_NORM_FWD_WARP(true, 8); else AXB_NORM_FWD_WARP(true, 16); }
+    else { if (H == 1024) AXB_NORM_FWD_WARP(false, 4); else if (H == 2048) AXB_NORM_FWD_WARP(false, 8); else AXB_NORM_FWD_WARP(false, 16); }
+#undef AXB_NORM_FWD_WARP
+    AXB_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (mode == 0 && H == H_total && H / 8 <= 2 * NORM_THREADS && H / 8 > 128) {
     const int ch = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
 #define AXB_NORM_FWD_ROWS(RMS_, CH_, R_)                                                                         \

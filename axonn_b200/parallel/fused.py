@@ -143,7 +143,7 @@ _group_ok = {}
 def _peer_capable(group) -> bool:
     """True when every rank of ``group`` sits on the same host, can address every other rank's GPU and a
     small symmetric allocation works.  Decided once per group, collectively (all ranks of the group reach
-    their first fused call at the same layer), and the verdict is agreed on with a MIN all-reduce so that no
+    their first fused call at the same layer), and the decision is agreed on with a MIN all-reduce so that no
     rank takes the fused path alone.  A group that spans hosts or lacks peer access keeps using
     ``torch.distributed``."""
     key = id(group)
