@@ -68,3 +68,37 @@ def test_fused_adamw_state_dict_roundtrip_keeps_fp32_state_for_bf16_parameters()
     for a, c in zip(ps_a, ps_c):
         assert torch.equal(a, c)
         assert torch.equal(opt_a.state[a]["master"], opt_c.state[c]["master"])
+
+
+def test_fused_sgd_cpu_path_matches_torch_sgd():
+    from axonn_b200.optim import FusedSGD
+
+    torch.manual_seed(3)
+    ours = [torch.nn.Parameter(torch.randn(7, 5)), torch.nn.Parameter(torch.randn(11))]
+    ref = [torch.nn.Parameter(p.detach().clone()) for p in ours]
+    a = FusedSGD(ours, lr=0.05, momentum=0.9, weight_decay=0.01)
+    b = torch.optim.SGD(ref, lr=0.05, momentum=0.9, weight_decay=0.01)
+    for _ in range(4):
+        for p, q in zip(ours, ref):
+            g = torch.randn_like(q)
+            p.grad, q.grad = g.clone(), g.clone()
+        a.step()
+        b.step()
+    for p, q in zip(ours, ref):
+        assert torch.allclose(p, q, atol=1e-6)
+
+
+def test_linear_batched_cpu_matches_per_expert_linear():
+    from axonn_b200 import ops
+
+    torch.manual_seed(4)
+    x = torch.randn(3, 16, 8, requires_grad=True)
+    w = torch.randn(3, 12, 8, requires_grad=True)
+    seg = torch.tensor([[4, 8], [0, 8], [8, 8]], dtype=torch.int32)     # ignored by the CPU path: rows are not masked
+    y = ops.linear_batched(x, w, seg, 8)
+    ref = torch.stack([x[e] @ w[e].t() for e in range(3)])
+    assert torch.allclose(y, ref, atol=1e-5)
+    g = torch.randn_like(y)
+    gx, gw = torch.autograd.grad(y, (x, w), g)
+    rx, rw = torch.autograd.grad(ref, (x, w), g)
+    assert torch.allclose(gx, rx, atol=1e-5) and torch.allclose(gw, rw, atol=1e-5)
