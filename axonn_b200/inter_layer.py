@@ -253,6 +253,8 @@ class AxoNN_Inter_Layer_Engine:
                 loss_sum += self._calc_loss(mb, self._get_subtensor(labels, mb), 1.0 / n, eval_mode)
                 if not eval_mode:
                     self._backward_pass(None, mb)
+        elif self._schedule() == "1f1b":
+            self._run_one_forward_one_backward(batch, labels, n, eval_mode, loss_sum)
         else:
             first, last = rank == 0, rank == G - 1
             fw_left = 0 if first else n
@@ -309,6 +311,56 @@ class AxoNN_Inter_Layer_Engine:
         value = float(loss_sum.item()) / n   # host synchronisation: the step's kernels have finished
         self._check_device_status()
         return value
+
+    def _schedule(self) -> str:
+        """``message``: every stage keeps a receive posted in each direction and works on whatever arrives (the
+        reference's schedule).  ``1f1b``: the fixed order that schedule settles into for equal-cost microbatches -
+        stage s runs ``G_inter - s`` forwards, then alternates one backward and one forward - with every receive
+        posted only at the moment its message is due, so no receive ever waits behind another one.
+        ``AXONN_PIPELINE_SCHEDULE`` selects one; by default NCCL stages use the fixed order when there are more
+        than two of them (a middle stage with two receives pending on NCCL communicators stopped making progress
+        there; two stages and CPU ranks run the message-driven form)."""
+        mode = os.environ.get("AXONN_PIPELINE_SCHEDULE", "auto")
+        if mode in ("message", "1f1b"):
+            return mode
+        return "1f1b" if (self.device.type == "cuda" and ax.config.G_inter > 2) else "message"
+
+    def _recv_now(self, kind):
+        shape, src = ((self.model.get_input_shape(), self._rank - 1) if kind == "fw"
+                      else (self.model.get_output_shape(), self._rank + 1))
+        buf = torch.empty(self._fill_shape(shape), device=self.device, dtype=self.computation_dtype)
+        ax.comm_handle.recv(buf, src, async_op=False)
+        if kind == "fw":
+            buf.requires_grad = True
+        return buf
+
+    def _run_one_forward_one_backward(self, batch, labels, n, eval_mode, loss_sum):
+        rank, G = self._rank, ax.config.G_inter
+        first, last = rank == 0, rank == G - 1
+
+        def forward(mb):
+            x = self._get_subtensor(batch, mb) if first else self._recv_now("fw")
+            self._forward_pass(x, mb, eval_mode)
+            if last:
+                loss_sum.add_(self._calc_loss(mb, self._get_subtensor(labels, mb), 1.0 / n, eval_mode))
+
+        def backward(mb):
+            self._backward_pass(None if last else self._recv_now("bw"), mb)
+
+        if eval_mode:
+            for mb in range(n):
+                forward(mb)
+        else:
+            warm = min(G - rank, n)
+            for mb in range(warm):
+                forward(mb)
+            nf = warm
+            for nb in range(n):
+                backward(nb)
+                if nf < n:
+                    forward(nf)
+                    nf += 1
+        self._clear_transit_tensors(clear_all=True)
 
     def _check_device_status(self):
         """Raise if a kernel of this step reported an expired device-side wait (read after the loss readback,

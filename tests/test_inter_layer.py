@@ -72,6 +72,17 @@ def test_pipeline_matches_single_stage_fp32():
     assert four == pytest.approx(ref, rel=1e-4)
 
 
+def test_fixed_order_schedule_matches_single_stage(monkeypatch):
+    """The one-forward-one-backward order (what NCCL stages use when there are more than two) must give the same
+    losses as a single stage, with two and with four stages."""
+    ref = run_distributed(_vit_run, 1, 1, 1, 4, "float32")[0]
+    monkeypatch.setenv("AXONN_PIPELINE_SCHEDULE", "1f1b")
+    four = run_distributed(_vit_run, 4, 4, 1, 4, "float32")[0]
+    assert four == pytest.approx(ref, rel=1e-4)
+    two = run_distributed(_vit_run, 4, 2, 2, 4, "float32")[0]
+    assert two == pytest.approx(ref, rel=1e-4)
+
+
 def test_pipeline_four_stages_bf16_trains():
     out = run_distributed(_vit_run, 4, 4, 1, 6, "bfloat16")[0]
     assert out[5] < out[0]
