@@ -103,6 +103,8 @@ class ExpertParallelMoE(nn.Module):
             p.is_expert_parallel = self.ep > 1
         self.last_aux_loss = None
         self.last_drop_fraction = None
+        self.last_assignments_per_expert = None
+        self.last_dropped_per_expert = None
 
     def capacity(self, tokens):
         c = math.ceil(self.capacity_factor * tokens * self.top_k / self.n_experts)
@@ -126,6 +128,14 @@ class ExpertParallelMoE(nn.Module):
         idx, gate, slot, keep, aux = route_top_k(logits, k, C)
         self.last_aux_loss = aux
         self.last_drop_fraction = 1.0 - keep.float().mean().detach()
+        # routing statistics of this rank's tokens (device tensors, no host synchronisation): assignments per
+        # expert before the capacity cut, and how many of them were dropped per expert
+        with torch.no_grad():
+            flat_idx = idx.reshape(-1)
+            ones = torch.ones(flat_idx.shape, dtype=torch.float32, device=flat_idx.device)
+            zeros = torch.zeros(E, dtype=torch.float32, device=flat_idx.device)
+            self.last_assignments_per_expert = zeros.index_add(0, flat_idx, ones)
+            self.last_dropped_per_expert = zeros.index_add(0, flat_idx, (~keep).reshape(-1).float())
         dest = (idx * C + slot.clamp(max=C - 1)).reshape(-1)           # row in the [E*C, H] send buffer
         keep_f = keep.reshape(-1)
         from . import moe_kernels

@@ -98,3 +98,24 @@ def _moe_easy_sync(rank, world):
 def test_easy_mode_sync_leaves_expert_gradients_unmixed():
     for ok_expert, ok_router in run_distributed(_moe_easy_sync, 2):
         assert ok_expert and ok_router
+
+
+
+def _routing_stats_case(rank, world):
+    from axonn_b200 import axonn as ax
+    from axonn_b200.parallel.moe import ExpertParallelMoE
+
+    ax.init(G_inter=1, G_data=world)
+    torch.manual_seed(2)
+    layer = ExpertParallelMoE(hidden=32, ffn=64, n_experts=4, top_k=2, capacity_factor=0.5, dtype=torch.float32)
+    layer(torch.randn(3, 16, 32))
+    a, d = layer.last_assignments_per_expert, layer.last_dropped_per_expert
+    return (int(a.sum()), float(d.sum()), float(layer.last_drop_fraction) * 48 * 2)
+
+
+def test_routing_statistics_add_up():
+    """Per-expert assignment and drop counts of the last forward: they sum to tokens * top_k and to the dropped
+    assignments that the drop fraction reports."""
+    total, dropped, from_fraction = run_distributed(_routing_stats_case, 1)[0]
+    assert total == 96
+    assert dropped > 0 and abs(dropped - from_fraction) < 1e-3
