@@ -8,6 +8,15 @@ over: ``load`` reads the file that ``save`` wrote and returns its content
 (the reference looks for ``<prefix>_<name>.pt`` and discards the result,
 ``checkpoint.py:29-37``), and with pipelining each stage gets its own
 ``_inter_K`` suffix so stages no longer overwrite one another.
+
+Besides the per-coordinate shard files there is a grid-independent form
+(:func:`consolidated_state`, :func:`save_consolidated`,
+:func:`load_consolidated`): every tensor-parallel parameter and every
+optimizer state tensor laid out like one is reassembled to its full shape, so a
+run can be resumed on a different ``(G_data, G_intra_r, G_intra_c, G_intra_d)``
+grid, e.g. after losing a node.  The reference has only the loading half of this
+(``axonn/intra_layer/fully_connected.py:350-400`` accepts a full matrix or a
+matching shard) and no optimizer-state resharding.
 """
 
 import os
@@ -63,3 +72,145 @@ def load(state, checkpoint_folder, checkpoint_name, map_location="cpu"):
         state.update(loaded)
         return state
     return loaded
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Grid-independent checkpoints
+# ----------------------------------------------------------------------------------------------------------
+
+_PER_PARAMETER_STATE = ("master", "exp_avg", "exp_avg_sq", "momentum_buffer")
+
+
+def _sharded_parameters(model):
+    """``{parameter name: (module, local name)}`` for every parameter whose owning module knows how to rebuild
+    the full tensor (``full_tensor`` / ``shard_tensor``: the tensor-parallel layers, the split-hidden norms, the
+    expert-parallel MoE layer).  All other parameters are replicated and stored as they are."""
+    out = {}
+    for mname, module in model.named_modules():
+        if not (hasattr(module, "full_tensor") and hasattr(module, "shard_tensor")):
+            continue
+        for pname, _ in module.named_parameters(recurse=False):
+            out[(mname + "." if mname else "") + pname] = (module, pname)
+    return out
+
+
+def _is_consolidation_writer() -> bool:
+    return config.data_parallel_rank == 0 and config.intra_layer_parallel_rank == 0
+
+
+def _consolidated_path(folder, name):
+    stage = f".inter_{config.inter_layer_parallel_rank}" if config.G_inter > 1 else ""
+    return os.path.join(folder, f"{name}.full{stage}.pt")
+
+
+@torch.no_grad()
+def consolidated_state(model, optimizer=None, keep=None):
+    """Reassemble the model (and optionally the optimizer state) into full, grid-independent tensors.
+
+    Collective: every rank of the job calls it with the same model.  Tensors are gathered one at a time and
+    moved to host memory; ranks for which ``keep`` is false (default: all but data-parallel rank 0 /
+    tensor-parallel rank 0 of each pipeline stage) drop them at once and get ``None`` back, so at most one
+    full tensor is alive on a device at any time.
+
+    The optimizer part is keyed by parameter *name*, not by index: ``{"state": {name: {"step": n, "exp_avg":
+    full tensor, ...}}, "param_groups": [hyper-parameters without the parameter lists]}``."""
+    keep = _is_consolidation_writer() if keep is None else keep
+    sharded = _sharded_parameters(model)
+    out_model = {}
+    for name, value in model.state_dict().items():
+        if name in sharded:
+            module, pname = sharded[name]
+            value = module.full_tensor(pname, value)
+        if keep:
+            out_model[name] = value.detach().to("cpu", copy=True)
+        del value
+    state = {"model": out_model if keep else None}
+    if optimizer is not None:
+        names = {p: n for n, p in model.named_parameters()}
+        opt_state = {}
+        for group in optimizer.param_groups:
+            for p in group["params"]:
+                name, st = names.get(p), optimizer.state.get(p)
+                if name is None or not st:
+                    continue
+                entry = {}
+                for key, value in st.items():
+                    if torch.is_tensor(value) and key in _PER_PARAMETER_STATE and value.numel() == p.numel():
+                        value = value.to(p.device).view_as(p)
+                        if name in sharded:
+                            module, pname = sharded[name]
+                            value = module.full_tensor(pname, value)
+                        value = value.detach().to("cpu", copy=True) if keep else None
+                    elif torch.is_tensor(value):
+                        value = value.detach().to("cpu", copy=True) if keep else None
+                    entry[key] = value
+                if keep:
+                    opt_state[name] = entry
+        groups = [{k: v for k, v in g.items() if k != "params"} for g in optimizer.param_groups]
+        state["optimizer"] = {"state": opt_state, "param_groups": groups,
+                              "steps": getattr(optimizer, "_steps", None)} if keep else None
+    return state if keep else None
+
+
+def save_consolidated(model, optimizer, checkpoint_folder, checkpoint_name, extra=None, overwrite=True):
+    """Write ``<folder>/<name>.full.pt`` (``.full.inter_K.pt`` per pipeline stage): one file that any grid can
+    load.  Collective; one rank per pipeline stage writes.  ``extra`` (step counters, RNG state, ...) is stored
+    under ``"extra"``.  Returns the path on the writing rank, ``None`` elsewhere."""
+    state = consolidated_state(model, optimizer)
+    if state is None:
+        return None
+    if extra is not None:
+        state["extra"] = extra
+    state["grid"] = {k: getattr(config, k) for k in ("G_inter", "G_data", "G_intra_r", "G_intra_c", "G_intra_d")}
+    path = _consolidated_path(checkpoint_folder, checkpoint_name)
+    os.makedirs(checkpoint_folder, exist_ok=True)
+    if os.path.exists(path) and not overwrite:
+        raise ValueError(f"Checkpoint {path} already exists")
+    tmp = path + f".tmp.{os.getpid()}"
+    torch.save(state, tmp)
+    os.replace(tmp, path)
+    return path
+
+
+@torch.no_grad()
+def load_consolidated(model, optimizer, checkpoint_folder, checkpoint_name, strict=True):
+    """Load a file written by :func:`save_consolidated` into a model / optimizer living on *this* grid.
+
+    Every rank reads the file (memory-mapped, so the ranks of a node share the page cache) and keeps its own
+    piece of each tensor: the layers' state-dict hooks cut the model tensors, ``shard_tensor`` cuts the
+    optimizer's.  No communication.  Returns the ``"extra"`` entry (or ``None``)."""
+    path = _consolidated_path(checkpoint_folder, checkpoint_name)
+    try:
+        state = torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+    except (RuntimeError, ValueError):
+        state = torch.load(path, map_location="cpu", weights_only=False)
+    model.load_state_dict(state["model"], strict=strict)
+    saved = state.get("optimizer")
+    if optimizer is not None and saved is not None:
+        sharded = _sharded_parameters(model)
+        names = {p: n for n, p in model.named_parameters()}
+        for group, hyper in zip(optimizer.param_groups, saved["param_groups"]):
+            group.update(hyper)
+            for p in group["params"]:
+                entry = saved["state"].get(names.get(p))
+                if entry is None:
+                    continue
+                host_state = hasattr(optimizer, "_host_state")  # CPUAdam: flat fp32 state in pinned host memory
+                st = optimizer._host_state(p) if host_state else optimizer.state[p]
+                for key, value in entry.items():
+                    if torch.is_tensor(value) and key in _PER_PARAMETER_STATE:
+                        if names[p] in sharded and value.shape != p.shape:
+                            module, pname = sharded[names[p]]
+                            value = module.shard_tensor(pname, value)
+                        if host_state:
+                            st[key].copy_(value.reshape(-1))
+                            continue
+                        value = value.to(device=p.device, copy=True).contiguous()
+                    elif torch.is_tensor(value):
+                        value = value.to(device=p.device, copy=True)
+                    st[key] = value
+        if saved.get("steps") is not None and hasattr(optimizer, "_steps"):
+            optimizer._steps = int(saved["steps"])
+        if hasattr(optimizer, "_tables"):
+            optimizer._tables.clear()  # cached pointer tables name the replaced state tensors
+    return state.get("extra")

@@ -25,6 +25,8 @@ from .communication import (
     ForwardAllReduce,
     ForwardGather_BackwardReduceScatter,
     Gather,
+    _drop,
+    _gather,
 )
 
 
@@ -130,3 +132,20 @@ class Conv2d(torch.nn.Module):
         if b is not None and b.size(0) == self.out_channels and self.outer_group_size > 1:
             state_dict[prefix + "bias"] = Drop.apply(b, self.outer_group).clone()
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
+    @torch.no_grad()
+    def full_tensor(self, name, t=None):
+        """Grid-independent form of a tensor laid out like parameter ``name`` (``"weight"``: the
+        ``[out_c, in_c, k, k]`` filter bank; ``"bias"``: ``[out_c]``).  Collective over the layer's groups."""
+        t = getattr(self, name).detach() if t is None else t
+        if name == "bias":
+            return _gather(t, 0, self.outer_group)
+        w = _gather(t, 0, self.depth_group).reshape(self.local_weight_shape)
+        w = _gather(w, 1, self.inner_group)
+        return _gather(w, 0, self.outer_group)
+
+    @torch.no_grad()
+    def shard_tensor(self, name, full):
+        if name == "bias":
+            return _drop(full, 0, self.outer_group).clone()
+        return extract_local_params_from_full_params(full, self.outer_group, self.inner_group, self.depth_group)

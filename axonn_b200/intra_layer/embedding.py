@@ -20,7 +20,7 @@ import torch.nn.functional as F
 
 from .. import axonn as ax
 from ..utils import divide
-from .communication import ForwardGather_BackwardReduceScatter, Gather
+from .communication import ForwardGather_BackwardReduceScatter, Gather, _gather
 
 
 @torch.no_grad()
@@ -169,3 +169,15 @@ class Embedding(torch.nn.Module):
             elif not self._is_sharded_weight_matrix(w):
                 raise ValueError("embedding weight is neither the full table nor this rank's shard")
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
+    @torch.no_grad()
+    def full_tensor(self, name, t=None):
+        """Grid-independent ``[num_embeddings, embedding_dim]`` form of the table or of an optimizer state
+        tensor laid out like it.  Collective over the depth and the hidden group."""
+        t = self.weight.detach() if t is None else t
+        w = _gather(t, 0, self.depth_group).reshape(self.local_in_features, self.local_out_features)
+        return _gather(w, 1, self.hidden_group)
+
+    @torch.no_grad()
+    def shard_tensor(self, name, full):
+        return extract_local_params_from_full_params(full, self.hidden_group, self.depth_group)

@@ -42,7 +42,7 @@ from .asym_communication import (
     Gatherv,
     gather_batch_sizes,
 )
-from .communication import Drop, GatherSumBackward, _gather, _reduce_scatter
+from .communication import Drop, GatherSumBackward, _drop, _gather, _reduce_scatter
 
 
 @torch.no_grad()
@@ -408,7 +408,23 @@ class Linear(torch.nn.Module):
     @torch.no_grad()
     def full_weight(self):
         """Reassemble the full ``[out, in]`` matrix on every rank (tests, export)."""
-        w = _gather(self.weight.detach(), 0, self.depth_group).reshape(self.local_weight_shape)
+        return self.full_tensor("weight")
+
+    @torch.no_grad()
+    def full_tensor(self, name, t=None):
+        """Grid-independent form of a tensor laid out like parameter ``name`` (``"weight"`` or ``"bias"``):
+        the parameter itself, or an optimizer state tensor of the same shape.  Collective over the layer's
+        three groups; every rank receives the result."""
+        t = getattr(self, name).detach() if t is None else t
+        if name == "bias":
+            return _gather(t, 0, self.outer_group)
+        w = _gather(t, 0, self.depth_group).reshape(self.local_weight_shape)
         w = _gather(w, 1, self.inner_group)
-        w = _gather(w, 0, self.outer_group)
-        return w
+        return _gather(w, 0, self.outer_group)
+
+    @torch.no_grad()
+    def shard_tensor(self, name, full):
+        """Inverse of :meth:`full_tensor`: this rank's piece of a full ``[out, in]`` matrix or ``[out]`` vector."""
+        if name == "bias":
+            return _drop(full, 0, self.outer_group).clone()
+        return extract_local_params_from_full_params(full, self.outer_group, self.inner_group, self.depth_group)

@@ -22,6 +22,7 @@ import torch.nn as nn
 from .. import axonn as ax
 from .. import ops
 from ..intra_layer import Gather, Linear
+from ..intra_layer.communication import _drop, _gather
 from ..utils import divide
 
 
@@ -57,6 +58,26 @@ class TPNorm(nn.Module):
         if self.rms:
             return ops.rms_norm(x, self.weight, self.eps, self.group)
         return ops.layer_norm(x, self.weight, self.bias, self.eps, self.group)
+
+    @torch.no_grad()
+    def full_tensor(self, name, t=None):
+        """The whole ``[hidden]`` vector of ``weight`` / ``bias`` (or of an optimizer state tensor laid out like
+        it); collective over the column group."""
+        t = getattr(self, name).detach() if t is None else t
+        return t if self.group is None else _gather(t, 0, self.group)
+
+    @torch.no_grad()
+    def shard_tensor(self, name, full):
+        return full if self.group is None else _drop(full, 0, self.group).clone()
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        """Accept the full ``[hidden]`` vectors (a checkpoint of another grid) as well as this rank's slices."""
+        if self.group is not None:
+            for name in ("weight", "bias"):
+                v = state_dict.get(prefix + name)
+                if v is not None and v.numel() == self.local * dist.get_world_size(self.group):
+                    state_dict[prefix + name] = self.shard_tensor(name, v)
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
     def add_norm(self, x, delta):
         """``h = x + delta`` and ``norm(h)`` in one kernel (the residual add fused into the normalisation);

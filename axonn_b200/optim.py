@@ -181,6 +181,31 @@ class CPUAdam(torch.optim.Optimizer):
             st["exp_avg_sq"] = torch.zeros(p.numel(), dtype=torch.float32, pin_memory=pin)
         return st
 
+    def state_dict(self):
+        """The step count lives on the optimizer (one count for all parameters), so it is added to the dict."""
+        sd = super().state_dict()
+        sd["steps"] = self._steps
+        return sd
+
+    def load_state_dict(self, state_dict):
+        """``torch.optim.Optimizer.load_state_dict`` would move the state to the parameters' device and cast it
+        to their dtype; this optimizer's state is flat fp32 in (pinned) host memory and stays there."""
+        ids = [i for g in state_dict["param_groups"] for i in g["params"]]
+        params = [p for g in self.param_groups for p in g["params"]]
+        if len(ids) != len(params):
+            raise ValueError("loaded state dict names a different number of parameters")
+        for group, saved in zip(self.param_groups, state_dict["param_groups"]):
+            group.update({k: v for k, v in saved.items() if k != "params"})
+        for i, p in zip(ids, params):
+            src = state_dict["state"].get(i)
+            if src is None:
+                continue
+            st = self._host_state(p)
+            for key in ("master", "exp_avg", "exp_avg_sq"):
+                st[key].copy_(src[key].detach().reshape(-1).float())
+            p.data.copy_(st["master"].view_as(p))
+        self._steps = int(state_dict.get("steps", self._steps))
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None

@@ -106,6 +106,32 @@ class ExpertParallelMoE(nn.Module):
         self.last_assignments_per_expert = None
         self.last_dropped_per_expert = None
 
+    @torch.no_grad()
+    def full_tensor(self, name, t=None):
+        """All experts' ``w1`` / ``w2`` (``[n_experts, ...]``; or an optimizer state tensor laid out like them),
+        gathered over the expert-parallel group; the router is replicated and returned as it is."""
+        t = getattr(self, name).detach() if t is None else t
+        if name == "router" or self.ep == 1:
+            return t
+        out = torch.empty((self.n_experts,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        return out
+
+    @torch.no_grad()
+    def shard_tensor(self, name, full):
+        if name == "router" or self.ep == 1:
+            return full
+        return full[self.ep_rank * self.n_local:(self.ep_rank + 1) * self.n_local].clone()
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        """Accept ``w1`` / ``w2`` holding all experts (a checkpoint of another grid) as well as the local ones."""
+        if self.ep > 1:
+            for name in ("w1", "w2"):
+                v = state_dict.get(prefix + name)
+                if v is not None and v.shape[0] == self.n_experts:
+                    state_dict[prefix + name] = self.shard_tensor(name, v)
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
     def capacity(self, tokens):
         c = math.ceil(self.capacity_factor * tokens * self.top_k / self.n_experts)
         return max(8, (c + 7) // 8 * 8)

@@ -72,7 +72,9 @@ def _ckpt_resume(rank, world, folder, phase):
     from axonn_b200.optim import FusedAdamW
     from axonn_b200.trainer import Trainer
 
-    r, c, d = (2, 1, 1) if phase != "resume_other_grid" else (1, 1, 2)
+    r, c, d = (2, 1, 1)
+    if phase.startswith("resume_grid_"):
+        r, c, d = (int(v) for v in phase.split("_")[2:])
     ax.init(G_inter=1, G_data=world // (r * c * d), G_intra_r=r, G_intra_c=c, G_intra_d=d)
     torch.manual_seed(3)
     cfg = GPTConfig.tiny()
@@ -85,8 +87,13 @@ def _ckpt_resume(rank, world, folder, phase):
     if phase == "train":
         losses = [tr.train_step(x, y) for _ in range(2)]
         checkpoint.save({"model": model.state_dict(), "optimizer": opt.state_dict()}, folder, "step2")
+        written = checkpoint.save_consolidated(model, opt, folder, "step2", extra={"step": 2})
+        assert (written is not None) == (rank == 0)
         losses += [tr.train_step(x, y) for _ in range(2)]
         return losses
+    if phase.startswith("resume_grid_"):
+        assert checkpoint.load_consolidated(model, opt, folder, "step2") == {"step": 2}
+        return [tr.train_step(x, y) for _ in range(2)]
     state = checkpoint.load(None, folder, "step2")
     model.load_state_dict(state["model"])
     opt.load_state_dict(state["optimizer"])
@@ -96,6 +103,12 @@ def _ckpt_resume(rank, world, folder, phase):
 def test_resume_from_sharded_checkpoint_reproduces_loss(tmp_path):
     folder = str(tmp_path / "ckpt")
     full = run_distributed(_ckpt_resume, 2, folder, "train")[0]
-    assert sorted(os.listdir(folder)) == ["tp_row_0_col_0_depth_0", "tp_row_1_col_0_depth_0"]
+    assert sorted(os.listdir(folder)) == ["step2.full.pt", "tp_row_0_col_0_depth_0", "tp_row_1_col_0_depth_0"]
     resumed = run_distributed(_ckpt_resume, 2, folder, "resume")[0]
     assert resumed == pytest.approx(full[2:], rel=1e-5)
+    # elastic restart: the grid-independent file written at the same step is loaded on other grids (other
+    # tensor-parallel shapes, a data-parallel pair, a single process) and the loss curve continues
+    assert "step2.full.pt" in os.listdir(folder)
+    for world, grid in ((2, "1_1_2"), (2, "1_2_1"), (2, "1_1_1"), (1, "1_1_1"), (4, "2_1_2")):
+        other = run_distributed(_ckpt_resume, world, folder, "resume_grid_" + grid)[0]
+        assert other == pytest.approx(full[2:], rel=2e-4), (world, grid)

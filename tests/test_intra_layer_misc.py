@@ -40,6 +40,11 @@ def _conv_emb(rank, world, grid):
     gw = _gather(_gather(gw, 1, inner), 0, outer)
     assert torch.allclose(gw, seq.weight.grad, atol=1e-4), (gw - seq.weight.grad).abs().max()
     assert torch.allclose(xp.grad, xs.grad, atol=1e-4)
+    # grid-independent form of the parameters (and of anything laid out like them) and back
+    assert torch.equal(par.full_tensor("weight"), seq.weight) and torch.equal(par.full_tensor("bias"), seq.bias)
+    assert torch.equal(par.full_tensor("weight", par.weight.grad), gw)
+    assert torch.equal(par.shard_tensor("weight", seq.weight.detach()), par.weight)
+    assert torch.equal(par.shard_tensor("bias", seq.bias.detach()), par.bias)
 
     # ---- embedding (hidden over the row group; needs c == 1 in easy mode)
     if c == 1:
@@ -56,6 +61,8 @@ def _conv_emb(rank, world, grid):
         ge = _gather(ge, 1, par_e.hidden_group)
         # the depth reduce-scatter sums the gradients of all depth ranks; here they all looked up the same ids
         assert torch.allclose(ge / d, seq_e.weight.grad, atol=1e-5)
+        assert torch.equal(par_e.full_tensor("weight"), seq_e.weight)
+        assert torch.equal(par_e.shard_tensor("weight", seq_e.weight.detach()), par_e.weight)
     return True
 
 

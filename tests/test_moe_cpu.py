@@ -119,3 +119,41 @@ def test_routing_statistics_add_up():
     total, dropped, from_fraction = run_distributed(_routing_stats_case, 1)[0]
     assert total == 96
     assert dropped > 0 and abs(dropped - from_fraction) < 1e-3
+
+
+def _moe_consolidated(rank, world, folder, phase):
+    from axonn_b200 import axonn as ax
+    from axonn_b200 import checkpoint
+    from axonn_b200.optim import FusedAdamW
+    from axonn_b200.parallel.moe import ExpertParallelMoE
+
+    ax.init(G_inter=1, G_data=world)
+    torch.manual_seed(5 if phase == "save" else 6)  # the loading run starts from other weights
+    layer = ExpertParallelMoE(hidden=32, ffn=64, n_experts=4, top_k=2, capacity_factor=4.0, dtype=torch.float32)
+    opt = FusedAdamW(layer.parameters(), lr=1e-2, weight_decay=0.0)
+    g = torch.Generator().manual_seed(11)
+    X = torch.randn(4, 8, 32, generator=g)
+    if phase == "save":
+        per = 4 // world
+        layer(X[rank * per:(rank + 1) * per]).square().sum().backward()
+        opt.step()
+        checkpoint.save_consolidated(layer, opt, folder, "moe")
+    else:
+        checkpoint.load_consolidated(layer, opt, folder, "moe")
+    st = opt.state[layer.w1]
+    return (layer.full_tensor("w1").numpy(), layer.full_tensor("w2").numpy(), layer.router.detach().numpy(),
+            layer.full_tensor("w1", st["exp_avg"]).numpy(), int(st["step"]))
+
+
+def test_expert_parallel_state_moves_between_group_sizes(tmp_path):
+    """Experts and their optimizer moments saved by 4 expert-parallel ranks arrive unchanged in 1 and 2 ranks."""
+    import numpy as np
+
+    folder = str(tmp_path)
+    saved = run_distributed(_moe_consolidated, 4, folder, "save")[0]
+    assert np.abs(saved[3]).max() > 0 and saved[4] == 1
+    for world in (1, 2):
+        for got in run_distributed(_moe_consolidated, world, folder, "load"):
+            for a, b in zip(got[:4], saved[:4]):
+                assert np.array_equal(a, b)
+            assert got[4] == 1

@@ -102,3 +102,31 @@ def test_linear_batched_cpu_matches_per_expert_linear():
     gx, gw = torch.autograd.grad(y, (x, w), g)
     rx, rw = torch.autograd.grad(ref, (x, w), g)
     assert torch.allclose(gx, rx, atol=1e-5) and torch.allclose(gw, rw, atol=1e-5)
+
+
+def test_cpu_adam_state_dict_roundtrip_keeps_step_count_and_host_state():
+    """Resuming from ``state_dict()`` continues exactly: the optimizer-wide step count (bias correction) and the
+    flat host-side moments come back."""
+    from axonn_b200.optim import CPUAdam
+
+    torch.manual_seed(0)
+    w0 = torch.randn(6, 5)
+    grads = [torch.randn(6, 5) for _ in range(3)]
+
+    def run(resume_after=None):
+        p = torch.nn.Parameter(w0.clone())
+        opt = CPUAdam([p], lr=1e-2, weight_decay=0.1)
+        for i, g in enumerate(grads):
+            if resume_after == i:
+                sd = opt.state_dict()
+                assert sd["steps"] == i
+                q = torch.nn.Parameter(torch.zeros_like(p))
+                opt = CPUAdam([q], lr=1.0)
+                opt.load_state_dict(sd)
+                assert opt.param_groups[0]["lr"] == 1e-2 and not opt.state[q]["exp_avg"].is_cuda
+                p = q
+            p.grad = g.clone()
+            opt.step()
+        return p.detach().clone()
+
+    assert torch.equal(run(), run(resume_after=2))
