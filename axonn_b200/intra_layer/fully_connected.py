@@ -194,7 +194,8 @@ class AsyncLinear(Function):
         bias_sum = None
         if pre_act is not None:
             if ctx.has_bias and ctx.needs_input_grad[2]:
-                go2, bias_sum = ops.gelu_backward_colsum(go2, pre_act, out_dtype=ctx.bias_dtype)   # bias gradient in the same pass
+                # bias gradient in the same pass
+                go2, bias_sum = ops.gelu_backward_colsum(go2, pre_act, out_dtype=ctx.bias_dtype)
             else:
                 go2 = ops.gelu_backward(go2, pre_act)
         x2 = input_.reshape(-1, input_.shape[-1])

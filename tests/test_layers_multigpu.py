@@ -108,7 +108,8 @@ def test_linear_matches_nn_linear_on_gpus(world):
         for expert in (True, False):
             cases.append((grid, expert, True, "bfloat16", 64, 1024, 2048))   # fused kernels
         cases.append((grid, True, True, "float32", 16, 256, 512))            # fp32: library path
-        cases.append((grid, True, False, "bfloat16", 16, 8 * 17 * world, 8 * 9 * world))  # widths the kernels refuse or barely take
+        # widths the kernels refuse or barely take
+        cases.append((grid, True, False, "bfloat16", 16, 8 * 17 * world, 8 * 9 * world))
     cases.append((_grids(world)[0], True, True, "float32", 8, 72 * world, 36 * world))   # local width not a multiple of 8
     assert run_distributed(_fc_suite, world, cases, backend="nccl", timeout=600) == [len(cases)] * world
 
