@@ -268,6 +268,16 @@ void axb_arena_free(void* ptr, long long size, int device, void* stream);
 unsigned long long axb_arena_stat(int device, int what);
 int axb_arena_contains(int device, const void* ptr, unsigned long long nbytes);
 
+/* ---- symmetric heap (symm_heap.cu): one allocation per rank (backend 0: host memory, 1: device memory through the
+ * CUDA virtual-memory-management API), all ranks' allocations mapped into one range, slot p = rank p.  The file
+ * descriptors returned by axb_heap_fd travel between the processes in the Python layer.  axb_heap_info: 0 = base
+ * address, 1 = bytes per slot, 2 = slots mapped, 3 = backend. */
+int axb_heap_create(int backend, int device, int rank, int nranks, unsigned long long bytes, void** out_heap);
+int axb_heap_fd(void* heap);
+int axb_heap_attach(void* heap, int peer, int fd);
+unsigned long long axb_heap_info(void* heap, int what);
+int axb_heap_destroy(void* heap);
+
 /* ---- top-k gradient pruning (prune.cu): keep the k largest |g|, zero the rest, in place.
  * dtype: the codes above (0 bf16, 1 fp16, 2 fp32).  `work`: device scratch of axb_prune_workspace_words() 32-bit words. */
 int axb_prune_workspace_words(void);

@@ -6,7 +6,8 @@ copies directly over NVLink from inside a kernel, and (when the fabric supports
 it) reach all copies at once through an NVSwitch multicast address
 (``multimem.*``).  Allocation and handle exchange use
 ``torch.distributed._symmetric_memory`` (CUDA VMM allocations exchanged over
-the process group's store); this module adds the per-group buffer cache, the
+the process group's store) or, with ``AXONN_SYMM_HEAP=own``, the package's own
+VMM heap (``parallel/heap.py`` over ``csrc/symm_heap.cu``); this module adds the per-group buffer cache, the
 peer-pointer tables that kernels take, and monotonically increasing epochs for
 the signal pads so that a stale flag can never satisfy a wait.
 
@@ -40,6 +41,12 @@ def enabled() -> bool:
     return torch.cuda.is_available() and _disabled_reason is None
 
 
+def own_heap_selected() -> bool:
+    """``AXONN_SYMM_HEAP=own`` allocates symmetric buffers with the package's own VMM heap (``parallel/heap.py``)
+    instead of ``torch.distributed._symmetric_memory`` (the default, ``torch``)."""
+    return os.environ.get("AXONN_SYMM_HEAP", "torch").lower() == "own"
+
+
 def disable(reason: str):
     global _disabled_reason
     _disabled_reason = reason
@@ -58,13 +65,27 @@ class SymmBuffer:
         dev = torch.device("cuda", torch.cuda.current_device())
         # CANARY_BYTES guard bytes follow the usable range; kernels never address them, so a changed guard
         # byte means that a kernel (of this rank or of a peer) wrote past the end of the buffer
-        self._full = symm_mem.empty(self.nbytes + CANARY_BYTES, dtype=torch.uint8, device=dev)
+        if own_heap_selected():
+            # the package's own allocator (parallel/heap.py): VMM allocations mapped into one address range;
+            # no signal pads (the kernels keep their flags inside the buffers) and no multicast binding
+            from .heap import SymmetricHeap
+
+            self.heap = SymmetricHeap(group, self.nbytes + CANARY_BYTES, dev)
+            self._full = self.heap.local[:self.nbytes + CANARY_BYTES]
+            self._full.zero_()
+            self.handle = None
+            self.peer_ptrs = list(self.heap.peer_ptrs)
+            self.signal_ptrs = []
+            self.multicast_ptr = 0
+        else:
+            self.heap = None
+            self._full = symm_mem.empty(self.nbytes + CANARY_BYTES, dtype=torch.uint8, device=dev)
+            self.handle = symm_mem.rendezvous(self._full, group=group)
+            self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            self.signal_ptrs = [int(p) for p in self.handle.signal_pad_ptrs]
+            self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self._full[self.nbytes:].fill_(CANARY_VALUE)
         self.local = self._full[:self.nbytes]
-        self.handle = symm_mem.rendezvous(self._full, group=group)
-        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self.signal_ptrs = [int(p) for p in self.handle.signal_pad_ptrs]
-        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.ptr_table = torch.tensor(self.peer_ptrs, dtype=torch.int64, device=dev)
         self.signal_table = torch.tensor(self.signal_ptrs, dtype=torch.int64, device=dev)
         self.epoch = 0
@@ -80,7 +101,11 @@ class SymmBuffer:
         return self.epoch
 
     def barrier(self):
-        self.handle.barrier()
+        if self.handle is None:
+            torch.cuda.current_stream().synchronize()
+            self.heap.barrier()
+        else:
+            self.handle.barrier()
 
     def canary_intact(self) -> bool:
         """True when the guard bytes behind the buffer still hold their pattern (synchronises the device)."""
