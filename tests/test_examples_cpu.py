@@ -1,5 +1,6 @@
 """The configuration entry points (Llama depth-sharded + pruning, Mixtral expert parallel, VGG-16 pipeline)
-run end to end on CPU ranks at tiny scale."""
+run end to end on CPU ranks at tiny scale, and so do the two tutorial scripts: a tensor-parallel MLP that is
+stopped and continued on another grid, and a pipelined ViT that has to converge."""
 
 import json
 import os
@@ -22,3 +23,28 @@ def test_config_entry_point_tiny(config, port):
     line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
     out = json.loads(line)
     assert out["config"] == config and out["value"] > 0 and out["loss"] == out["loss"]
+
+
+def _torchrun(nproc, port, script, *args, env=None):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc),
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "examples", script), *args]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900,
+                       env=dict(os.environ, CUDA_VISIBLE_DEVICES="", **(env or {})))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    return json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+
+
+def test_tensor_parallel_tutorial_continues_on_another_grid(tmp_path):
+    folder = str(tmp_path / "ckpt")
+    a = _torchrun(4, 29711, "train_mlp_tensor_parallel.py", "--G-intra-r", "2", "--G-intra-d", "2", "--steps", "30",
+                  "--save", folder)
+    assert a["steps"] == 30 and a["last_loss"] < 0.75 * a["first_loss"]
+    b = _torchrun(2, 29712, "train_mlp_tensor_parallel.py", "--G-intra-c", "2", "--steps", "30", "--resume", folder)
+    assert b["first_step"] == 30 and b["steps"] == 60
+    # no restart bump: the continued run starts about where the first one stopped and keeps improving
+    assert b["first_loss"] < 1.1 * a["last_loss"] and b["last_loss"] < a["last_loss"]
+
+
+def test_pipelined_vit_tutorial_converges():
+    out = _torchrun(4, 29713, "train_vit_pipeline.py", env={"G_inter": "2", "G_data": "2"})
+    assert out["steps"] == 32 and out["final_loss"] < 0.1 < out["first_loss"]
