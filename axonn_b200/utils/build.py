@@ -109,8 +109,28 @@ def build_debug_library():
     return build_variant(DEBUG_LIB_PATH, ["-DAXB_DEBUG_BOUNDS"], os.path.join(LIB_DIR, "obj_debug"))
 
 
+SANITIZER_LIB_PATH = os.path.join(LIB_DIR, "libaxonn_b200_asan.so")
+
+
+def build_sanitizer_library():
+    """The host code of the library (allocators, symmetric heap, launch wrappers, status handling) compiled with
+    AddressSanitizer and UndefinedBehaviorSanitizer; device code is unchanged.  Run the CPU tests against it with
+
+        AXONN_LIB_PATH=<this file> LD_PRELOAD="$(gcc -print-file-name=libasan.so) $(gcc -print-file-name=libubsan.so)" \
+        ASAN_OPTIONS=detect_leaks=0:abort_on_error=1 UBSAN_OPTIONS=halt_on_error=1 \
+        python -m pytest tests/test_arena_cpu.py tests/test_symm_heap_cpu.py tests/test_ops_cpu.py
+
+    (leak detection is off because the Python interpreter itself never frees everything)."""
+    os.makedirs(LIB_DIR, exist_ok=True)
+    flags = ["-Xcompiler", "-fsanitize=address", "-Xcompiler", "-fsanitize=undefined", "-Xcompiler",
+             "-fno-omit-frame-pointer"]
+    return build_variant(SANITIZER_LIB_PATH, flags, os.path.join(LIB_DIR, "obj_asan"))
+
+
 if __name__ == "__main__":
     if "--debug-bounds" in sys.argv:
         print(build_debug_library())
+    elif "--sanitize" in sys.argv:
+        print(build_sanitizer_library())
     else:
         build_library(force="--force" in sys.argv)
