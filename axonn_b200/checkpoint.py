@@ -75,6 +75,106 @@ def load(state, checkpoint_folder, checkpoint_name, map_location="cpu"):
 
 
 # ----------------------------------------------------------------------------------------------------------
+# Writing in the background
+# ----------------------------------------------------------------------------------------------------------
+
+class PendingSave:
+    """Handle of a checkpoint that is being written by a background thread."""
+
+    def __init__(self, path):
+        self.path = path
+        self._thread = None
+        self._error = None
+
+    def done(self) -> bool:
+        return self._thread is None or not self._thread.is_alive()
+
+    def wait(self):
+        """Block until the file is in place; re-raises whatever the writer thread raised."""
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+        if self._error is not None:
+            err, self._error = self._error, None
+            raise err
+        return self.path
+
+
+_pending = None
+
+
+def _snapshot(obj, stream):
+    """Copy of ``obj`` (nested dicts / lists / tuples of tensors and plain values) in host memory.  Device tensors
+    are copied on ``stream`` into pinned buffers without blocking the host; host tensors are cloned."""
+    if torch.is_tensor(obj):
+        if obj.is_cuda:
+            host = torch.empty(obj.shape, dtype=obj.dtype, device="cpu", pin_memory=True)
+            with torch.cuda.stream(stream):
+                host.copy_(obj, non_blocking=True)
+            return host
+        return obj.detach().clone()
+    if isinstance(obj, dict):
+        return type(obj)((k, _snapshot(v, stream)) for k, v in obj.items())
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_snapshot(v, stream) for v in obj)
+    return obj
+
+
+def save_async(state, checkpoint_folder, checkpoint_name, overwrite=True):
+    """:func:`save` without stopping the training loop for the file write.
+
+    The call returns after a snapshot of ``state`` has been started: device tensors are copied to pinned host
+    memory on a side stream that waits for the work already queued on the current stream (so the snapshot holds
+    the values as of this call, and later optimizer steps may overwrite the originals at once), host tensors
+    are cloned.  A background thread waits for the copies, writes the file under a temporary name and renames it.
+    Only one write is in flight: a second call first waits for the previous one.  Returns a :class:`PendingSave`
+    (``None`` on ranks that do not write); :func:`wait_for_pending_save` blocks until the file exists - call it
+    before the process exits."""
+    import threading
+
+    global _pending
+    wait_for_pending_save()
+    if config.data_parallel_rank != 0:
+        return None
+    path = checkpoint_path(checkpoint_folder, checkpoint_name)
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    if os.path.exists(path) and not overwrite:
+        raise ValueError(f"Checkpoint {path} already exists")
+    stream = event = None
+    if torch.cuda.is_available() and torch.cuda.is_initialized():
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+    snap = _snapshot(state, stream)
+    if stream is not None:
+        event = torch.cuda.Event()
+        event.record(stream)
+    pending = PendingSave(path)
+
+    def write():
+        try:
+            if event is not None:
+                event.synchronize()
+            tmp = path + f".tmp.{os.getpid()}"
+            torch.save(snap, tmp)
+            os.replace(tmp, path)
+        except BaseException as e:  # noqa: BLE001  (handed to the caller of wait())
+            pending._error = e
+
+    pending._thread = threading.Thread(target=write, name="axonn-checkpoint-writer", daemon=False)
+    pending._thread.start()
+    _pending = pending
+    return pending
+
+
+def wait_for_pending_save():
+    """Block until the checkpoint started by the last :func:`save_async` is on disk (no-op when there is none)."""
+    global _pending
+    if _pending is not None:
+        pending, _pending = _pending, None
+        pending.wait()
+
+
+# ----------------------------------------------------------------------------------------------------------
 # Grid-independent checkpoints
 # ----------------------------------------------------------------------------------------------------------
 

@@ -146,6 +146,12 @@ class AxonnStrategyCore:
     def no_backward_sync(self, module=None, enabled: bool = True):
         return self._backward_sync_control.no_backward_sync(module, enabled)
 
+    @property
+    def process_group_backend(self):
+        """The backend given at construction (``None``: chosen from the device when the process group is created;
+        reference ``axonn/lightning/axonn_strategy.py:116-118``)."""
+        return self._process_group_backend
+
     def get_timers(self):
         assert self.enable_timers, "create the strategy with enable_timers=True"
         return ax.get_timers()

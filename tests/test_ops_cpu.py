@@ -1,5 +1,8 @@
 """CPU fallbacks of the small ops and the host-side status helpers (no GPU, no process group)."""
 
+import os
+
+import pytest
 import torch
 
 from axonn_b200 import ops
@@ -130,3 +133,37 @@ def test_cpu_adam_state_dict_roundtrip_keeps_step_count_and_host_state():
         return p.detach().clone()
 
     assert torch.equal(run(), run(resume_after=2))
+
+
+def test_background_checkpoint_holds_the_values_of_the_call(tmp_path):
+    """``save_async`` snapshots first and writes later: parameters changed right after the call do not leak into
+    the file, a second call waits for the first, and a failing write surfaces in ``wait()``."""
+    from axonn_b200 import checkpoint, config
+
+    config.reset()
+    model = torch.nn.Linear(64, 64)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    model(torch.randn(4, 64)).sum().backward()
+    opt.step()
+    want = {k: v.clone() for k, v in model.state_dict().items()}
+    state = {"model": model.state_dict(), "optimizer": opt.state_dict(), "step": 7}
+    pending = checkpoint.save_async(state, str(tmp_path), "a")
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(1.0)                                   # the training loop goes on
+    second = checkpoint.save_async({"model": model.state_dict(), "step": 8}, str(tmp_path), "b")
+    assert pending.done()                                 # the second call waited for the first
+    checkpoint.wait_for_pending_save()
+    assert second.done() and second.wait() == checkpoint.checkpoint_path(str(tmp_path), "b")
+    a = checkpoint.load(None, str(tmp_path), "a")
+    b = checkpoint.load(None, str(tmp_path), "b")
+    assert a["step"] == 7 and b["step"] == 8
+    for k, v in want.items():
+        assert torch.equal(a["model"][k], v) and torch.equal(b["model"][k], v + 1.0)
+    assert torch.equal(a["optimizer"]["state"][0]["momentum_buffer"], opt.state_dict()["state"][0]["momentum_buffer"])
+    with pytest.raises(ValueError):
+        checkpoint.save_async(state, str(tmp_path), "a", overwrite=False)
+    bad = checkpoint.save_async({"f": lambda: 0}, str(tmp_path), "c")     # not picklable: the writer thread fails
+    with pytest.raises(Exception):
+        bad.wait()
+    assert not os.path.exists(checkpoint.checkpoint_path(str(tmp_path), "c"))
