@@ -135,6 +135,7 @@ def create_dataloader(
 
 
 def get_timers() -> Timers:
+    """The timers created by ``init(enable_internal_timers=True)`` (a no-op object otherwise)."""
     global timers
     if timers is None:
         timers = _NullTimers()

@@ -27,6 +27,7 @@ from . import config
 
 
 def get_prefix_for_checkpoint() -> str:
+    """``tp_row_R_col_C_depth_D`` of this rank (``_inter_K`` appended when pipelining)."""
     prefix = (
         f"tp_row_{config.intra_layer_row_parallel_rank}"
         f"_col_{config.intra_layer_column_parallel_rank}"
@@ -38,6 +39,7 @@ def get_prefix_for_checkpoint() -> str:
 
 
 def checkpoint_path(checkpoint_folder: str, checkpoint_name: str) -> str:
+    """``<folder>/<prefix of this rank>/<name>.pt``."""
     return os.path.join(checkpoint_folder, get_prefix_for_checkpoint(), f"{checkpoint_name}.pt")
 
 

@@ -33,6 +33,9 @@ import torch.distributed as dist
 
 @dataclass(frozen=True)
 class GridCoords:
+    """Coordinates of one rank in the (data, pipeline, depth, row, column) grid; ``intra`` is its index inside
+    its tensor-parallel group."""
+
     data: int
     inter: int
     intra: int
@@ -58,6 +61,7 @@ def coords_of(world_rank: int, G_inter: int, G_data: int, r: int, c: int, d: int
 
 def rank_of(data: int, inter: int, depth: int, row: int, col: int,
             G_inter: int, G_data: int, r: int, c: int, d: int) -> int:
+    """Inverse of :func:`coords_of`: the world rank at the given grid coordinates."""
     G_intra = r * c * d
     return data * G_inter * G_intra + inter * G_intra + depth * r * c + row * c + col
 

@@ -96,6 +96,15 @@ class _Request:
 
 
 class AxoNN_Inter_Layer_Engine:
+    """Pipeline training step over ``G_inter`` stages (reference ``axonn/inter_layer.py:40-460``).
+
+    ``model`` is this stage's part of the network with ``get_input_shape()`` / ``get_output_shape()`` (``-1`` for
+    the microbatch dimension); ``forward_backward_optimizer(batch, labels, optimizer)`` splits the batch into
+    microbatches of ``config.micro_batch_size``, runs them through the stages with activations and gradients
+    travelling over point-to-point messages, reduces gradients over the data-parallel group, handles fp16 loss
+    scaling and steps the optimizer.  A stage that hears nothing from a neighbour for ``timeout_s`` raises
+    ``PipelineTimeout``."""
+
     def __init__(self, model, loss_fn, computation_dtype=torch.bfloat16, timeout_s: float = 600.0):
         assert ax.is_initialized, "call axonn_b200.axonn.init(...) before creating the engine"
         self.model, self.criterion = model, loss_fn

@@ -101,6 +101,8 @@ sync_gradients_depth_parallel = sync_gradients_expert_mode_depth_parallel
 
 @torch.no_grad()
 def sync_gradients_expert_mode_data_parallel(model, gradient_attr_name="grad", mean=False, vectorize=False):
+    """Data-parallel reduction of every gradient except those of expert-parallel parameters (whose data-parallel
+    ranks hold different experts); ``mean`` divides by the data-parallel size."""
     if NO_GRADIENT_SYNC:
         return
     group = ax.comm_handle.data_parallel_group

@@ -21,6 +21,7 @@ _original_embedding = nn.Embedding
 
 
 def is_parallelizable_linear(in_features, out_features):
+    """``out`` divisible by the row size, ``in`` by the column size, and the local block by the depth size."""
     c = ax.config
     return (out_features % c.G_intra_r == 0 and in_features % c.G_intra_c == 0
             and (out_features * in_features // (c.G_intra_r * c.G_intra_c)) % c.G_intra_d == 0)
@@ -60,6 +61,10 @@ class patched_embedding:
 
 @contextmanager
 def auto_parallelize(embeddings=False):
+    """Context manager under which ``torch.nn.Linear(...)`` builds a tensor-parallel ``Linear`` (easy mode)
+    whenever the shape divides the grid (:func:`is_parallelizable_linear`), and the plain layer otherwise;
+    ``embeddings=True`` does the same for ``torch.nn.Embedding``.  ``device`` and ``dtype`` arguments are applied
+    to the new layer (reference ``axonn/intra_layer/automatic_parallelism.py:15-96``)."""
     nn.Linear = patched_linear
     if embeddings:
         nn.Embedding = patched_embedding

@@ -47,6 +47,10 @@ def default_init_method(weight):
 
 
 class Conv2d(torch.nn.Module):
+    """Drop-in ``nn.Conv2d`` (square kernels) whose filter bank is sharded over the 3-D grid: output channels over
+    the outer group, input channels over the inner group, the flattened block over the depth group.
+    ``forward(x, scatter_input=True, gather_output=True)`` takes and returns full tensors by default."""
+
     def __init__(self, in_channels, out_channels, kernel_size, *args, transpose=False, bias=True,
                  skip_bias_add=False, init_method=None, stride=1, padding=0, dilation=1, groups=1,
                  dtype=None, **kwargs):

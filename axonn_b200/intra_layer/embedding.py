@@ -66,6 +66,11 @@ class _EmbeddingRowsP2P(torch.autograd.Function):
 
 
 class Embedding(torch.nn.Module):
+    """Drop-in ``nn.Embedding`` whose table is split along the embedding dimension over one tensor-parallel group
+    (the outer group, or the inner one with ``transpose=True``) and flat-sharded over the depth group.  On GPUs
+    with a depth group the needed rows are fetched from the owning ranks over peer memory instead of gathering
+    the table (reference ``axonn/intra_layer/embedding.py:57-222``)."""
+
     def __init__(self, num_embeddings, embedding_dim, padding_idx=None, max_norm=None, norm_type=2.0,
                  scale_grad_by_freq=False, sparse=False, _weight=None, _freeze=False, *args,
                  transpose=False, init_method=None, expert_mode=False, dtype=None, **kwargs):

@@ -31,6 +31,11 @@ def _local_norm_pow(grads, norm_type):
 
 
 def clip_grad_norm_(parameters, max_norm, norm_type=2.0, error_if_nonfinite=False):
+    """``torch.nn.utils.clip_grad_norm_`` for sharded parameters: the local norms of tensor-parallel parameters
+    are reduced over ``param.process_group_for_norm_reduction`` (replicas counted once), combined with the norm
+    of the replicated parameters, and every gradient is scaled by ``min(1, max_norm / (total + 1e-6))``.  Any
+    ``norm_type`` > 0 including ``inf``; returns the total norm (reference
+    ``axonn/intra_layer/gradient_normalization.py:18-95``, which has no ``inf`` norm)."""
     if isinstance(parameters, torch.Tensor):
         parameters = [parameters]
     parameters = list(parameters)

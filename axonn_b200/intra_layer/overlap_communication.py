@@ -74,6 +74,7 @@ def accumulate():
 
 
 def clear_weights_cache():
+    """Drop the all-gathered weights kept by ``cache_weights`` / the prefetcher."""
     global weights_cache
     weights_cache = {}
 

@@ -103,6 +103,8 @@ COMM_KERNEL_PATTERNS = ("nccl", "allreduce_twoshot", "grad_allreduce", "bucket_c
 
 
 def is_comm_kernel(name: str) -> bool:
+    """True for kernels whose time counts as communication in the exposed-communication figure (NCCL kernels
+    and this package's stand-alone peer-memory collectives)."""
     low = name.lower()
     return any(p in low for p in COMM_KERNEL_PATTERNS)
 

@@ -149,6 +149,8 @@ class ParallelMLP(nn.Module):
 
 
 class TransformerBlock(nn.Module):
+    """Pre-norm block: ``x + attn(norm1(x))`` then ``+ mlp(norm2(.))``, LayerNorm or RMSNorm, GELU or SwiGLU."""
+
     def __init__(self, hidden, n_heads, ffn, n_kv_heads=None, activation="gelu", rms=False, bias=True,
                  rope_theta=None, max_seq=4096, eps=1e-5, dtype=None, n_layers=1):
         super().__init__()

@@ -19,6 +19,8 @@ from .blocks import ParallelLMHead, TPNorm, TransformerBlock, count_parameters
 
 @dataclass
 class GPTConfig:
+    """Shape of a GPT-style model; ``gpt_1p3b()`` is the benchmark configuration, ``tiny()`` the test one."""
+
     n_layers: int = 24
     hidden: int = 2048
     n_heads: int = 16
@@ -45,6 +47,10 @@ class GPTConfig:
 
 
 class GPT(nn.Module):
+    """Decoder-only transformer with learned positions, LayerNorm and GELU feed-forward layers on the
+    tensor-parallel building blocks; ``forward(tokens, targets)`` returns the loss, ``forward(tokens)`` the
+    (vocabulary-sharded) logits."""
+
     def __init__(self, cfg: GPTConfig, dtype=torch.bfloat16):
         super().__init__()
         self.cfg = cfg

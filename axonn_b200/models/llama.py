@@ -19,6 +19,8 @@ from .blocks import ParallelLMHead, TPNorm, TransformerBlock, count_parameters
 
 @dataclass
 class LlamaConfig:
+    """Shape of a Llama-style model; ``llama_8b()`` is the benchmark configuration, ``tiny()`` the test one."""
+
     n_layers: int = 32
     hidden: int = 4096
     n_heads: int = 32
@@ -46,6 +48,10 @@ class LlamaConfig:
 
 
 class Llama(nn.Module):
+    """Decoder-only transformer with RMSNorm, rotary grouped-query attention and SwiGLU feed-forward layers on the
+    tensor-parallel building blocks; ``forward(tokens, targets)`` returns the loss, ``forward(tokens)`` the
+    (vocabulary-sharded) logits."""
+
     def __init__(self, cfg: LlamaConfig, dtype=torch.bfloat16):
         super().__init__()
         self.cfg = cfg

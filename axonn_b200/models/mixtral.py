@@ -23,6 +23,8 @@ from .blocks import ParallelLMHead, TPNorm, TransformerBlock, count_parameters
 
 @dataclass
 class MixtralConfig:
+    """Shape of a Mixtral-style model; ``mixtral_16l()`` is the benchmark configuration, ``tiny()`` the test one."""
+
     n_layers: int = 16
     hidden: int = 4096
     n_heads: int = 32
@@ -69,6 +71,10 @@ class MoEBlock(TransformerBlock):
 
 
 class Mixtral(nn.Module):
+    """Decoder-only transformer with RMSNorm, rotary grouped-query attention and an ``ExpertParallelMoE``
+    feed-forward in every block; ``forward(tokens, targets)`` returns the loss including the routers' auxiliary
+    loss, ``forward(tokens)`` the (vocabulary-sharded) logits."""
+
     def __init__(self, cfg: MixtralConfig, dtype=torch.bfloat16):
         super().__init__()
         self.cfg = cfg

@@ -67,6 +67,9 @@ def partition(flops, stages):
 
 
 class DistributedVGG16(nn.Module):
+    """One pipeline stage of VGG-16: the network's units (convolution blocks, classifier layers) are dealt to the
+    ``G_inter`` stages so that their forward FLOPs balance; same stage contract as ``DistributedViT``."""
+
     def __init__(self, image_size=224, num_classes=1000, channels=3, G_inter=None, stage=None):
         super().__init__()
         G_inter = ax.config.G_inter if G_inter is None else G_inter

@@ -33,6 +33,11 @@ class _EncoderLayer(nn.Module):
 
 
 class DistributedViT(nn.Module):
+    """One pipeline stage of a vision transformer: ``depth // G_inter`` encoder layers; the first stage also owns
+    patch embedding, class token and positions, the last one the classification head.  ``get_input_shape()`` /
+    ``get_output_shape()`` give the engine the shapes of the tensors that travel between stages (``-1`` = the
+    microbatch dimension) - the contract of the upstream ``external/models/vit.py:121-217``."""
+
     def __init__(self, *, image_size, patch_size, num_classes, dim, depth, heads, mlp_dim, channels=3,
                  dropout=0.0, G_inter=None, stage=None):
         super().__init__()

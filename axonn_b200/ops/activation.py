@@ -70,6 +70,7 @@ def gelu_backward(dy, x):
 
 
 def gelu(x):
+    """GELU (tanh form) with its backward as one kernel each."""
     return _GeluFn.apply(x)
 
 
@@ -124,4 +125,6 @@ def _split_gu(gu):
 
 
 def swiglu(gu):
+    """``silu(gate) * up`` of a fused ``[..., 2 * ffn]`` projection whose gate and up columns alternate in blocks
+    of 8 (the layout the fused gate|up weight of ``ParallelMLP`` produces); returns ``[..., ffn]``."""
     return _SwiGLUFn.apply(gu)

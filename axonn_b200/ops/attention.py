@@ -27,6 +27,9 @@ def _sdpa(q, k, v, causal, scale):
 
 
 def flash_attention(q, k, v, causal=True, scale=None):
+    """Attention of ``q [B, S, heads, D]`` against ``k, v [B, S, kv_heads, D]`` (grouped-query when ``kv_heads <
+    heads``) on the package's tcgen05 kernels (CUDA, D 64 or 128, S a multiple of 128) or through
+    ``scaled_dot_product_attention`` otherwise; returns ``[B, S, heads, D]``."""
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if q.is_cuda and not _IMPL["force_torch"]:
@@ -42,6 +45,8 @@ def flash_attention(q, k, v, causal=True, scale=None):
 
 
 def flash_attention_packed(qkv, causal=True, scale=None):
+    """Attention on the packed projection output ``[B, S, kv_groups, q_per_kv + 2, D]`` (per KV group: its query
+    heads, then K, then V) without splitting it into three tensors; returns ``[B, S, kv_groups * q_per_kv, D]``."""
     B, S, G, n, D = qkv.shape
     qpk = n - 2
     if scale is None:

@@ -242,6 +242,8 @@ def layer_norm(x, gamma, beta, eps=1e-5, group=None):
 
 
 def rms_norm(x, gamma, eps=1e-6, group=None):
+    """RMSNorm over the last dimension; with ``group`` the last dimension is one shard of a hidden dimension
+    split over that process group."""
     return _NormFn.apply(x, gamma, None, eps, True, group)
 
 

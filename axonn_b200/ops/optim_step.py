@@ -29,6 +29,9 @@ class AdamTable:
 
 
 def multi_tensor_adamw(table, lr, beta1, beta2, eps, weight_decay, step, grad_scale=None, found_inf=None):
+    """One AdamW step for every tensor of ``table`` (an ``AdamTable``) in a single launch: fp32 master and
+    moments updated, the 16-bit model copy written in the same pass; ``grad_scale`` (0-d device tensor) multiplies
+    the gradients, a non-zero ``found_inf`` skips the update."""
     bc1 = 1.0 - beta1 ** step
     bc2 = 1.0 - beta2 ** step
     st = _lib.lib().axb_multi_adamw(

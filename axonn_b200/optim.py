@@ -24,6 +24,11 @@ from .ops import _lib, multi_tensor as _mt
 
 
 class FusedAdamW(torch.optim.Optimizer):
+    """AdamW whose whole step is one multi-tensor kernel per parameter group: fp32 master weights (for 16-bit
+    parameters; ``master_weights`` forces either way) and fp32 moments are updated and the 16-bit model copy is
+    written in the same pass.  ``grad_scale`` / ``found_inf`` (0-d device tensors) unscale the gradients and skip
+    the update without a host synchronisation.  On CPU the same arithmetic runs in PyTorch."""
+
     def __init__(self, params: Iterable, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
                  master_weights: Optional[bool] = None):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)

@@ -76,6 +76,13 @@ def route_top_k(logits, top_k, capacity):
 
 
 class ExpertParallelMoE(nn.Module):
+    """Mixture-of-experts feed-forward layer with whole experts placed on the ranks of ``ep_group`` (default: the
+    data-parallel group): top-``top_k`` routing with a per-expert capacity of ``capacity_factor * tokens * top_k /
+    n_experts`` rows, dispatch of the routed rows to the experts' ranks, SwiGLU experts as two batched GEMMs over
+    all local experts, combine weighted by the gate values.  After a forward, ``last_aux_loss`` (load-balancing
+    loss), ``last_drop_fraction``, ``last_assignments_per_expert`` and ``last_dropped_per_expert`` describe the
+    routing (device tensors, no host synchronisation)."""
+
     def __init__(self, hidden, ffn, n_experts=8, top_k=2, capacity_factor=1.25, ep_group=None, dtype=None,
                  init_std=0.02, out_init_std=None):
         super().__init__()

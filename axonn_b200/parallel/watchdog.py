@@ -26,6 +26,9 @@ class RankFailure(RuntimeError):
 
 
 class Watchdog:
+    """Heartbeat thread of one rank: ``start()``, then ``check()`` at step boundaries (raises ``RankFailure`` naming
+    the silent rank), ``stop()`` at the end.  ``store`` defaults to the default process group's store."""
+
     def __init__(self, store=None, rank: Optional[int] = None, world_size: Optional[int] = None,
                  interval_s: float = 0.5, timeout_s: float = 10.0,
                  on_failure: Optional[Callable[[int, float], None]] = None, prefix: str = "axonn_hb"):

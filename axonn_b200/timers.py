@@ -27,6 +27,11 @@ class _CpuStamp:
 
 
 class Timers:
+    """Nested region timers (reference ``axonn/timers.py:7-46``): ``start(key)`` / ``stop(key)`` pairs may nest,
+    and a region is accounted under the tuple of all keys open at that moment, so the same inner key under two
+    different parents gives two series.  Times come from CUDA events on GPUs (no host synchronisation until
+    ``get_times``) and from ``perf_counter`` on CPU; every region is also an NVTX range."""
+
     def __init__(self, enabled=True, use_cuda=None, nvtx=True):
         self.enabled = enabled
         self.use_cuda = torch.cuda.is_available() if use_cuda is None else use_cuda

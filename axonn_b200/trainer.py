@@ -26,6 +26,11 @@ from .intra_layer import (clip_grad_norm_, no_grad_sync, optimize_communication,
 
 
 class Trainer:
+    """One optimizer step per call for models without pipelining: ``train_step(tokens, targets)`` (host tensors in,
+    loss as a float out) and ``train_step_device`` (device tensors, loss stays on the device).  Microbatches of
+    ``micro_batch_size``, communication overlap, optional top-k gradient pruning (``prune_keep_fraction``),
+    gradient synchronisation, clipping at ``clip_grad`` and the optimizer step."""
+
     def __init__(self, model, optimizer, micro_batch_size: Optional[int] = None, clip_grad: float = 0.0,
                  prune_keep_fraction: Optional[float] = None, overlap: bool = True,
                  loss_fn: Optional[Callable] = None, expert_mode: bool = True,
@@ -120,10 +125,12 @@ def replica_index() -> int:
 
 
 def num_replicas() -> int:
+    """Number of different data shards per step: data-parallel size x depth size."""
     return ax.config.G_data * ax.config.G_intra_d
 
 
 def all_reduce_max(value: float, device) -> float:
+    """Maximum of a host value over all ranks (how multi-GPU timings are reported)."""
     t = torch.tensor([value], dtype=torch.float64, device=device)
     if dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
