@@ -48,3 +48,45 @@ def test_tensor_parallel_tutorial_continues_on_another_grid(tmp_path):
 def test_pipelined_vit_tutorial_converges():
     out = _torchrun(4, 29713, "train_vit_pipeline.py", env={"G_inter": "2", "G_data": "2"})
     assert out["steps"] == 32 and out["final_loss"] < 0.1 < out["first_loss"]
+
+
+def test_language_model_example_learns_a_text_file(tmp_path):
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("the quick brown fox jumps over the lazy dog. pack my box with five dozen liquor jugs. " * 300)
+    out = _torchrun(4, 29714, "train_lm.py", "--G-intra-r", "2", "--G-intra-d", "2", "--data", str(corpus), "--steps",
+                    "30", "--seq-len", "64")
+    assert out["vocab"] == 256 and out["steps"] == 30 and out["last_loss"] < 0.3 * out["first_loss"]
+
+
+def test_token_windows():
+    import numpy as np
+    import torch
+
+    from axonn_b200.utils.data import TokenWindows, load_tokens
+
+    stream = np.arange(103, dtype=np.int64)
+    ds = TokenWindows(stream, seq_len=10)
+    assert len(ds) == 10                                    # windows of 11 tokens starting every 10
+    x, y = ds[9]
+    assert x.tolist() == list(range(90, 100)) and y.tolist() == list(range(91, 101)) and x.dtype == torch.long
+    assert len(TokenWindows(stream, seq_len=10, stride=1)) == 93
+    with pytest.raises(ValueError):
+        TokenWindows(stream, seq_len=10, vocab=100)         # id 102 does not fit
+    with pytest.raises(ValueError):
+        TokenWindows(stream[:5], seq_len=10)
+    with pytest.raises(IndexError):
+        ds[10]
+
+
+def test_load_tokens_formats(tmp_path):
+    import numpy as np
+
+    from axonn_b200.utils.data import load_tokens
+
+    ids = np.array([1, 500, 65535, 7], dtype=np.uint16)
+    ids.tofile(tmp_path / "a.bin")
+    np.save(tmp_path / "a.npy", ids.astype(np.int32).reshape(2, 2))
+    (tmp_path / "a.txt").write_bytes(b"abc")
+    assert load_tokens(str(tmp_path / "a.bin")).tolist() == ids.tolist()
+    assert load_tokens(str(tmp_path / "a.npy")).tolist() == ids.tolist()
+    assert load_tokens(str(tmp_path / "a.txt")).tolist() == [97, 98, 99]
