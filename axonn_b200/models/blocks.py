@@ -106,6 +106,7 @@ class ParallelAttention(nn.Module):
         self.q_per_kv = divide(n_heads, n_kv_heads)
         self.groups_l = divide(n_kv_heads, r)
         self.rope_theta, self.max_seq = rope_theta, max_seq
+        self.sequence_group = None     # set by parallel.sequence.enable_sequence_parallel
         qkv_out = (n_heads + 2 * n_kv_heads) * self.head_dim
         self.qkv = Linear(hidden, qkv_out, bias=bias, expert_mode=True, dtype=dtype,
                           init_method=lambda w: nn.init.normal_(w, std=init_std))
@@ -116,14 +117,27 @@ class ParallelAttention(nn.Module):
         B, S, _ = x.shape
         D, G, qpk = self.head_dim, self.groups_l, self.q_per_kv
         qkv = self.qkv(x).view(B, S, G, qpk + 2, D)
-        if self.rope_theta is not None:
-            table = ops.rope_table(max(S, self.max_seq), D, self.rope_theta, x.device)
-            if x.is_cuda:
-                ops.apply_rope(qkv[:, :, :, :qpk + 1], table)  # q heads and the k head, in place
-            else:
-                qkv = torch.cat([ops.apply_rope(qkv[:, :, :, :qpk + 1], table), qkv[:, :, :, qpk + 1:]], 3)
-        o = ops.flash_attention_packed(qkv, causal=True)  # [B, S, G * qpk, D]
+        if self.sequence_group is not None:
+            # x holds a slice of every sequence: trade it for whole sequences of a share of the heads, attend,
+            # trade back (rotary embedding in between, on whole sequences)
+            from ..parallel.sequence import ulysses_attention_packed
+
+            o = ulysses_attention_packed(qkv, self.sequence_group, self._rope if self.rope_theta is not None else None)
+        else:
+            if self.rope_theta is not None:
+                qkv = self._rope(qkv)
+            o = ops.flash_attention_packed(qkv, causal=True)  # [B, S, G * qpk, D]
         return self.proj(o.reshape(B, S, G * qpk * D))
+
+    def _rope(self, qkv):
+        """Rotary embedding of the query heads and the key head of every group of ``[B, S, groups, q_per_kv + 2, D]``
+        (positions 0 .. S-1)."""
+        S, qpk, D = qkv.shape[1], self.q_per_kv, self.head_dim
+        table = ops.rope_table(max(S, self.max_seq), D, self.rope_theta, qkv.device)
+        if qkv.is_cuda:
+            ops.apply_rope(qkv[:, :, :, :qpk + 1], table)  # in place
+            return qkv
+        return torch.cat([ops.apply_rope(qkv[:, :, :, :qpk + 1], table), qkv[:, :, :, qpk + 1:]], 3)
 
 
 class ParallelMLP(nn.Module):

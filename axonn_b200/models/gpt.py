@@ -9,6 +9,7 @@ Own model definition standing in for ``external/models/nvidia_transformer.py``
 from dataclasses import dataclass
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 from torch.utils.checkpoint import checkpoint
 
@@ -65,10 +66,13 @@ class GPT(nn.Module):
             for _ in range(cfg.n_layers)])
         self.norm_f = TPNorm(cfg.hidden, dtype=dtype)
         self.head = ParallelLMHead(cfg.hidden, cfg.vocab, dtype=dtype)
+        self.sequence_group = None     # set by parallel.sequence.enable_sequence_parallel
 
     def forward(self, tokens, targets=None):
         B, S = tokens.shape
         pos = torch.arange(S, device=tokens.device)
+        if self.sequence_group is not None:
+            pos = pos + dist.get_rank(self.sequence_group) * S      # this rank's slice of the positions
         x = self.tok_emb(tokens) + self.pos_emb(pos)[None]
         delta = None   # MLP output of the previous block, added to x inside the next norm kernel
         for blk in self.blocks:
