@@ -112,3 +112,41 @@ def test_resume_from_sharded_checkpoint_reproduces_loss(tmp_path):
     for world, grid in ((2, "1_1_2"), (2, "1_2_1"), (2, "1_1_1"), (1, "1_1_1"), (4, "2_1_2")):
         other = run_distributed(_ckpt_resume, world, folder, "resume_grid_" + grid)[0]
         assert other == pytest.approx(full[2:], rel=2e-4), (world, grid)
+
+
+def _pipeline_consolidated(rank, world, folder):
+    """Two pipeline stages x two data-parallel replicas: one consolidated file per stage, written by replica 0."""
+    import torch
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200 import checkpoint
+    from axonn_b200.models import DistributedViT
+
+    ax.init(G_inter=2, G_data=2)
+    torch.manual_seed(11 + ax.config.inter_layer_parallel_rank)
+    model = DistributedViT(image_size=8, patch_size=4, num_classes=4, dim=16, depth=2, heads=2, mlp_dim=32, channels=1)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    for p in model.parameters():
+        p.grad = torch.ones_like(p)
+    opt.step()
+    path = checkpoint.save_consolidated(model, opt, folder, "pp", extra={"stage": ax.config.inter_layer_parallel_rank})
+    assert (path is not None) == (ax.config.data_parallel_rank == 0)
+    want = {k: v.clone() for k, v in model.state_dict().items()}
+    with torch.no_grad():
+        for p in model.parameters():
+            p.zero_()
+    opt2 = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    import torch.distributed as dist
+
+    dist.barrier()
+    extra = checkpoint.load_consolidated(model, opt2, folder, "pp")
+    assert extra == {"stage": ax.config.inter_layer_parallel_rank}
+    assert all(torch.equal(v, model.state_dict()[k]) for k, v in want.items())
+    p0 = next(iter(model.parameters()))
+    assert torch.equal(opt2.state[p0]["momentum_buffer"], torch.ones_like(p0))
+    return sorted(os.listdir(folder))
+
+
+def test_consolidated_checkpoint_has_one_file_per_pipeline_stage(tmp_path):
+    out = run_distributed(_pipeline_consolidated, 4, str(tmp_path))
+    assert all(files == ["pp.full.inter_0.pt", "pp.full.inter_1.pt"] for files in out)
