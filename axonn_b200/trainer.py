@@ -116,6 +116,49 @@ class Trainer:
             symm.verify_canaries()
         return value
 
+    # ------------------------------------------------------------------ a whole run, restartable
+    def fit(self, batches, steps: int, checkpoint_folder: Optional[str] = None, checkpoint_every: int = 0,
+            resume: bool = True, watchdog=None, on_step: Optional[Callable] = None):
+        """Run optimizer steps ``first .. steps - 1`` over ``batches`` and return ``{step: loss}``.
+
+        ``batches(step)`` returns the ``(inputs, targets)`` of this rank for a step (a function of the step
+        number, so that a restarted run sees the data the first run would have seen).  With ``checkpoint_folder``
+        a grid-independent checkpoint is written every ``checkpoint_every`` steps (``checkpoint.save_consolidated``)
+        and the name of the newest complete one is recorded in ``<folder>/latest``; with ``resume`` a run that
+        finds such a record continues from it - on the same grid or on another one.  ``watchdog`` (a started
+        ``parallel.watchdog.Watchdog``) is checked at every step boundary, so a silent peer ends the run with
+        ``RankFailure`` instead of a blocked collective.  ``on_step(step, loss)`` is called after every step.
+
+        The reference leaves all of this to the user's script; it has no restart logic."""
+        from . import checkpoint
+
+        first = 0
+        marker = os.path.join(checkpoint_folder, "latest") if checkpoint_folder else None
+        if marker and resume and os.path.exists(marker):
+            with open(marker) as f:
+                name = f.read().strip()
+            first = int(checkpoint.load_consolidated(self.model, self.optimizer, checkpoint_folder, name)["step"])
+        losses = {}
+        for step in range(first, steps):
+            if watchdog is not None:
+                watchdog.check()
+            inputs, targets = batches(step)
+            losses[step] = self.train_step(inputs, targets)
+            if on_step is not None:
+                on_step(step, losses[step])
+            done = step + 1
+            if marker and checkpoint_every and done % checkpoint_every == 0:
+                name = f"step{done}"
+                checkpoint.save_consolidated(self.model, self.optimizer, checkpoint_folder, name, extra={"step": done})
+                if dist.is_initialized():
+                    dist.barrier()                      # every stage's file is complete before the record moves
+                if not dist.is_initialized() or dist.get_rank() == 0:
+                    tmp = marker + f".tmp.{os.getpid()}"
+                    with open(tmp, "w") as f:
+                        f.write(name)
+                    os.replace(tmp, marker)
+        return losses
+
 
 def replica_index() -> int:
     """Index of this rank's data shard: ranks that differ only in row/column

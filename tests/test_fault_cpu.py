@@ -150,3 +150,59 @@ def _pipeline_consolidated(rank, world, folder):
 def test_consolidated_checkpoint_has_one_file_per_pipeline_stage(tmp_path):
     out = run_distributed(_pipeline_consolidated, 4, str(tmp_path))
     assert all(files == ["pp.full.inter_0.pt", "pp.full.inter_1.pt"] for files in out)
+
+
+class _Crash(RuntimeError):
+    pass
+
+
+def _fit(rank, world, folder, grid, steps, crash_at):
+    from axonn_b200 import axonn as ax
+    from axonn_b200.models import GPT, GPTConfig
+    from axonn_b200.optim import FusedAdamW
+    from axonn_b200.trainer import Trainer, num_replicas, replica_index
+
+    r, c, d = grid
+    ax.init(G_inter=1, G_data=world // (r * c * d), G_intra_r=r, G_intra_c=c, G_intra_d=d)
+    torch.manual_seed(3)
+    cfg = GPTConfig.tiny()
+    model = GPT(cfg, dtype=torch.float32)
+    tr = Trainer(model, FusedAdamW(model.parameters(), lr=1e-3, weight_decay=0.0))
+
+    def batches(step):                      # a function of the step: global batch of 4, this replica's share
+        g = torch.Generator().manual_seed(100 + step)
+        data = torch.randint(0, cfg.vocab, (4, cfg.seq_len + 1), generator=g)
+        per = 4 // num_replicas()
+        mine = data[replica_index() * per:(replica_index() + 1) * per]
+        return mine[:, :-1].contiguous(), mine[:, 1:].contiguous()
+
+    def on_step(step, loss):
+        if step == crash_at:
+            raise _Crash(f"injected at step {step}")
+
+    try:
+        losses = tr.fit(batches, steps, checkpoint_folder=folder, checkpoint_every=2, on_step=on_step)
+    except _Crash:
+        return "crashed"
+    import torch.distributed as dist
+
+    out = {}
+    for step, v in losses.items():          # replicas saw different samples: the global loss is their mean
+        t = torch.tensor(v, dtype=torch.float64)
+        dist.all_reduce(t)
+        out[step] = float(t) / world
+    return out
+
+
+def test_fit_restarts_from_its_last_checkpoint_on_another_grid(tmp_path):
+    """A run that dies after step 4 (checkpoints after steps 2 and 4) is started again on a different grid and
+    finishes with the losses of a run that never stopped."""
+    whole = run_distributed(_fit, 2, str(tmp_path / "a"), (2, 1, 1), 7, None)[0]
+    assert sorted(whole) == list(range(7))
+    folder = str(tmp_path / "b")
+    assert run_distributed(_fit, 2, folder, (2, 1, 1), 7, 4) == ["crashed", "crashed"]
+    assert open(os.path.join(folder, "latest")).read() == "step4"
+    rest = run_distributed(_fit, 2, folder, (1, 1, 2), 7, None)[0]
+    assert sorted(rest) == [4, 5, 6]
+    for step in rest:
+        assert rest[step] == pytest.approx(whole[step], rel=2e-4)
