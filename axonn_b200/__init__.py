@@ -14,9 +14,11 @@ __version__ = "0.1.0"
 import os as _os
 
 # A pipeline stage keeps several blocking NCCL point-to-point kernels in flight (one communicator per neighbour and
-# direction) next to its compute stream.  With the default of 8 hardware work queues per device, two of those streams
-# can share a queue, and a send that sits behind a receive which is still waiting for its peer never starts: with four
-# stages the middle ranks deadlocked that way.  Ask for the maximum number of queues before the CUDA context exists.
+# direction) next to its compute stream.  With the default of 8 hardware work queues per device two of those streams
+# can share a queue, and a send queued behind a receive that still waits for its peer cannot start.  Asking for the
+# maximum number of queues (before the CUDA context exists) makes such false dependencies less likely; it did not by
+# itself cure the stall of the message-driven schedule on four NCCL stages, which is why the pipeline engine also
+# posts its receives in a fixed order there.
 _os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
 
 from . import config  # noqa: F401

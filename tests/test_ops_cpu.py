@@ -167,3 +167,46 @@ def test_background_checkpoint_holds_the_values_of_the_call(tmp_path):
     with pytest.raises(Exception):
         bad.wait()
     assert not os.path.exists(checkpoint.checkpoint_path(str(tmp_path), "c"))
+
+
+def test_upstream_import_names_resolve_after_the_alias_is_installed():
+    """A script written against the upstream package's module names runs unchanged (child process: the alias
+    changes ``sys.modules``)."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = r"""
+import sys
+sys.path.insert(0, %r)
+import axonn_b200.compat
+axonn_b200.compat.install_as_axonn()
+axonn_b200.compat.install_as_axonn()          # idempotent
+from axonn import axonn as ax
+import axonn.config as config
+from axonn.intra_layer import (Linear, Conv2d, Embedding, Drop, Gather, clip_grad_norm_, auto_parallelize,
+                               optimize_communication, overlap_all_gathers_for_checkpointed_forward, no_grad_sync,
+                               sync_gradients)
+from axonn.intra_layer.communication import ForwardAllReduce, BackwardAllReduce, ForwardGather_BackwardReduceScatter
+from axonn.intra_layer.fully_connected import extract_local_params_from_full_params
+from axonn.inter_layer import AxoNN_Inter_Layer_Engine
+from axonn.checkpoint import save, load, get_prefix_for_checkpoint
+from axonn.lightning import AxonnStrategy
+from axonn.models.transformers import parallelize
+from axonn.timers import Timers
+import axonn_b200
+assert ax is axonn_b200.axonn and Linear is axonn_b200.intra_layer.Linear and config is axonn_b200.config
+import torch, torch.distributed as dist, os
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29731")
+dist.init_process_group("gloo", rank=0, world_size=1)
+ax.init(G_inter=1, G_data=1, G_intra_r=1, G_intra_c=1, G_intra_d=1)
+with auto_parallelize():
+    net = torch.nn.Linear(8, 8)
+assert isinstance(net, Linear)
+net(torch.randn(2, 8)).sum().backward()
+sync_gradients(net)
+print("alias ok")
+""" % root
+    r = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0 and "alias ok" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
