@@ -49,3 +49,38 @@ def test_tiny_model_same_on_1_and_8_ranks(family):
         assert losses == pytest.approx(ref_losses, rel=2e-4)
         assert w == pytest.approx(ref_w, rel=1e-4)
     assert ref_losses[-1] < ref_losses[0]
+
+
+def _generate(rank, world, family, grid):
+    from axonn_b200 import axonn as ax
+    from axonn_b200.models import GPT, GPTConfig, Llama, LlamaConfig, greedy_generate, parallel_argmax
+
+    r, c, d = grid
+    ax.init(G_inter=1, G_data=world // (r * c * d), G_intra_r=r, G_intra_c=c, G_intra_d=d)
+    torch.manual_seed(4)
+    if family == "gpt":
+        model = GPT(GPTConfig(n_layers=2, hidden=64, n_heads=4, ffn=128, vocab=128, seq_len=24), dtype=torch.float32)
+    else:
+        model = Llama(LlamaConfig(n_layers=2, hidden=64, n_heads=4, n_kv_heads=2, ffn=128, vocab=128, seq_len=24),
+                      dtype=torch.float32)
+    prompt = torch.tensor([[5, 17, 99, 3], [64, 2, 2, 120]])
+    out = greedy_generate(model, prompt, 6)
+    assert out.shape == (2, 10) and torch.equal(out[:, :4], prompt) and model.training
+    # decoding stops at the sequence length of the model, and at an end-of-sequence token
+    assert greedy_generate(model, prompt, 100).shape[1] == 24
+    eos = int(out[0, 5])
+    stopped = greedy_generate(model, prompt, 6, eos_id=eos)
+    assert bool((stopped[0, 5:] == eos).all())
+    # ties go to the lowest global index, whichever rank holds it
+    group = getattr(model.head, "group", None)
+    tied = torch.zeros(3, model(prompt).shape[-1])
+    assert parallel_argmax(tied, group).tolist() == [0, 0, 0]
+    return out.tolist()
+
+
+@pytest.mark.parametrize("family", ["gpt", "llama"])
+def test_greedy_decoding_is_the_same_on_every_grid(family):
+    ref = run_distributed(_generate, 1, family, (1, 1, 1))[0]
+    for world, grid in ((2, (2, 1, 1)), (4, (2, 2, 1)), (4, (1, 2, 2))):
+        for got in run_distributed(_generate, world, family, grid):
+            assert got == ref, (grid, got, ref)
