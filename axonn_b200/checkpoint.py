@@ -113,6 +113,7 @@ def _snapshot(obj, stream):
             host = torch.empty(obj.shape, dtype=obj.dtype, device="cpu", pin_memory=True)
             with torch.cuda.stream(stream):
                 host.copy_(obj, non_blocking=True)
+            obj.record_stream(stream)      # the allocator must not hand the source to someone else before the copy ran
             return host
         return obj.detach().clone()
     if isinstance(obj, dict):
