@@ -101,3 +101,47 @@ def test_nested_timers_key_regions_by_their_parents():
     off.start("x")
     off.stop("y")                            # disabled timers accept anything
     assert off.get_times() == ({}, {})
+
+
+def test_exposed_communication_interval_arithmetic_matches_a_brute_force_timeline():
+    """Union / subtraction of kernel intervals against a per-tick timeline, on random integer intervals."""
+    import random
+
+    from axonn_b200.metrics import exposed_comm_from_intervals
+
+    rng = random.Random(7)
+    for _ in range(200):
+        kernels = []
+        for _ in range(rng.randint(0, 12)):
+            s = rng.randint(0, 60)
+            e = s + rng.randint(0, 15)                       # empty intervals occur and must not count
+            kernels.append((rng.choice(["ncclDevKernel_AllReduce", "gemm_pair_kernel", "axb::a2a_v_rows",
+                                        "fa_fwd_pingpong_kernel"]), s, e))
+        comm = [False] * 80
+        comp = [False] * 80
+        for name, s, e in kernels:
+            line = comm if ("nccl" in name.lower() or "a2a_v" in name) else comp
+            for t in range(s, e):
+                line[t] = True
+        want = (sum(c and not p for c, p in zip(comm, comp)), sum(comm), sum(comp))
+        assert exposed_comm_from_intervals(kernels) == want, kernels
+
+
+def test_step_meter_reports_throughput_and_writes_jsonl(tmp_path):
+    import json
+    import time
+
+    from axonn_b200.metrics import StepMeter
+
+    log = tmp_path / "steps.jsonl"
+    meter = StepMeter(flops_per_token=1e9, world_size=1, log_path=str(log))
+    meter.use_cuda = False                                    # host clock, whatever the machine has
+    for _ in range(3):
+        with meter.step(1000):
+            time.sleep(0.01)
+    out = meter.summary()
+    assert out["steps"] == 3 and 10.0 <= out["ms_per_step"] < 200.0
+    assert out["tokens_per_s"] == pytest.approx(3000 / (3 * out["ms_per_step"] / 1e3))
+    assert out["mfu"] == pytest.approx(1e9 * out["tokens_per_s"] / (out["mfu_peak_tflops"] * 1e12))
+    assert json.loads(log.read_text().splitlines()[-1])["steps"] == 3
+    assert meter.summary()["steps"] == 0                      # reset after reading
