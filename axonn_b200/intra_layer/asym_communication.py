@@ -101,10 +101,17 @@ def _allgatherv(tensor, rank_local_batch_sizes, process_group=None):
     out = torch.empty((sum(sizes),) + tail, dtype=tensor.dtype, device=tensor.device)
     if len(set(sizes)) == 1:
         dist.all_gather_into_tensor(out, tensor, group=process_group)
-    else:
+    elif tensor.is_cuda:
         # unequal heights: an all-to-all whose sends are all the same block
         outs = list(torch.split(out, sizes, dim=0))
         dist.all_to_all(outs, [tensor for _ in range(n)], group=process_group)
+    else:
+        # the same exchange through the single-tensor form (gloo has no list all-to-all): the block is sent once
+        # per rank out of an n-fold copy
+        m = tensor.shape[0]
+        send = tensor.unsqueeze(0).expand((n,) + tuple(tensor.shape)).reshape((n * m,) + tail)
+        dist.all_to_all_single(out, send.contiguous(), output_split_sizes=sizes, input_split_sizes=[m] * n,
+                               group=process_group)
     t.stop("allgatherv")
     return out
 

@@ -156,3 +156,47 @@ def _mlp_config1(rank, world):
 def test_mlp_config1_world2():
     a, b = run_distributed(_mlp_config1, 2)
     assert a == b
+
+
+def _fc_uneven(rank, world, grid):
+    """Easy mode with a different number of rows on every rank (the variable-size layout switches)."""
+    import torch.distributed as dist
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200.intra_layer import Linear, sync_gradients
+
+    r, c, d = grid
+    ax.init(G_inter=1, G_data=world // (r * c * d), G_intra_r=r, G_intra_c=c, G_intra_d=d)
+    torch.manual_seed(7)
+    H = 16
+    seq = torch.nn.Linear(H, 2 * H)
+    par = Linear(H, 2 * H)
+    par.load_state_dict(seq.state_dict())
+    sizes = [3 + 2 * i for i in range(world)]                 # 3, 5, 7, 9 rows
+    X = torch.randn(sum(sizes), H)
+    G = torch.randn(sum(sizes), 2 * H)
+    lo = sum(sizes[:rank])
+    x = X[lo:lo + sizes[rank]].clone().requires_grad_(True)
+    for _ in range(2):                                        # the second pass uses the cached row counts
+        x.grad = None
+        par.zero_grad()
+        y = par(x)
+        y.backward(G[lo:lo + sizes[rank]])
+    sync_gradients(par)
+    xs = X.clone().requires_grad_(True)
+    ys = seq(xs)
+    ys.backward(G)
+    assert y.shape == (sizes[rank], 2 * H)
+    assert torch.allclose(y, ys[lo:lo + sizes[rank]], atol=1e-5), (y - ys[lo:lo + sizes[rank]]).abs().max()
+    assert torch.allclose(x.grad, xs.grad[lo:lo + sizes[rank]], atol=1e-5)
+    assert torch.allclose(par.full_tensor("weight", par.weight.grad), seq.weight.grad, atol=1e-4)
+    assert torch.allclose(par.full_tensor("bias", par.bias.grad), seq.bias.grad, atol=1e-4)
+    # a rank changes its batch size: the counts are exchanged again
+    x2 = X[:sizes[rank] + 1].clone()
+    assert torch.allclose(par(x2), seq(x2), atol=1e-5)
+    return True
+
+
+@pytest.mark.parametrize("grid", [(2, 2, 1), (2, 1, 2), (1, 2, 2), (4, 1, 1)])
+def test_fc_easy_mode_with_uneven_batches(grid):
+    assert all(run_distributed(_fc_uneven, 4, grid))
