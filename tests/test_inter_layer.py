@@ -156,3 +156,47 @@ def test_gpt_pipeline_stages_match_single_stage():
     two = run_distributed(_gpt_run, 2, 2, 3)[0]
     assert ref[-1] < ref[0]
     assert all(abs(a - b) < 1e-4 for a, b in zip(ref, two)), (ref, two)
+
+
+def _fp16_scaling(rank, world):
+    """fp16 through the pipeline with dynamic loss scaling: an overflowing batch skips the optimizer step on every
+    stage and halves the scale; clean batches grow it back after the scaling window."""
+    from axonn_b200 import axonn as ax
+    from axonn_b200.inter_layer import AxoNN_Inter_Layer_Engine
+    from axonn_b200.models import DistributedViT
+
+    ax.init(G_inter=2, G_data=1)
+    torch.manual_seed(20 + rank)
+    model = DistributedViT(image_size=8, patch_size=4, num_classes=4, dim=16, depth=2, heads=2, mlp_dim=32, channels=1)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    engine = AxoNN_Inter_Layer_Engine(model, torch.nn.functional.cross_entropy, computation_dtype=torch.float16)
+    ax.config.micro_batch_size = 2
+    g = torch.Generator().manual_seed(1)
+    x, y = torch.randn(4, 1, 8, 8, generator=g), torch.randint(0, 4, (4,), generator=g)
+    engine.scaler.scaling_window = 10 ** 9                    # first let the scale settle where fp16 holds the gradients
+    for _ in range(12):
+        start = engine.scaler.loss_scale
+        opt.zero_grad()
+        first = engine.forward_backward_optimizer(x, y, opt)
+        if engine.scaler.loss_scale == start:
+            break
+    assert first == first and engine.scaler.loss_scale == start and start >= engine.scaler.min_scale
+    engine.scaler.scaling_window, engine.scaler.no_overflow_iters = 2, 0
+    before = [p.detach().clone() for p in model.parameters()]
+    bad = x.clone()
+    bad[0] = 6.0e4                                            # activations leave the fp16 range on the way
+    opt.zero_grad()
+    engine.forward_backward_optimizer(bad, y, opt)
+    assert engine.scaler.loss_scale == start / 2              # every stage learned of the overflow ...
+    assert all(torch.equal(a, b) for a, b in zip(before, model.parameters()))   # ... and skipped its update
+    for _ in range(2):
+        opt.zero_grad()
+        loss = engine.forward_backward_optimizer(x, y, opt)
+    assert engine.scaler.loss_scale == start and loss == loss
+    assert any(not torch.equal(a, b) for a, b in zip(before, model.parameters()))
+    return engine.scaler.loss_scale
+
+
+def test_fp16_loss_scaling_skips_overflowing_steps_on_every_stage():
+    a, b = run_distributed(_fp16_scaling, 2)
+    assert a == b                                             # the stages agree on the scale
