@@ -106,3 +106,53 @@ def _options(rank, world, grid):
 @pytest.mark.parametrize("grid", [(2, 2, 1), (1, 2, 2), (2, 1, 2)])
 def test_layer_options_match_torch(grid):
     assert all(run_distributed(_options, 4, grid))
+
+
+def _easy_trainer(rank, world, grid):
+    """``Trainer`` around an auto-parallelised (easy-mode) model with a user loss function: every rank feeds its own
+    shard of the batch; three AdamW steps must follow single-process training on the whole batch."""
+    import torch.distributed as dist
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200.intra_layer import auto_parallelize
+    from axonn_b200.optim import FusedAdamW
+    from axonn_b200.trainer import Trainer
+
+    r, c, d = grid
+    ax.init(G_inter=1, G_data=world // (r * c * d), G_intra_r=r, G_intra_c=c, G_intra_d=d)
+
+    def build():
+        torch.manual_seed(3)
+        return torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 8))
+
+    ref = build()
+    with auto_parallelize():
+        par = build()
+    par.load_state_dict(ref.state_dict())
+    loss_fn = torch.nn.functional.cross_entropy
+    tr = Trainer(par, FusedAdamW(par.parameters(), lr=1e-2, weight_decay=0.0), loss_fn=loss_fn, expert_mode=False,
+                 clip_grad=1.0)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    g = torch.Generator().manual_seed(9)
+    losses = []
+    for _ in range(3):
+        X, Y = torch.randn(4 * world, 16, generator=g), torch.randint(0, 8, (4 * world,), generator=g)
+        mine = tr.train_step(X[rank * 4:(rank + 1) * 4], Y[rank * 4:(rank + 1) * 4])
+        t = torch.tensor(mine, dtype=torch.float64)
+        dist.all_reduce(t)
+        opt.zero_grad()
+        loss = loss_fn(ref(X), Y)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        opt.step()
+        losses.append((float(t) / world, float(loss)))
+    for got, want in losses:
+        assert got == pytest.approx(want, rel=1e-4), losses
+    assert torch.allclose(par[0].full_weight(), ref[0].weight, rtol=1e-3, atol=1e-5)
+    assert torch.allclose(par[2].full_tensor("bias"), ref[2].bias, rtol=1e-3, atol=1e-5)
+    return True
+
+
+@pytest.mark.parametrize("grid", [(2, 1, 2), (2, 2, 1), (1, 1, 2)])
+def test_trainer_with_easy_mode_model_and_user_loss(grid):
+    assert all(run_distributed(_easy_trainer, 4, grid))
