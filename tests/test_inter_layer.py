@@ -200,3 +200,66 @@ def _fp16_scaling(rank, world):
 def test_fp16_loss_scaling_skips_overflowing_steps_on_every_stage():
     a, b = run_distributed(_fp16_scaling, 2)
     assert a == b                                             # the stages agree on the scale
+
+
+def _gpt_4d(rank, world, G_inter, G_data, r, c, d, steps):
+    """Pipeline stages whose layers are tensor parallel, with data parallelism on top: all four dimensions."""
+    import torch.distributed as dist
+
+    from axonn_b200 import axonn as ax
+    from axonn_b200 import ops
+    from axonn_b200.inter_layer import AxoNN_Inter_Layer_Engine
+    from axonn_b200.models import DistributedGPT, GPTConfig
+
+    ax.init(G_inter=G_inter, G_data=G_data, G_intra_r=r, G_intra_c=c, G_intra_d=d)
+    cfg = GPTConfig(n_layers=4, hidden=32, n_heads=4, ffn=64, vocab=64, seq_len=16)
+    torch.manual_seed(7)
+    full = DistributedGPT(cfg, dtype=torch.float32, G_inter=1, stage=0)        # same shards, all layers
+    mine = DistributedGPT(cfg, dtype=torch.float32)
+    per = cfg.n_layers // G_inter
+    stage = ax.config.inter_layer_parallel_rank
+    new = {}
+    for k, v in full.state_dict().items():
+        if k.startswith("blocks."):
+            idx = int(k.split(".")[1])
+            if stage * per <= idx < (stage + 1) * per:
+                new["blocks.%d.%s" % (idx - stage * per, k.split(".", 2)[2])] = v
+        elif k in mine.state_dict():
+            new[k] = v
+    mine.load_state_dict(new)
+    group = mine.head.group if mine.last else None
+    loss_fn = lambda logits, y: ops.cross_entropy(logits, y, group=group)  # noqa: E731  (vocabulary-parallel loss)
+    engine = AxoNN_Inter_Layer_Engine(mine, loss_fn, computation_dtype=torch.float32)
+    ax.config.micro_batch_size = 2
+    g = torch.Generator().manual_seed(5)
+    X = torch.randint(0, 64, (8, 16), generator=g)
+    Y = torch.randint(0, 64, (8, 16), generator=g)
+    replicas = G_data * d                                        # the batch is split over data and depth
+    me = ax.config.G_intra_d * ax.config.data_parallel_rank + ax.config.intra_layer_depth_parallel_rank
+    n = 8 // replicas
+    xb, yb = X[me * n:(me + 1) * n], Y[me * n:(me + 1) * n]
+    opt = torch.optim.SGD(mine.parameters(), lr=0.1)
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        losses.append(engine.forward_backward_optimizer(xb, yb, opt))
+    t = torch.tensor(losses, dtype=torch.float64)
+    if stage != G_inter - 1:
+        t.zero_()
+    dist.all_reduce(t)                                           # last-stage ranks: tensor-parallel copies x replicas
+    return (t / (r * c * d * G_data)).tolist()
+
+
+_REF_4D = []
+
+
+@pytest.mark.parametrize("layout", [(2, 1, 2, 1, 1), (2, 1, 1, 2, 1), (2, 1, 1, 1, 2), (2, 2, 2, 1, 1)])
+def test_gpt_pipeline_with_tensor_and_data_parallel_stages(layout):
+    G_inter, G_data, r, c, d = layout
+    if not _REF_4D:
+        _REF_4D.append(run_distributed(_gpt_4d, 1, 1, 1, 1, 1, 1, 3)[0])
+    ref = _REF_4D[0]
+    world = G_inter * G_data * r * c * d
+    got = run_distributed(_gpt_4d, world, G_inter, G_data, r, c, d, 3, timeout=400)[0]
+    assert ref[-1] < ref[0]
+    assert all(abs(a - b) < 2e-4 for a, b in zip(ref, got)), (layout, ref, got)
