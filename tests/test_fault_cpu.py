@@ -206,3 +206,56 @@ def test_fit_restarts_from_its_last_checkpoint_on_another_grid(tmp_path):
     assert sorted(rest) == [4, 5, 6]
     for step in rest:
         assert rest[step] == pytest.approx(whole[step], rel=2e-4)
+
+
+def _cpu_adam_moves(rank, world, folder, phase):
+    """Host-resident optimizer state (CPUAdam keeps it flat, whatever the parameter's shape) through the
+    grid-independent checkpoint: saved on a row-parallel grid, continued on a depth-parallel one."""
+    from axonn_b200 import axonn as ax
+    from axonn_b200 import checkpoint
+    from axonn_b200.models import MLP
+    from axonn_b200.optim import CPUAdam
+
+    r, d = (2, 1) if phase != "resume" else (1, 2)
+    ax.init(G_inter=1, G_data=1, G_intra_r=r, G_intra_d=d)
+    torch.manual_seed(3)
+    model = MLP(16, 32, 16, dtype=torch.float32)
+    extra = torch.nn.Parameter(torch.ones(4, 4))              # a replicated 2-D parameter next to the sharded ones
+    model.register_parameter("extra", extra)
+    opt = CPUAdam(model.parameters(), lr=1e-2)
+    g = torch.Generator().manual_seed(1)
+    X = torch.randn(4, 16, generator=g)
+    inner = ax.comm_handle.inner_intra_layer_parallel_group
+    outer = ax.comm_handle.outer_intra_layer_parallel_group
+
+    def step():
+        from axonn_b200.intra_layer import sync_gradients
+        from axonn_b200.intra_layer.communication import _drop, _gather
+
+        opt.zero_grad()
+        x = _drop(_drop(X, 0, ax.comm_handle.depth_intra_layer_parallel_group), 1, inner)
+        y = model(x)
+        loss = y.square().sum() * (model.extra.sum() / 16)
+        loss.backward()
+        sync_gradients(model, expert_mode=True)
+        opt.step()
+        total = _gather(loss.detach().reshape(1), 0, ax.comm_handle.depth_intra_layer_parallel_group).sum()
+        return float(total)
+
+    if phase == "whole":
+        return [step() for _ in range(4)]
+    if phase == "save":
+        out = [step() for _ in range(2)]
+        checkpoint.save_consolidated(model, opt, folder, "adam")
+        return out
+    checkpoint.load_consolidated(model, opt, folder, "adam")
+    assert opt._steps == 2 and not opt.state[model.extra]["exp_avg"].is_cuda
+    assert opt.state[model.extra]["exp_avg"].shape == (16,)   # flat host state of the 4 x 4 parameter
+    return [step() for _ in range(2)]
+
+
+def test_host_resident_optimizer_state_moves_between_grids(tmp_path):
+    whole = run_distributed(_cpu_adam_moves, 2, str(tmp_path), "whole")[0]
+    first = run_distributed(_cpu_adam_moves, 2, str(tmp_path), "save")[0]
+    rest = run_distributed(_cpu_adam_moves, 2, str(tmp_path), "resume")[0]
+    assert first + rest == pytest.approx(whole, rel=1e-4)
