@@ -106,10 +106,11 @@ def test_resume_from_sharded_checkpoint_reproduces_loss(tmp_path):
     assert sorted(os.listdir(folder)) == ["step2.full.pt", "tp_row_0_col_0_depth_0", "tp_row_1_col_0_depth_0"]
     resumed = run_distributed(_ckpt_resume, 2, folder, "resume")[0]
     assert resumed == pytest.approx(full[2:], rel=1e-5)
-    # elastic restart: the grid-independent file written at the same step is loaded on other grids (other
-    # tensor-parallel shapes, a data-parallel pair, a single process) and the loss curve continues
+    # elastic restart: the grid-independent file written at the same step is loaded on other grids (depth instead
+    # of row parallelism, a data-parallel pair, four ranks) and the loss curve continues; column parallelism and a
+    # single process are covered by the tutorial test and the MoE test
     assert "step2.full.pt" in os.listdir(folder)
-    for world, grid in ((2, "1_1_2"), (2, "1_2_1"), (2, "1_1_1"), (1, "1_1_1"), (4, "2_1_2")):
+    for world, grid in ((2, "1_1_2"), (2, "1_1_1"), (4, "2_1_2")):
         other = run_distributed(_ckpt_resume, world, folder, "resume_grid_" + grid)[0]
         assert other == pytest.approx(full[2:], rel=2e-4), (world, grid)
 
