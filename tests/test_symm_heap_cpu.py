@@ -2,10 +2,16 @@
 runs the same create / export / descriptor exchange / attach sequence as the device backend, with shared pages
 in the place of peer-mapped device memory."""
 
+import shutil
+
 import pytest
 import torch
 
 from _dist import run_distributed
+from axonn_b200.ops import _lib
+
+# the heap is native code: needs the built library, or nvcc to build it on first use
+pytestmark = pytest.mark.skipif(not (_lib.available() or shutil.which("nvcc")), reason="native library not built")
 
 
 def _heap_roundtrip(rank, world):
