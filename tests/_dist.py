@@ -51,3 +51,15 @@ def run_distributed(fn, world, *args, backend="gloo", timeout=240):
         if errors:
             raise AssertionError(f"rank {errors[0][0]} failed:\n{errors[0][1]}")
     return [results[r] for r in range(world)]
+
+
+_cache = {}
+
+
+def run_cached(fn, world, *args, **kwargs):
+    """``run_distributed`` whose result is remembered for the rest of the test session: single-process reference
+    runs that several tests compare against are computed once."""
+    key = (fn.__module__, fn.__name__, world, repr(args))
+    if key not in _cache:
+        _cache[key] = run_distributed(fn, world, *args, **kwargs)
+    return _cache[key]

@@ -6,7 +6,7 @@ eval mode must not change the weights (pattern of the reference's
 import pytest
 import torch
 
-from _dist import run_distributed
+from _dist import run_cached, run_distributed
 
 
 def _vit_run(rank, world, G_inter, G_data, steps, dtype_name):
@@ -64,7 +64,7 @@ def _vit_run(rank, world, G_inter, G_data, steps, dtype_name):
 
 
 def test_pipeline_matches_single_stage_fp32():
-    ref = run_distributed(_vit_run, 1, 1, 1, 4, "float32")[0]
+    ref = run_cached(_vit_run, 1, 1, 1, 4, "float32")[0]
     two = run_distributed(_vit_run, 2, 2, 1, 4, "float32")[0]
     assert two == pytest.approx(ref, rel=1e-5)
     assert ref[3] < ref[0]
@@ -75,7 +75,7 @@ def test_pipeline_matches_single_stage_fp32():
 def test_fixed_order_schedule_matches_single_stage(monkeypatch):
     """The one-forward-one-backward order (what NCCL stages use when there are more than two) must give the same
     losses as a single stage, with two and with four stages."""
-    ref = run_distributed(_vit_run, 1, 1, 1, 4, "float32")[0]
+    ref = run_cached(_vit_run, 1, 1, 1, 4, "float32")[0]
     monkeypatch.setenv("AXONN_PIPELINE_SCHEDULE", "1f1b")
     four = run_distributed(_vit_run, 4, 4, 1, 4, "float32")[0]
     assert four == pytest.approx(ref, rel=1e-4)

@@ -5,7 +5,7 @@ sees whole sequences.  Also together with row tensor parallelism."""
 import pytest
 import torch
 
-from _dist import run_distributed
+from _dist import run_cached, run_distributed
 
 
 def _exchange_roundtrip(rank, world):
@@ -77,7 +77,7 @@ def _lm(rank, world, family, r, sp):
 def test_sequence_parallel_model_matches_whole_sequences(family, r, sp):
     import numpy as np
 
-    ref_loss, ref_grads = run_distributed(_lm, 1, family, 1, 1)[0]
+    ref_loss, ref_grads = run_cached(_lm, 1, family, 1, 1)[0]
     for loss, grads in run_distributed(_lm, r * sp, family, r, sp):
         assert loss == pytest.approx(ref_loss, rel=1e-5)
         for k, v in grads.items():
